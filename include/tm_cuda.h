@@ -1,0 +1,309 @@
+/*
+ * tm_cuda.h -- TuckCore <-> CUDA narrow C ABI for NVIDIA B200 (sm_100a).
+ *
+ * The CUDA counterpart of the reference's device interface
+ * native/metal/tm_metal.h: one context owns one device, one in-order stream
+ * and the kernels for the operations declared here; buffers are opaque
+ * handles with explicit lifetime; every operation is asynchronous, ordered on
+ * the context's stream, and returns 0 or a TM_CUDA_ERR_* code with a
+ * NUL-terminated message in the caller-owned `err` (may be NULL).  A context
+ * is used from one thread at a time; counters may be read from any thread.
+ *
+ * Each declaration cites the reference declaration it replaces
+ * (native/metal/tm_metal.h:<line>).  Declarations marked "no counterpart"
+ * exist because CUDA needs them (weight repacking, retained graphs, device
+ * positions, multi-GPU row split); a host that only knows the reference
+ * surface can ignore them and still run every operator.
+ *
+ * There is no CPU fallback anywhere behind this interface: without a usable
+ * CUDA device tm_cuda_create fails with TM_CUDA_ERR_NO_DEVICE.
+ */
+#ifndef TM_CUDA_H
+#define TM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tm_cuda_ctx tm_cuda_ctx;
+typedef struct tm_cuda_buffer tm_cuda_buffer;
+typedef struct tm_cuda_graph tm_cuda_graph;
+
+/* Error codes: the values of tm_metal.h:32-40. */
+enum {
+    TM_CUDA_OK = 0,
+    TM_CUDA_ERR_NO_DEVICE = -1,   /* no CUDA device / wrong architecture */
+    TM_CUDA_ERR_SOURCE = -2,      /* kernel image failed to load */
+    TM_CUDA_ERR_ALLOC = -3,       /* buffer allocation failed */
+    TM_CUDA_ERR_BOUNDS = -4,      /* size/range mismatch, zero length */
+    TM_CUDA_ERR_UNSUPPORTED = -5, /* invalid arguments / mode */
+    TM_CUDA_ERR_INTERNAL = -6     /* CUDA runtime failure */
+};
+
+/* tm_metal.h:43 tm_metal_available -- number of usable sm_100 devices. */
+int tm_cuda_available(void);
+/* tm_metal.h:47 tm_metal_runtime_info -- one-line description, static. */
+const char *tm_cuda_runtime_info(void);
+/* tm_metal.h:52 tm_metal_create -- device `device` (0-based) and its stream.
+ * NULL on failure, `err` filled. */
+tm_cuda_ctx *tm_cuda_create(int device, char *err, size_t err_cap);
+/* tm_metal.h:56 tm_metal_destroy -- buffers must have been freed first. */
+void tm_cuda_destroy(tm_cuda_ctx *ctx);
+
+/* tm_metal.h:61 tm_metal_buffer_new -- `shared` buffers are pinned host
+ * memory mapped into the device (CPU-readable through
+ * tm_cuda_buffer_contents); private buffers live in HBM. */
+tm_cuda_buffer *tm_cuda_buffer_new(tm_cuda_ctx *ctx, size_t bytes, int shared, char *err,
+                                   size_t err_cap);
+/* tm_metal.h:66 tm_metal_buffer_free -- waits for the device to finish the
+ * work already committed, so storage is never reused under a running kernel. */
+void tm_cuda_buffer_free(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer);
+/* tm_metal.h:70 tm_metal_buffer_contents. */
+void *tm_cuda_buffer_contents(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer);
+/* tm_metal.h:73 tm_metal_buffer_len. */
+size_t tm_cuda_buffer_len(const tm_cuda_ctx *ctx, const tm_cuda_buffer *buffer);
+/* tm_metal.h:78 tm_metal_buffer_zero. */
+int tm_cuda_buffer_zero(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer, size_t off, size_t len,
+                        char *err, size_t err_cap);
+/* tm_metal.h:82,84 tm_metal_upload / tm_metal_download -- ordered after all
+ * committed work; return when the copy is complete.  No open group. */
+int tm_cuda_upload(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, size_t off, const void *src, size_t len,
+                   char *err, size_t err_cap);
+int tm_cuda_download(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, void *dst, size_t len,
+                     char *err, size_t err_cap);
+/* No counterpart: a handle aliasing `len` bytes of `parent` at byte offset
+ * `off` (256-byte aligned), so operators without offset arguments can work
+ * on a slice of a fused output.  Counts 0 bytes in the ledger; must be freed
+ * before its parent. */
+tm_cuda_buffer *tm_cuda_buffer_view(tm_cuda_ctx *ctx, tm_cuda_buffer *parent, size_t off,
+                                    size_t len, char *err, size_t err_cap);
+/* No counterpart: raw device address of a buffer (for a host that shares the
+ * CUDA primary context, e.g. to hand a buffer to NCCL or torch). */
+void *tm_cuda_buffer_device_ptr(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer);
+
+/* ---------------- elementwise utilities ---------------- */
+/* tm_metal.h:88 tm_metal_f32_scale: y[i] = x[i] * factor. */
+int tm_cuda_f32_scale(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, float factor,
+                      uint32_t n, char *err, size_t err_cap);
+/* tm_metal.h:121 tm_metal_f32_axpy: y[i] += alpha * a[i]. */
+int tm_cuda_f32_axpy(tm_cuda_ctx *ctx, tm_cuda_buffer *a, tm_cuda_buffer *y, float alpha,
+                     uint32_t n, char *err, size_t err_cap);
+/* tm_metal.h:117 tm_metal_copy_f32: dst[dst_off+i] = src[src_off+i]. */
+int tm_cuda_copy_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t src_off, tm_cuda_buffer *dst,
+                     uint32_t dst_off, uint32_t n, char *err, size_t err_cap);
+/* tm_metal.h:125,129 casts between binary16 and f32 (encode rounds to
+ * nearest even and saturates to infinity). */
+int tm_cuda_cast_f16_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t n,
+                         char *err, size_t err_cap);
+int tm_cuda_cast_f32_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t n,
+                         char *err, size_t err_cap);
+/* tm_metal.h:99 tm_metal_argmax_f32 -- NaN skipped, largest wins, ties to the
+ * lowest index, 0xFFFFFFFF when every entry is NaN; `partial` is 512 bytes. */
+int tm_cuda_argmax_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cuda_buffer *partial,
+                       tm_cuda_buffer *out, uint32_t out_index, char *err, size_t err_cap);
+/* tm_metal.h:161 tm_metal_rmsnorm_f32. */
+int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *weight,
+                        tm_cuda_buffer *y, uint32_t rows, uint32_t cols, float eps, char *err,
+                        size_t err_cap);
+/* tm_metal.h:202 tm_metal_silu_mul_f32 / :206 tm_metal_gelu_tanh_mul_f32. */
+int tm_cuda_silu_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_buffer *up,
+                         tm_cuda_buffer *out, uint32_t n, char *err, size_t err_cap);
+int tm_cuda_gelu_tanh_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_buffer *up,
+                              tm_cuda_buffer *out, uint32_t n, char *err, size_t err_cap);
+
+/* ---------------- Q8_0 weights ---------------- */
+/*
+ * Weight layout.  The reference keeps a Q8_0 matrix as the GGUF bytes
+ * verbatim (tm_metal.h:209-212: rows * cols/32 blocks of 34 bytes).  A 34-byte
+ * stride leaves quants 2-byte aligned, which rules out 128-bit loads, so this
+ * library keeps the SAME values in two planes inside one buffer:
+ *   int8  q[rows][cols]      at byte 0
+ *   f16   d[rows][cols/32]   at byte tm_cuda_q8_0_packed_bytes' q-plane size
+ *                            rounded up to 256
+ * Repacking moves bytes; no value changes (1.0625 bytes per weight either
+ * way).  Every Q8_0 operator below takes a PACKED buffer produced by
+ * tm_cuda_q8_0_pack and refuses anything else with TM_CUDA_ERR_UNSUPPORTED.
+ */
+/* No counterpart: bytes of the packed form of a rows x cols matrix
+ * (0 when cols is not a positive multiple of 32 or rows is 0). */
+size_t tm_cuda_q8_0_packed_bytes(uint32_t rows, uint32_t cols);
+/* No counterpart: repack `nrows` raw GGUF rows held in `raw` (device buffer,
+ * nrows * cols/32 * 34 bytes at byte offset raw_off) into rows
+ * [row0, row0+nrows) of the packed matrix `dst` (rows x cols).  A matrix is
+ * usable by the operators once every row has been packed. */
+int tm_cuda_q8_0_pack(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, uint32_t rows, uint32_t cols,
+                      tm_cuda_buffer *raw, size_t raw_off, uint32_t row0, uint32_t nrows,
+                      char *err, size_t err_cap);
+/* No counterpart: the inverse, for round-trip checks: write rows
+ * [row0,row0+nrows) of packed `src` as raw GGUF bytes into `raw`. */
+int tm_cuda_q8_0_unpack(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t rows, uint32_t cols,
+                        tm_cuda_buffer *raw, size_t raw_off, uint32_t row0, uint32_t nrows,
+                        char *err, size_t err_cap);
+
+/* tm_metal.h:213 tm_metal_q8_0_gemv: y[r] = dot(dequant(w_row_r), x), f32. */
+int tm_cuda_q8_0_gemv(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y,
+                      uint32_t rows, uint32_t cols, char *err, size_t err_cap);
+/* tm_metal.h:176 tm_metal_q8_0_gemm: Y[b,:] = W X[b,:], b < batch (1..32), X
+ * at f32 offset x_off, Y at y_off; per-token arithmetic is that of the GEMV,
+ * so any batch is bit-identical to `batch` GEMV calls. */
+#define TM_CUDA_GEMM_MAX_BATCH 32u
+int tm_cuda_q8_0_gemm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y,
+                      uint32_t rows, uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off,
+                      char *err, size_t err_cap);
+/* tm_metal.h:170,187 tm_metal_q8_0_gemm_mma: the same contract on the tensor
+ * cores (tcgen05, f16 operands: x and d*q are rounded to binary16, f32
+ * accumulation in tensor memory); tolerance-qualified, not bit-identical.
+ * The batch limit is the reference's 512 raised to what one launch tiles. */
+#define TM_CUDA_GEMM_MMA_MAX_BATCH 8192u
+int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x,
+                          tm_cuda_buffer *y, uint32_t rows, uint32_t cols, uint32_t batch,
+                          uint32_t x_off, uint32_t y_off, char *err, size_t err_cap);
+/* tm_metal.h:151 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
+int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
+                         uint32_t cols, uint32_t out_off, char *err, size_t err_cap);
+/* tm_metal.h:108 tm_metal_row_indirect_f32: row ids[slot] (type 8 only); an
+ * id >= rows writes zeros. */
+int tm_cuda_row_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t type_id, uint32_t rows,
+                             uint32_t cols, tm_cuda_buffer *ids, uint32_t slot,
+                             tm_cuda_buffer *out, char *err, size_t err_cap);
+
+/* No counterpart: the GEMV with the neighbouring elementwise operators folded
+ * into its activation load and its store, so a decode layer is a handful of
+ * launches.  Per-row arithmetic is that of tm_cuda_q8_0_gemv on the same
+ * activation values.
+ *   prologue: 0 x as is | 1 x = rmsnorm(x, pw, eps) | 2 x = silu(x) * px
+ *             | 3 x = gelu_tanh(x) * px            (pw/px: `pro` buffer)
+ *   epilogue: 0 y = Wx  | 1 y += Wx */
+enum { TM_CUDA_PRO_NONE = 0, TM_CUDA_PRO_RMSNORM = 1, TM_CUDA_PRO_SILU_MUL = 2,
+       TM_CUDA_PRO_GELU_MUL = 3 };
+enum { TM_CUDA_EPI_STORE = 0, TM_CUDA_EPI_ADD = 1 };
+int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x,
+                            tm_cuda_buffer *y, uint32_t rows, uint32_t cols, int prologue,
+                            tm_cuda_buffer *pro, float eps, int epilogue, char *err,
+                            size_t err_cap);
+
+/* ---------------- grouped encoding ---------------- */
+/* tm_metal.h:141-143 begin/end/abort_group: operations between begin and end
+ * are captured into one CUDA graph launched at end_group; abort discards
+ * them without running anything.  Copies and fence need no open group. */
+int tm_cuda_begin_group(tm_cuda_ctx *ctx, char *err, size_t err_cap);
+int tm_cuda_end_group(tm_cuda_ctx *ctx, char *err, size_t err_cap);
+int tm_cuda_abort_group(tm_cuda_ctx *ctx, char *err, size_t err_cap);
+/* No counterpart: end the open group WITHOUT running it and keep it as a
+ * replayable graph; each launch is one committed dispatch.  A decode step
+ * whose position lives on the device (below) is recorded once and replayed
+ * per token. */
+int tm_cuda_end_group_retain(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, size_t err_cap);
+int tm_cuda_graph_launch(tm_cuda_ctx *ctx, tm_cuda_graph *graph, char *err, size_t err_cap);
+void tm_cuda_graph_free(tm_cuda_ctx *ctx, tm_cuda_graph *graph);
+
+/* tm_metal.h:281 tm_metal_fence. */
+int tm_cuda_fence(tm_cuda_ctx *ctx, char *err, size_t err_cap);
+/* tm_metal.h:284,290 committed / completed dispatch counters. */
+uint64_t tm_cuda_committed_dispatches(const tm_cuda_ctx *ctx);
+uint64_t tm_cuda_completed_dispatches(const tm_cuda_ctx *ctx);
+/* tm_metal.h:289 tm_metal_download_after: copy from a SHARED buffer once the
+ * first `completed_target` committed dispatches have completed. */
+int tm_cuda_download_after(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, void *dst,
+                           size_t len, uint64_t completed_target, char *err, size_t err_cap);
+/* tm_metal.h:293,296 GPU time of the last completed dispatch / cumulative. */
+double tm_cuda_last_gpu_ms(const tm_cuda_ctx *ctx);
+uint64_t tm_cuda_gpu_nanos_total(const tm_cuda_ctx *ctx);
+/* tm_metal.h:301,304 per-operator attribution (CUDA events per dispatch). */
+int tm_cuda_profile_set(tm_cuda_ctx *ctx, int enabled);
+int tm_cuda_profile_read(tm_cuda_ctx *ctx, uint32_t index, char *name, size_t name_cap,
+                         uint64_t *nanos, uint64_t *count);
+/* tm_metal.h:307 live bytes in buffers; :314 bytes leased by pending work
+ * (always 0 here: tm_cuda_buffer_free waits instead of leasing). */
+uint64_t tm_cuda_allocated_bytes(const tm_cuda_ctx *ctx);
+uint64_t tm_cuda_in_flight_bytes(const tm_cuda_ctx *ctx);
+/* No counterpart: kernels launched by this context so far (each operator
+ * launch and each graph node counts one). */
+uint64_t tm_cuda_kernel_launches(const tm_cuda_ctx *ctx);
+/* No counterpart: the context's cudaStream_t, so a host that shares the CUDA
+ * primary context can record its own events on the stream the kernels run on. */
+void *tm_cuda_stream(tm_cuda_ctx *ctx);
+
+/* ---------------- attention operators ---------------- */
+/* tm_metal.h:252 tm_metal_qwen35_rope_partial: split-half RoPE on the first
+ * n_rot dims of every q/k head row, angle (float)pos * inv_freq[i]. */
+int tm_cuda_qwen35_rope_partial(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
+                                tm_cuda_buffer *inv_freq, uint32_t pos, uint32_t n_q_heads,
+                                uint32_t n_kv_heads, uint32_t head_dim, uint32_t n_rot, char *err,
+                                size_t err_cap);
+/* tm_metal.h:357 ..._rope_partial_chunk: token t rotates at pos0 + t. */
+int tm_cuda_qwen35_rope_partial_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
+                                      tm_cuda_buffer *inv_freq, uint32_t pos0, uint32_t n_q_heads,
+                                      uint32_t n_kv_heads, uint32_t head_dim, uint32_t n_rot,
+                                      uint32_t n, char *err, size_t err_cap);
+/* tm_metal.h:259 ..._kv_store_f16 / :362 ..._kv_store_f16_chunk:
+ * cache[h][pos0+t][d] = (half) src[t][h][d], planes [kv_head][cap][head_dim]. */
+int tm_cuda_qwen35_kv_store_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *k_src, tm_cuda_buffer *v_src,
+                                tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, uint32_t pos,
+                                uint32_t cap, uint32_t head_dim, uint32_t kv_heads, char *err,
+                                size_t err_cap);
+int tm_cuda_qwen35_kv_store_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *k_src,
+                                      tm_cuda_buffer *v_src, tm_cuda_buffer *k_cache,
+                                      tm_cuda_buffer *v_cache, uint32_t pos0, uint32_t cap,
+                                      uint32_t head_dim, uint32_t kv_heads, uint32_t n, char *err,
+                                      size_t err_cap);
+/* tm_metal.h:265 ..._attention_f16: causal GQA attention of one query row
+ * over keys 0..=pos of a packed f16 cache; scratch is heads*cap f32. */
+int tm_cuda_qwen35_attention_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache,
+                                 tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                 tm_cuda_buffer *scratch, uint32_t heads, uint32_t pos,
+                                 uint32_t cap, uint32_t head_dim, uint32_t group, float scale,
+                                 char *err, size_t err_cap);
+/* tm_metal.h:367 ..._attention_f16_chunk: query row t attends keys
+ * [start, pos0+t] where start = seq > window ? seq - window : 0 (window 0 =
+ * full causal); scratch is n*heads*cap f32. */
+int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
+                                       tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache,
+                                       tm_cuda_buffer *out, tm_cuda_buffer *scratch,
+                                       uint32_t heads, uint32_t pos0, uint32_t cap,
+                                       uint32_t head_dim, uint32_t group, float scale, uint32_t n,
+                                       uint32_t window, char *err, size_t err_cap);
+
+/* No counterpart: the per-token attention core with the position read from
+ * device memory (u32 pos_buf[pos_index]), so one recorded decode graph serves
+ * every step: per-head q/k RMS norm, RoPE, f16 KV store and (windowed) causal
+ * attention for ONE token -- the sequence of tm_cuda_rmsnorm_f32 x2,
+ * tm_cuda_qwen35_rope_partial, tm_cuda_qwen35_kv_store_f16 and
+ * tm_cuda_qwen35_attention_f16_chunk(n = 1) with the same arithmetic.  A
+ * position >= cap writes nothing and sets bit 0 of status[0] (u32, shared). */
+int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
+                                 tm_cuda_buffer *v, tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm,
+                                 tm_cuda_buffer *inv_freq, tm_cuda_buffer *k_cache,
+                                 tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                 tm_cuda_buffer *scratch, tm_cuda_buffer *pos_buf,
+                                 uint32_t pos_index, tm_cuda_buffer *status, uint32_t heads,
+                                 uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
+                                 uint32_t cap, uint32_t window, float eps, float scale, char *err,
+                                 size_t err_cap);
+/* No counterpart: buf[index] += delta (u32), to advance a device position
+ * inside a recorded graph. */
+int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint32_t delta,
+                    char *err, size_t err_cap);
+/* No counterpart: argmax whose output index is taken from the device,
+ * out[base + pos_buf[pos_index]], so a replayed graph appends each step's
+ * token to a device-side token log the host reads with download_after. */
+int tm_cuda_argmax_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n,
+                           tm_cuda_buffer *partial, tm_cuda_buffer *out, uint32_t base,
+                           tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
+                           char *err, size_t err_cap);
+/* No counterpart: tm_cuda_row_indirect_f32 whose slot is base +
+ * pos_buf[pos_index] + bias (bias may be negative: "the previous token"),
+ * followed by an optional scale (0 = none). */
+int tm_cuda_row_indirect_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                                 tm_cuda_buffer *ids, uint32_t base, tm_cuda_buffer *pos_buf,
+                                 uint32_t pos_index, int32_t bias, float scale,
+                                 tm_cuda_buffer *out, char *err, size_t err_cap);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TM_CUDA_H */

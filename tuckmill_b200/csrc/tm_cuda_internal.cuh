@@ -1,0 +1,150 @@
+// Internal definitions shared by the translation units of libtm_cuda.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "tm_cuda.h"
+
+// What a buffer is known to hold (set by the packing entry point, checked by
+// the Q8_0 operators so a raw GGUF upload is never misread as packed planes).
+enum tm_layout : uint32_t { TM_LAYOUT_OPAQUE = 0, TM_LAYOUT_Q8_0_PACKED = 1 };
+
+struct tm_cuda_buffer {
+    tm_cuda_ctx *owner = nullptr;
+    tm_cuda_buffer *parent = nullptr;  // non-null for a view
+    unsigned char *dev = nullptr;      // device-visible address
+    size_t len = 0;
+    int shared = 0;
+    uint32_t views = 0;                // live views of this buffer
+    tm_layout layout = TM_LAYOUT_OPAQUE;
+    uint32_t rows = 0, cols = 0;       // geometry of a packed matrix
+};
+
+struct tm_cuda_graph {
+    tm_cuda_ctx *owner = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
+};
+
+struct tm_commit {
+    uint64_t seq = 0;
+    cudaEvent_t begin = nullptr, end = nullptr;
+    int label = -1;
+};
+
+struct tm_profile_row {
+    std::string name;
+    uint64_t nanos = 0, count = 0;
+};
+
+struct tm_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    std::unordered_set<const tm_cuda_buffer *> live;
+    std::unordered_set<const tm_cuda_graph *> graphs;
+    std::atomic<uint64_t> allocated{0};
+    std::atomic<uint64_t> committed{0};
+    std::atomic<uint64_t> completed{0};
+    std::atomic<uint64_t> gpu_nanos{0};
+    std::atomic<uint64_t> launches{0};
+    std::atomic<uint64_t> last_gpu_ns{0};
+    bool group_open = false;
+    uint64_t group_kernels = 0;
+    bool profiling = false;
+    std::deque<tm_commit> pending;       // committed, completion not yet observed
+    tm_commit open_commit;               // the ungrouped dispatch being encoded
+    std::vector<cudaEvent_t> event_pool;
+    std::vector<tm_profile_row> profile;
+    // Scratch owned by the context for the tensor-core GEMM (f16 copy of X).
+    unsigned char *mma_scratch = nullptr;
+    size_t mma_scratch_bytes = 0;
+    void *comm = nullptr;  // multi-GPU communicator state (tm_cuda_comm.cu)
+};
+
+// ---- error plumbing -------------------------------------------------------
+
+inline int tm_fail(char *err, size_t cap, int code, const char *fmt, ...) {
+    if (err && cap) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, cap, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define TM_CUDA_TRY(expr)                                                                   \
+    do {                                                                                    \
+        cudaError_t e_ = (expr);                                                            \
+        if (e_ != cudaSuccess)                                                              \
+            return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "%s failed: %s", #expr,      \
+                           cudaGetErrorString(e_));                                         \
+    } while (0)
+
+// Owned-and-large-enough check, the CUDA twin of tm_check_buffer
+// (native/metal/tm_metal.m:153-171).
+inline int tm_check(tm_cuda_ctx *ctx, const tm_cuda_buffer *b, size_t need, const char *what,
+                    char *err, size_t err_cap) {
+    if (!b || ctx->live.find(b) == ctx->live.end())
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
+                       "%s buffer does not belong to this context", what);
+    if (need == 0 || b->len < need)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "%s buffer holds %zu bytes, needs %zu",
+                       what, b->len, need);
+    return TM_CUDA_OK;
+}
+
+#define TM_CHECK_BUF(buf, need, what)                                        \
+    do {                                                                     \
+        int rc_ = tm_check(ctx, (buf), (need), (what), err, err_cap);        \
+        if (rc_ != TM_CUDA_OK) return rc_;                                   \
+    } while (0)
+
+// Every operator entry point opens with this: context present, device current,
+// dispatch serialised (crates/metal/src/lib.rs:695-707 holds a mutex the same way).
+#define TM_ENTER()                                                                          \
+    if (!ctx) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null context");        \
+    std::lock_guard<std::mutex> lock_(ctx->mu);                                             \
+    TM_CUDA_TRY(cudaSetDevice(ctx->device))
+
+// Book-keeping around one operator launch (ungrouped: one dispatch per op with
+// its own timing events; grouped: counted into the open group).
+int tm_op_begin(tm_cuda_ctx *ctx, const char *label, char *err, size_t err_cap);
+int tm_op_end(tm_cuda_ctx *ctx, uint64_t kernels, char *err, size_t err_cap);
+
+#define TM_OP_BEGIN(label)                                          \
+    do {                                                            \
+        int rc_ = tm_op_begin(ctx, (label), err, err_cap);          \
+        if (rc_ != TM_CUDA_OK) return rc_;                          \
+    } while (0)
+#define TM_OP_END(kernels)                                                          \
+    do {                                                                            \
+        cudaError_t le_ = cudaGetLastError();                                       \
+        if (le_ != cudaSuccess)                                                     \
+            return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "launch failed: %s", \
+                           cudaGetErrorString(le_));                                \
+        return tm_op_end(ctx, (kernels), err, err_cap);                             \
+    } while (0)
+
+inline size_t tm_round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline size_t tm_q8_qplane_bytes(uint32_t rows, uint32_t cols) {
+    return tm_round_up((size_t)rows * cols, 256);
+}
+
+// Checks `w` is a packed rows x cols Q8_0 matrix of this context.
+int tm_check_packed(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                    char *err, size_t err_cap);

@@ -1,0 +1,381 @@
+"""Typed host wrapper over the ``tm_cuda`` C ABI (``include/tm_cuda.h``).
+
+The Python twin of the reference's device wrapper crate
+(crates/metal/src/lib.rs:755-2650: ``MetalContext`` with one method per
+operator, RAII ``MetalBuffer`` handles, error-code mapping :732-747): the same
+method names and argument order, ``CudaError`` carrying the ABI's code and
+message.  It calls the shared library only -- there is no fallback: loading
+fails loudly when ``libtm_cuda.so`` has not been built.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_PKG = Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "libtm_cuda.so"
+
+ERR_NAMES = {0: "OK", -1: "NO_DEVICE", -2: "SOURCE", -3: "ALLOC", -4: "BOUNDS", -5: "UNSUPPORTED", -6: "INTERNAL"}
+ARGMAX_NONE = 0xFFFFFFFF
+GEMM_MAX_BATCH = 32
+GEMM_MMA_MAX_BATCH = 8192
+PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL, PRO_GELU_MUL = 0, 1, 2, 3
+EPI_STORE, EPI_ADD = 0, 1
+
+
+class CudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"TM_CUDA_ERR_{ERR_NAMES.get(code, code)}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+_P, _U32, _SZ, _F, _I = C.c_void_p, C.c_uint32, C.c_size_t, C.c_float, C.c_int
+_ERR = [C.c_char_p, C.c_size_t]
+
+# name -> argument types WITHOUT the trailing (err, err_cap); all return int.
+_OPS = {
+    "buffer_zero": [_P, _P, _SZ, _SZ],
+    "upload": [_P, _P, _SZ, _P, _SZ],
+    "download": [_P, _P, _SZ, _P, _SZ],
+    "download_after": [_P, _P, _SZ, _P, _SZ, C.c_uint64],
+    "f32_scale": [_P, _P, _P, _F, _U32],
+    "f32_axpy": [_P, _P, _P, _F, _U32],
+    "copy_f32": [_P, _P, _U32, _P, _U32, _U32],
+    "cast_f16_f32": [_P, _P, _P, _U32],
+    "cast_f32_f16": [_P, _P, _P, _U32],
+    "argmax_f32": [_P, _P, _U32, _P, _P, _U32],
+    "argmax_f32_dev": [_P, _P, _U32, _P, _P, _U32, _P, _U32, _U32],
+    "rmsnorm_f32": [_P, _P, _P, _P, _U32, _U32, _F],
+    "silu_mul_f32": [_P, _P, _P, _P, _U32],
+    "gelu_tanh_mul_f32": [_P, _P, _P, _P, _U32],
+    "q8_0_pack": [_P, _P, _U32, _U32, _P, _SZ, _U32, _U32],
+    "q8_0_unpack": [_P, _P, _U32, _U32, _P, _SZ, _U32, _U32],
+    "q8_0_gemv": [_P, _P, _P, _P, _U32, _U32],
+    "q8_0_gemm": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
+    "q8_0_gemm_mma": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
+    "q8_0_gemv_fused": [_P, _P, _P, _P, _U32, _U32, _I, _P, _F, _I],
+    "q8_0_row_f32": [_P, _P, _P, _U32, _U32, _U32],
+    "row_indirect_f32": [_P, _P, _U32, _U32, _U32, _P, _U32, _P],
+    "row_indirect_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
+    "begin_group": [_P],
+    "end_group": [_P],
+    "abort_group": [_P],
+    "end_group_retain": [_P, C.POINTER(C.c_void_p)],
+    "graph_launch": [_P, _P],
+    "fence": [_P],
+    "u32_add": [_P, _P, _U32, _U32],
+    "qwen35_rope_partial": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
+    "qwen35_rope_partial_chunk": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _U32],
+    "qwen35_kv_store_f16": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32],
+    "qwen35_kv_store_f16_chunk": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
+    "qwen35_attention_f16": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F],
+    "qwen35_attention_f16_chunk": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
+    "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F],
+}
+
+
+def load_library() -> C.CDLL:
+    """Load ``libtm_cuda.so``; raise (never fall back) when it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise ImportError(f"{_LIB_PATH} is not built; run `python -m tuckmill_b200.build` "
+                          "(there is no CPU fallback for the CUDA path)")
+    L = C.CDLL(str(_LIB_PATH))
+    for name, args in _OPS.items():
+        fn = getattr(L, "tm_cuda_" + name)
+        fn.restype = C.c_int
+        fn.argtypes = args + _ERR
+    L.tm_cuda_available.restype = C.c_int
+    L.tm_cuda_runtime_info.restype = C.c_char_p
+    L.tm_cuda_create.restype = _P
+    L.tm_cuda_create.argtypes = [_I] + _ERR
+    L.tm_cuda_destroy.argtypes = [_P]
+    L.tm_cuda_buffer_new.restype = _P
+    L.tm_cuda_buffer_new.argtypes = [_P, _SZ, _I] + _ERR
+    L.tm_cuda_buffer_view.restype = _P
+    L.tm_cuda_buffer_view.argtypes = [_P, _P, _SZ, _SZ] + _ERR
+    L.tm_cuda_buffer_free.argtypes = [_P, _P]
+    L.tm_cuda_buffer_contents.restype = _P
+    L.tm_cuda_buffer_contents.argtypes = [_P, _P]
+    L.tm_cuda_buffer_device_ptr.restype = _P
+    L.tm_cuda_buffer_device_ptr.argtypes = [_P, _P]
+    L.tm_cuda_buffer_len.restype = _SZ
+    L.tm_cuda_buffer_len.argtypes = [_P, _P]
+    L.tm_cuda_q8_0_packed_bytes.restype = _SZ
+    L.tm_cuda_q8_0_packed_bytes.argtypes = [_U32, _U32]
+    L.tm_cuda_graph_free.argtypes = [_P, _P]
+    for name in ("committed_dispatches", "completed_dispatches", "gpu_nanos_total", "allocated_bytes",
+                 "in_flight_bytes", "kernel_launches"):
+        fn = getattr(L, "tm_cuda_" + name)
+        fn.restype = C.c_uint64
+        fn.argtypes = [_P]
+    L.tm_cuda_last_gpu_ms.restype = C.c_double
+    L.tm_cuda_last_gpu_ms.argtypes = [_P]
+    L.tm_cuda_stream.restype = _P
+    L.tm_cuda_stream.argtypes = [_P]
+    L.tm_cuda_profile_set.argtypes = [_P, _I]
+    L.tm_cuda_profile_read.restype = C.c_int
+    L.tm_cuda_profile_read.argtypes = [_P, _U32, C.c_char_p, _SZ, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    _lib = L
+    return L
+
+
+def available() -> int:
+    return int(load_library().tm_cuda_available())
+
+
+def runtime_info() -> str:
+    return load_library().tm_cuda_runtime_info().decode()
+
+
+def packed_bytes(rows: int, cols: int) -> int:
+    return int(load_library().tm_cuda_q8_0_packed_bytes(rows, cols))
+
+
+class CudaBuffer:
+    """RAII handle of a context buffer (crates/metal/src/lib.rs:2482-2650)."""
+
+    def __init__(self, ctx: "CudaContext", handle: int, parent: "CudaBuffer | None" = None):
+        self.ctx, self.handle, self._parent = ctx, handle, parent
+
+    def __len__(self) -> int:
+        return int(self.ctx._l.tm_cuda_buffer_len(self.ctx.handle, self.handle))
+
+    def len(self) -> int:
+        return len(self)
+
+    def zero(self, off: int = 0, length: int | None = None):
+        self.ctx._call("buffer_zero", self.handle, off, len(self) if length is None else length)
+
+    def upload(self, off: int, data) -> None:
+        a = np.ascontiguousarray(data)
+        self.ctx._call("upload", self.handle, off, a.ctypes.data, a.nbytes)
+
+    def download(self, off: int, nbytes: int, dtype=np.uint8) -> np.ndarray:
+        out = np.empty(nbytes, dtype=np.uint8)
+        self.ctx._call("download", self.handle, off, out.ctypes.data, nbytes)
+        return out.view(dtype)
+
+    def download_after(self, off: int, nbytes: int, completed_target: int, dtype=np.uint8) -> np.ndarray:
+        out = np.empty(nbytes, dtype=np.uint8)
+        self.ctx._call("download_after", self.handle, off, out.ctypes.data, nbytes, completed_target)
+        return out.view(dtype)
+
+    def view(self, off: int, length: int) -> "CudaBuffer":
+        err = C.create_string_buffer(256)
+        h = self.ctx._l.tm_cuda_buffer_view(self.ctx.handle, self.handle, off, length, err, 256)
+        if not h:
+            raise CudaError(-4, err.value.decode())
+        return CudaBuffer(self.ctx, h, parent=self)
+
+    def device_ptr(self) -> int:
+        return int(self.ctx._l.tm_cuda_buffer_device_ptr(self.ctx.handle, self.handle) or 0)
+
+    def free(self):
+        if self.handle and self.ctx.handle:
+            self.ctx._l.tm_cuda_buffer_free(self.ctx.handle, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CudaGraph:
+    def __init__(self, ctx: "CudaContext", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def launch(self):
+        self.ctx._call("graph_launch", self.handle)
+
+    def free(self):
+        if self.handle and self.ctx.handle:
+            self.ctx._l.tm_cuda_graph_free(self.ctx.handle, self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CudaContext:
+    """One device + one stream; one method per operator of the ABI."""
+
+    def __init__(self, device: int = 0):
+        self._l = load_library()
+        err = C.create_string_buffer(512)
+        self.handle = self._l.tm_cuda_create(device, err, 512)
+        if not self.handle:
+            raise CudaError(-1, err.value.decode())
+        self.device = device
+
+    def close(self):
+        if self.handle:
+            self._l.tm_cuda_destroy(self.handle)
+            self.handle = None
+
+    def _call(self, name: str, *args):
+        err = C.create_string_buffer(512)
+        fn = getattr(self._l, "tm_cuda_" + name)
+        rc = fn(self.handle, *args, err, 512)
+        if rc != 0:
+            raise CudaError(rc, err.value.decode())
+
+    @staticmethod
+    def _h(b):
+        return b.handle if b is not None else None
+
+    # -- buffers -----------------------------------------------------------
+    def buffer(self, nbytes: int, shared: bool = False) -> CudaBuffer:
+        err = C.create_string_buffer(512)
+        h = self._l.tm_cuda_buffer_new(self.handle, nbytes, int(shared), err, 512)
+        if not h:
+            raise CudaError(-3 if nbytes else -4, err.value.decode())
+        return CudaBuffer(self, h)
+
+    def floats(self, data, shared: bool = False) -> CudaBuffer:
+        a = np.ascontiguousarray(data, dtype=np.float32)
+        b = self.buffer(max(a.nbytes, 4), shared)
+        if a.nbytes:
+            b.upload(0, a)
+        return b
+
+    def from_array(self, a: np.ndarray, shared: bool = False) -> CudaBuffer:
+        a = np.ascontiguousarray(a)
+        b = self.buffer(a.nbytes, shared)
+        b.upload(0, a)
+        return b
+
+    def q8_0_matrix(self, raw: np.ndarray, rows: int, cols: int, chunk_rows: int | None = None) -> CudaBuffer:
+        """Upload raw GGUF Q8_0 bytes and repack them into the two-plane form
+        (the load path of crates/tuckcore/src/engine/metal.rs:119-154, with
+        the repack step the CUDA kernels need)."""
+        raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+        row_bytes = cols // 32 * 34
+        assert raw.size == rows * row_bytes
+        dst = self.buffer(packed_bytes(rows, cols))
+        step = chunk_rows or max(1, (4 << 20) // row_bytes)
+        stage = self.buffer(min(rows, step) * row_bytes)
+        for r0 in range(0, rows, step):
+            n = min(step, rows - r0)
+            stage.upload(0, raw[r0 * row_bytes:(r0 + n) * row_bytes])
+            self._call("q8_0_pack", dst.handle, rows, cols, stage.handle, 0, r0, n)
+        self.fence()
+        stage.free()
+        return dst
+
+    def q8_0_unpack(self, w: CudaBuffer, rows: int, cols: int) -> np.ndarray:
+        raw = self.buffer(rows * (cols // 32) * 34)
+        self._call("q8_0_unpack", w.handle, rows, cols, raw.handle, 0, 0, rows)
+        out = raw.download(0, len(raw))
+        raw.free()
+        return out
+
+    # -- operators (names and argument order of crates/metal/src/lib.rs) ----
+    def f32_scale(self, x, y, factor, n): self._call("f32_scale", x.handle, y.handle, factor, n)
+    def f32_axpy(self, a, y, alpha, n): self._call("f32_axpy", a.handle, y.handle, alpha, n)
+    def copy_f32(self, src, src_off, dst, dst_off, n): self._call("copy_f32", src.handle, src_off, dst.handle, dst_off, n)
+    def cast_f16_f32(self, x, y, n): self._call("cast_f16_f32", x.handle, y.handle, n)
+    def cast_f32_f16(self, x, y, n): self._call("cast_f32_f16", x.handle, y.handle, n)
+    def argmax_f32(self, x, n, partial, out, out_index): self._call("argmax_f32", x.handle, n, partial.handle, out.handle, out_index)
+    def rmsnorm(self, x, weight, y, rows, cols, eps): self._call("rmsnorm_f32", x.handle, weight.handle, y.handle, rows, cols, eps)
+    def silu_mul(self, gate, up, out, n): self._call("silu_mul_f32", gate.handle, up.handle, out.handle, n)
+    def gelu_tanh_mul(self, gate, up, out, n): self._call("gelu_tanh_mul_f32", gate.handle, up.handle, out.handle, n)
+    def q8_0_gemv(self, w, x, y, rows, cols): self._call("q8_0_gemv", w.handle, x.handle, y.handle, rows, cols)
+
+    def q8_0_gemm(self, w, x, y, rows, cols, batch, x_off=0, y_off=0):
+        self._call("q8_0_gemm", w.handle, x.handle, y.handle, rows, cols, batch, x_off, y_off)
+
+    def q8_0_gemm_mma(self, w, x, y, rows, cols, batch, x_off=0, y_off=0):
+        self._call("q8_0_gemm_mma", w.handle, x.handle, y.handle, rows, cols, batch, x_off, y_off)
+
+    def q8_0_gemv_fused(self, w, x, y, rows, cols, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
+        self._call("q8_0_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)
+
+    def q8_0_row(self, w, out, row, cols, out_off=0): self._call("q8_0_row_f32", w.handle, out.handle, row, cols, out_off)
+
+    def row_indirect_f32(self, w, type_id, rows, cols, ids, slot, out):
+        self._call("row_indirect_f32", w.handle, type_id, rows, cols, ids.handle, slot, out.handle)
+
+    def qwen35_rope_partial(self, q, k, inv_freq, pos, n_q, n_kv, head_dim, n_rot):
+        self._call("qwen35_rope_partial", q.handle, k.handle, inv_freq.handle, pos, n_q, n_kv, head_dim, n_rot)
+
+    def qwen35_rope_partial_chunk(self, q, k, inv_freq, pos0, n_q, n_kv, head_dim, n_rot, n):
+        self._call("qwen35_rope_partial_chunk", q.handle, k.handle, inv_freq.handle, pos0, n_q, n_kv, head_dim, n_rot, n)
+
+    def qwen35_kv_store_f16(self, k_src, v_src, k_cache, v_cache, pos, cap, head_dim, kv_heads):
+        self._call("qwen35_kv_store_f16", k_src.handle, v_src.handle, k_cache.handle, v_cache.handle, pos, cap, head_dim, kv_heads)
+
+    def qwen35_kv_store_chunk(self, k_src, v_src, k_cache, v_cache, pos0, cap, head_dim, kv_heads, n):
+        self._call("qwen35_kv_store_f16_chunk", k_src.handle, v_src.handle, k_cache.handle, v_cache.handle, pos0, cap, head_dim, kv_heads, n)
+
+    def qwen35_attention_f16(self, q, k_cache, v_cache, out, scratch, heads, pos, cap, head_dim, group, scale):
+        self._call("qwen35_attention_f16", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos, cap, head_dim, group, scale)
+
+    def qwen35_attention_chunk(self, q, k_cache, v_cache, out, scratch, heads, pos0, cap, head_dim, group, scale, n, window):
+        self._call("qwen35_attention_f16_chunk", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos0, cap, head_dim, group, scale, n, window)
+
+    def attention_decode_dev(self, q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, out, scratch, pos_buf,
+                             pos_index, status, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale):
+        self._call("attention_decode_dev", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle,
+                   inv_freq.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, pos_buf.handle,
+                   pos_index, status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale)
+
+    def u32_add(self, buf, index, delta): self._call("u32_add", buf.handle, index, delta)
+
+    # -- grouping, fences, measurement ---------------------------------------
+    def begin_group(self): self._call("begin_group")
+    def end_group(self): self._call("end_group")
+    def abort_group(self): self._call("abort_group")
+
+    def end_group_retain(self) -> CudaGraph:
+        out = C.c_void_p()
+        self._call("end_group_retain", C.byref(out))
+        return CudaGraph(self, out.value)
+
+    def grouped(self, encode):
+        """Encode ``encode()`` into one dispatch; abort it on error
+        (crates/tuckcore/src/qwen35_gpu.rs:66-86)."""
+        self.begin_group()
+        try:
+            encode()
+        except Exception:
+            self.abort_group()
+            raise
+        self.end_group()
+
+    def fence(self): self._call("fence")
+    def committed_dispatches(self) -> int: return int(self._l.tm_cuda_committed_dispatches(self.handle))
+    def completed_dispatches(self) -> int: return int(self._l.tm_cuda_completed_dispatches(self.handle))
+    def gpu_nanos_total(self) -> int: return int(self._l.tm_cuda_gpu_nanos_total(self.handle))
+    def last_gpu_ms(self) -> float: return float(self._l.tm_cuda_last_gpu_ms(self.handle))
+    def allocated_bytes(self) -> int: return int(self._l.tm_cuda_allocated_bytes(self.handle))
+    def in_flight_bytes(self) -> int: return int(self._l.tm_cuda_in_flight_bytes(self.handle))
+    def kernel_launches(self) -> int: return int(self._l.tm_cuda_kernel_launches(self.handle))
+    def stream(self) -> int: return int(self._l.tm_cuda_stream(self.handle) or 0)
+    def set_profiling(self, enabled: bool): self._l.tm_cuda_profile_set(self.handle, int(enabled))
+
+    def profile_snapshot(self) -> list[tuple[str, int, int]]:
+        rows, i = [], 0
+        name = C.create_string_buffer(128)
+        nanos, count = C.c_uint64(), C.c_uint64()
+        while self._l.tm_cuda_profile_read(self.handle, i, name, 128, C.byref(nanos), C.byref(count)):
+            rows.append((name.value.decode(), nanos.value, count.value))
+            i += 1
+        return rows
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

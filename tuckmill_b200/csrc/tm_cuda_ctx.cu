@@ -309,7 +309,7 @@ int tm_cuda_upload(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, size_t off, const void
     if (!src || len == 0 || off > SIZE_MAX - len)
         return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "upload range is empty or overflows");
     TM_CHECK_BUF(dst, off + len, "upload target");
-    TM_CUDA_TRY(cudaMemcpyAsync(dst->dev + off, src, len, cudaMemcpyHostToDevice, ctx->stream));
+    TM_CUDA_TRY(cudaMemcpyAsync(dst->dev + off, src, len, cudaMemcpyDefault, ctx->stream));
     TM_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     poll_locked(ctx, false);
     return TM_CUDA_OK;
@@ -323,7 +323,7 @@ int tm_cuda_download(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, void *ds
     if (!dst || len == 0 || off > SIZE_MAX - len)
         return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "download range is empty or overflows");
     TM_CHECK_BUF(src, off + len, "download source");
-    TM_CUDA_TRY(cudaMemcpyAsync(dst, src->dev + off, len, cudaMemcpyDeviceToHost, ctx->stream));
+    TM_CUDA_TRY(cudaMemcpyAsync(dst, src->dev + off, len, cudaMemcpyDefault, ctx->stream));
     TM_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     poll_locked(ctx, false);
     return TM_CUDA_OK;

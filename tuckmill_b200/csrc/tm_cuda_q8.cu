@@ -3,15 +3,10 @@
 //
 // Arithmetic contract (the reference's device GEMV, native/metal/kernels.metal:
 // 72-118, and its batched twin :434-476): y[r] = sum over blocks of
-// d_{r,b} * sum_l q_{r,b,l} * x[32b+l], f32 throughout, reduction order free
-// (tolerance-registered against the scalar CPU order, crates/tuckcore/src/
-// kernels.rs:186-204).  The design is not the Metal kernel's: weights sit in two
-// planes so a lane fetches 16 quants with one 128-bit load, the activations are
-// staged once per CTA in shared memory in a lane-major permutation (conflict
-// free 128-bit reads), each warp owns whole rows, and row sums finish with a
-// multi-value shuffle butterfly.  The lane -> column mapping and the butterfly
-// order are the same for every tile shape and batch, so a (row, token) result
-// is bit-identical whichever configuration computed it.
+// d_{r,b} * sum_l q_{r,b,l} * x[32b+l] with f32 accumulation, reduction order
+// free (tolerance-registered against the scalar CPU order,
+// crates/tuckcore/src/kernels.rs:186-204).  The design is not the Metal
+// kernel's; it is described at q8_gemv_kernel below.
 #include "tm_cuda_internal.cuh"
 #include "tm_cuda_device.cuh"
 
@@ -22,62 +17,23 @@ constexpr int kWarps = tmdev::kWarps;
 using tmdev::block_sumsq;
 using tmdev::silu_f;
 using tmdev::gelu_tanh_f;
-constexpr int kGroupCols = 512;  // one warp-wide 128-bit load of quants
+constexpr int kChunkCols = 64;  // columns one m16n8k32 pair covers (two Q8_0 blocks)
 
 __device__ __forceinline__ int4 ldg_stream(const int4 *p) {
     int4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
 }
 
-// Four signed bytes of `w` as floats (exact).
-__device__ __forceinline__ void unpack4(int w, float &a, float &b, float &c, float &d) {
-    a = (float)(signed char)(w);
-    b = (float)(signed char)(w >> 8);
-    c = (float)(signed char)(w >> 16);
-    d = (float)(w >> 24);
-}
-
-// Shared-memory slot of column c of one token: group-major, then the four
-// 4-float pieces of every lane interleaved so lanes read consecutive float4s.
-__device__ __forceinline__ uint32_t x_slot(uint32_t c) {
-    const uint32_t g = c / kGroupCols, w = c % kGroupCols;
-    const uint32_t lane = w >> 4, piece = (w >> 2) & 3u, e = w & 3u;
-    return g * kGroupCols + ((piece * 32u + lane) << 2) + e;
-}
-
-// Reduce R per-lane row partials across the warp.  Pairing order is lane bit
-// 4,3,2,1,0 for every R; on return lane `row_lane(s)` holds row slot s.
-template <int R>
-__device__ __forceinline__ float reduce_rows(float (&a)[R], int lane) {
-    float v;
-    if (R == 4) {
-        const bool hi = lane & 16;
-        float k0 = hi ? a[2] : a[0], k1 = hi ? a[3] : a[1];
-        const float s0 = hi ? a[0] : a[2], s1 = hi ? a[1] : a[3];
-        k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
-        k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-        const bool hi2 = lane & 8;
-        v = hi2 ? k1 : k0;
-        const float s = hi2 ? k0 : k1;
-        v += __shfl_xor_sync(0xffffffffu, s, 8);
-    } else if (R == 2) {
-        const bool hi = lane & 16;
-        v = hi ? a[1] : a[0];
-        const float s = hi ? a[0] : a[1];
-        v += __shfl_xor_sync(0xffffffffu, s, 16);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-    } else {
-        v = a[0];
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-    }
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v;
+// D += A(16x32 s8, row) * B(32x8 s8, col), s32 accumulate.
+__device__ __forceinline__ void mma_s8(int (&d)[4], int a0, int a1, int a2, int a3, int b0, int b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 struct gemv_args {
@@ -89,171 +45,323 @@ struct gemv_args {
     uint32_t rows, cols;
     float eps;
     int prologue, epilogue;
+    uint32_t plane;         // bytes between digit planes (== 64 mod 128)
+    uint32_t ks;            // column splits per row tile (1, 2, 4 or 8)
 };
 
-// M tokens, R rows per warp step.
-template <int M, int R>
-__global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
-    extern __shared__ __align__(16) float xs[];  // [M][colsPad], permuted
-    __shared__ float red[kWarps];
-    const uint32_t cols = a.cols, rows = a.rows;
-    const uint32_t cols_pad = (cols + kGroupCols - 1) / kGroupCols * kGroupCols;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Bytes of shared memory one token's staged activations take.
+__host__ __device__ inline size_t token_smem(uint32_t cols, uint32_t plane) {
+    return 4u * (size_t)plane + (size_t)(cols / 32u) * 16u;
+}
 
-    // ---- stage the activations (with the folded elementwise operator) ----
+/*
+ * The decode GEMV, HBM-bound by construction: the int8 quants go from global
+ * memory straight into the A operand of the integer tensor-core MMA, with no
+ * per-weight conversion at all.  To keep f32 accuracy the f32 activations are
+ * split, once per CTA, into four signed 7-bit digits against a power-of-two
+ * block scale: x = 2^e * (a0 + a1/2^7 + a2/2^14 + a3/2^21), exact for every
+ * element whose bits lie within 2^-27 of its block's largest magnitude.  The
+ * digits of the two blocks of a 64-column chunk are the eight B columns, so
+ * one accumulator tile holds sum(q * a_k) per (row, block, digit) exactly in
+ * s32; f32 work is 4 conversions and 6 FMAs per 32 weights:
+ *     y[r] += d[r,b] * sum_k float(S[r,b,k]) * 2^(e_b - 7k).
+ * A warp owns a 16-row tile; lane (g, t) loads 16 quants of rows g and g+8 at
+ * columns chunk*64 + t*16.  `ks` warps split the chunks of a tile (interleaved)
+ * and their partial row sums are added in a fixed order, so small matrices
+ * still spread over the machine.  ks and the lane mapping depend only on the
+ * matrix shape, never on the batch, which keeps a (row, token) result
+ * bit-identical between the GEMV and any batched call.
+ */
+template <int M>
+__global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float red[kWarps];
+    __shared__ float partial[kWarps][M][16];
+    const uint32_t cols = a.cols, rows = a.rows, nb = cols / 32u, plane = a.plane;
+    const size_t tok = token_smem(cols, plane);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const uint32_t ks = a.ks, tiles_per_cta = kWarps / ks;
+    const uint32_t my_ks = warp % ks, my_tile = warp / ks;
+    const uint32_t n_tiles = (rows + 15u) / 16u;
+    const uint32_t n_chunks = (cols + kChunkCols - 1u) / kChunkCols;
+
+    // Weights do not depend on the activations: start pulling this warp's
+    // first tile towards L2 while the activations are being staged.
+    {
+        const uint32_t tile = blockIdx.x * tiles_per_cta + my_tile;
+        if (tile < n_tiles) {
+            const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) {
+                const uint32_t c0 = (my_ks + j * ks) * kChunkCols + t4 * 16u;
+                if (c0 < cols) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_a * cols + c0));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_b * cols + c0));
+                }
+            }
+        }
+    }
+
+    // ---- stage the activations: elementwise prologue, then digit planes ----
 #pragma unroll 1
     for (int m = 0; m < M; ++m) {
         const float *xm = a.x + (size_t)m * cols;
-        float *dst = xs + (size_t)m * cols_pad;
+        signed char *dig = (signed char *)(smem + (size_t)m * tok);
+        float *coef = (float *)(smem + (size_t)m * tok + 4u * (size_t)plane);
+        float inv_rms = 0.0f;
         if (a.prologue == TM_CUDA_PRO_RMSNORM) {
             const float ss = block_sumsq(xm, cols, red);
-            const float inv = 1.0f / sqrtf(ss / (float)cols + a.eps);
-            for (uint32_t c = threadIdx.x; c < cols; c += kThreads)
-                dst[x_slot(c)] = xm[c] * inv * a.pro[c];
-        } else if (a.prologue == TM_CUDA_PRO_SILU_MUL) {
-            const float *um = a.pro + (size_t)m * cols;
-            for (uint32_t c = threadIdx.x; c < cols; c += kThreads)
-                dst[x_slot(c)] = silu_f(xm[c]) * um[c];
-        } else if (a.prologue == TM_CUDA_PRO_GELU_MUL) {
-            const float *um = a.pro + (size_t)m * cols;
-            for (uint32_t c = threadIdx.x; c < cols; c += kThreads)
-                dst[x_slot(c)] = gelu_tanh_f(xm[c]) * um[c];
-        } else {
-            for (uint32_t c = threadIdx.x; c < cols; c += kThreads) dst[x_slot(c)] = xm[c];
+            inv_rms = 1.0f / sqrtf(ss / (float)cols + a.eps);
+        }
+        // Each thread takes 4 consecutive columns, so 8 adjacent lanes own one
+        // 32-column block; kBatch such quads are loaded before any is digitised.
+        constexpr int kBatch = 4;
+        const bool vec_ok = (((size_t)xm | (size_t)a.pro) & 15u) == 0 && (cols & 3u) == 0;
+#pragma unroll 1
+        for (uint32_t cb = 0; cb < cols; cb += kThreads * 4 * kBatch) {
+            float4 vs[kBatch], ps[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t c = cb + (i * kThreads + threadIdx.x) * 4u;
+                vs[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                ps[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (c < cols) {
+                    const float *pp = a.prologue == TM_CUDA_PRO_RMSNORM ? a.pro + c
+                                      : a.prologue != TM_CUDA_PRO_NONE ? a.pro + (size_t)m * cols + c
+                                                                       : nullptr;
+                    if (vec_ok) {
+                        vs[i] = *(const float4 *)(xm + c);
+                        if (pp) ps[i] = *(const float4 *)pp;
+                    } else {
+                        vs[i] = make_float4(xm[c], xm[c + 1], xm[c + 2], xm[c + 3]);
+                        if (pp) ps[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const uint32_t c = cb + (i * kThreads + threadIdx.x) * 4u;
+                // Whole warps leave together: 32 lanes x 4 columns = 128 columns, and
+                // cols is a multiple of 32, so a partially filled warp keeps its
+                // out-of-range lanes (zeros) in the shuffles below.
+                if (cb + (i * kThreads + (threadIdx.x & ~31u)) * 4u >= cols) break;
+                float v[4] = {vs[i].x, vs[i].y, vs[i].z, vs[i].w};
+                const float pw[4] = {ps[i].x, ps[i].y, ps[i].z, ps[i].w};
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (a.prologue == TM_CUDA_PRO_RMSNORM) v[j] = v[j] * inv_rms * pw[j];
+                    else if (a.prologue == TM_CUDA_PRO_SILU_MUL) v[j] = silu_f(v[j]) * pw[j];
+                    else if (a.prologue == TM_CUDA_PRO_GELU_MUL) v[j] = gelu_tanh_f(v[j]) * pw[j];
+                    // a non-finite value poisons its block (amax = inf -> NaN coefficient)
+                    amax = fmaxf(amax, fabsf(v[j]) <= 3.402823466e38f ? fabsf(v[j]) : INFINITY);
+                }
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                if (c < cols) {
+                    const bool bad = !(amax <= 3.402823466e38f);
+                    int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 5;
+                    e = e < -126 ? -126 : e > 122 ? 122 : e;
+                    const float inv = __uint_as_float((uint32_t)(127 - e) << 23);
+                    uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float r = v[j] * inv;  // |r| < 64, exact
+                        const float a0 = rintf(r);
+                        r = (r - a0) * 128.0f;
+                        const float a1 = rintf(r);
+                        r = (r - a1) * 128.0f;
+                        const float a2 = rintf(r);
+                        r = (r - a2) * 128.0f;
+                        const float a3 = rintf(r);
+                        w0 |= ((uint32_t)(int)a0 & 0xffu) << (8 * j);
+                        w1 |= ((uint32_t)(int)a1 & 0xffu) << (8 * j);
+                        w2 |= ((uint32_t)(int)a2 & 0xffu) << (8 * j);
+                        w3 |= ((uint32_t)(int)a3 & 0xffu) << (8 * j);
+                    }
+                    *(uint32_t *)(dig + c) = w0;
+                    *(uint32_t *)(dig + plane + c) = w1;
+                    *(uint32_t *)(dig + 2u * plane + c) = w2;
+                    *(uint32_t *)(dig + 3u * plane + c) = w3;
+                    const int k = lane & 7;
+                    if (k < 4) {
+                        const int ex = 127 + e - 7 * k;  // 2^(e - 7k); below the normal range -> 0
+                        float sc = ex > 0 ? __uint_as_float((uint32_t)ex << 23) : 0.0f;
+                        if (amax == 0.0f) sc = 0.0f;
+                        if (bad) sc = __uint_as_float(0x7fc00000u);
+                        coef[(c >> 5) * 4u + k] = sc;
+                    }
+                }
+            }
         }
     }
     __syncthreads();
 
-    const uint32_t nb = cols / 32u;
-    const uint32_t groups = cols_pad / kGroupCols;
-    const uint32_t steps = (rows + R - 1) / R;  // row tiles of R rows
-    for (uint32_t t = blockIdx.x * kWarps + warp; t < steps; t += gridDim.x * kWarps) {
-        const uint32_t r0 = t * R;
-        float acc[M][R];
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-            for (int r = 0; r < R; ++r) acc[m][r] = 0.0f;
+    const bool b_live = (t4 >> 1) == (g >> 2);  // this lane's k-slots belong to column n = g's block
 
-#pragma unroll 2
-        for (uint32_t g = 0; g < groups; ++g) {
-            const uint32_t c0 = g * kGroupCols + lane * 16u;
-            if (c0 < cols) {
-                int4 qv[R];
-                float dv[R];
+    for (uint32_t base = blockIdx.x * tiles_per_cta; base < n_tiles; base += gridDim.x * tiles_per_cta) {
+        const uint32_t tile = base + my_tile;
+        const bool tile_ok = tile < n_tiles;
+        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+        float acc[M][2];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint32_t row = min(r0 + r, rows - 1u);
-                    qv[r] = ldg_stream((const int4 *)(a.q + (size_t)row * cols + c0));
-                    dv[r] = __half2float(__ldg(a.d + (size_t)row * nb + (c0 >> 5)));
-                }
-                float part[M][R];
+        for (int m = 0; m < M; ++m) acc[m][0] = acc[m][1] = 0.0f;
+
+        if (tile_ok) {
+            // Per-lane bases; a chunk advances them by 64 quants / 2 scales.
+            const signed char *pa = a.q + (size_t)row_a * cols + t4 * 16u;
+            const signed char *pb = a.q + (size_t)row_b * cols + t4 * 16u;
+            const unsigned short *sa = (const unsigned short *)a.d + (size_t)row_a * nb + (t4 >> 1);
+            const unsigned short *sb = (const unsigned short *)a.d + (size_t)row_b * nb + (t4 >> 1);
+            constexpr int U = 4;  // chunks whose loads are issued before any is consumed
+#pragma unroll 1
+            for (uint32_t ch0 = my_ks; ch0 < n_chunks; ch0 += ks * U) {
+                int4 wa[U], wb[U];
+                unsigned short ha[U], hb[U];
 #pragma unroll
-                for (int m = 0; m < M; ++m)
-#pragma unroll
-                    for (int r = 0; r < R; ++r) part[m][r] = 0.0f;
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    float w[R][4];
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const int word = p == 0 ? qv[r].x : p == 1 ? qv[r].y : p == 2 ? qv[r].z : qv[r].w;
-                        unpack4(word, w[r][0], w[r][1], w[r][2], w[r][3]);
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t ch = ch0 + u * ks;
+                    const bool inb = ch < n_chunks && ch * kChunkCols + t4 * 16u < cols;
+                    wa[u] = wb[u] = make_int4(0, 0, 0, 0);
+                    ha[u] = hb[u] = 0;
+                    if (inb) {
+                        wa[u] = ldg_stream((const int4 *)(pa + (size_t)ch * kChunkCols));
+                        wb[u] = ldg_stream((const int4 *)(pb + (size_t)ch * kChunkCols));
+                        ha[u] = __ldg(sa + ch * 2u);
+                        hb[u] = __ldg(sb + ch * 2u);
                     }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t ch = ch0 + u * ks;
+                    const uint32_t c0 = ch * kChunkCols + t4 * 16u;
+                    const bool inb = ch < n_chunks && c0 < cols;
+                    if (ch >= n_chunks) break;
+                    const float da = __half2float(__ushort_as_half(ha[u]));
+                    const float db = __half2float(__ushort_as_half(hb[u]));
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        const float4 xv = *(const float4 *)(xs + (size_t)m * cols_pad +
-                                                            g * kGroupCols + ((p * 32 + lane) << 2));
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            float s = part[m][r];
-                            s = fmaf(w[r][0], xv.x, s);
-                            s = fmaf(w[r][1], xv.y, s);
-                            s = fmaf(w[r][2], xv.z, s);
-                            s = fmaf(w[r][3], xv.w, s);
-                            part[m][r] = s;
+                        const unsigned char *tokp = smem + (size_t)m * tok;
+                        int4 bx = make_int4(0, 0, 0, 0);
+                        if (b_live) bx = *(const int4 *)(tokp + (size_t)(g & 3) * plane + c0);
+                        int dd[4] = {0, 0, 0, 0};
+                        mma_s8(dd, wa[u].x, wb[u].x, wa[u].y, wb[u].y, bx.x, bx.y);
+                        mma_s8(dd, wa[u].z, wb[u].z, wa[u].w, wb[u].w, bx.z, bx.w);
+                        if (inb) {
+                            const float2 cx = *(const float2 *)(tokp + 4u * (size_t)plane +
+                                                                ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
+                            const float va = fmaf((float)dd[1], cx.y, (float)dd[0] * cx.x);
+                            const float vb = fmaf((float)dd[3], cx.y, (float)dd[2] * cx.x);
+                            acc[m][0] = fmaf(da, va, acc[m][0]);
+                            acc[m][1] = fmaf(db, vb, acc[m][1]);
                         }
                     }
                 }
+            }
+        }
+        // ---- add the four lanes of each row, then the ks column splits ----
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v = acc[m][h];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                acc[m][h] = v;
+            }
+        if (ks == 1) {
+            if (tile_ok && t4 == 0) {
 #pragma unroll
                 for (int m = 0; m < M; ++m)
 #pragma unroll
-                    for (int r = 0; r < R; ++r) acc[m][r] = fmaf(dv[r], part[m][r], acc[m][r]);
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t row = tile * 16u + g + 8u * h;
+                        if (row < rows) {
+                            float *yp = a.y + (size_t)m * rows + row;
+                            *yp = a.epilogue == TM_CUDA_EPI_ADD ? *yp + acc[m][h] : acc[m][h];
+                        }
+                    }
             }
-        }
-        // ---- finish the rows ----
-        const int slot = R == 4 ? (((lane >> 4) & 1) * 2 + ((lane >> 3) & 1)) : R == 2 ? ((lane >> 4) & 1) : 0;
-        const bool writer = R == 4 ? (lane & 7) == 0 : R == 2 ? (lane & 15) == 0 : lane == 0;
+        } else {
+            __syncthreads();  // previous round's readers are done with `partial`
+            if (t4 == 0) {
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const float v = reduce_rows<R>(acc[m], lane);
-            const uint32_t row = r0 + slot;
-            if (writer && row < rows) {
-                float *yp = a.y + (size_t)m * rows + row;
-                *yp = a.epilogue == TM_CUDA_EPI_ADD ? *yp + v : v;
+                for (int m = 0; m < M; ++m) {
+                    partial[warp][m][g] = acc[m][0];
+                    partial[warp][m][g + 8] = acc[m][1];
+                }
+            }
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < tiles_per_cta * M * 16u; i += kThreads) {
+                const uint32_t r16 = i & 15u, m = (i >> 4) % M, tl = i / (16u * M);
+                const uint32_t row = (base + tl) * 16u + r16;
+                if (base + tl < n_tiles && row < rows) {
+                    float v = 0.0f;
+                    for (uint32_t k = 0; k < ks; ++k) v += partial[tl * ks + k][m][r16];
+                    float *yp = a.y + (size_t)m * rows + row;
+                    *yp = a.epilogue == TM_CUDA_EPI_ADD ? *yp + v : v;
+                }
             }
         }
     }
-}
-
-template <int M, int R>
-cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
-    static bool attr_set[16] = {};  // per device
-    if (ctx->device < 16 && !attr_set[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M, R>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)ctx->smem_optin - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[ctx->device] = true;
-    }
-    q8_gemv_kernel<M, R><<<grid, kThreads, smem, ctx->stream>>>(a);
-    return cudaGetLastError();
 }
 
 template <int M>
-cudaError_t launch_gemv_r(tm_cuda_ctx *ctx, const gemv_args &a, int R, int grid, size_t smem) {
-    switch (R) {
-        case 4: return launch_gemv<M, 4>(ctx, a, grid, smem);
-        case 2: return launch_gemv<M, 2>(ctx, a, grid, smem);
-        default: return launch_gemv<M, 1>(ctx, a, grid, smem);
+cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
+    static bool attr_set[16] = {};  // per device
+    if (ctx->device < 16 && !attr_set[ctx->device]) {
+        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)ctx->smem_optin - 8192);
+        if (e != cudaSuccess) return e;
+        attr_set[ctx->device] = true;
     }
+    q8_gemv_kernel<M><<<grid, kThreads, smem, ctx->stream>>>(a);
+    return cudaGetLastError();
 }
 
-// One launch for `m` tokens (m in {1,2,4,8}); picks the row tile from the
-// matrix height so small projections still fill the machine.
+uint32_t digit_plane_bytes(uint32_t cols) {
+    const uint32_t pad = (uint32_t)tm_round_up(cols, kChunkCols);
+    return pad % 128u == 0 ? pad + 64u : pad;
+}
+
+// One launch for `m` tokens (m in {1,2,4,8}).  The column split comes from
+// the matrix shape alone, so small projections still fill the machine.
 cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
-    const size_t cols_pad = tm_round_up(a.cols, kGroupCols);
-    const size_t smem = (size_t)m * cols_pad * sizeof(float);
-    const uint32_t target = (uint32_t)ctx->sm_count * 2u * kWarps;  // warps wanted in flight
-    int R = 4;
-    if (m >= 8) R = 2;
-    while (R > 1 && (a.rows + R - 1) / R < target) R >>= 1;
-    const uint32_t steps = (a.rows + R - 1) / R;
-    uint32_t ctas = (steps + kWarps - 1) / kWarps;
-    const uint32_t max_ctas = (uint32_t)ctx->sm_count * (smem > 48 * 1024 ? 2u : 8u);
-    if (ctas > max_ctas) ctas = max_ctas;
+    a.plane = digit_plane_bytes(a.cols);
+    const size_t smem = (size_t)m * token_smem(a.cols, a.plane);
+    const uint32_t n_tiles = (a.rows + 15u) / 16u;
+    const uint32_t n_chunks = (a.cols + kChunkCols - 1u) / kChunkCols;
+    const uint32_t want = (uint32_t)ctx->sm_count * 32u;  // warps that fill the machine
+    uint32_t ks = 1;
+    while (ks < (uint32_t)kWarps && n_tiles * ks < want && ks * 2u <= n_chunks) ks <<= 1;
+    a.ks = ks;
+    const uint32_t tiles_per_cta = kWarps / ks;
+    uint32_t ctas = (n_tiles + tiles_per_cta - 1u) / tiles_per_cta;
+    if (ctas > 1u << 20) ctas = 1u << 20;  // the kernel strides over any remainder
     switch (m) {
-        case 8: return launch_gemv_r<8>(ctx, a, R, (int)ctas, smem);
-        case 4: return launch_gemv_r<4>(ctx, a, R, (int)ctas, smem);
-        case 2: return launch_gemv_r<2>(ctx, a, R, (int)ctas, smem);
-        default: return launch_gemv_r<1>(ctx, a, R, (int)ctas, smem);
+        case 8: return launch_gemv<8>(ctx, a, (int)ctas, smem);
+        case 4: return launch_gemv<4>(ctx, a, (int)ctas, smem);
+        case 2: return launch_gemv<2>(ctx, a, (int)ctas, smem);
+        default: return launch_gemv<1>(ctx, a, (int)ctas, smem);
     }
 }
 
 // Whole batch in slices of 8/4/2/1 tokens that fit shared memory.
 int gemv_batch(tm_cuda_ctx *ctx, gemv_args a, uint32_t batch, uint64_t *kernels, char *err,
                size_t err_cap) {
-    const size_t cols_pad = tm_round_up(a.cols, kGroupCols);
-    const size_t budget = ctx->smem_optin - 2048;
-    if (cols_pad * sizeof(float) > budget)
+    const size_t per_token = token_smem(a.cols, digit_plane_bytes(a.cols));
+    const size_t budget = ctx->smem_optin - 16384;
+    if (per_token > budget)
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
-                       "cols %u exceeds the %zu-float activation stage of one CTA", a.cols,
-                       budget / sizeof(float));
+                       "cols %u exceeds the activation stage of one CTA (%zu bytes)", a.cols, budget);
     uint32_t done = 0;
     while (done < batch) {
         int m = 8;
-        while (m > 1 && ((uint32_t)m > batch - done || (size_t)m * cols_pad * sizeof(float) > budget))
-            m >>= 1;
+        while (m > 1 && ((uint32_t)m > batch - done || (size_t)m * per_token > budget)) m >>= 1;
         gemv_args s = a;
         s.x = a.x + (size_t)done * a.cols;
         s.y = a.y + (size_t)done * a.rows;

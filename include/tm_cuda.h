@@ -75,7 +75,7 @@ int tm_cuda_upload(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, size_t off, const void
 int tm_cuda_download(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, void *dst, size_t len,
                      char *err, size_t err_cap);
 /* No counterpart: a handle aliasing `len` bytes of `parent` at byte offset
- * `off` (256-byte aligned), so operators without offset arguments can work
+ * `off` (16-byte aligned), so operators without offset arguments can work
  * on a slice of a fused output.  Counts 0 bytes in the ledger; must be freed
  * before its parent. */
 tm_cuda_buffer *tm_cuda_buffer_view(tm_cuda_ctx *ctx, tm_cuda_buffer *parent, size_t off,
@@ -137,6 +137,12 @@ size_t tm_cuda_q8_0_packed_bytes(uint32_t rows, uint32_t cols);
 int tm_cuda_q8_0_pack(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, uint32_t rows, uint32_t cols,
                       tm_cuda_buffer *raw, size_t raw_off, uint32_t row0, uint32_t nrows,
                       char *err, size_t err_cap);
+/* No counterpart: a handle on rows [row0, row0+nrows) of a packed matrix, usable
+ * wherever a packed nrows x cols matrix is (so projections stored as one fused
+ * matrix can also be multiplied one at a time).  Freed like a buffer view. */
+tm_cuda_buffer *tm_cuda_q8_0_row_view(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows,
+                                      uint32_t cols, uint32_t row0, uint32_t nrows, char *err,
+                                      size_t err_cap);
 /* No counterpart: the inverse, for round-trip checks: write rows
  * [row0,row0+nrows) of packed `src` as raw GGUF bytes into `raw`. */
 int tm_cuda_q8_0_unpack(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t rows, uint32_t cols,
@@ -169,6 +175,13 @@ int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *ou
 int tm_cuda_row_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t type_id, uint32_t rows,
                              uint32_t cols, tm_cuda_buffer *ids, uint32_t slot,
                              tm_cuda_buffer *out, char *err, size_t err_cap);
+
+/* No counterpart: the batched embedding lookup of a prefill chunk, one launch:
+ * out[t] = row ids[first + t] (times `scale` when non-zero), t < n; an id
+ * >= rows writes zeros.  Replaces n calls of tm_cuda_q8_0_row_f32. */
+int tm_cuda_rows_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                              tm_cuda_buffer *ids, uint32_t first, uint32_t n, float scale,
+                              tm_cuda_buffer *out, char *err, size_t err_cap);
 
 /* No counterpart: the GEMV with the neighbouring elementwise operators folded
  * into its activation load and its store, so a decode layer is a handful of
@@ -223,6 +236,9 @@ uint64_t tm_cuda_in_flight_bytes(const tm_cuda_ctx *ctx);
 /* No counterpart: kernels launched by this context so far (each operator
  * launch and each graph node counts one). */
 uint64_t tm_cuda_kernel_launches(const tm_cuda_ctx *ctx);
+/* No counterpart: free and total bytes of the context's device (the budget B
+ * the planner admits against when the caller names none). */
+int tm_cuda_device_memory(tm_cuda_ctx *ctx, uint64_t *free_bytes, uint64_t *total_bytes);
 /* No counterpart: the context's cudaStream_t, so a host that shares the CUDA
  * primary context can record its own events on the stream the kernels run on. */
 void *tm_cuda_stream(tm_cuda_ctx *ctx);
@@ -289,11 +305,12 @@ int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint3
                     char *err, size_t err_cap);
 /* No counterpart: argmax whose output index is taken from the device,
  * out[base + pos_buf[pos_index]], so a replayed graph appends each step's
- * token to a device-side token log the host reads with download_after. */
+ * token to a device-side token log; `mirror` (optional, same length, shared)
+ * receives the same value for the host to read with download_after. */
 int tm_cuda_argmax_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n,
                            tm_cuda_buffer *partial, tm_cuda_buffer *out, uint32_t base,
                            tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
-                           char *err, size_t err_cap);
+                           tm_cuda_buffer *mirror, char *err, size_t err_cap);
 /* No counterpart: tm_cuda_row_indirect_f32 whose slot is base +
  * pos_buf[pos_index] + bias (bias may be negative: "the previous token"),
  * followed by an optional scale (0 = none). */

@@ -206,7 +206,7 @@ def test_buffers_ledger_and_ownership(ctx):
     a.upload(256, np.arange(128, dtype=np.float32))
     np.testing.assert_array_equal(v.download(0, 512, np.float32), np.arange(128, dtype=np.float32))
     with pytest.raises(cuda.CudaError):
-        a.view(100, 10)  # unaligned
+        a.view(100, 10)  # not 16-byte aligned
     with pytest.raises(cuda.CudaError):
         a.upload(990, np.zeros(20, np.uint8))
     with pytest.raises(cuda.CudaError):

@@ -55,7 +55,32 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     if jobs or not LIB.exists():
         run([NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-Xlinker", "--no-undefined",
              "-ldl", "-lpthread"])
+    build_engine(verbose, force)
     return LIB
+
+
+ENGINE_LIB = PKG / "libtm_engine.so"
+CXX = os.environ.get("CXX", "g++")
+
+
+def build_engine(verbose: bool = False, force: bool = False) -> Path:
+    """The C++ host layer (csrc/engine) -> libtm_engine.so, linked against
+    libtm_cuda.so next to it (rpath $ORIGIN)."""
+    src_dir = CSRC / "engine"
+    sources = sorted(src_dir.glob("*.cpp"))
+    deps = sources + list(src_dir.glob("*.hpp")) + list((ROOT / "include").glob("*.h")) + [LIB]
+    if not force and not _stale(ENGINE_LIB, deps):
+        return ENGINE_LIB
+    cmd = [CXX, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-Wextra", "-I", str(ROOT / "include"),
+           "-I", str(src_dir), *map(str, sources), "-o", str(ENGINE_LIB),
+           "-L", str(PKG), "-ltm_cuda", "-Wl,-rpath,$ORIGIN",
+           "-Wl,--no-undefined", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("engine build failed: " + " ".join(cmd))
+    return ENGINE_LIB
 
 
 if __name__ == "__main__":

@@ -1,0 +1,625 @@
+#include "engine.hpp"
+
+#include <chrono>
+#include <cmath>
+#include <cstring>
+
+namespace tuckmill {
+
+namespace {
+
+uint64_t f32_bytes(size_t elems) { return 4ull * (elems ? elems : 1); }
+
+// Allocation accumulator mirroring every buffer a block creates
+// (crates/tuckcore/src/engine/metal.rs:254-272).
+struct Plan {
+    uint64_t weights = 0, state = 0, scratch = 0;
+    void weights_f32(size_t n) { weights += f32_bytes(n); }
+    void scratch_f32(size_t n) { scratch += f32_bytes(n); }
+    void scratch_bytes(size_t n) { scratch += n ? n : 4; }
+};
+
+size_t vector_len(const WeightSource &src, Tensor t) {
+    auto d = src.tensor_dims(t.index);
+    return (size_t)(d.first * (d.second ? d.second : 1));
+}
+
+CudaBuffer vector(const CudaContext &ctx, const WeightSource &src, Tensor t) {
+    std::vector<float> v = src.read_vector(t.index);
+    return ctx.floats(v);
+}
+
+CudaBuffer zeros_f32(const CudaContext &ctx, size_t elems) { return ctx.zeros(f32_bytes(elems)); }
+
+// RoPE inverse-frequency table, f64 pow then f32 (crates/tuckcore/src/qwen35_ops.rs:265-272).
+std::vector<float> rope_inv_freq(size_t rope_dims, float base) {
+    std::vector<float> out(rope_dims / 2);
+    for (size_t i = 0; i < out.size(); ++i) {
+        const double exponent = 2.0 * (double)i / (double)rope_dims;
+        out[i] = (float)(1.0 / std::pow((double)base, exponent));
+    }
+    return out;
+}
+
+// A device matrix: one or more Q8_0 tensors of equal width, rows concatenated,
+// repacked into the two-plane form at upload (crates/tuckcore/src/engine/
+// metal.rs:107-226 uploads the GGUF bytes verbatim; the row concatenation and
+// the repack are this engine's).
+struct Matrix {
+    CudaBuffer buf;
+    std::vector<CudaBuffer> parts;  // row views, one per source tensor (empty when single)
+    std::vector<uint32_t> part_rows;
+    uint32_t rows = 0, cols = 0;
+
+    static void geometry(const WeightSource &src, const std::vector<Tensor> &ts, uint32_t *rows, uint32_t *cols) {
+        *rows = 0;
+        *cols = 0;
+        for (Tensor t : ts) {
+            const uint32_t ty = src.tensor_type_id(t.index);
+            auto d = src.tensor_dims(t.index);
+            if (d.second <= 1)
+                throw TuckmillError(ErrorCode::Internal,
+                                    "tensor " + std::to_string(t.index) + " is 1-D; vectors use the f32 path");
+            if (ty != 8)
+                throw TuckmillError(ErrorCode::UnsupportedQuantization,
+                                    "CUDA engine matrices must be Q8_0; tensor " + std::to_string(t.index) +
+                                        " is type " + std::to_string(ty));
+            if (d.first % 32 != 0 || d.first > UINT32_MAX || d.second > UINT32_MAX)
+                throw TuckmillError(ErrorCode::InvalidArtifact, "Q8_0 tensor rows are not block aligned");
+            if (*cols != 0 && *cols != (uint32_t)d.first)
+                throw TuckmillError(ErrorCode::Internal, "fused projections differ in input width");
+            *cols = (uint32_t)d.first;
+            *rows += (uint32_t)d.second;
+        }
+    }
+
+    static uint64_t plan(const WeightSource &src, const std::vector<Tensor> &ts) {
+        uint32_t rows, cols;
+        geometry(src, ts, &rows, &cols);
+        return tm_cuda_q8_0_packed_bytes(rows, cols);
+    }
+
+    static Matrix load(const CudaContext &ctx, const WeightSource &src, const std::vector<Tensor> &ts) {
+        Matrix m;
+        geometry(src, ts, &m.rows, &m.cols);
+        m.buf = ctx.buffer(tm_cuda_q8_0_packed_bytes(m.rows, m.cols));
+        const size_t row_bytes = (size_t)m.cols / 32 * 34;
+        const size_t step = std::max<size_t>(1, kStagingChunkBytes / row_bytes);
+        CudaBuffer stage = ctx.buffer(step * row_bytes);  // transient: freed before the ledger is checked
+        std::vector<unsigned char> host(step * row_bytes);
+        uint32_t row0 = 0;
+        for (Tensor t : ts) {
+            const uint32_t n = (uint32_t)src.tensor_dims(t.index).second;
+            for (uint32_t r = 0; r < n; r += (uint32_t)step) {
+                const uint32_t k = std::min<uint32_t>((uint32_t)step, n - r);
+                src.read_tensor_into(t.index, (uint64_t)r * row_bytes, host.data(), (size_t)k * row_bytes);
+                stage.upload(0, host.data(), (size_t)k * row_bytes);
+                ctx.q8_0_pack(m.buf, m.rows, m.cols, stage, 0, row0 + r, k);
+            }
+            m.part_rows.push_back(n);
+            row0 += n;
+        }
+        ctx.fence();
+        if (ts.size() > 1) {
+            uint32_t r = 0;
+            for (uint32_t n : m.part_rows) {
+                m.parts.push_back(ctx.row_view(m.buf, m.rows, m.cols, r, n));
+                r += n;
+            }
+        }
+        return m;
+    }
+
+    // Y[b] = W X[b].  Batch 1 and `exact` keep the GEMV's per-row arithmetic in
+    // slices of at most 32 tokens; other batches use the tensor cores in one
+    // launch (the dispatch rule of engine/metal.rs:167-196).
+    static void gemm(const CudaContext &ctx, const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &x,
+                     const CudaBuffer &y, uint32_t batch, bool exact) {
+        if (!exact && batch >= 2 && batch <= TM_CUDA_GEMM_MMA_MAX_BATCH) {
+            ctx.q8_0_gemm_mma(w, x, y, rows, cols, batch, 0, 0);
+            return;
+        }
+        for (uint32_t t0 = 0; t0 < batch; t0 += TM_CUDA_GEMM_MAX_BATCH) {
+            const uint32_t n = std::min<uint32_t>(batch - t0, TM_CUDA_GEMM_MAX_BATCH);
+            ctx.q8_0_gemm(w, x, y, rows, cols, n, t0 * cols, t0 * rows);
+        }
+    }
+    void gemm_part(const CudaContext &ctx, size_t part, const CudaBuffer &x, const CudaBuffer &y, uint32_t batch,
+                   bool exact) const {
+        gemm(ctx, parts[part], part_rows[part], cols, x, y, batch, exact);
+    }
+    void gemm_all(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &y, uint32_t batch, bool exact) const {
+        gemm(ctx, buf, rows, cols, x, y, batch, exact);
+    }
+};
+
+// Chunk-wide scratch shared by every layer (engine/metal.rs:334-425): rows are
+// token-major, `n` = prefill batch.
+struct PrefillScratch {
+    CudaBuffer x, h, a, b, c, e, proj, h2, g, u, d2, ascr;
+    static void plan(const ModelGraph &g, size_t cap, size_t n, Plan &p) {
+        size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
+        for (const LayerSpec &l : g.layers) {
+            aw = std::max(aw, l.mixer.heads * l.mixer.head_dim);
+            kvw = std::max(kvw, l.mixer.kv_heads * l.mixer.head_dim);
+            ffn = std::max(ffn, l.ffn.width);
+            heads = std::max(heads, l.mixer.heads);
+        }
+        for (size_t e : {g.hidden, g.hidden, aw, kvw, kvw, aw, g.hidden, g.hidden, ffn, ffn, g.hidden})
+            p.scratch_f32(n * e);
+        p.scratch_f32(n * heads * cap);
+    }
+    static PrefillScratch alloc(const CudaContext &ctx, const ModelGraph &g, size_t cap, size_t n) {
+        size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
+        for (const LayerSpec &l : g.layers) {
+            aw = std::max(aw, l.mixer.heads * l.mixer.head_dim);
+            kvw = std::max(kvw, l.mixer.kv_heads * l.mixer.head_dim);
+            ffn = std::max(ffn, l.ffn.width);
+            heads = std::max(heads, l.mixer.heads);
+        }
+        PrefillScratch s;
+        s.x = zeros_f32(ctx, n * g.hidden);
+        s.h = zeros_f32(ctx, n * g.hidden);
+        s.a = zeros_f32(ctx, n * aw);
+        s.b = zeros_f32(ctx, n * kvw);
+        s.c = zeros_f32(ctx, n * kvw);
+        s.e = zeros_f32(ctx, n * aw);
+        s.proj = zeros_f32(ctx, n * g.hidden);
+        s.h2 = zeros_f32(ctx, n * g.hidden);
+        s.g = zeros_f32(ctx, n * ffn);
+        s.u = zeros_f32(ctx, n * ffn);
+        s.d2 = zeros_f32(ctx, n * g.hidden);
+        s.ascr = zeros_f32(ctx, n * heads * cap);
+        return s;
+    }
+};
+
+// Gated FFN: down(act(gate x) * up x), optional RMS norm on the output before
+// the residual add (engine/metal.rs:431-535).  gate|up are one matrix.
+struct SwiGluBlock {
+    Matrix gate_up, down;
+    GluActivation act = GluActivation::Silu;
+    CudaBuffer out_norm;  // empty unless the artifact has it
+    float eps = 0;
+    CudaBuffer gu, g_view, u_view, out;
+    size_t width = 0;
+
+    static void plan(const FfnSpec &f, bool has_norm, Tensor norm, size_t hidden, const WeightSource &src, Plan &p) {
+        p.weights += Matrix::plan(src, {f.gate, f.up}) + Matrix::plan(src, {f.down});
+        if (has_norm) p.weights_f32(vector_len(src, norm));
+        p.scratch_f32(2 * f.width);
+        p.scratch_f32(hidden);
+    }
+    static SwiGluBlock load(const CudaContext &ctx, const WeightSource &src, const FfnSpec &f, bool has_norm,
+                            Tensor norm, size_t hidden, float eps) {
+        SwiGluBlock b;
+        b.gate_up = Matrix::load(ctx, src, {f.gate, f.up});
+        b.down = Matrix::load(ctx, src, {f.down});
+        b.act = f.act;
+        if (has_norm) b.out_norm = vector(ctx, src, norm);
+        b.eps = eps;
+        b.width = f.width;
+        b.gu = zeros_f32(ctx, 2 * f.width);
+        b.g_view = b.gu.view(0, f.width * 4);
+        b.u_view = b.gu.view(f.width * 4, f.width * 4);
+        b.out = zeros_f32(ctx, hidden);
+        return b;
+    }
+    // x += ffn(norm(x, post_norm)) for one token: 2 launches (3 more with an output norm).
+    void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &post_norm, size_t hidden) const {
+        ctx.q8_0_gemv_fused(gate_up.buf, x, gu, gate_up.rows, gate_up.cols, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
+                            TM_CUDA_EPI_STORE);
+        const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        if (out_norm) {
+            ctx.q8_0_gemv_fused(down.buf, g_view, out, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
+            ctx.rmsnorm(out, out_norm, out, 1, (uint32_t)hidden, eps);
+            ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
+        } else {
+            ctx.q8_0_gemv_fused(down.buf, g_view, x, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_ADD);
+        }
+    }
+    // x += ffn(h2) for the n chunk rows of s.h2 / s.x (engine/metal.rs:514-534).
+    void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, size_t hidden, bool exact) const {
+        const uint32_t nn = (uint32_t)n;
+        gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
+        gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
+        if (act == GluActivation::Silu) ctx.silu_mul(s.g, s.u, s.g, (uint32_t)(n * width));
+        else ctx.gelu_tanh_mul(s.g, s.u, s.g, (uint32_t)(n * width));
+        down.gemm_all(ctx, s.g, s.d2, nn, exact);
+        if (out_norm) ctx.rmsnorm(s.d2, out_norm, s.d2, nn, (uint32_t)hidden, eps);
+        ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+    }
+};
+
+// Grouped-query attention with per-head Q/K RMS norms, RoPE, packed f16 KV and
+// an optional sliding window (engine/metal.rs:989-1364).  q|k|v are one matrix.
+struct AttentionBlock {
+    AttentionSpec spec;
+    float eps = 0;
+    Matrix qkv, o;
+    CudaBuffer q_norm, k_norm, inv_freq, k_cache, v_cache;
+    CudaBuffer qkv_out, q_view, k_view, v_view, attn, kv_scratch;
+    size_t cap = 0;
+
+    static uint64_t kv_plane_bytes(const AttentionSpec &s, size_t cap) { return (uint64_t)s.kv_heads * cap * s.head_dim * 2; }
+
+    static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, Plan &p) {
+        p.weights += Matrix::plan(src, {s.q, s.k, s.v}) + Matrix::plan(src, {s.o});
+        p.weights_f32(vector_len(src, s.q_norm));
+        p.weights_f32(vector_len(src, s.k_norm));
+        // The RoPE table is derived by the engine, not artifact bytes: scratch.
+        p.scratch_f32(s.rope_dims / 2);
+        p.state += 2 * kv_plane_bytes(s, cap);
+        const size_t hd = s.heads * s.head_dim, kv = s.kv_heads * s.head_dim;
+        p.scratch_f32(hd + 2 * kv);
+        p.scratch_f32(hd);
+        p.scratch_f32(s.heads * cap);
+    }
+    static AttentionBlock load(const CudaContext &ctx, const WeightSource &src, const AttentionSpec &s, float eps,
+                               size_t cap) {
+        if (s.head_dim % 2 != 0 || s.head_dim > 512 || s.rope_dims % 2 != 0)
+            throw TuckmillError(ErrorCode::UnsupportedArchitecture,
+                                "attention head size " + std::to_string(s.head_dim) + " has no CUDA block");
+        AttentionBlock b;
+        b.spec = s;
+        b.eps = eps;
+        b.cap = cap;
+        b.qkv = Matrix::load(ctx, src, {s.q, s.k, s.v});
+        b.o = Matrix::load(ctx, src, {s.o});
+        const size_t hd = s.heads * s.head_dim, kv = s.kv_heads * s.head_dim;
+        if (b.qkv.part_rows[0] != hd || b.qkv.part_rows[1] != kv || b.qkv.part_rows[2] != kv || b.o.cols != hd)
+            throw TuckmillError(ErrorCode::UnsupportedArchitecture, "attention projection shapes do not match the head geometry");
+        b.q_norm = vector(ctx, src, s.q_norm);
+        b.k_norm = vector(ctx, src, s.k_norm);
+        b.inv_freq = ctx.floats(rope_inv_freq(s.rope_dims, s.rope_base));
+        b.k_cache = ctx.buffer(kv_plane_bytes(s, cap));
+        b.v_cache = ctx.buffer(kv_plane_bytes(s, cap));
+        b.qkv_out = zeros_f32(ctx, hd + 2 * kv);
+        b.q_view = b.qkv_out.view(0, hd * 4);
+        b.k_view = b.qkv_out.view(hd * 4, kv * 4);
+        b.v_view = b.qkv_out.view((hd + kv) * 4, kv * 4);
+        b.attn = zeros_f32(ctx, hd);
+        b.kv_scratch = zeros_f32(ctx, s.heads * cap);
+        return b;
+    }
+    void reset() const {
+        k_cache.zero();
+        v_cache.zero();
+    }
+    float scale() const { return 1.0f / std::sqrt((float)spec.head_dim); }
+
+    // attn = attention(norm(x, pre_norm)) at the device-held position: 2 launches.
+    void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pre_norm, const CudaBuffer &pos_buf,
+                const CudaBuffer &status) const {
+        ctx.q8_0_gemv_fused(qkv.buf, x, qkv_out, qkv.rows, qkv.cols, TM_CUDA_PRO_RMSNORM, &pre_norm, eps,
+                            TM_CUDA_EPI_STORE);
+        ctx.attention_decode_dev(q_view, k_view, v_view, q_norm, k_norm, inv_freq, k_cache, v_cache, attn, kv_scratch,
+                                 pos_buf, 0, status, (uint32_t)spec.heads, (uint32_t)spec.kv_heads,
+                                 (uint32_t)spec.head_dim, (uint32_t)spec.rope_dims, (uint32_t)cap,
+                                 (uint32_t)spec.window, eps, scale());
+    }
+    // Chunk core over n queries at pos0.. (engine/metal.rs:1170-1233): every
+    // chunk K/V row is stored before any chunk query attends.
+    void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, bool exact) const {
+        const uint32_t nn = (uint32_t)n, heads = (uint32_t)spec.heads, kv = (uint32_t)spec.kv_heads,
+                       hd = (uint32_t)spec.head_dim;
+        qkv.gemm_part(ctx, 0, s.h, s.a, nn, exact);
+        qkv.gemm_part(ctx, 1, s.h, s.b, nn, exact);
+        qkv.gemm_part(ctx, 2, s.h, s.c, nn, exact);
+        ctx.rmsnorm(s.a, q_norm, s.a, nn * heads, hd, eps);
+        ctx.rmsnorm(s.b, k_norm, s.b, nn * kv, hd, eps);
+        ctx.rope_partial_chunk(s.a, s.b, inv_freq, pos0, heads, kv, hd, (uint32_t)spec.rope_dims, nn);
+        ctx.kv_store_chunk(s.b, s.c, k_cache, v_cache, pos0, (uint32_t)cap, hd, kv, nn);
+        ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
+                            (uint32_t)spec.window);
+        o.gemm_all(ctx, s.e, s.proj, nn, exact);
+    }
+};
+
+// One layer: x += [norm](mixer(norm(x))); x += [norm](ffn(norm(x))) (engine/metal.rs:1379-1525).
+struct Layer {
+    CudaBuffer pre_norm, mixer_out_norm, post_norm, proj;
+    AttentionBlock mixer;
+    SwiGluBlock ffn;
+
+    static void plan(const LayerSpec &l, const ModelGraph &g, const WeightSource &src, size_t cap, Plan &p) {
+        p.weights_f32(vector_len(src, l.pre_norm));
+        p.weights_f32(vector_len(src, l.post_norm));
+        if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
+        p.scratch_f32(g.hidden);  // proj
+        AttentionBlock::plan(l.mixer, src, cap, p);
+        SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, p);
+    }
+    static Layer load(const CudaContext &ctx, const WeightSource &src, const LayerSpec &l, const ModelGraph &g,
+                      size_t cap) {
+        Layer L;
+        L.pre_norm = vector(ctx, src, l.pre_norm);
+        if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
+        L.post_norm = vector(ctx, src, l.post_norm);
+        L.proj = zeros_f32(ctx, g.hidden);
+        L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap);
+        L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps);
+        return L;
+    }
+    void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pos_buf, const CudaBuffer &status,
+                size_t hidden, float eps) const {
+        mixer.decode(ctx, x, pre_norm, pos_buf, status);
+        if (mixer_out_norm) {
+            ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
+            ctx.rmsnorm(proj, mixer_out_norm, proj, 1, (uint32_t)hidden, eps);
+            ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
+        } else {
+            ctx.q8_0_gemv_fused(mixer.o.buf, mixer.attn, x, mixer.o.rows, mixer.o.cols, TM_CUDA_PRO_NONE, nullptr, 0.0f,
+                                TM_CUDA_EPI_ADD);
+        }
+        ffn.decode(ctx, x, post_norm, hidden);
+    }
+    void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, size_t hidden, float eps,
+                 bool exact) const {
+        const uint32_t nn = (uint32_t)n;
+        ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
+        mixer.prefill(ctx, s, n, pos0, exact);
+        if (mixer_out_norm) ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
+        ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+        ctx.rmsnorm(s.x, post_norm, s.h2, nn, (uint32_t)hidden, eps);
+        ffn.prefill(ctx, s, n, hidden, exact);
+    }
+};
+
+uint64_t now_ns() {
+    return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
+               std::chrono::steady_clock::now().time_since_epoch())
+        .count();
+}
+
+}  // namespace
+
+struct EngineModel::Impl {
+    Matrix embedding, head_own;
+    bool tied = false;
+    CudaBuffer final_norm, x, logits, partial, tokens, tokens_mirror, pos_buf, status;
+    std::vector<Layer> layers;
+    PrefillScratch scratch;
+    CudaGraph decode_graph;
+    const Matrix &head() const { return tied ? embedding : head_own; }
+};
+
+GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, size_t capacity,
+                             const EngineOptions &opts) {
+    if (opts.shard_world != 1)
+        throw TuckmillError(ErrorCode::InvalidRequest, "row-sharded loading goes through the sharded engine entry point");
+    Plan p;
+    for (const LayerSpec &l : graph.layers) Layer::plan(l, graph, src, capacity, p);
+    p.weights += Matrix::plan(src, {graph.embedding});
+    if (graph.head != graph.embedding) p.weights += Matrix::plan(src, {graph.head});
+    p.weights_f32(vector_len(src, graph.final_norm));
+    p.scratch_f32(graph.hidden);              // x
+    p.scratch_f32(graph.vocab);               // logits
+    p.scratch_bytes(kArgmaxPartialBytes);     // argmax partials
+    p.scratch_bytes((capacity + 1) * 4);      // device token log
+    p.scratch_bytes((capacity + 1) * 4);      // its host-visible mirror
+    p.scratch_bytes(16);                      // device position
+    p.scratch_bytes(16);                      // status word
+    PrefillScratch::plan(graph, capacity, std::min<size_t>(opts.prefill_batch, capacity), p);
+    GpuAllocPlan out;
+    out.weights = p.weights;
+    out.state = p.state;
+    out.scratch = p.scratch;
+    return out;
+}
+
+std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext> ctx, ModelGraph graph,
+                                                    const WeightSource &src, size_t capacity,
+                                                    uint64_t expected_total, const EngineOptions &opts) {
+    if (capacity == 0 || capacity > (1u << 24))
+        throw TuckmillError(ErrorCode::InvalidRequest, "context capacity " + std::to_string(capacity) + " is out of range");
+    if (opts.prefill_batch == 0 || opts.prefill_batch > TM_CUDA_GEMM_MMA_MAX_BATCH)
+        throw TuckmillError(ErrorCode::InvalidRequest, "prefill batch must be 1.." + std::to_string(TM_CUDA_GEMM_MMA_MAX_BATCH));
+    std::unique_ptr<EngineModel> m(new EngineModel());
+    m->ctx_ = ctx;
+    m->opts_ = opts;
+    m->capacity_ = capacity;
+    m->plan_ = alloc_plan_with(graph, src, capacity, opts);
+    if (m->plan_.total() != expected_total)
+        throw TuckmillError(ErrorCode::Internal, "engine preflight " + std::to_string(m->plan_.total()) +
+                                                     " differs from the admitted total " + std::to_string(expected_total));
+    const uint64_t base = ctx->allocated_bytes();
+    m->impl_.reset(new Impl());
+    Impl &I = *m->impl_;
+    const CudaContext &c = *ctx;
+    I.layers.reserve(graph.layers.size());
+    for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity));
+    I.embedding = Matrix::load(c, src, {graph.embedding});
+    I.tied = graph.head == graph.embedding;
+    if (!I.tied) I.head_own = Matrix::load(c, src, {graph.head});
+    if (I.embedding.cols != graph.hidden || I.head().cols != graph.hidden || I.head().rows != graph.vocab)
+        throw TuckmillError(ErrorCode::UnsupportedArchitecture, "embedding / head shapes do not match the graph");
+    I.final_norm = vector(c, src, graph.final_norm);
+    I.x = zeros_f32(c, graph.hidden);
+    I.logits = zeros_f32(c, graph.vocab);
+    I.partial = c.zeros(kArgmaxPartialBytes);
+    I.tokens = c.zeros((capacity + 1) * 4);
+    I.tokens_mirror = c.zeros((capacity + 1) * 4, true);
+    I.pos_buf = c.zeros(16);
+    I.status = c.zeros(16, true);
+    I.scratch = PrefillScratch::alloc(c, graph, capacity, std::min<size_t>(opts.prefill_batch, capacity));
+    m->graph_ = std::move(graph);
+    const ModelGraph &g = m->graph_;
+
+    // The ledger must equal the preflight (crates/tuckcore/src/executor.rs:1571-1580).
+    const uint64_t held = ctx->allocated_bytes() - base;
+    if (held != m->plan_.total())
+        throw TuckmillError(ErrorCode::Internal, g.architecture + " GPU ledger holds " + std::to_string(held) +
+                                                     " but the preflight priced " + std::to_string(m->plan_.total()) +
+                                                     "; refusing an unaccounted allocation");
+
+    // Record the decode step once: embedding of the logged token at the device
+    // position, every layer, last norm + head, greedy token appended to the log,
+    // position advanced.  (One command buffer per step in the reference:
+    // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)
+    c.begin_group();
+    try {
+        c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
+                           g.embedding_scale, I.x);
+        for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps);
+        c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
+                          &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
+        c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity + 1,
+                     &I.tokens_mirror);
+        c.u32_add(I.pos_buf, 0, 1);
+    } catch (...) {
+        c.abort_group();
+        throw;
+    }
+    I.decode_graph = c.end_group_retain();
+    m->reset();
+    return m;
+}
+
+EngineModel::~EngineModel() {
+    if (ctx_) {
+        try {
+            ctx_->fence();
+        } catch (...) {
+        }
+    }
+}
+
+void EngineModel::reset() {
+    for (const Layer &L : impl_->layers) L.mixer.reset();
+    impl_->pos_buf.zero();
+    impl_->status.zero();
+    ctx_->fence();
+    pos_ = 0;
+}
+
+void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) {
+    if (n == 0) throw TuckmillError(ErrorCode::InvalidRequest, "prefill of zero tokens");
+    if (pos_ + n > capacity_)
+        throw TuckmillError(ErrorCode::ContextExceedsBudget, "position " + std::to_string(pos_ + n - 1) +
+                                                                 " exceeds KV capacity " + std::to_string(capacity_));
+    for (size_t i = 0; i < n; ++i)
+        if (tokens[i] >= graph_.vocab)
+            throw TuckmillError(ErrorCode::InvalidRequest, "token id " + std::to_string(tokens[i]) +
+                                                               " is outside the vocabulary (0.." +
+                                                               std::to_string(graph_.vocab) + ")");
+    Impl &I = *impl_;
+    const CudaContext &c = *ctx_;
+    I.tokens.upload(pos_ * 4, tokens, n * 4);
+    const size_t batch = std::min<size_t>(opts_.prefill_batch, capacity_);
+    for (size_t t0 = 0; t0 < n; t0 += batch) {
+        const size_t k = std::min(batch, n - t0);
+        const bool last = t0 + k == n;
+        const uint32_t pos0 = (uint32_t)(pos_ + t0);
+        c.grouped([&] {
+            c.rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
+                            graph_.embedding_scale, I.scratch.x);
+            for (const Layer &L : I.layers) L.prefill(c, I.scratch, k, pos0, graph_.hidden, graph_.eps, opts_.exact);
+            if (last && want_token) {
+                // Vocabulary projection for the last row only (engine/metal.rs:2610-2617).
+                c.copy_f32(I.scratch.x, (uint32_t)((k - 1) * graph_.hidden), I.x, 0, (uint32_t)graph_.hidden);
+                c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
+                                  &I.final_norm, graph_.eps, TM_CUDA_EPI_STORE);
+                c.argmax_f32(I.logits, (uint32_t)graph_.vocab, I.partial, I.tokens, pos0 + (uint32_t)k);
+            }
+        });
+    }
+    pos_ += n;
+    const uint32_t p32 = (uint32_t)pos_;
+    I.pos_buf.upload(0, &p32, 4);
+}
+
+uint32_t EngineModel::prefill_token() {
+    uint32_t t = 0;
+    impl_->tokens.download(pos_ * 4, &t, 4);
+    return t;
+}
+
+void EngineModel::step(uint32_t token) {
+    if (token >= graph_.vocab)
+        throw TuckmillError(ErrorCode::InvalidRequest, "token id " + std::to_string(token) +
+                                                           " is outside the vocabulary (0.." +
+                                                           std::to_string(graph_.vocab) + ")");
+    if (pos_ >= capacity_)
+        throw TuckmillError(ErrorCode::ContextExceedsBudget,
+                            "position " + std::to_string(pos_) + " exceeds KV capacity " + std::to_string(capacity_));
+    impl_->tokens.upload(pos_ * 4, &token, 4);
+    impl_->decode_graph.launch();
+    pos_ += 1;
+}
+
+void EngineModel::logits(float *out) { impl_->logits.download(0, out, graph_.vocab * 4); }
+
+EngineModel::Ticket EngineModel::submit_greedy() {
+    if (pos_ >= capacity_)
+        throw TuckmillError(ErrorCode::ContextExceedsBudget,
+                            "position " + std::to_string(pos_) + " exceeds KV capacity " + std::to_string(capacity_));
+    impl_->decode_graph.launch();
+    Ticket t;
+    t.dispatch = ctx_->committed();
+    t.slot = pos_ + 1;
+    pos_ += 1;
+    return t;
+}
+
+uint32_t EngineModel::collect_greedy(const Ticket &t) {
+    uint32_t tok = 0;
+    impl_->tokens_mirror.download_after(t.slot * 4, &tok, 4, t.dispatch);
+    return tok;
+}
+
+std::vector<uint32_t> EngineModel::generate(const uint32_t *prompt, size_t n_prompt, size_t max_new, bool ignore_eos,
+                                            GenerateStats *stats) {
+    std::vector<uint32_t> out;
+    if (max_new == 0) return out;
+    const uint64_t l0 = ctx_->kernel_launches(), d0 = ctx_->committed();
+    const uint64_t t_start = now_ns();
+    reset();
+    prefill(prompt, n_prompt, true);
+    uint32_t tok = prefill_token();
+    const uint64_t t_first = now_ns();
+    uint64_t t_last = t_first;
+    auto is_stop = [&](uint32_t t) {
+        return t == 0xFFFFFFFFu || (!ignore_eos && graph_.has_eos && t == graph_.eos_token_id);
+    };
+    out.push_back(tok);
+    if (tok == 0xFFFFFFFFu)
+        throw TuckmillError(ErrorCode::Internal, "every logit was NaN; refusing to guess a token");
+    if (!is_stop(tok)) {
+        // Step i+1 is submitted before step i is collected (executor.rs:1080-1087):
+        // the device already has token i in its log.
+        std::vector<Ticket> inflight;
+        size_t submitted = 0;
+        const size_t want = max_new - 1;
+        auto can_submit = [&] { return submitted < want && pos_ < capacity_; };
+        if (can_submit()) { inflight.push_back(submit_greedy()); ++submitted; }
+        while (!inflight.empty()) {
+            if (can_submit()) { inflight.push_back(submit_greedy()); ++submitted; }
+            const Ticket t = inflight.front();
+            inflight.erase(inflight.begin());
+            tok = collect_greedy(t);
+            t_last = now_ns();
+            if (tok == 0xFFFFFFFFu)
+                throw TuckmillError(ErrorCode::Internal, "every logit was NaN; refusing to guess a token");
+            out.push_back(tok);
+            if (is_stop(tok)) break;
+        }
+        ctx_->fence();
+    }
+    uint32_t st = 0;
+    impl_->status.download(0, &st, 4);
+    if (st != 0) throw TuckmillError(ErrorCode::Internal, "a decode step ran past the KV capacity on the device");
+    if (stats) {
+        stats->ttft_ns = t_first - t_start;
+        stats->decode_span_ns = t_last - t_first;
+        stats->prompt_tokens = n_prompt;
+        stats->generated = out.size();
+        stats->kernel_launches = ctx_->kernel_launches() - l0;
+        stats->dispatches = ctx_->committed() - d0;
+        stats->h2d_bytes = n_prompt * 4 + 4;
+        stats->d2h_bytes = out.size() * 4 + 4;
+    }
+    return out;
+}
+
+}  // namespace tuckmill

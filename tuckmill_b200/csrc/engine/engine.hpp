@@ -1,0 +1,108 @@
+// The unified layer engine on CUDA: executes a typed ModelGraph with the
+// operators of the tm_cuda C ABI.  Host-side counterpart of
+// crates/tuckcore/src/engine/metal.rs (Matrix :107-226, Plan :254-272,
+// PrefillScratch :365-425, SwiGluBlock :431-535, AttentionBlock :989-1364,
+// Layer :1379-1525, alloc_plan_with :1729-1758, EngineModel :1774-2677), keeping
+// its contracts -- exact byte ledger priced before any allocation, one dispatch
+// per step, last-position-only vocabulary projection, device-side greedy with
+// a pipelined host read -- re-designed for a B200:
+//   * q|k|v and gate|up are stored as one row-concatenated matrix each, so a
+//     decode layer is 5 launches (fused norm / activation / residual around the
+//     GEMVs) instead of ~17;
+//   * the position and the token log live on the device, so ONE recorded CUDA
+//     graph is replayed for every decode step;
+//   * prefill chunks are 512 tokens through the tensor-core GEMM.
+#pragma once
+#include <memory>
+#include <vector>
+
+#include "cuda.hpp"
+#include "gguf.hpp"
+#include "graph.hpp"
+
+namespace tuckmill {
+
+constexpr uint32_t kPrefillBatchDefault = 512;  // reference PREFILL_BATCH is 128 (engine/metal.rs:25)
+constexpr uint32_t kArgmaxPartialBytes = 512;
+constexpr size_t kStagingChunkBytes = 4u << 20;  // crates/tuckcore/src/qwen35_gpu.rs:1176
+
+struct EngineOptions {
+    uint32_t prefill_batch = kPrefillBatchDefault;
+    bool exact = false;  // batched projections keep the GEMV's per-row arithmetic (no tensor cores)
+    // Output-row split of every projection across `world` devices (rank owns
+    // rows [rank*N/world, (rank+1)*N/world)); 1 = single device.
+    uint32_t shard_rank = 0, shard_world = 1;
+};
+
+// Exact device bytes by class (crates/tuckcore/src/qwen35_gpu.rs:1181-1193).
+struct GpuAllocPlan {
+    uint64_t weights = 0, state = 0, scratch = 0;
+    uint64_t total() const { return weights + state + scratch; }
+};
+
+GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, size_t capacity,
+                             const EngineOptions &opts);
+
+struct GenerateStats {
+    uint64_t ttft_ns = 0;         // request start -> first generated token on the host
+    uint64_t decode_span_ns = 0;  // first -> last generated token (reference tok/s span)
+    uint64_t prompt_tokens = 0, generated = 0;
+    uint64_t kernel_launches = 0, dispatches = 0;
+    uint64_t h2d_bytes = 0, d2h_bytes = 0;
+};
+
+class EngineModel {
+public:
+    // Prices the model (alloc_plan_with), allocates exactly that, uploads and
+    // repacks every matrix, records the decode graph.  `expected_total` is the
+    // preflight total the caller admitted; a ledger that differs is refused.
+    static std::unique_ptr<EngineModel> load_with(std::shared_ptr<CudaContext> ctx, ModelGraph graph,
+                                                  const WeightSource &src, size_t capacity,
+                                                  uint64_t expected_total, const EngineOptions &opts);
+    ~EngineModel();
+
+    const ModelGraph &graph() const { return graph_; }
+    size_t capacity() const { return capacity_; }
+    size_t position() const { return pos_; }
+    uint64_t allocated_bytes() const { return ctx_->allocated_bytes(); }
+    const GpuAllocPlan &plan() const { return plan_; }
+    CudaContext &context() { return *ctx_; }
+
+    // Start a new sequence at position 0 (KV planes zero-filled on the device).
+    void reset();
+    // Feed `n` prompt tokens at the current position in chunks; with
+    // `want_token` the last chunk also projects the last row onto the
+    // vocabulary and writes its greedy token into the token log.
+    void prefill(const uint32_t *tokens, size_t n, bool want_token);
+    // One decode step for `token` at the current position; returns after the
+    // logits are on the device (download with `logits`).
+    void step(uint32_t token);
+    void logits(float *out);
+    // Device-greedy pipeline: `submit_greedy` replays the decode graph (the
+    // token comes from the device-side log), `collect_greedy` reads the token
+    // produced by the submit that returned `ticket`, without waiting for later
+    // submits.
+    struct Ticket { uint64_t dispatch = 0; size_t slot = 0; };
+    Ticket submit_greedy();
+    uint32_t collect_greedy(const Ticket &t);
+    // Token the last prefill(want_token) chose (blocking read).
+    uint32_t prefill_token();
+    // The reference's run_session loop (crates/tuckcore/src/executor.rs:870-1125)
+    // for a greedy request: chunked prefill, then decode with step i+1 submitted
+    // before step i is collected.  Stops at `max_new` tokens, at EOS unless
+    // `ignore_eos`, or at capacity.
+    std::vector<uint32_t> generate(const uint32_t *prompt, size_t n_prompt, size_t max_new, bool ignore_eos,
+                                   GenerateStats *stats);
+
+private:
+    struct Impl;
+    EngineModel() = default;
+    std::shared_ptr<CudaContext> ctx_;
+    ModelGraph graph_;
+    EngineOptions opts_;
+    GpuAllocPlan plan_;
+    size_t capacity_ = 0, pos_ = 0;
+    std::unique_ptr<Impl> impl_;
+};
+
+}  // namespace tuckmill

@@ -96,9 +96,11 @@ int tm_check_packed(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, ui
         return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
                        "Q8_0 geometry %u x %u: rows and cols must be positive, cols a multiple of 32",
                        rows, cols);
-    const size_t need = tm_cuda_q8_0_packed_bytes(rows, cols);
-    int rc = tm_check(ctx, w, need, "weight", err, err_cap);
-    if (rc != TM_CUDA_OK) return rc;
+    if (!w || ctx->live.find(w) == ctx->live.end())
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "weight buffer does not belong to this context");
+    if (!w->parent && w->len < tm_cuda_q8_0_packed_bytes(rows, cols))
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "weight buffer holds %zu bytes, needs %zu",
+                       w->len, tm_cuda_q8_0_packed_bytes(rows, cols));
     if (w->layout != TM_LAYOUT_Q8_0_PACKED || w->rows != rows || w->cols != cols)
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
                        "weight buffer is not a packed %u x %u Q8_0 matrix (pack it with "
@@ -234,9 +236,9 @@ tm_cuda_buffer *tm_cuda_buffer_view(tm_cuda_ctx *ctx, tm_cuda_buffer *parent, si
         tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "parent buffer does not belong to this context");
         return nullptr;
     }
-    if (len == 0 || off % 256 != 0 || off > parent->len || len > parent->len - off) {
+    if (len == 0 || off % 16 != 0 || off > parent->len || len > parent->len - off) {
         tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
-                "view [%zu, +%zu) of a %zu-byte buffer (offset must be 256-byte aligned)", off, len,
+                "view [%zu, +%zu) of a %zu-byte buffer (offset must be 16-byte aligned)", off, len,
                 parent->len);
         return nullptr;
     }
@@ -511,6 +513,18 @@ int tm_cuda_profile_read(tm_cuda_ctx *ctx, uint32_t index, char *name, size_t na
 uint64_t tm_cuda_allocated_bytes(const tm_cuda_ctx *ctx) { return ctx ? ctx->allocated.load() : 0; }
 uint64_t tm_cuda_in_flight_bytes(const tm_cuda_ctx *) { return 0; }
 uint64_t tm_cuda_kernel_launches(const tm_cuda_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
+int tm_cuda_device_memory(tm_cuda_ctx *ctx, uint64_t *free_bytes, uint64_t *total_bytes) {
+    if (!ctx) return TM_CUDA_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    size_t f = 0, t = 0;
+    if (cudaSetDevice(ctx->device) != cudaSuccess || cudaMemGetInfo(&f, &t) != cudaSuccess) {
+        cudaGetLastError();
+        return TM_CUDA_ERR_INTERNAL;
+    }
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return TM_CUDA_OK;
+}
 void *tm_cuda_stream(tm_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
 }  // extern "C"

@@ -29,6 +29,8 @@ struct tm_cuda_buffer {
     uint32_t views = 0;                // live views of this buffer
     tm_layout layout = TM_LAYOUT_OPAQUE;
     uint32_t rows = 0, cols = 0;       // geometry of a packed matrix
+    const unsigned char *qp = nullptr; // packed: int8 quant plane of row 0
+    const unsigned char *dp = nullptr; // packed: f16 scale plane of row 0
 };
 
 struct tm_cuda_graph {

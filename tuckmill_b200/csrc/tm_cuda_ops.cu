@@ -104,7 +104,8 @@ __global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const float *x
 }
 __global__ void __launch_bounds__(kThreads) argmax_final_kernel(const float *pv, const uint32_t *pi,
                                                                 uint32_t *out, uint32_t out_index,
-                                                                const uint32_t *pos, uint32_t out_cap) {
+                                                                const uint32_t *pos, uint32_t out_cap,
+                                                                uint32_t *mirror) {
     __shared__ float tv[kWarps];
     __shared__ uint32_t ti[kWarps];
     float v = threadIdx.x < kArgmaxGroups ? pv[threadIdx.x] : -INFINITY;
@@ -112,7 +113,10 @@ __global__ void __launch_bounds__(kThreads) argmax_final_kernel(const float *pv,
     argmax_block(v, i, tv, ti);
     if (threadIdx.x == 0) {
         const uint32_t slot = pos ? out_index + *pos : out_index;
-        if (slot < out_cap) out[slot] = i;
+        if (slot < out_cap) {
+            out[slot] = i;
+            if (mirror) mirror[slot] = i;
+        }
     }
 }
 
@@ -417,7 +421,7 @@ int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *wei
 
 static int argmax_common(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cuda_buffer *partial,
                          tm_cuda_buffer *out, uint32_t out_index, const uint32_t *pos,
-                         uint32_t out_cap, char *err, size_t err_cap) {
+                         uint32_t out_cap, uint32_t *mirror, char *err, size_t err_cap) {
     if (n == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "argmax over zero elements");
     TM_CHECK_BUF(x, (size_t)n * 4, "logits");
     TM_CHECK_BUF(partial, 512, "argmax partials");
@@ -426,7 +430,7 @@ static int argmax_common(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cud
     uint32_t *pi = (uint32_t *)(partial->dev + 256);
     argmax_partial_kernel<<<kArgmaxGroups, kThreads, 0, ctx->stream>>>((const float *)x->dev, pv, pi, n);
     argmax_final_kernel<<<1, kThreads, 0, ctx->stream>>>(pv, pi, (uint32_t *)out->dev, out_index, pos,
-                                                         out_cap);
+                                                         out_cap, mirror);
     TM_OP_END(2);
 }
 
@@ -434,20 +438,21 @@ int tm_cuda_argmax_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cuda_
                        tm_cuda_buffer *out, uint32_t out_index, char *err, size_t err_cap) {
     TM_ENTER();
     TM_CHECK_BUF(out, ((size_t)out_index + 1) * 4, "argmax output");
-    return argmax_common(ctx, x, n, partial, out, out_index, nullptr, (uint32_t)(out->len / 4), err,
-                         err_cap);
+    return argmax_common(ctx, x, n, partial, out, out_index, nullptr, (uint32_t)(out->len / 4),
+                         nullptr, err, err_cap);
 }
 
 int tm_cuda_argmax_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n,
                            tm_cuda_buffer *partial, tm_cuda_buffer *out, uint32_t base,
                            tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
-                           char *err, size_t err_cap) {
+                           tm_cuda_buffer *mirror, char *err, size_t err_cap) {
     TM_ENTER();
+    if (mirror) TM_CHECK_BUF(mirror, (size_t)out_cap * 4, "token log mirror");
     if (out_cap == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "empty token log");
     TM_CHECK_BUF(out, (size_t)out_cap * 4, "token log");
     TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
     return argmax_common(ctx, x, n, partial, out, base, (const uint32_t *)pos_buf->dev + pos_index,
-                         out_cap, err, err_cap);
+                         out_cap, mirror ? (uint32_t *)mirror->dev : nullptr, err, err_cap);
 }
 
 static int rope_common(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,

@@ -446,6 +446,21 @@ __global__ void q8_row_indirect_kernel(const signed char *q, const __half *d, ui
     dequant_row(q, d, cols, row, scale, out);
 }
 
+// out[t][c] = dequant(row ids[first + t])[c] (* scale), t < n; ids outside the table write zeros.
+__global__ void q8_rows_gather_kernel(const signed char *q, const __half *d, uint32_t rows, uint32_t cols,
+                                      const uint32_t *ids, uint32_t first, float scale, float *out) {
+    const uint32_t t = blockIdx.y, nb = cols / 32u;
+    const uint32_t id = ids[first + t];
+    for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
+        float v = 0.0f;
+        if (id < rows) {
+            v = __half2float(d[(size_t)id * nb + c / 32u]) * (float)q[(size_t)id * cols + c];
+            if (scale != 0.0f) v *= scale;
+        }
+        out[(size_t)t * cols + c] = v;
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -481,7 +496,37 @@ int tm_cuda_q8_0_pack(tm_cuda_ctx *ctx, tm_cuda_buffer *dst, uint32_t rows, uint
     dst->layout = TM_LAYOUT_Q8_0_PACKED;
     dst->rows = rows;
     dst->cols = cols;
+    dst->qp = dst->dev;
+    dst->dp = dst->dev + tm_q8_qplane_bytes(rows, cols);
     TM_OP_END(1);
+}
+
+tm_cuda_buffer *tm_cuda_q8_0_row_view(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows,
+                                      uint32_t cols, uint32_t row0, uint32_t nrows, char *err,
+                                      size_t err_cap) {
+    if (!ctx) {
+        tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null context");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (tm_check_packed(ctx, w, rows, cols, err, err_cap) != TM_CUDA_OK) return nullptr;
+    if (nrows == 0 || row0 >= rows || nrows > rows - row0) {
+        tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "row view [%u, +%u) of a %u-row matrix", row0, nrows, rows);
+        return nullptr;
+    }
+    tm_cuda_buffer *b = new tm_cuda_buffer();
+    b->owner = ctx;
+    b->parent = w;
+    b->dev = w->dev;
+    b->len = w->len;
+    b->layout = TM_LAYOUT_Q8_0_PACKED;
+    b->rows = nrows;
+    b->cols = cols;
+    b->qp = w->qp + (size_t)row0 * cols;
+    b->dp = w->dp + (size_t)row0 * (cols / 32) * 2;
+    w->views += 1;
+    ctx->live.insert(b);
+    return b;
 }
 
 int tm_cuda_q8_0_unpack(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t rows, uint32_t cols,
@@ -497,8 +542,7 @@ int tm_cuda_q8_0_unpack(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t rows, ui
     const size_t total = (size_t)nrows * (cols / 32);
     const int grid = (int)((total + 255) / 256 > 65535 ? 65535 : (total + 255) / 256);
     q8_unpack_kernel<<<grid, 256, 0, ctx->stream>>>(
-        raw->dev + raw_off, (const signed char *)src->dev,
-        (const __half *)(src->dev + tm_q8_qplane_bytes(rows, cols)), cols, row0, nrows);
+        raw->dev + raw_off, (const signed char *)src->qp, (const __half *)src->dp, cols, row0, nrows);
     TM_OP_END(1);
 }
 
@@ -520,8 +564,8 @@ static int gemv_common(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, t
     if (prologue == TM_CUDA_PRO_SILU_MUL || prologue == TM_CUDA_PRO_GELU_MUL)
         TM_CHECK_BUF(pro, (size_t)batch * cols * 4, "gate multiplicand");
     gemv_args a;
-    a.q = (const signed char *)w->dev;
-    a.d = (const __half *)(w->dev + tm_q8_qplane_bytes(rows, cols));
+    a.q = (const signed char *)w->qp;
+    a.d = (const __half *)w->dp;
     a.x = (const float *)x->dev + x_off;
     a.y = (float *)y->dev + y_off;
     a.pro = pro ? (const float *)pro->dev : nullptr;
@@ -573,8 +617,7 @@ int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *ou
     TM_CHECK_BUF(out, ((size_t)out_off + cols) * 4, "row output");
     TM_OP_BEGIN("q8_0_row");
     q8_row_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(
-        (const signed char *)w->dev, (const __half *)(w->dev + tm_q8_qplane_bytes(w->rows, cols)),
-        cols, row, (float *)out->dev + out_off);
+        (const signed char *)w->qp, (const __half *)w->dp, cols, row, (float *)out->dev + out_off);
     TM_OP_END(1);
 }
 
@@ -593,7 +636,7 @@ static int row_indirect(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint
     }
     TM_OP_BEGIN("row_indirect");
     q8_row_indirect_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(
-        (const signed char *)w->dev, (const __half *)(w->dev + tm_q8_qplane_bytes(rows, cols)), rows,
+        (const signed char *)w->qp, (const __half *)w->dp, rows,
         cols, (const uint32_t *)ids->dev, slot, pos, bias, (uint32_t)(ids->len / 4), scale,
         (float *)out->dev);
     TM_OP_END(1);
@@ -607,6 +650,22 @@ int tm_cuda_row_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t type_
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
                        "row_indirect supports Q8_0 (type 8) matrices; got type %u", type_id);
     return row_indirect(ctx, w, rows, cols, ids, slot, nullptr, 0, 0, 0.0f, out, err, err_cap);
+}
+
+int tm_cuda_rows_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                              tm_cuda_buffer *ids, uint32_t first, uint32_t n, float scale,
+                              tm_cuda_buffer *out, char *err, size_t err_cap) {
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (n == 0 || n > 65535u) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "row count %u outside 1..65535", n);
+    TM_CHECK_BUF(ids, ((size_t)first + n) * 4, "token ids");
+    TM_CHECK_BUF(out, (size_t)n * cols * 4, "rows output");
+    TM_OP_BEGIN("rows_indirect");
+    q8_rows_gather_kernel<<<dim3((cols + 255) / 256, n), 256, 0, ctx->stream>>>(
+        (const signed char *)w->qp, (const __half *)w->dp, rows, cols, (const uint32_t *)ids->dev, first,
+        scale, (float *)out->dev);
+    TM_OP_END(1);
 }
 
 int tm_cuda_row_indirect_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,

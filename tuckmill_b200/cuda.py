@@ -48,7 +48,7 @@ _OPS = {
     "cast_f16_f32": [_P, _P, _P, _U32],
     "cast_f32_f16": [_P, _P, _P, _U32],
     "argmax_f32": [_P, _P, _U32, _P, _P, _U32],
-    "argmax_f32_dev": [_P, _P, _U32, _P, _P, _U32, _P, _U32, _U32],
+    "argmax_f32_dev": [_P, _P, _U32, _P, _P, _U32, _P, _U32, _U32, _P],
     "rmsnorm_f32": [_P, _P, _P, _P, _U32, _U32, _F],
     "silu_mul_f32": [_P, _P, _P, _P, _U32],
     "gelu_tanh_mul_f32": [_P, _P, _P, _P, _U32],
@@ -60,6 +60,7 @@ _OPS = {
     "q8_0_gemv_fused": [_P, _P, _P, _P, _U32, _U32, _I, _P, _F, _I],
     "q8_0_row_f32": [_P, _P, _P, _U32, _U32, _U32],
     "row_indirect_f32": [_P, _P, _U32, _U32, _U32, _P, _U32, _P],
+    "rows_indirect_f32": [_P, _P, _U32, _U32, _P, _U32, _U32, _F, _P],
     "row_indirect_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
     "begin_group": [_P],
     "end_group": [_P],
@@ -101,6 +102,8 @@ def load_library() -> C.CDLL:
     L.tm_cuda_buffer_view.restype = _P
     L.tm_cuda_buffer_view.argtypes = [_P, _P, _SZ, _SZ] + _ERR
     L.tm_cuda_buffer_free.argtypes = [_P, _P]
+    L.tm_cuda_q8_0_row_view.restype = _P
+    L.tm_cuda_q8_0_row_view.argtypes = [_P, _P, _U32, _U32, _U32, _U32] + _ERR
     L.tm_cuda_buffer_contents.restype = _P
     L.tm_cuda_buffer_contents.argtypes = [_P, _P]
     L.tm_cuda_buffer_device_ptr.restype = _P
@@ -273,6 +276,13 @@ class CudaContext:
         self.fence()
         stage.free()
         return dst
+
+    def q8_0_row_view(self, w: CudaBuffer, rows: int, cols: int, row0: int, nrows: int) -> CudaBuffer:
+        err = C.create_string_buffer(256)
+        h = self._l.tm_cuda_q8_0_row_view(self.handle, w.handle, rows, cols, row0, nrows, err, 256)
+        if not h:
+            raise CudaError(-4, err.value.decode())
+        return CudaBuffer(self, h, parent=w)
 
     def q8_0_unpack(self, w: CudaBuffer, rows: int, cols: int) -> np.ndarray:
         raw = self.buffer(rows * (cols // 32) * 34)

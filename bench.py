@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Headline benchmark: Q8_0 greedy decode on the Qwen3-0.6B-shaped decoder.
+
+One "step" is one request of the reference's standard workload shape
+(benchmarks/standard-v1.json:10-12: 512-token prompt, 256 greedy tokens, batch
+1) on seeded synthetic Q8_0 weights.  Rank r of an N-GPU run serves its own
+request on its own GPU (replicas, weak scaling, no data-path collective).
+
+  value       decode tok/s with everything resident in HBM: the recorded decode
+              graph replayed 255 times per request, CUDA events on the
+              engine's stream, summed over ranks
+  e2e         the same metric through the engine's public generate() call with
+              host buffers: prompt ids uploaded, every token read back by the
+              host (reference definition: (generated-1) / first->last token span)
+  roofline    the Q8_0 GEMV launches of one decode step timed one dispatch each
+              with CUDA events: algorithmic bytes / time against the measured
+              HBM copy bandwidth
+  cpu_baseline  the CPU oracle (a port of the reference's scalar executor) on a
+              bounded sample of the same workload
+
+`--impl reference` times that CPU port alone on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from tuckmill_b200 import testing as T  # noqa: E402
+
+WORKLOADS = {
+    "qwen3-0.6b": (T.QWEN3_0_6B, 512, 256),
+    "gemma3-1b": (T.GEMMA3_1B, 512, 256),
+    "tiny-qwen3": (T.TINY_QWEN3, 32, 16),
+}
+METRIC = "q8_0_decode_tok_s"
+
+
+def artifact(name: str, seed: int = 0) -> Path:
+    shape = WORKLOADS[name][0]
+    d = Path(os.environ.get("TUCKMILL_BENCH_DIR", "/dev/shm" if os.path.isdir("/dev/shm") else "/tmp"))
+    path = d / f"tuckmill_{name}_seed{seed}.gguf"
+    marker = path.with_suffix(".done")
+    if not marker.exists():
+        tmp = path.with_suffix(f".tmp{os.getpid()}")
+        T.write_gguf(tmp, shape, seed=seed)
+        os.replace(tmp, path)
+        marker.write_text("ok")
+    return path
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle reasons sampled during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                self.samples.append([c.strip() for c in out.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            if len(s) < 6:
+                continue
+            try:
+                mhz.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def cpu_leg(name: str, threads: int | None, prompt_n: int, decode_n: int, seed: int):
+    """Bounded sample of the workload on the CPU oracle: batched prefill of
+    `prompt_n` tokens, then `decode_n` one-token steps.  Returns decode tok/s."""
+    import oracle as O
+
+    O.build()
+    shape = WORKLOADS[name][0]
+    path = artifact(name, seed)
+    m = O.Model(path, kv_f16=True, threads=threads)
+    m.reset(prompt_n + decode_n + 1)
+    prompt = T.token_ids(seed, prompt_n, shape.vocab)
+    logits = m.forward(prompt)
+    tok = O.argmax(logits)
+    t0 = time.perf_counter()
+    for _ in range(decode_n):
+        tok = O.argmax(m.forward([tok]))
+    dt = time.perf_counter() - t0
+    return decode_n / dt, m.threads, f"{prompt_n} prompt + {decode_n} decode tokens of the {name} workload"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    shape, prompt_n, decode_n = WORKLOADS[args.workload]
+    vals = []
+    t_all = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        v, threads, sample = cpu_leg(args.workload, None, 8, 12, args.seed)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * (time.perf_counter() - t_all) / max(1, args.steps + args.warmup),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1,
+                   "kv": "f16", "weights": "Q8_0 random-init, seed %d" % args.seed},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def gemv_roofline(eng, shape, hbm_gbs):
+    """Time the decode step's operators one dispatch each and attribute."""
+    from tuckmill_b200 import engine as E  # noqa: F401
+
+    eng.reset()
+    eng.prefill(T.token_ids(1, 64, shape.vocab), want_token=True)
+    eng.decode_ungrouped(3)
+    eng.fence()
+    eng.profile(True)
+    steps = 8
+    eng.decode_ungrouped(steps)
+    eng.fence()
+    rows = {n: (ns, c) for n, ns, c in eng.profile_rows()}
+    eng.profile(False)
+    gemv_ns = sum(ns for n, (ns, c) in rows.items() if n.startswith("q8_0_gemv"))
+    gemv_launches = sum(c for n, (ns, c) in rows.items() if n.startswith("q8_0_gemv"))
+    total_ns = sum(ns for ns, c in rows.values())
+    # algorithmic bytes of the GEMV launches of one step: weights once, f32 in, f32 out
+    per_step = shape.decode_weight_bytes()
+    act = 0
+    for _, o, i in shape.matrices(0):
+        act += 4 * i + 4 * o
+    per_step += act * shape.layers + 4 * shape.hidden + 4 * shape.vocab
+    achieved = per_step * steps / gemv_ns  # bytes/ns == GB/s
+    return {
+        "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+        "traffic": None, "kernel": "q8_gemv_kernel", "launches_per_step": gemv_launches / steps,
+        "bytes_per_launch": per_step / (gemv_launches / steps), "us_per_launch": gemv_ns / gemv_launches / 1e3,
+        "gemv_share_of_step": gemv_ns / total_ns,
+        "by_operator_us_per_step": {n: round(ns / steps / 1e3, 2) for n, (ns, c) in sorted(rows.items())},
+    }
+
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+
+    from tuckmill_b200 import engine as E
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    shape, prompt_n, decode_n = WORKLOADS[args.workload]
+    if rank == 0:
+        path = artifact(args.workload, args.seed)
+    if world > 1:
+        dist.barrier()
+    path = artifact(args.workload, args.seed)
+    context = prompt_n + decode_n + 16
+    eng = E.Engine(path, context=context, device=local)
+    stream = torch.cuda.ExternalStream(eng.stream(), device=local)
+    prompt = T.token_ids(args.seed + 1000 * rank, prompt_n, shape.vocab)
+    hbm_gbs, peak_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        eng.fence()
+        torch.cuda.synchronize()
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e.record()
+        return e
+
+    # ---- device-resident arm: prefill, then the decode graph replayed ----
+    def session():
+        eng.reset()
+        e0 = ev()
+        eng.prefill(prompt, want_token=True)
+        e1 = ev()
+        eng.decode_steps(decode_n - 1)
+        e2 = ev()
+        return e0, e1, e2
+
+    for _ in range(args.warmup):
+        session()
+    barrier()
+    launches0 = _launches(eng)
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        evs = [session() for _ in range(args.steps)]
+        barrier()
+        wall = time.perf_counter() - t0
+    launches = _launches(eng) - launches0
+    prefill_ms = sum(a.elapsed_time(b) for a, b, c in evs)
+    decode_ms = sum(b.elapsed_time(c) for a, b, c in evs)
+    total_ms = prefill_ms + decode_ms
+    tokens = eng_tokens = None
+
+    # ---- end-to-end arm: the public generate() call with host buffers ----
+    for _ in range(max(1, args.warmup // 2)):
+        eng.generate(prompt, decode_n)
+    barrier()
+    spans, ttfts, gen = 0, 0, 0
+    for _ in range(args.steps):
+        tokens, st = eng.generate(prompt, decode_n)
+        spans += st.decode_span_ns
+        ttfts += st.ttft_ns
+        gen += st.generated - 1
+        h2d, d2h = st.h2d_bytes, st.d2h_bytes
+    barrier()
+
+    vals = torch.tensor([decode_ms, total_ms, prefill_ms, spans / 1e6, ttfts / 1e6], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    decode_ms, total_ms, prefill_ms, span_ms, ttft_ms = vals.tolist()
+    dec_tokens = args.steps * (decode_n - 1)
+    value = world * dec_tokens / (decode_ms / 1e3)
+    e2e = world * gen / (span_ms / 1e3)
+
+    if rank == 0:
+        roof = gemv_roofline(eng, shape, hbm_gbs)
+        roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"
+        step_bytes = shape.decode_weight_bytes()
+        cpu = None
+        if not args.no_cpu:
+            v, threads, sample = cpu_leg(args.workload, None, 8, 12 if shape.layers > 8 else 64, args.seed)
+            cpu = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample}
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8 x s8 -> s32 tensor-core products, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1,
+                       "kv": "f16", "weights": "Q8_0 random-init, seed %d" % args.seed,
+                       "parallelism": f"replicas x{world}" if world > 1 else "single",
+                       "l2": "per-token weight stream %.0f MB exceeds the 126 MB L2" % (step_bytes / 1e6)},
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "ttft_ms": ttft_ms / args.steps, "prefill_tok_s": world * args.steps * prompt_n / (ttft_ms / 1e3)},
+            "gpu_launches": int(launches),
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "clocks": clocks.summary(),
+            "prefill_tok_s": world * args.steps * prompt_n / (prefill_ms / 1e3),
+            "decode_us_per_token": 1e3 * decode_ms / dec_tokens,
+            "decode_step_hbm_frac": step_bytes / (1e3 * decode_ms / dec_tokens * 1e3) / hbm_gbs,
+            "wall_s": wall,
+            "tokens_head": [int(t) for t in tokens[:8]],
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _launches(eng) -> int:
+    from tuckmill_b200 import cuda as C
+
+    return int(C.load_library().tm_cuda_kernel_launches(eng.cuda_ctx()))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--workload", default="qwen3-0.6b", choices=sorted(WORKLOADS))
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

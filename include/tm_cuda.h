@@ -267,7 +267,7 @@ int tm_cuda_qwen35_kv_store_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *k_src,
                                       uint32_t head_dim, uint32_t kv_heads, uint32_t n, char *err,
                                       size_t err_cap);
 /* tm_metal.h:265 ..._attention_f16: causal GQA attention of one query row
- * over keys 0..=pos of a packed f16 cache; scratch is heads*cap f32. */
+ * over keys 0..=pos of a packed f16 cache (`scratch`: see the chunk form). */
 int tm_cuda_qwen35_attention_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache,
                                  tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
                                  tm_cuda_buffer *scratch, uint32_t heads, uint32_t pos,
@@ -275,7 +275,9 @@ int tm_cuda_qwen35_attention_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                                  char *err, size_t err_cap);
 /* tm_metal.h:367 ..._attention_f16_chunk: query row t attends keys
  * [start, pos0+t] where start = seq > window ? seq - window : 0 (window 0 =
- * full causal); scratch is n*heads*cap f32. */
+ * full causal).  The reference's scratch is n*heads*cap f32 of scores; this
+ * implementation streams key blocks through registers and only requires
+ * `scratch` to be a valid buffer (>= 4 bytes). */
 int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
                                        tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache,
                                        tm_cuda_buffer *out, tm_cuda_buffer *scratch,
@@ -289,7 +291,13 @@ int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
  * attention for ONE token -- the sequence of tm_cuda_rmsnorm_f32 x2,
  * tm_cuda_qwen35_rope_partial, tm_cuda_qwen35_kv_store_f16 and
  * tm_cuda_qwen35_attention_f16_chunk(n = 1) with the same arithmetic.  A
- * position >= cap writes nothing and sets bit 0 of status[0] (u32, shared). */
+ * position >= cap writes nothing and sets bit 0 of status[0] (u32, shared).
+ * `scratch` holds the per-key-block partial results and arrival counters
+ * (tm_cuda_attention_decode_scratch_bytes, zero-filled once by the caller;
+ * the kernel leaves the counters at zero).  Calls sharing one scratch buffer
+ * must be ordered on the stream. */
+size_t tm_cuda_attention_decode_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                                              uint32_t cap);
 int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
                                  tm_cuda_buffer *v, tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm,
                                  tm_cuda_buffer *inv_freq, tm_cuda_buffer *k_cache,

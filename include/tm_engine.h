@@ -86,6 +86,11 @@ int tm_engine_generate(tm_engine *e, const uint32_t *prompt, uint32_t n_prompt, 
  * for kernel-only timing; the caller brackets it with events on the stream. */
 int tm_engine_decode_steps(tm_engine *e, uint32_t steps, char *err, size_t err_cap);
 
+/* The same steps encoded operator by operator (one dispatch per operator), so
+ * the device context's profile table (tm_cuda_profile_set / _read) attributes
+ * GPU time per operator: crates/tuckcore/src/engine/metal.rs:1964-1968. */
+int tm_engine_decode_ungrouped(tm_engine *e, uint32_t steps, char *err, size_t err_cap);
+
 /* Stand-alone admission arithmetic (R + U + H <= B) for a GGUF at a context,
  * without touching a device: fills the budget fields of `out`; returns
  * TM_ENGINE_*_EXCEEDS_BUDGET when the plan does not fit. */

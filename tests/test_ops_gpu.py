@@ -123,9 +123,9 @@ def test_rope_and_kv_store(ctx, oracle):
         ctx.qwen35_kv_store_chunk(kb, vb, kc, vc, cap - 1, cap, hd, nkv, n)
 
 
-@pytest.mark.parametrize("heads,kvh,hd,window", [(4, 2, 32, 0), (16, 8, 128, 0), (4, 1, 256, 8), (4, 1, 256, 0), (6, 2, 96, 5)])
+@pytest.mark.parametrize("heads,kvh,hd,window", [(4, 2, 32, 0), (16, 8, 128, 0), (4, 1, 256, 8), (4, 1, 256, 0), (6, 2, 96, 5), (12, 2, 64, 0)])
 def test_attention_chunk_matches_scalar_executor(ctx, oracle, heads, kvh, hd, window):
-    cap, pos0, n = 40, 17, 6
+    cap, pos0, n = 90, 57, 6
     group = heads // kvh
     kf = T.activations(0, 10, kvh * cap * hd).astype(np.float16).reshape(kvh, cap, hd)
     vf = T.activations(0, 11, kvh * cap * hd).astype(np.float16).reshape(kvh, cap, hd)
@@ -148,12 +148,13 @@ def test_attention_chunk_matches_scalar_executor(ctx, oracle, heads, kvh, hd, wi
         np.testing.assert_array_equal(f32(o1, heads * hd).reshape(heads, hd), got[0])
 
 
-@pytest.mark.parametrize("heads,kvh,hd,window", [(16, 8, 128, 0), (4, 1, 256, 6)])
-def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh, hd, window):
+@pytest.mark.parametrize("heads,kvh,hd,window,cap,steps", [(16, 8, 128, 0, 24, 10), (4, 1, 256, 6, 24, 10),
+                                                            (4, 2, 32, 0, 100, 70), (12, 2, 64, 40, 100, 90)])
+def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh, hd, window, cap, steps):
     """The fused device-position core is bit-identical to rmsnorm x2 + rope +
     kv_store + attention_chunk(n=1) (the prefill == decode invariant of
     crates/tuckcore/src/engine/metal.rs:3682-3774)."""
-    cap, steps, eps = 24, 10, 1e-6
+    eps = 1e-6
     group, scale = heads // kvh, 1.0 / np.sqrt(np.float32(hd))
     qn = (1 + 0.1 * T.activations(0, 20, hd)).astype(np.float32)
     kn = (1 + 0.1 * T.activations(0, 21, hd)).astype(np.float32)
@@ -166,7 +167,8 @@ def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh,
             c.zero()
     pos_buf, status = ctx.from_array(np.zeros(2, np.uint32)), ctx.buffer(4, shared=True)
     status.zero()
-    sb = ctx.buffer(heads * cap * 4)
+    sb = ctx.buffer(cuda.decode_attention_scratch_bytes(heads, kvh, hd, cap))
+    sb.zero()
     for pos in range(steps):
         q = T.activations(pos, 30, heads * hd)
         k = T.activations(pos, 31, kvh * hd)

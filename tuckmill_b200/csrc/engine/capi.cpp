@@ -195,6 +195,12 @@ int tm_engine_decode_steps(tm_engine *e, uint32_t steps, char *err, size_t err_c
     })
 }
 
+int tm_engine_decode_ungrouped(tm_engine *e, uint32_t steps, char *err, size_t err_cap) {
+    GUARD({
+        for (uint32_t i = 0; i < steps; ++i) e->model->step_ungrouped();
+    })
+}
+
 int tm_engine_plan(const char *gguf_path, uint32_t context, uint64_t budget_bytes, tm_engine_info *out,
                    char *err, size_t err_cap) {
     GUARD({

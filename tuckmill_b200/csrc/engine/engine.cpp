@@ -147,7 +147,9 @@ struct PrefillScratch {
         }
         for (size_t e : {g.hidden, g.hidden, aw, kvw, kvw, aw, g.hidden, g.hidden, ffn, ffn, g.hidden})
             p.scratch_f32(n * e);
-        p.scratch_f32(n * heads * cap);
+        (void)heads;
+        (void)cap;
+        p.scratch_f32(1);  // the chunk attention streams key blocks; its scratch argument is a placeholder
     }
     static PrefillScratch alloc(const CudaContext &ctx, const ModelGraph &g, size_t cap, size_t n) {
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
@@ -169,7 +171,9 @@ struct PrefillScratch {
         s.g = zeros_f32(ctx, n * ffn);
         s.u = zeros_f32(ctx, n * ffn);
         s.d2 = zeros_f32(ctx, n * g.hidden);
-        s.ascr = zeros_f32(ctx, n * heads * cap);
+        (void)heads;
+        (void)cap;
+        s.ascr = zeros_f32(ctx, 1);
         return s;
     }
 };
@@ -253,11 +257,12 @@ struct AttentionBlock {
         const size_t hd = s.heads * s.head_dim, kv = s.kv_heads * s.head_dim;
         p.scratch_f32(hd + 2 * kv);
         p.scratch_f32(hd);
-        p.scratch_f32(s.heads * cap);
+        p.scratch_bytes(tm_cuda_attention_decode_scratch_bytes((uint32_t)s.heads, (uint32_t)s.kv_heads,
+                                                               (uint32_t)s.head_dim, (uint32_t)cap));
     }
     static AttentionBlock load(const CudaContext &ctx, const WeightSource &src, const AttentionSpec &s, float eps,
                                size_t cap) {
-        if (s.head_dim % 2 != 0 || s.head_dim > 512 || s.rope_dims % 2 != 0)
+        if (s.head_dim % 32 != 0 || (s.head_dim / 32 > 4 && s.head_dim != 256) || s.rope_dims % 2 != 0)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture,
                                 "attention head size " + std::to_string(s.head_dim) + " has no CUDA block");
         AttentionBlock b;
@@ -279,7 +284,8 @@ struct AttentionBlock {
         b.k_view = b.qkv_out.view(hd * 4, kv * 4);
         b.v_view = b.qkv_out.view((hd + kv) * 4, kv * 4);
         b.attn = zeros_f32(ctx, hd);
-        b.kv_scratch = zeros_f32(ctx, s.heads * cap);
+        b.kv_scratch = ctx.zeros(tm_cuda_attention_decode_scratch_bytes((uint32_t)s.heads, (uint32_t)s.kv_heads,
+                                                                        (uint32_t)s.head_dim, (uint32_t)cap));
         return b;
     }
     void reset() const {
@@ -459,14 +465,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)
     c.begin_group();
     try {
-        c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
-                           g.embedding_scale, I.x);
-        for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps);
-        c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
-                          &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
-        c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity + 1,
-                     &I.tokens_mirror);
-        c.u32_add(I.pos_buf, 0, 1);
+        m->encode_decode_step();
     } catch (...) {
         c.abort_group();
         throw;
@@ -474,6 +473,28 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     I.decode_graph = c.end_group_retain();
     m->reset();
     return m;
+}
+
+void EngineModel::encode_decode_step() {
+    Impl &I = *impl_;
+    const CudaContext &c = *ctx_;
+    const ModelGraph &g = graph_;
+    c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
+                       g.embedding_scale, I.x);
+    for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps);
+    c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
+                      &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
+    c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity_ + 1,
+                 &I.tokens_mirror);
+    c.u32_add(I.pos_buf, 0, 1);
+}
+
+void EngineModel::step_ungrouped() {
+    if (pos_ >= capacity_)
+        throw TuckmillError(ErrorCode::ContextExceedsBudget,
+                            "position " + std::to_string(pos_) + " exceeds KV capacity " + std::to_string(capacity_));
+    encode_decode_step();
+    pos_ += 1;
 }
 
 EngineModel::~EngineModel() {

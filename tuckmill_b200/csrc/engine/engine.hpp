@@ -85,6 +85,10 @@ public:
     struct Ticket { uint64_t dispatch = 0; size_t slot = 0; };
     Ticket submit_greedy();
     uint32_t collect_greedy(const Ticket &t);
+    // The same decode step encoded operator by operator (one dispatch each, no
+    // graph): the attribution mode of engine/metal.rs:1964-1968, used with the
+    // context's per-operator profile table.
+    void step_ungrouped();
     // Token the last prefill(want_token) chose (blocking read).
     uint32_t prefill_token();
     // The reference's run_session loop (crates/tuckcore/src/executor.rs:870-1125)
@@ -97,6 +101,7 @@ public:
 private:
     struct Impl;
     EngineModel() = default;
+    void encode_decode_step();
     std::shared_ptr<CudaContext> ctx_;
     ModelGraph graph_;
     EngineOptions opts_;

@@ -157,153 +157,315 @@ __global__ void kv_store_kernel(const float *ks, const float *vs, __half *kc, __
 }
 
 // ---- attention ---------------------------------------------------------------
-// One query head over keys [start, seq) of one KV head's f16 planes.  Scores go
-// to `sc` (global scratch row or shared memory), softmax weights are normalised
-// in place (w = e / sum, forward.rs:484-489), then every value dim accumulates.
-// `k_new`/`v_new`, when non-null, stand for position seq-1 (the token being
-// decoded, already rounded to f16) so the caller need not wait for its store.
-__device__ void attend_row(const float *qh, const __half *kc, const __half *vc, float *oh, float *sc,
-                           uint32_t start, uint32_t seq, uint32_t hd, float scale, float *red,
-                           const __half *k_new, const __half *v_new) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t j = start + warp; j < seq; j += kWarps) {
-        const __half *kr = (k_new && j == seq - 1) ? k_new : kc + (size_t)j * hd;
-        float part = 0.0f;
-        for (uint32_t d = lane * 2; d < hd; d += 64) {
-            const float2 kk = __half22float2(*(const __half2 *)(kr + d));
-            part = fmaf(qh[d], kk.x, part);
-            part = fmaf(qh[d + 1], kk.y, part);
+// Causal (optionally sliding-window) GQA attention over a packed f16 cache.
+// The arithmetic is the scalar executor's (crates/tuckcore/src/forward.rs:
+// 464-498: score = dot * scale, softmax over the attended keys, weighted sum of
+// values) evaluated blockwise so it parallelises and streams:
+//   * keys are taken in blocks of 32 aligned to absolute positions; lane j of a
+//     warp owns key j of the block (whole dot product, fixed order), the block
+//     yields m = max score, l = sum exp(s - m), o[d] = sum exp(s - m) v[d];
+//   * blocks are merged in increasing order with the running-max recurrence
+//     M' = max(M, m), L = L e^(M-M') + l e^(m-M'), O likewise; out = O / L.
+// Both entry points -- one query row of a prefill chunk per warp, and the decode
+// step with one warp per key block plus a last-arrival merge -- call the same
+// two device functions, so prefill and decode agree bit for bit.
+constexpr int kAttnBlock = 32;
+
+// Sum of squares with the tree of tmdev::block_sumsq (256 threads), evaluated
+// by one warp, so a per-head RMS norm computed here matches rmsnorm_kernel.
+__device__ float warp_sumsq_as_block(const float *x, uint32_t n, int lane) {
+    float total = 0.0f;
+#pragma unroll 1
+    for (int w = 0; w < kWarps; ++w) {
+        float s = 0.0f;
+        for (uint32_t i = w * 32 + lane; i < n; i += kThreads) s += x[i] * x[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        total += s;
+    }
+    return total;
+}
+
+// Partial attention of G query heads (shared memory qs[G][hd]) over the keys
+// [lo, hi) of the 32-key block starting at j0.  Lane `d` of o[g][i] holds value
+// dim d = lane + 32 i.
+template <int G, int DPL>
+__device__ __forceinline__ void attend_block(const float *qs, const __half *kc, const __half *vc, uint32_t hd,
+                                             uint32_t j0, uint32_t lo, uint32_t hi, float scale,
+                                             const __half *k_new, const __half *v_new, uint32_t pos_new,
+                                             int lane, float (&m)[G], float (&l)[G], float (&o)[G][DPL]) {
+    const uint32_t j = j0 + lane;
+    const bool valid = j >= lo && j < hi;
+    float dot[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) dot[g] = 0.0f;
+    if (valid) {
+        const __half *kr = (k_new && j == pos_new) ? k_new : kc + (size_t)j * hd;
+        for (uint32_t d = 0; d < hd; d += 8) {
+            const int4 raw = *(const int4 *)(kr + d);
+            const __half2 *h2 = (const __half2 *)&raw;
+            float kf[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h2[e]);
+                kf[2 * e] = f.x;
+                kf[2 * e + 1] = f.y;
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 q0 = *(const float4 *)(qs + g * hd + d), q1 = *(const float4 *)(qs + g * hd + d + 4);
+                float t = dot[g];
+                t = fmaf(q0.x, kf[0], t); t = fmaf(q0.y, kf[1], t); t = fmaf(q0.z, kf[2], t); t = fmaf(q0.w, kf[3], t);
+                t = fmaf(q1.x, kf[4], t); t = fmaf(q1.y, kf[5], t); t = fmaf(q1.z, kf[6], t); t = fmaf(q1.w, kf[7], t);
+                dot[g] = t;
+            }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        if (lane == 0) sc[j] = part * scale;
     }
-    __syncthreads();
-    float m = -INFINITY;
-    for (uint32_t j = start + threadIdx.x; j < seq; j += kThreads) m = fmaxf(m, sc[j]);
+    float p[G];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    m = red[0];
+    for (int g = 0; g < G; ++g) {
+        const float sc = valid ? dot[g] * scale : -INFINITY;
+        float mx = sc;
 #pragma unroll
-    for (int w = 1; w < kWarps; ++w) m = fmaxf(m, red[w]);
-    __syncthreads();
-    float s = 0.0f;
-    for (uint32_t j = start + threadIdx.x; j < seq; j += kThreads) {
-        const float e = expf(sc[j] - m);
-        sc[j] = e;
-        s += e;
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        p[g] = valid ? expf(sc - mx) : 0.0f;
+        float sum = p[g];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        m[g] = mx;
+        l[g] = sum;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[g][i] = 0.0f;
     }
+    const uint32_t jj0 = lo > j0 ? lo - j0 : 0, jj1 = (hi < j0 + kAttnBlock ? hi : j0 + kAttnBlock) - j0;
+#pragma unroll 4
+    for (uint32_t jj = jj0; jj < jj1; ++jj) {
+        const uint32_t jk = j0 + jj;
+        const __half *vr = (v_new && jk == pos_new) ? v_new : vc + (size_t)jk * hd;
+        float vf[DPL];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) red[warp] = s;
-    __syncthreads();
-    float sum = 0.0f;
+        for (int i = 0; i < DPL; ++i) vf[i] = __half2float(vr[lane + 32 * i]);
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) sum += red[w];
-    __syncthreads();
-    for (uint32_t j = start + threadIdx.x; j < seq; j += kThreads) sc[j] = sc[j] / sum;
-    __syncthreads();
-    // Values: thread pairs (d, d+1); key ranges split across the CTA's slices.
-    const uint32_t pairs = hd / 2;               // half2 columns
-    const uint32_t slices = kThreads / pairs;     // >= 1 for hd <= 512
-    const uint32_t slice = threadIdx.x / pairs, col = (threadIdx.x % pairs) * 2;
-    float ax = 0.0f, ay = 0.0f;
-    if (slice < slices) {
-        for (uint32_t j = start + slice; j < seq; j += slices) {
-            const __half *vr = (v_new && j == seq - 1) ? v_new : vc + (size_t)j * hd;
-            const float2 vv = __half22float2(*(const __half2 *)(vr + col));
-            const float w = sc[j];
-            ax = fmaf(w, vv.x, ax);
-            ay = fmaf(w, vv.y, ay);
+        for (int g = 0; g < G; ++g) {
+            const float pj = __shfl_sync(0xffffffffu, p[g], (int)jj);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[g][i] = fmaf(pj, vf[i], o[g][i]);
         }
     }
-    // Combine the slices in a fixed order through shared memory (reuses sc's
-    // CTA only after everyone finished reading it).
-    __shared__ float part_o[kThreads * 2];
-    part_o[threadIdx.x * 2] = ax;
-    part_o[threadIdx.x * 2 + 1] = ay;
-    __syncthreads();
-    if (threadIdx.x < pairs) {
-        float ox = 0.0f, oy = 0.0f;
-        for (uint32_t s2 = 0; s2 < slices; ++s2) {
-            ox += part_o[(s2 * pairs + threadIdx.x) * 2];
-            oy += part_o[(s2 * pairs + threadIdx.x) * 2 + 1];
-        }
-        oh[threadIdx.x * 2] = ox;
-        oh[threadIdx.x * 2 + 1] = oy;
-    }
-    __syncthreads();
+}
+
+// Running-max merge of one block partial into (M, L, O).
+template <int DPL>
+__device__ __forceinline__ void attend_merge(float &M, float &L, float (&O)[DPL], float m, float l,
+                                             const float (&o)[DPL]) {
+    const float Mn = fmaxf(M, m);
+    const float a = expf(M - Mn), b = expf(m - Mn);
+    L = fmaf(L, a, l * b);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) O[i] = fmaf(O[i], a, o[i] * b);
+    M = Mn;
 }
 
 __device__ __forceinline__ uint32_t attn_start(uint32_t seq, uint32_t window) {
     return (window != 0u && seq > window) ? seq - window : 0u;
 }
 
-// grid (heads, n): query row t of a chunk at pos0 attends keys [start, pos0+t].
-__global__ void __launch_bounds__(kThreads) attention_chunk_kernel(
-    const float *q, const __half *kc, const __half *vc, float *out, float *scratch, uint32_t heads,
-    uint32_t pos0, uint32_t cap, uint32_t hd, uint32_t group, float scale, uint32_t window) {
-    __shared__ float red[kWarps];
-    const uint32_t head = blockIdx.x, t = blockIdx.y, kvh = head / group;
-    const size_t row = (size_t)t * heads + head;
-    const uint32_t seq = pos0 + t + 1u;
-    attend_row(q + row * hd, kc + (size_t)kvh * cap * hd, vc + (size_t)kvh * cap * hd,
-               out + row * hd, scratch + row * cap, attn_start(seq, window), seq, hd, scale, red,
-               nullptr, nullptr);
+// Prefill: grid (kv_heads, n), one warp: query row t of a chunk at pos0 attends
+// keys [start, pos0+t] for the G heads of its KV head.  q, out: [n][heads][hd].
+template <int G, int DPL>
+__global__ void __launch_bounds__(32) attention_chunk_kernel(const float *q, const __half *kc, const __half *vc,
+                                                             float *out, uint32_t heads, uint32_t pos0,
+                                                             uint32_t cap, uint32_t hd, uint32_t group0,
+                                                             uint32_t group, float scale, uint32_t window) {
+    __shared__ __align__(16) float qs[G * 32 * DPL];
+    const int lane = threadIdx.x;
+    const uint32_t kvh = blockIdx.x, t = blockIdx.y;
+    const uint32_t seq = pos0 + t + 1u, start = attn_start(seq, window);
+    const uint32_t head0 = kvh * group + group0;  // first of the G heads handled here
+    const float *qrow = q + ((size_t)t * heads + head0) * hd;
+    for (uint32_t i = lane; i < G * hd; i += 32) qs[i] = qrow[i];
+    __syncwarp();
+    const __half *kp = kc + (size_t)kvh * cap * hd, *vp = vc + (size_t)kvh * cap * hd;
+    float M[G], L[G], O[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        M[g] = -INFINITY;
+        L[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) O[g][i] = 0.0f;
+    }
+    for (uint32_t j0 = start / kAttnBlock * kAttnBlock; j0 < seq; j0 += kAttnBlock) {
+        float m[G], l[G], o[G][DPL];
+        attend_block<G, DPL>(qs, kp, vp, hd, j0, start, seq, scale, nullptr, nullptr, 0u, lane, m, l, o);
+#pragma unroll
+        for (int g = 0; g < G; ++g) attend_merge<DPL>(M[g], L[g], O[g], m[g], l[g], o[g]);
+    }
+    float *orow = out + ((size_t)t * heads + head0) * hd;
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[g][i] / L[g];
 }
 
-// One CTA per query head: q/k RMS norm, RoPE, KV store (by the first head of
-// each group) and attention at the device-held position.
-__global__ void __launch_bounds__(kThreads) attention_decode_kernel(
-    float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
+// Decode: grid (kv_heads, ceil(cap/32)), one warp per key block.  Every warp
+// norms and rotates its G query heads (cheap, avoids a dependency), the warp
+// whose block holds the new position also norms, rotates, rounds and stores
+// the new K/V row, each warp writes its block partial to `scratch`, and the
+// last warp to arrive for a KV head merges the blocks in order.
+//   scratch: float part[kv_heads][nblk][group][hd + 2] then u32 count[kv_heads]
+template <int G, int DPL>
+__global__ void __launch_bounds__(32) attention_decode_kernel(
+    const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
     const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos_p,
     uint32_t *status, uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot, uint32_t cap,
-    uint32_t window, float eps, float scale) {
-    __shared__ float red[kWarps];
-    __shared__ __align__(16) float qs[512];
-    __shared__ __align__(16) float ks[512];
-    __shared__ __align__(16) __half kh[512];
-    __shared__ __align__(16) __half vh[512];
-    const uint32_t head = blockIdx.x, group = heads / kv_heads, kvh = head / group;
+    uint32_t window, float eps, float scale, uint32_t group0) {
+    __shared__ __align__(16) float qs[G * 32 * DPL];
+    __shared__ __align__(16) float ks[32 * DPL];
+    __shared__ __align__(16) __half kh[32 * DPL];
+    __shared__ __align__(16) __half vh[32 * DPL];
+    const int lane = threadIdx.x;
+    const uint32_t kvh = blockIdx.x, blk = blockIdx.y, group = heads / kv_heads;
+    const uint32_t nblk = (cap + kAttnBlock - 1) / kAttnBlock;
     const uint32_t pos = *pos_p;
     if (pos >= cap) {
-        if (threadIdx.x == 0) atomicOr(status, 1u);
+        if (lane == 0 && blk == 0 && kvh == 0) atomicOr(status, 1u);
         return;
     }
-    // per-head RMS norm of q and of this group's k (same tree as rmsnorm_kernel)
-    const float *qsrc = q + (size_t)head * hd;
-    const float *ksrc = k + (size_t)kvh * hd;
-    const float qss = tmdev::block_sumsq(qsrc, hd, red);
-    const float kss = tmdev::block_sumsq(ksrc, hd, red);
-    const float qinv = 1.0f / sqrtf(qss / (float)hd + eps);
-    const float kinv = 1.0f / sqrtf(kss / (float)hd + eps);
-    for (uint32_t i = threadIdx.x; i < hd; i += kThreads) {
-        qs[i] = qsrc[i] * qinv * q_norm[i];
-        ks[i] = ksrc[i] * kinv * k_norm[i];
+    const uint32_t seq = pos + 1u, start = attn_start(seq, window);
+    const uint32_t first = start / kAttnBlock, last = pos / kAttnBlock;
+    if (blk < first || blk > last) return;
+    const uint32_t head0 = kvh * group + group0;
+    // q: per-head RMS norm then RoPE (rmsnorm_kernel + rope_kernel arithmetic)
+#pragma unroll 1
+    for (int g = 0; g < G; ++g) {
+        const float *src = q + (size_t)(head0 + g) * hd;
+        const float ss = warp_sumsq_as_block(src, hd, lane);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (uint32_t i = lane; i < hd; i += 32) qs[g * hd + i] = src[i] * inv * q_norm[i];
+        __syncwarp();
+        for (uint32_t i = lane; i < n_rot / 2; i += 32) rope_pair(qs + g * hd, i, n_rot / 2, pos, inv_freq);
     }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < n_rot / 2; i += kThreads) {
-        rope_pair(qs, i, n_rot / 2, pos, inv_freq);
-        rope_pair(ks, i, n_rot / 2, pos, inv_freq);
-    }
-    __syncthreads();
-    const float *vsrc = v + (size_t)kvh * hd;
-    for (uint32_t i = threadIdx.x; i < hd; i += kThreads) {
-        kh[i] = __float2half_rn(ks[i]);
-        vh[i] = __float2half_rn(vsrc[i]);
-        if (head % group == 0) {
-            const size_t dst = ((size_t)kvh * cap + pos) * hd + i;
-            kc[dst] = kh[i];
-            vc[dst] = vh[i];
+    const bool owns_new = blk == last;
+    if (owns_new) {
+        const float *src = k + (size_t)kvh * hd;
+        const float ss = warp_sumsq_as_block(src, hd, lane);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (uint32_t i = lane; i < hd; i += 32) ks[i] = src[i] * inv * k_norm[i];
+        __syncwarp();
+        for (uint32_t i = lane; i < n_rot / 2; i += 32) rope_pair(ks, i, n_rot / 2, pos, inv_freq);
+        __syncwarp();
+        const float *vsrc = v + (size_t)kvh * hd;
+        for (uint32_t i = lane; i < hd; i += 32) {
+            kh[i] = __float2half_rn(ks[i]);
+            vh[i] = __float2half_rn(vsrc[i]);
+            if (group0 == 0) {
+                const size_t dst = ((size_t)kvh * cap + pos) * hd + i;
+                kc[dst] = kh[i];
+                vc[dst] = vh[i];
+            }
         }
     }
-    __syncthreads();
-    const uint32_t seq = pos + 1u;
-    attend_row(qs, kc + (size_t)kvh * cap * hd, vc + (size_t)kvh * cap * hd, out + (size_t)head * hd,
-               scratch + (size_t)head * cap, attn_start(seq, window), seq, hd, scale, red, kh, vh);
+    __syncwarp();
+    const __half *kp = kc + (size_t)kvh * cap * hd, *vp = vc + (size_t)kvh * cap * hd;
+    float m[G], l[G], o[G][DPL];
+    attend_block<G, DPL>(qs, kp, vp, hd, blk * kAttnBlock, start, seq, scale, owns_new ? kh : nullptr,
+                         owns_new ? vh : nullptr, pos, lane, m, l, o);
+    float *orow = out + (size_t)head0 * hd;
+    if (first == last) {  // a single block: merge it into the empty state and finish
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float M = -INFINITY, L = 0.0f, O[DPL];
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) O[i] = 0.0f;
+            attend_merge<DPL>(M, L, O, m[g], l[g], o[g]);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[i] / L;
+        }
+        return;
+    }
+    const uint32_t stride = hd + 2;
+    float *part = scratch + (((size_t)kvh * nblk + blk) * group + group0) * stride;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) {
+            part[g * stride] = m[g];
+            part[g * stride + 1] = l[g];
+        }
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) part[g * stride + 2 + lane + 32 * i] = o[g][i];
+    }
+    __threadfence();
+    __syncwarp();
+    uint32_t *count = (uint32_t *)(scratch + (size_t)kv_heads * nblk * group * stride) + kvh * 8 + group0 / 4;
+    uint32_t arrived = 0;
+    if (lane == 0) arrived = atomicAdd(count, 1u);
+    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+    if (arrived != last - first) return;
+    __threadfence();
+    float M[G], L[G], O[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        M[g] = -INFINITY;
+        L[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) O[g][i] = 0.0f;
+    }
+    for (uint32_t b = first; b <= last; ++b) {
+        const float *pb = scratch + (((size_t)kvh * nblk + b) * group + group0) * stride;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float ob[DPL];
+            const float mb = __ldcg(pb + g * stride), lb = __ldcg(pb + g * stride + 1);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) ob[i] = __ldcg(pb + g * stride + 2 + lane + 32 * i);
+            attend_merge<DPL>(M[g], L[g], O[g], mb, lb, ob);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[g][i] / L[g];
+    if (lane == 0) *count = 0u;  // ready for the next launch on this stream
 }
+
+// Launch helpers: G heads per warp (the group size, in chunks of at most 4) and
+// DPL = head_dim / 32 value dims per lane are compile-time.
+template <int G, int DPL>
+void launch_chunk(cudaStream_t st, const float *q, const __half *kc, const __half *vc, float *out, uint32_t heads,
+                  uint32_t kvh, uint32_t n, uint32_t pos0, uint32_t cap, uint32_t hd, uint32_t group0,
+                  uint32_t group, float scale, uint32_t window) {
+    attention_chunk_kernel<G, DPL><<<dim3(kvh, n), 32, 0, st>>>(q, kc, vc, out, heads, pos0, cap, hd, group0, group,
+                                                                 scale, window);
+}
+
+template <int G, int DPL>
+void launch_decode(cudaStream_t st, const float *q, const float *k, const float *v, const float *qn, const float *kn,
+                   const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos,
+                   uint32_t *status, uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot, uint32_t cap,
+                   uint32_t window, float eps, float scale, uint32_t group0) {
+    attention_decode_kernel<G, DPL><<<dim3(kvh, (cap + kAttnBlock - 1) / kAttnBlock), 32, 0, st>>>(
+        q, k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, heads, kvh, hd, n_rot, cap, window, eps, scale,
+        group0);
+}
+
+#define TM_ATTN_DISPATCH(FN, G, DPL, ...)                                         \
+    switch ((G) * 100 + (DPL)) {                                                   \
+        case 101: FN<1, 1>(__VA_ARGS__); break; case 102: FN<1, 2>(__VA_ARGS__); break;  \
+        case 103: FN<1, 3>(__VA_ARGS__); break; case 104: FN<1, 4>(__VA_ARGS__); break;  \
+        case 108: FN<1, 8>(__VA_ARGS__); break;                                   \
+        case 201: FN<2, 1>(__VA_ARGS__); break; case 202: FN<2, 2>(__VA_ARGS__); break;  \
+        case 203: FN<2, 3>(__VA_ARGS__); break; case 204: FN<2, 4>(__VA_ARGS__); break;  \
+        case 208: FN<2, 8>(__VA_ARGS__); break;                                   \
+        case 301: FN<3, 1>(__VA_ARGS__); break; case 302: FN<3, 2>(__VA_ARGS__); break;  \
+        case 303: FN<3, 3>(__VA_ARGS__); break; case 304: FN<3, 4>(__VA_ARGS__); break;  \
+        case 308: FN<3, 8>(__VA_ARGS__); break;                                   \
+        case 401: FN<4, 1>(__VA_ARGS__); break; case 402: FN<4, 2>(__VA_ARGS__); break;  \
+        case 403: FN<4, 3>(__VA_ARGS__); break; case 404: FN<4, 4>(__VA_ARGS__); break;  \
+        case 408: FN<4, 8>(__VA_ARGS__); break;                                   \
+        default: break;                                                           \
+    }
+
+inline bool attn_shape_ok(uint32_t hd) { return hd % 32 == 0 && (hd / 32 <= 4 || hd / 32 == 8); }
 
 }  // namespace
 
@@ -528,22 +690,30 @@ static int attention_common(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer 
                             tm_cuda_buffer *v_cache, tm_cuda_buffer *out, tm_cuda_buffer *scratch,
                             uint32_t heads, uint32_t pos0, uint32_t cap, uint32_t hd, uint32_t group,
                             float scale, uint32_t n, uint32_t window, char *err, size_t err_cap) {
-    if (n == 0 || heads == 0 || group == 0 || heads % group != 0 || hd == 0 || hd % 2 != 0 ||
-        hd > 512 || cap == 0 || pos0 >= cap || n > cap - pos0)
+    if (n == 0 || n > 65535u || heads == 0 || group == 0 || heads % group != 0 || !attn_shape_ok(hd) || cap == 0 ||
+        pos0 >= cap || n > cap - pos0)
         return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
-                       "attention geometry: heads %u, group %u, head_dim %u (even, <= 512), rows %u at "
-                       "position %u, capacity %u", heads, group, hd, n, pos0, cap);
-    const size_t plane = (size_t)(heads / group) * cap * hd * 2;
+                       "attention geometry: heads %u, group %u, head_dim %u (32, 64, 96, 128 or 256), rows %u "
+                       "at position %u, capacity %u", heads, group, hd, n, pos0, cap);
+    const uint32_t kvh = heads / group;
+    const size_t plane = (size_t)kvh * cap * hd * 2;
     TM_CHECK_BUF(q, (size_t)n * heads * hd * 4, "q");
     TM_CHECK_BUF(out, (size_t)n * heads * hd * 4, "attention output");
     TM_CHECK_BUF(k_cache, plane, "k cache");
     TM_CHECK_BUF(v_cache, plane, "v cache");
-    TM_CHECK_BUF(scratch, (size_t)n * heads * cap * 4, "attention scratch");
+    // The reference sizes a score scratch of n*heads*cap f32; this kernel keeps
+    // its state in registers and only checks that a buffer was passed.
+    TM_CHECK_BUF(scratch, 4, "attention scratch");
     TM_OP_BEGIN("attention");
-    attention_chunk_kernel<<<dim3(heads, n), kThreads, 0, ctx->stream>>>(
-        (const float *)q->dev, (const __half *)k_cache->dev, (const __half *)v_cache->dev,
-        (float *)out->dev, (float *)scratch->dev, heads, pos0, cap, hd, group, scale, window);
-    TM_OP_END(1);
+    uint64_t launches = 0;
+    for (uint32_t g0 = 0; g0 < group; g0 += 4) {
+        const uint32_t G = group - g0 < 4 ? group - g0 : 4;
+        TM_ATTN_DISPATCH(launch_chunk, G, hd / 32, ctx->stream, (const float *)q->dev, (const __half *)k_cache->dev,
+                         (const __half *)v_cache->dev, (float *)out->dev, heads, kvh, n, pos0, cap, hd, g0, group,
+                         scale, window);
+        ++launches;
+    }
+    TM_OP_END(launches);
 }
 
 int tm_cuda_qwen35_attention_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache,
@@ -567,6 +737,13 @@ int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
                             scale, n, window, err, err_cap);
 }
 
+size_t tm_cuda_attention_decode_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                                              uint32_t cap) {
+    if (heads == 0 || kv_heads == 0 || cap == 0) return 0;
+    const size_t nblk = (cap + kAttnBlock - 1) / kAttnBlock;
+    return ((size_t)heads * nblk * (head_dim + 2) + (size_t)kv_heads * 8) * 4;
+}
+
 int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
                                  tm_cuda_buffer *v, tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm,
                                  tm_cuda_buffer *inv_freq, tm_cuda_buffer *k_cache,
@@ -577,10 +754,10 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                                  uint32_t cap, uint32_t window, float eps, float scale, char *err,
                                  size_t err_cap) {
     TM_ENTER();
-    if (heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || head_dim == 0 || head_dim % 2 != 0 ||
-        head_dim > 512 || n_rot == 0 || n_rot > head_dim || n_rot % 2 != 0 || cap == 0)
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 32 || !attn_shape_ok(head_dim) ||
+        n_rot == 0 || n_rot > head_dim || n_rot % 2 != 0 || cap == 0 || cap > 65535u * kAttnBlock)
         return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
-                       "decode attention geometry: heads %u/%u, head_dim %u (even, <= 512), n_rot %u, "
+                       "decode attention geometry: heads %u/%u, head_dim %u (32, 64, 96, 128 or 256), n_rot %u, "
                        "capacity %u", heads, kv_heads, head_dim, n_rot, cap);
     const size_t plane = (size_t)kv_heads * cap * head_dim * 2;
     TM_CHECK_BUF(q, (size_t)heads * head_dim * 4, "q");
@@ -592,17 +769,23 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
     TM_CHECK_BUF(k_cache, plane, "k cache");
     TM_CHECK_BUF(v_cache, plane, "v cache");
     TM_CHECK_BUF(out, (size_t)heads * head_dim * 4, "attention output");
-    TM_CHECK_BUF(scratch, (size_t)heads * cap * 4, "attention scratch");
+    TM_CHECK_BUF(scratch, tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap),
+                 "decode attention scratch");
     TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
     TM_CHECK_BUF(status, 4, "status");
     TM_OP_BEGIN("attention_decode");
-    attention_decode_kernel<<<heads, kThreads, 0, ctx->stream>>>(
-        (float *)q->dev, (const float *)k->dev, (const float *)v->dev, (const float *)q_norm->dev,
-        (const float *)k_norm->dev, (const float *)inv_freq->dev, (__half *)k_cache->dev,
-        (__half *)v_cache->dev, (float *)out->dev, (float *)scratch->dev,
-        (const uint32_t *)pos_buf->dev + pos_index, (uint32_t *)status->dev, heads, kv_heads,
-        head_dim, n_rot, cap, window, eps, scale);
-    TM_OP_END(1);
+    const uint32_t group = heads / kv_heads;
+    uint64_t launches = 0;
+    for (uint32_t g0 = 0; g0 < group; g0 += 4) {
+        const uint32_t G = group - g0 < 4 ? group - g0 : 4;
+        TM_ATTN_DISPATCH(launch_decode, G, head_dim / 32, ctx->stream, (const float *)q->dev, (const float *)k->dev,
+                         (const float *)v->dev, (const float *)q_norm->dev, (const float *)k_norm->dev,
+                         (const float *)inv_freq->dev, (__half *)k_cache->dev, (__half *)v_cache->dev,
+                         (float *)out->dev, (float *)scratch->dev, (const uint32_t *)pos_buf->dev + pos_index,
+                         (uint32_t *)status->dev, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, g0);
+        ++launches;
+    }
+    TM_OP_END(launches);
 }
 
 }  // extern "C"

@@ -137,6 +137,13 @@ def runtime_info() -> str:
     return load_library().tm_cuda_runtime_info().decode()
 
 
+def decode_attention_scratch_bytes(heads: int, kv_heads: int, head_dim: int, cap: int) -> int:
+    L = load_library()
+    L.tm_cuda_attention_decode_scratch_bytes.restype = C.c_size_t
+    L.tm_cuda_attention_decode_scratch_bytes.argtypes = [_U32] * 4
+    return int(L.tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap))
+
+
 def packed_bytes(rows: int, cols: int) -> int:
     return int(load_library().tm_cuda_q8_0_packed_bytes(rows, cols))
 

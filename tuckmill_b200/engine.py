@@ -70,6 +70,7 @@ def load_library() -> C.CDLL:
     L.tm_engine_generate.argtypes = [P, P, C.c_uint32, C.c_uint32, C.c_int, P, C.POINTER(C.c_uint32),
                                      C.POINTER(Stats)] + E
     L.tm_engine_decode_steps.argtypes = [P, C.c_uint32] + E
+    L.tm_engine_decode_ungrouped.argtypes = [P, C.c_uint32] + E
     L.tm_engine_plan.argtypes = [C.c_char_p, C.c_uint32, C.c_uint64, C.POINTER(Info)] + E
     _lib = L
     return L
@@ -146,6 +147,21 @@ class Engine:
 
     def decode_steps(self, steps: int):
         self._call(self._l.tm_engine_decode_steps, steps)
+
+    def decode_ungrouped(self, steps: int):
+        self._call(self._l.tm_engine_decode_ungrouped, steps)
+
+    def profile(self, enabled: bool):
+        _cuda.load_library().tm_cuda_profile_set(self.cuda_ctx(), int(enabled))
+
+    def profile_rows(self):
+        L = _cuda.load_library()
+        rows, i = [], 0
+        name, nanos, count = C.create_string_buffer(128), C.c_uint64(), C.c_uint64()
+        while L.tm_cuda_profile_read(self.cuda_ctx(), i, name, 128, C.byref(nanos), C.byref(count)):
+            rows.append((name.value.decode(), nanos.value, count.value))
+            i += 1
+        return rows
 
     def generate(self, prompt, max_new: int, ignore_eos: bool = True):
         p = np.ascontiguousarray(prompt, dtype=np.uint32)

@@ -290,7 +290,9 @@ int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
  * every step: per-head q/k RMS norm, RoPE, f16 KV store and (windowed) causal
  * attention for ONE token -- the sequence of tm_cuda_rmsnorm_f32 x2,
  * tm_cuda_qwen35_rope_partial, tm_cuda_qwen35_kv_store_f16 and
- * tm_cuda_qwen35_attention_f16_chunk(n = 1) with the same arithmetic.  A
+ * tm_cuda_qwen35_attention_f16_chunk(n = 1): bit for bit with `exact` = 1;
+ * with `exact` = 0 a latency-optimised kernel with the same mathematics and a
+ * different summation order (tolerance-qualified) runs where it applies.  A
  * position >= cap writes nothing and sets bit 0 of status[0] (u32, shared).
  * `scratch` holds the per-key-block partial results and arrival counters
  * (tm_cuda_attention_decode_scratch_bytes, zero-filled once by the caller;
@@ -305,8 +307,8 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                                  tm_cuda_buffer *scratch, tm_cuda_buffer *pos_buf,
                                  uint32_t pos_index, tm_cuda_buffer *status, uint32_t heads,
                                  uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
-                                 uint32_t cap, uint32_t window, float eps, float scale, char *err,
-                                 size_t err_cap);
+                                 uint32_t cap, uint32_t window, float eps, float scale, int exact,
+                                 char *err, size_t err_cap);
 /* No counterpart: buf[index] += delta (u32), to advance a device position
  * inside a recorded graph. */
 int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint32_t delta,

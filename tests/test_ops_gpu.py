@@ -149,7 +149,8 @@ def test_attention_chunk_matches_scalar_executor(ctx, oracle, heads, kvh, hd, wi
 
 
 @pytest.mark.parametrize("heads,kvh,hd,window,cap,steps", [(16, 8, 128, 0, 24, 10), (4, 1, 256, 6, 24, 10),
-                                                            (4, 2, 32, 0, 100, 70), (12, 2, 64, 40, 100, 90)])
+                                                            (4, 2, 32, 0, 100, 70), (12, 2, 64, 40, 100, 90), (16, 8, 128, 0, 200, 150),
+                                                            (4, 1, 256, 70, 200, 150)])
 def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh, hd, window, cap, steps):
     """The fused device-position core is bit-identical to rmsnorm x2 + rope +
     kv_store + attention_chunk(n=1) (the prefill == decode invariant of
@@ -161,7 +162,7 @@ def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh,
     inv = oracle.rope_inv_freq(hd, 1e4)
     qnb, knb, ib = ctx.floats(qn), ctx.floats(kn), ctx.floats(inv)
     plane = kvh * cap * hd * 2
-    caches = [[ctx.buffer(plane), ctx.buffer(plane)] for _ in range(2)]
+    caches = [[ctx.buffer(plane), ctx.buffer(plane)] for _ in range(3)]
     for pair in caches:
         for c in pair:
             c.zero()
@@ -169,6 +170,8 @@ def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh,
     status.zero()
     sb = ctx.buffer(cuda.decode_attention_scratch_bytes(heads, kvh, hd, cap))
     sb.zero()
+    sb2 = ctx.buffer(cuda.decode_attention_scratch_bytes(heads, kvh, hd, cap))
+    sb2.zero()
     for pos in range(steps):
         q = T.activations(pos, 30, heads * hd)
         k = T.activations(pos, 31, kvh * hd)
@@ -186,6 +189,17 @@ def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh,
                                  status, heads, kvh, hd, hd, cap, window, eps, scale)
         ctx.u32_add(pos_buf, 1, 1)
         np.testing.assert_array_equal(f32(of, heads * hd), f32(oa, heads * hd))
+        # (c) the latency-optimised kernel: same mathematics, tolerance-qualified
+        og = ctx.buffer(heads * hd * 4)
+        ctx.attention_decode_dev(ctx.floats(q), ctx.floats(k), ctx.floats(v), qnb, knb, ib, caches[2][0], caches[2][1],
+                                 og, sb2, pos_buf, 0, status, heads, kvh, hd, hd, cap, window, eps, scale, exact=False)
+        ctx.u32_add(pos_buf, 0, 1)
+        assert rel_err(f32(og, heads * hd), f32(oa, heads * hd)) <= 1e-4
+    # its stored K rows agree to f16 rounding (different norm / sincos summation order)
+    ka = caches[0][0].download(0, plane, np.float16).astype(np.float32)
+    kb = caches[2][0].download(0, plane, np.float16).astype(np.float32)
+    assert rel_err(kb, ka) <= 2e-3
+    np.testing.assert_array_equal(caches[0][1].download(0, plane), caches[2][1].download(0, plane))
     for i in range(2):
         np.testing.assert_array_equal(caches[0][i].download(0, plane), caches[1][i].download(0, plane))
     assert int(status.download(0, 4, np.uint32)[0]) == 0

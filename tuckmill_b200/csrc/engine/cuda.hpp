@@ -239,10 +239,10 @@ public:
                               const CudaBuffer &vc, const CudaBuffer &out, const CudaBuffer &scratch,
                               const CudaBuffer &pos, uint32_t pos_index, const CudaBuffer &status, uint32_t heads,
                               uint32_t kvh, uint32_t hd, uint32_t n_rot, uint32_t cap, uint32_t window, float eps,
-                              float scale) const {
+                              float scale, bool exact) const {
         TM_CALL(tm_cuda_attention_decode_dev, q.raw(), k.raw(), v.raw(), qn.raw(), kn.raw(), inv_freq.raw(),
                 kc.raw(), vc.raw(), out.raw(), scratch.raw(), pos.raw(), pos_index, status.raw(), heads, kvh, hd,
-                n_rot, cap, window, eps, scale);
+                n_rot, cap, window, eps, scale, exact ? 1 : 0);
     }
 
     // ---- grouping / measurement (crates/tuckcore/src/qwen35_gpu.rs:62-86) ----

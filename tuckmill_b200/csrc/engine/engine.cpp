@@ -296,13 +296,13 @@ struct AttentionBlock {
 
     // attn = attention(norm(x, pre_norm)) at the device-held position: 2 launches.
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pre_norm, const CudaBuffer &pos_buf,
-                const CudaBuffer &status) const {
+                const CudaBuffer &status, bool exact) const {
         ctx.q8_0_gemv_fused(qkv.buf, x, qkv_out, qkv.rows, qkv.cols, TM_CUDA_PRO_RMSNORM, &pre_norm, eps,
                             TM_CUDA_EPI_STORE);
         ctx.attention_decode_dev(q_view, k_view, v_view, q_norm, k_norm, inv_freq, k_cache, v_cache, attn, kv_scratch,
                                  pos_buf, 0, status, (uint32_t)spec.heads, (uint32_t)spec.kv_heads,
                                  (uint32_t)spec.head_dim, (uint32_t)spec.rope_dims, (uint32_t)cap,
-                                 (uint32_t)spec.window, eps, scale());
+                                 (uint32_t)spec.window, eps, scale(), exact);
     }
     // Chunk core over n queries at pos0.. (engine/metal.rs:1170-1233): every
     // chunk K/V row is stored before any chunk query attends.
@@ -348,8 +348,8 @@ struct Layer {
         return L;
     }
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pos_buf, const CudaBuffer &status,
-                size_t hidden, float eps) const {
-        mixer.decode(ctx, x, pre_norm, pos_buf, status);
+                size_t hidden, float eps, bool exact) const {
+        mixer.decode(ctx, x, pre_norm, pos_buf, status, exact);
         if (mixer_out_norm) {
             ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
             ctx.rmsnorm(proj, mixer_out_norm, proj, 1, (uint32_t)hidden, eps);
@@ -481,7 +481,7 @@ void EngineModel::encode_decode_step() {
     const ModelGraph &g = graph_;
     c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
                        g.embedding_scale, I.x);
-    for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps);
+    for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
     c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
                       &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
     c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity_ + 1,

@@ -4,6 +4,8 @@
 // completion counters); this is the CUDA design of the same contract: one
 // device + one in-order stream, stream capture for groups, events for
 // completion and GPU time.
+#include <cstdlib>
+
 #include "tm_cuda_internal.cuh"
 
 namespace {
@@ -172,6 +174,7 @@ tm_cuda_ctx *tm_cuda_create(int device, char *err, size_t err_cap) {
     ctx->device = device;
     ctx->sm_count = sms;
     ctx->smem_optin = (size_t)optin;
+    if (const char *e = getenv("TM_CUDA_PDL")) ctx->pdl = e[0] != '0';
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
         tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cannot create a stream: %s",
                 cudaGetErrorString(cudaGetLastError()));

@@ -67,6 +67,7 @@ struct tm_cuda_ctx {
     bool group_open = false;
     uint64_t group_kernels = 0;
     bool profiling = false;
+    bool pdl = true;                     // chain kernels with programmatic dependent launch
     std::deque<tm_commit> pending;       // committed, completion not yet observed
     tm_commit open_commit;               // the ungrouped dispatch being encoded
     std::vector<cudaEvent_t> event_pool;
@@ -150,3 +151,22 @@ inline size_t tm_q8_qplane_bytes(uint32_t rows, uint32_t cols) {
 // Checks `w` is a packed rows x cols Q8_0 matrix of this context.
 int tm_check_packed(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
                     char *err, size_t err_cap);
+
+// Launch on the context's stream, allowing the kernel to overlap the tail of
+// its predecessor (the kernel itself orders its dependent reads with
+// griddepcontrol.wait).
+template <class... KArgs, class... Args>
+inline cudaError_t tm_launch_pdl(tm_cuda_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -26,6 +26,8 @@ __global__ void scale_kernel(const float *x, float *y, float f, uint32_t n) {
         y[i] = x[i] * f;
 }
 __global__ void axpy_kernel(const float *a, float *y, float alpha, uint32_t n) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         y[i] = y[i] + alpha * a[i];
 }
@@ -49,12 +51,18 @@ __global__ void gelu_mul_kernel(const float *g, const float *u, float *o, uint32
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         o[i] = tmdev::gelu_tanh_f(g[i]) * u[i];
 }
-__global__ void u32_add_kernel(uint32_t *p, uint32_t delta) { *p += delta; }
+__global__ void u32_add_kernel(uint32_t *p, uint32_t delta) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    *p += delta;
+}
 
 // y[row] = x[row] * rsqrt(mean(x^2) + eps) * w; one CTA per row; in place is safe.
 __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const float *x, const float *w, float *y,
                                                            uint32_t cols, float eps) {
     __shared__ float red[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
     const float *xr = x + (size_t)blockIdx.x * cols;
     float *yr = y + (size_t)blockIdx.x * cols;
     const float ss = tmdev::block_sumsq(xr, cols, red);
@@ -93,6 +101,8 @@ __global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const float *x
                                                                   uint32_t *pi, uint32_t n) {
     __shared__ float tv[kWarps];
     __shared__ uint32_t ti[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
     float v = -INFINITY;
     uint32_t i = kArgmaxNone;
     for (uint32_t k = blockIdx.x * kThreads + threadIdx.x; k < n; k += kArgmaxGroups * kThreads) {
@@ -108,6 +118,8 @@ __global__ void __launch_bounds__(kThreads) argmax_final_kernel(const float *pv,
                                                                 uint32_t *mirror) {
     __shared__ float tv[kWarps];
     __shared__ uint32_t ti[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
     float v = threadIdx.x < kArgmaxGroups ? pv[threadIdx.x] : -INFINITY;
     uint32_t i = threadIdx.x < kArgmaxGroups ? pi[threadIdx.x] : kArgmaxNone;
     argmax_block(v, i, tv, ti);
@@ -121,14 +133,20 @@ __global__ void __launch_bounds__(kThreads) argmax_final_kernel(const float *pv,
 }
 
 // ---- RoPE / KV store ---------------------------------------------------------
+// (x, y) = (a c - b s, a s + b c), with the fused multiply-adds spelled out so
+// every kernel that rotates rounds the same way.
+__device__ __forceinline__ void rope_rotate(float a, float b, float c, float s, float &x, float &y) {
+    x = fmaf(a, c, -__fmul_rn(b, s));
+    y = fmaf(a, s, __fmul_rn(b, c));
+}
+
 // Split-half rotation of the first n_rot dims of `row`; pairs (i, i + n_rot/2).
 __device__ __forceinline__ void rope_pair(float *row, uint32_t i, uint32_t half_rot, uint32_t pos,
                                           const float *inv_freq) {
     const float angle = (float)pos * inv_freq[i];
     const float c = cosf(angle), s = sinf(angle);
     const float a = row[i], b = row[i + half_rot];
-    row[i] = a * c - b * s;
-    row[i + half_rot] = a * s + b * c;
+    rope_rotate(a, b, c, s, row[i], row[i + half_rot]);
 }
 
 // grid (n_q_heads + n_kv_heads, n tokens): q [n][n_q][hd], k [n][n_kv][hd].
@@ -186,9 +204,16 @@ __device__ float warp_sumsq_as_block(const float *x, uint32_t n, int lane) {
     return total;
 }
 
+// Value dim held in slot i of lane `lane`: with an even number of slots the
+// lane owns adjacent pairs (one 4-byte load per pair), otherwise single dims.
+template <int DPL>
+__device__ __forceinline__ uint32_t attn_dim(int lane, int i) {
+    return DPL % 2 == 0 ? 2u * lane + 64u * (i / 2) + (i & 1) : (uint32_t)lane + 32u * i;
+}
+
 // Partial attention of G query heads (shared memory qs[G][hd]) over the keys
-// [lo, hi) of the 32-key block starting at j0.  Lane `d` of o[g][i] holds value
-// dim d = lane + 32 i.
+// [lo, hi) of the 32-key block starting at j0.  Slot i of o[g] holds value dim
+// attn_dim(lane, i).  Per head the arithmetic does not depend on G.
 template <int G, int DPL>
 __device__ __forceinline__ void attend_block(const float *qs, const __half *kc, const __half *vc, uint32_t hd,
                                              uint32_t j0, uint32_t lo, uint32_t hi, float scale,
@@ -196,35 +221,45 @@ __device__ __forceinline__ void attend_block(const float *qs, const __half *kc, 
                                              int lane, float (&m)[G], float (&l)[G], float (&o)[G][DPL]) {
     const uint32_t j = j0 + lane;
     const bool valid = j >= lo && j < hi;
-    float dot[G];
+    // Four interleaved partial sums per head (chunk c of 8 dims goes to sum
+    // c % 4), added as (s0 + s1) + (s2 + s3).
+    float dot[G][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) dot[g] = 0.0f;
+    for (int g = 0; g < G; ++g) dot[g][0] = dot[g][1] = dot[g][2] = dot[g][3] = 0.0f;
     if (valid) {
         const __half *kr = (k_new && j == pos_new) ? k_new : kc + (size_t)j * hd;
-        for (uint32_t d = 0; d < hd; d += 8) {
-            const int4 raw = *(const int4 *)(kr + d);
-            const __half2 *h2 = (const __half2 *)&raw;
-            float kf[8];
+        constexpr int KB = DPL * 4 < 16 ? DPL * 4 : 16;  // 16-byte loads in flight (hd/8, at most 16)
+        for (uint32_t d0 = 0; d0 < hd; d0 += KB * 8) {
+            int4 raw[KB];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(h2[e]);
-                kf[2 * e] = f.x;
-                kf[2 * e + 1] = f.y;
-            }
+            for (int c = 0; c < KB; ++c) raw[c] = *(const int4 *)(kr + d0 + c * 8);
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4 q0 = *(const float4 *)(qs + g * hd + d), q1 = *(const float4 *)(qs + g * hd + d + 4);
-                float t = dot[g];
-                t = fmaf(q0.x, kf[0], t); t = fmaf(q0.y, kf[1], t); t = fmaf(q0.z, kf[2], t); t = fmaf(q0.w, kf[3], t);
-                t = fmaf(q1.x, kf[4], t); t = fmaf(q1.y, kf[5], t); t = fmaf(q1.z, kf[6], t); t = fmaf(q1.w, kf[7], t);
-                dot[g] = t;
+            for (int c = 0; c < KB; ++c) {
+                const uint32_t d = d0 + c * 8;
+                const __half2 *h2 = (const __half2 *)&raw[c];
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h2[e]);
+                    kf[2 * e] = f.x;
+                    kf[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float4 q0 = *(const float4 *)(qs + g * hd + d), q1 = *(const float4 *)(qs + g * hd + d + 4);
+                    float t = dot[g][c & 3];
+                    t = fmaf(q0.x, kf[0], t); t = fmaf(q0.y, kf[1], t); t = fmaf(q0.z, kf[2], t); t = fmaf(q0.w, kf[3], t);
+                    t = fmaf(q1.x, kf[4], t); t = fmaf(q1.y, kf[5], t); t = fmaf(q1.z, kf[6], t); t = fmaf(q1.w, kf[7], t);
+                    dot[g][c & 3] = t;
+                }
             }
         }
     }
     float p[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const float sc = valid ? dot[g] * scale : -INFINITY;
+        const float dsum = __fadd_rn(__fadd_rn(dot[g][0], dot[g][1]), __fadd_rn(dot[g][2], dot[g][3]));
+        const float sc = valid ? __fmul_rn(dsum, scale) : -INFINITY;
         float mx = sc;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -238,18 +273,36 @@ __device__ __forceinline__ void attend_block(const float *qs, const __half *kc, 
         for (int i = 0; i < DPL; ++i) o[g][i] = 0.0f;
     }
     const uint32_t jj0 = lo > j0 ? lo - j0 : 0, jj1 = (hi < j0 + kAttnBlock ? hi : j0 + kAttnBlock) - j0;
-#pragma unroll 4
-    for (uint32_t jj = jj0; jj < jj1; ++jj) {
-        const uint32_t jk = j0 + jj;
-        const __half *vr = (v_new && jk == pos_new) ? v_new : vc + (size_t)jk * hd;
-        float vf[DPL];
+    // Keys in increasing order; the value rows of VB keys are loaded before use.
+    constexpr int VB = DPL <= 4 ? 16 : 8;
+    for (uint32_t jb = jj0; jb < jj1; jb += VB) {
+        float vf[VB][DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) vf[i] = __half2float(vr[lane + 32 * i]);
+        for (int c = 0; c < VB; ++c) {
+            const uint32_t jk = j0 + jb + c;
+            const bool ok = jb + c < jj1;
+            const __half *vr = (v_new && jk == pos_new) ? v_new : vc + (size_t)(ok ? jk : j0 + jj0) * hd;
+            if (DPL % 2 == 0) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float pj = __shfl_sync(0xffffffffu, p[g], (int)jj);
+                for (int i = 0; i < DPL; i += 2) {
+                    const float2 f = __half22float2(*(const __half2 *)(vr + attn_dim<DPL>(lane, i)));
+                    vf[c][i] = f.x;
+                    vf[c][i + 1] = f.y;
+                }
+            } else {
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) o[g][i] = fmaf(pj, vf[i], o[g][i]);
+                for (int i = 0; i < DPL; ++i) vf[c][i] = __half2float(vr[attn_dim<DPL>(lane, i)]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < VB; ++c) {
+            if (jb + c >= jj1) break;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pj = __shfl_sync(0xffffffffu, p[g], (int)(jb + c));
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) o[g][i] = fmaf(pj, vf[c][i], o[g][i]);
+            }
         }
     }
 }
@@ -304,128 +357,471 @@ __global__ void __launch_bounds__(32) attention_chunk_kernel(const float *q, con
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[g][i] / L[g];
+        for (int i = 0; i < DPL; ++i) orow[g * hd + attn_dim<DPL>(lane, i)] = O[g][i] / L[g];
 }
 
-// Decode: grid (kv_heads, ceil(cap/32)), one warp per key block.  Every warp
-// norms and rotates its G query heads (cheap, avoids a dependency), the warp
-// whose block holds the new position also norms, rotates, rounds and stores
-// the new K/V row, each warp writes its block partial to `scratch`, and the
-// last warp to arrive for a KV head merges the blocks in order.
-//   scratch: float part[kv_heads][nblk][group][hd + 2] then u32 count[kv_heads]
-template <int G, int DPL>
+// Decode: grid (heads, ceil(cap/32)), one warp per (query head, key block).
+// Every warp norms and rotates its query head (cheap, avoids a dependency); the
+// warps whose block holds the new position also norm, rotate and round the new
+// K/V row (the first head of each group stores it), each warp writes its block
+// partial to `scratch`, and the last warp to arrive for a head merges that
+// head's blocks in order.
+//   scratch: float part[heads][nblk][hd + 2], then u32 count[heads]
+template <int DPL>
 __global__ void __launch_bounds__(32) attention_decode_kernel(
     const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
     const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos_p,
     uint32_t *status, uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot, uint32_t cap,
-    uint32_t window, float eps, float scale, uint32_t group0) {
-    __shared__ __align__(16) float qs[G * 32 * DPL];
+    uint32_t window, float eps, float scale) {
+    __shared__ __align__(16) float qs[32 * DPL];
     __shared__ __align__(16) float ks[32 * DPL];
     __shared__ __align__(16) __half kh[32 * DPL];
     __shared__ __align__(16) __half vh[32 * DPL];
     const int lane = threadIdx.x;
-    const uint32_t kvh = blockIdx.x, blk = blockIdx.y, group = heads / kv_heads;
+    const uint32_t head = blockIdx.x, blk = blockIdx.y, group = heads / kv_heads, kvh = head / group;
     const uint32_t nblk = (cap + kAttnBlock - 1) / kAttnBlock;
+    const __half *kp = kc + (size_t)kvh * cap * hd, *vp = vc + (size_t)kvh * cap * hd;
+    // The cache rows of this block do not depend on the predecessor's output
+    // (except the new row, taken from shared memory below): pull them close now.
+    {
+        const uint32_t j = min(blk * kAttnBlock + lane, cap - 1u);
+        for (uint32_t off = 0; off < hd * 2u; off += 128u) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(kp + (size_t)j * hd) + off));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(vp + (size_t)j * hd) + off));
+        }
+    }
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    // Every small input is fetched in one trip, before the position is needed.
+    // Lane l holds quads l and l + 32 of a row.
+    constexpr int QW = DPL > 4 ? 2 : 1;
+    constexpr int RP = (DPL + 1) / 2;
+    const uint32_t nquad = hd / 4, half_rot = n_rot / 2;
+    float4 qv[QW], qnv[QW], kv4[QW], knv[QW], vv4[QW];
+    float fr[RP];
+#pragma unroll
+    for (int w = 0; w < QW; ++w) {
+        const uint32_t quad = w * 32 + lane;
+        const bool ok = quad < nquad;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        qnv[w] = ok ? ((const float4 *)q_norm)[quad] : z;
+        knv[w] = ok ? ((const float4 *)k_norm)[quad] : z;
+        kv4[w] = ok ? ((const float4 *)(k + (size_t)kvh * hd))[quad] : z;
+        vv4[w] = ok ? ((const float4 *)(v + (size_t)kvh * hd))[quad] : z;
+        qv[w] = ok ? ((const float4 *)(q + (size_t)head * hd))[quad] : z;
+    }
+#pragma unroll
+    for (int r = 0; r < RP; ++r) fr[r] = lane + 32 * r < half_rot ? inv_freq[lane + 32 * r] : 0.0f;
     const uint32_t pos = *pos_p;
     if (pos >= cap) {
-        if (lane == 0 && blk == 0 && kvh == 0) atomicOr(status, 1u);
+        if (lane == 0 && blk == 0 && head == 0) atomicOr(status, 1u);
         return;
     }
     const uint32_t seq = pos + 1u, start = attn_start(seq, window);
     const uint32_t first = start / kAttnBlock, last = pos / kAttnBlock;
     if (blk < first || blk > last) return;
-    const uint32_t head0 = kvh * group + group0;
-    // q: per-head RMS norm then RoPE (rmsnorm_kernel + rope_kernel arithmetic)
-#pragma unroll 1
-    for (int g = 0; g < G; ++g) {
-        const float *src = q + (size_t)(head0 + g) * hd;
-        const float ss = warp_sumsq_as_block(src, hd, lane);
-        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-        for (uint32_t i = lane; i < hd; i += 32) qs[g * hd + i] = src[i] * inv * q_norm[i];
-        __syncwarp();
-        for (uint32_t i = lane; i < n_rot / 2; i += 32) rope_pair(qs + g * hd, i, n_rot / 2, pos, inv_freq);
+    float rc[RP], rs[RP];
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+        const float angle = (float)pos * fr[r];
+        rc[r] = cosf(angle);
+        rs[r] = sinf(angle);
     }
+    // Per-head RMS norm (the canonical sum-of-squares tree: quads of virtual
+    // warps 0 and 1, ordered sum) into shared memory, then RoPE in place.
+    auto norm_rope = [&](const float4 (&x)[QW], const float4 (&nw)[QW], float *dst) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < QW; ++w) {
+            float sq = tmdev::sumsq_quad(0.0f, x[w]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+            total += sq;
+        }
+        const float inv = 1.0f / sqrtf(total / (float)hd + eps);
+#pragma unroll
+        for (int w = 0; w < QW; ++w) {
+            const uint32_t quad = w * 32 + lane;
+            if (quad < nquad) {
+                float4 y;
+                y.x = x[w].x * inv * nw[w].x;
+                y.y = x[w].y * inv * nw[w].y;
+                y.z = x[w].z * inv * nw[w].z;
+                y.w = x[w].w * inv * nw[w].w;
+                ((float4 *)dst)[quad] = y;
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < RP; ++r) {
+            const uint32_t i = lane + 32 * r;
+            if (i < half_rot) {
+                const float a0 = dst[i], b0 = dst[i + half_rot];
+                rope_rotate(a0, b0, rc[r], rs[r], dst[i], dst[i + half_rot]);
+            }
+        }
+        __syncwarp();
+    };
+    norm_rope(qv, qnv, qs);
     const bool owns_new = blk == last;
     if (owns_new) {
-        const float *src = k + (size_t)kvh * hd;
-        const float ss = warp_sumsq_as_block(src, hd, lane);
-        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-        for (uint32_t i = lane; i < hd; i += 32) ks[i] = src[i] * inv * k_norm[i];
-        __syncwarp();
-        for (uint32_t i = lane; i < n_rot / 2; i += 32) rope_pair(ks, i, n_rot / 2, pos, inv_freq);
-        __syncwarp();
-        const float *vsrc = v + (size_t)kvh * hd;
-        for (uint32_t i = lane; i < hd; i += 32) {
-            kh[i] = __float2half_rn(ks[i]);
-            vh[i] = __float2half_rn(vsrc[i]);
-            if (group0 == 0) {
-                const size_t dst = ((size_t)kvh * cap + pos) * hd + i;
-                kc[dst] = kh[i];
-                vc[dst] = vh[i];
+        norm_rope(kv4, knv, ks);
+#pragma unroll
+        for (int w = 0; w < QW; ++w) {
+            const uint32_t quad = w * 32 + lane;
+            if (quad < nquad) {
+                const float4 kq = ((const float4 *)ks)[quad];
+                const __half2 k01 = __floats2half2_rn(kq.x, kq.y), k23 = __floats2half2_rn(kq.z, kq.w);
+                const __half2 v01 = __floats2half2_rn(vv4[w].x, vv4[w].y), v23 = __floats2half2_rn(vv4[w].z, vv4[w].w);
+                ((__half2 *)kh)[quad * 2] = k01;
+                ((__half2 *)kh)[quad * 2 + 1] = k23;
+                ((__half2 *)vh)[quad * 2] = v01;
+                ((__half2 *)vh)[quad * 2 + 1] = v23;
+                if (head % group == 0) {
+                    __half2 *kd = (__half2 *)(kc + ((size_t)kvh * cap + pos) * hd) + quad * 2;
+                    __half2 *vd = (__half2 *)(vc + ((size_t)kvh * cap + pos) * hd) + quad * 2;
+                    kd[0] = k01;
+                    kd[1] = k23;
+                    vd[0] = v01;
+                    vd[1] = v23;
+                }
             }
         }
     }
     __syncwarp();
-    const __half *kp = kc + (size_t)kvh * cap * hd, *vp = vc + (size_t)kvh * cap * hd;
-    float m[G], l[G], o[G][DPL];
-    attend_block<G, DPL>(qs, kp, vp, hd, blk * kAttnBlock, start, seq, scale, owns_new ? kh : nullptr,
+    float m[1], l[1], o[1][DPL];
+    attend_block<1, DPL>(qs, kp, vp, hd, blk * kAttnBlock, start, seq, scale, owns_new ? kh : nullptr,
                          owns_new ? vh : nullptr, pos, lane, m, l, o);
-    float *orow = out + (size_t)head0 * hd;
+    float *orow = out + (size_t)head * hd;
     if (first == last) {  // a single block: merge it into the empty state and finish
+        float M = -INFINITY, L = 0.0f, O[DPL];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float M = -INFINITY, L = 0.0f, O[DPL];
+        for (int i = 0; i < DPL; ++i) O[i] = 0.0f;
+        attend_merge<DPL>(M, L, O, m[0], l[0], o[0]);
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) O[i] = 0.0f;
-            attend_merge<DPL>(M, L, O, m[g], l[g], o[g]);
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[i] / L;
-        }
+        for (int i = 0; i < DPL; ++i) orow[attn_dim<DPL>(lane, i)] = O[i] / L;
         return;
     }
     const uint32_t stride = hd + 2;
-    float *part = scratch + (((size_t)kvh * nblk + blk) * group + group0) * stride;
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (lane == 0) {
-            part[g * stride] = m[g];
-            part[g * stride + 1] = l[g];
-        }
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) part[g * stride + 2 + lane + 32 * i] = o[g][i];
+    float *part = scratch + ((size_t)head * nblk + blk) * stride;
+    if (lane == 0) {
+        part[0] = m[0];
+        part[1] = l[0];
     }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) part[2 + attn_dim<DPL>(lane, i)] = o[0][i];
     __threadfence();
     __syncwarp();
-    uint32_t *count = (uint32_t *)(scratch + (size_t)kv_heads * nblk * group * stride) + kvh * 8 + group0 / 4;
+    uint32_t *count = (uint32_t *)(scratch + (size_t)heads * nblk * stride) + head;
     uint32_t arrived = 0;
     if (lane == 0) arrived = atomicAdd(count, 1u);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
     if (arrived != last - first) return;
     __threadfence();
-    float M[G], L[G], O[G][DPL];
+    float M = -INFINITY, L = 0.0f, O[DPL];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        M[g] = -INFINITY;
-        L[g] = 0.0f;
+    for (int i = 0; i < DPL; ++i) O[i] = 0.0f;
+    // Partials of 8 blocks are fetched together, then merged in block order.
+    for (uint32_t b0 = first; b0 <= last; b0 += 8) {
+        float mb[8], lb[8], ob[8][DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) O[g][i] = 0.0f;
-    }
-    for (uint32_t b = first; b <= last; ++b) {
-        const float *pb = scratch + (((size_t)kvh * nblk + b) * group + group0) * stride;
+        for (int c = 0; c < 8; ++c) {
+            const uint32_t b = b0 + c <= last ? b0 + c : last;
+            const float *pb = scratch + ((size_t)head * nblk + b) * stride;
+            mb[c] = __ldcg(pb);
+            lb[c] = __ldcg(pb + 1);
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float ob[DPL];
-            const float mb = __ldcg(pb + g * stride), lb = __ldcg(pb + g * stride + 1);
+            for (int i = 0; i < DPL; ++i) ob[c][i] = __ldcg(pb + 2 + attn_dim<DPL>(lane, i));
+        }
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) ob[i] = __ldcg(pb + g * stride + 2 + lane + 32 * i);
-            attend_merge<DPL>(M[g], L[g], O[g], mb, lb, ob);
+        for (int c = 0; c < 8; ++c) {
+            if (b0 + c > last) break;
+            attend_merge<DPL>(M, L, O, mb[c], lb[c], ob[c]);
         }
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) orow[g * hd + lane + 32 * i] = O[g][i] / L[g];
+    for (int i = 0; i < DPL; ++i) orow[attn_dim<DPL>(lane, i)] = O[i] / L;
     if (lane == 0) *count = 0u;  // ready for the next launch on this stream
+}
+
+// ---- decode attention, latency-optimised form ---------------------------------
+// Same mathematics as attention_decode_kernel, tolerance-qualified instead of
+// bit-identical to the prefill kernel (the engine uses it unless `exact` is
+// asked): one CTA of 128 threads per (KV head, 64-key split) serves all G query
+// heads of the group, so K and V are read once; the per-thread instruction
+// chain is short (two threads share a key's dot product, the value sum is
+// spread over dim pairs x key halves) and the last CTA to arrive for a KV head
+// merges the splits with a two-pass softmax, one thread per value dim.
+//   scratch: float part[kv_heads][nsplit][G][HD + 2], then u32 count[kv_heads]
+constexpr int kFastSplit = 64;
+constexpr int kFastThreads = 128;
+
+template <int G, int HD>
+__global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
+    const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
+    const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos_p,
+    uint32_t *status, uint32_t kv_heads, uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale) {
+    constexpr int EPL = HD / 32;          // elements of a head vector per lane (strided by 32)
+    constexpr int PAIRS = HD / 2;         // value dim pairs
+    constexpr int KP = kFastThreads / PAIRS > 0 ? kFastThreads / PAIRS : 1;  // key parts in the value sum
+    constexpr int PPT = PAIRS / kFastThreads > 0 ? PAIRS / kFastThreads : 1; // dim pairs per thread
+    __shared__ __align__(16) float qs[G][HD];
+    __shared__ __align__(16) __half kh[HD];
+    __shared__ __align__(16) __half vh[HD];
+    __shared__ float sc[G][kFastSplit];
+    __shared__ float stat[G][2];
+    __shared__ float opart[KP][G][HD];
+    __shared__ uint32_t s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y;
+    const uint32_t nsplit = (cap + kFastSplit - 1) / kFastSplit;
+    const __half *kp = kc + (size_t)kvh * cap * HD, *vp = vc + (size_t)kvh * cap * HD;
+    {   // cache rows of this split: independent of the predecessor, pull them close
+        const uint32_t j = min(split * kFastSplit + (tid >> 1), cap - 1u);
+        const uint32_t half_bytes = HD;  // half a row of f16
+        for (uint32_t off = 0; off < half_bytes; off += 128u) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(kp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(vp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
+        }
+    }
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t pos = *pos_p;
+    if (pos >= cap) {
+        if (tid == 0 && split == 0 && kvh == 0) atomicOr(status, 1u);
+        return;
+    }
+    const uint32_t seq = pos + 1u, start = attn_start(seq, window);
+    const uint32_t first = start / kFastSplit, last = pos / kFastSplit;
+    if (split < first || split > last) return;
+    const bool owns_new = split == last;
+    (void)n_rot;
+
+    // ---- vectors q_0..q_{G-1} (and k for the owning split): RMS norm + RoPE, one warp each ----
+    for (int vec = warp; vec < G + (owns_new ? 1 : 0); vec += kFastThreads / 32) {
+        const bool is_k = vec == G;
+        const float *src = is_k ? k + (size_t)kvh * HD : q + ((size_t)kvh * G + vec) * HD;
+        const float *nw = is_k ? k_norm : q_norm;
+        float x[EPL], w[EPL];
+#pragma unroll
+        for (int r = 0; r < EPL; ++r) {
+            x[r] = src[lane + 32 * r];
+            w[r] = nw[lane + 32 * r];
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < EPL; ++r) ss = fmaf(x[r], x[r], ss);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int r = 0; r < EPL; ++r) x[r] = x[r] * inv * w[r];
+        // full rotation (n_rot == HD, checked by the host): pair (i, i + HD/2), i = lane + 32 r,
+        // has both members in this lane
+#pragma unroll
+        for (int r = 0; r < EPL / 2; ++r) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[lane + 32 * r], &sn, &cs);
+            const float a0 = x[r], b0 = x[r + EPL / 2];
+            x[r] = a0 * cs - b0 * sn;
+            x[r + EPL / 2] = a0 * sn + b0 * cs;
+        }
+        if (is_k) {
+            const float *vsrc = v + (size_t)kvh * HD;
+#pragma unroll
+            for (int r = 0; r < EPL; ++r) {
+                const uint32_t e = lane + 32 * r;
+                const __half hk = __float2half_rn(x[r]), hv = __float2half_rn(vsrc[e]);
+                kh[e] = hk;
+                vh[e] = hv;
+                kc[((size_t)kvh * cap + pos) * HD + e] = hk;
+                vc[((size_t)kvh * cap + pos) * HD + e] = hv;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < EPL; ++r) qs[vec][lane + 32 * r] = x[r];
+        }
+    }
+    __syncthreads();
+    // ---- scores: two threads per key, half the dims each ----
+    {
+        const uint32_t jj = tid >> 1, hsel = tid & 1, j = split * kFastSplit + jj;
+        const bool valid = j >= start && j < seq;
+        float dot[G][2];
+#pragma unroll
+        for (int g = 0; g < G; ++g) dot[g][0] = dot[g][1] = 0.0f;
+        if (valid) {
+            const __half *kr = (owns_new && j == pos ? kh : kp + (size_t)j * HD) + hsel * (HD / 2);
+            constexpr int NL = HD / 16;  // 16-byte loads per thread
+            int4 raw[NL];
+#pragma unroll
+            for (int c = 0; c < NL; ++c) raw[c] = *(const int4 *)(kr + c * 8);
+#pragma unroll
+            for (int c = 0; c < NL; ++c) {
+                const __half2 *h2 = (const __half2 *)&raw[c];
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h2[e]);
+                    kf[2 * e] = f.x;
+                    kf[2 * e + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float *qp = &qs[g][hsel * (HD / 2) + c * 8];
+                    const float4 q0 = *(const float4 *)qp, q1 = *(const float4 *)(qp + 4);
+                    float t = dot[g][c & 1];
+                    t = fmaf(q0.x, kf[0], t); t = fmaf(q0.y, kf[1], t); t = fmaf(q0.z, kf[2], t); t = fmaf(q0.w, kf[3], t);
+                    t = fmaf(q1.x, kf[4], t); t = fmaf(q1.y, kf[5], t); t = fmaf(q1.z, kf[6], t); t = fmaf(q1.w, kf[7], t);
+                    dot[g][c & 1] = t;
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float d = dot[g][0] + dot[g][1];
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            if (hsel == 0) sc[g][jj] = valid ? d * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    // ---- split softmax: warp g owns head g ----
+    for (int g = warp; g < G; g += kFastThreads / 32) {
+        const float s0 = sc[g][lane], s1 = sc[g][lane + 32];
+        float mx = fmaxf(s0, s1);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float p0 = s0 == -INFINITY ? 0.0f : expf(s0 - mx), p1 = s1 == -INFINITY ? 0.0f : expf(s1 - mx);
+        float sum = p0 + p1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        sc[g][lane] = p0;
+        sc[g][lane + 32] = p1;
+        if (lane == 0) {
+            stat[g][0] = mx;
+            stat[g][1] = sum;
+        }
+    }
+    __syncthreads();
+    // ---- values: thread = (dim pair(s), key part); keys of a part in order ----
+    {
+        const uint32_t kpart = tid / PAIRS < KP ? tid / PAIRS : 0, dp0 = tid % PAIRS;
+        constexpr int KEYS = kFastSplit / KP;
+        const uint32_t jbase = split * kFastSplit + kpart * KEYS;
+        float acc[PPT][G][2];
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[pp][g][0] = acc[pp][g][1] = 0.0f;
+#pragma unroll 1
+        for (int kb = 0; kb < KEYS; kb += 8) {
+            __half2 vv[8][PPT];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t j = jbase + kb + c;
+                const uint32_t jc = j < seq ? j : pos;  // rows past the sequence carry weight 0
+                const __half *vr = owns_new && jc == pos ? vh : vp + (size_t)jc * HD;
+#pragma unroll
+                for (int pp = 0; pp < PPT; ++pp) vv[c][pp] = *(const __half2 *)(vr + 2 * (dp0 + pp * kFastThreads));
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pj = sc[g][kpart * KEYS + kb + c];
+#pragma unroll
+                    for (int pp = 0; pp < PPT; ++pp) {
+                        const float2 f = __half22float2(vv[c][pp]);
+                        acc[pp][g][0] = fmaf(pj, f.x, acc[pp][g][0]);
+                        acc[pp][g][1] = fmaf(pj, f.y, acc[pp][g][1]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const uint32_t d = 2 * (dp0 + pp * kFastThreads);
+                opart[kpart][g][d] = acc[pp][g][0];
+                opart[kpart][g][d + 1] = acc[pp][g][1];
+            }
+    }
+    __syncthreads();
+    // ---- this split's (m, l, o); finish here when it is the only one ----
+    const bool single = first == last;
+    constexpr uint32_t stride = HD + 2;
+    float *part = scratch + ((size_t)kvh * nsplit + split) * G * stride;
+    for (uint32_t i = tid; i < G * HD; i += kFastThreads) {
+        const uint32_t g = i / HD, d = i % HD;
+        float o = 0.0f;
+#pragma unroll
+        for (int kq = 0; kq < KP; ++kq) o += opart[kq][g][d];
+        if (single) out[((size_t)kvh * G + g) * HD + d] = o / stat[g][1];
+        else part[g * stride + 2 + d] = o;
+    }
+    if (single) return;
+    if (tid < G) {
+        part[tid * stride] = stat[tid][0];
+        part[tid * stride + 1] = stat[tid][1];
+    }
+    __threadfence();
+    __syncthreads();
+    uint32_t *count = (uint32_t *)(scratch + (size_t)kv_heads * nsplit * G * stride) + kvh;
+    if (tid == 0) s_last = atomicAdd(count, 1u) == last - first ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // ---- merge with a running maximum, one thread per (head, dim); the partials
+    // of 8 splits are fetched together so the loop costs one trip per 8 splits ----
+    for (uint32_t i = tid; i < G * HD; i += kFastThreads) {
+        const uint32_t g = i / HD, d = i % HD;
+        const float *base = scratch + ((size_t)kvh * nsplit + first) * G * stride + g * stride;
+        const uint32_t nact = last - first + 1;
+        float M = -INFINITY, L = 0.0f, O = 0.0f;
+        for (uint32_t s0 = 0; s0 < nact; s0 += 8) {
+            float mb[8], lb[8], ob[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float *pb = base + (size_t)(s0 + c < nact ? s0 + c : nact - 1) * G * stride;
+                mb[c] = __ldcg(pb);
+                lb[c] = __ldcg(pb + 1);
+                ob[c] = __ldcg(pb + 2 + d);
+            }
+            float mx = M;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (s0 + c < nact) mx = fmaxf(mx, mb[c]);
+            const float a = expf(M - mx);
+            L *= a;
+            O *= a;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (s0 + c < nact) {
+                    const float wgt = expf(mb[c] - mx);
+                    L = fmaf(wgt, lb[c], L);
+                    O = fmaf(wgt, ob[c], O);
+                }
+            M = mx;
+        }
+        out[((size_t)kvh * G + g) * HD + d] = O / L;
+    }
+    if (tid == 0) *count = 0u;  // ready for the next launch on this stream
+}
+
+template <int G, int HD>
+void launch_decode_fast(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v, const float *qn,
+                        const float *kn, const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch,
+                        const uint32_t *pos, uint32_t *status, uint32_t kvh, uint32_t n_rot, uint32_t cap,
+                        uint32_t window, float eps, float scale) {
+    tm_launch_pdl(ctx, attention_decode_fast_kernel<G, HD>, dim3(kvh, (cap + kFastSplit - 1) / kFastSplit),
+                  dim3(kFastThreads), 0, q, k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, kvh, n_rot, cap,
+                  window, eps, scale);
+}
+
+inline bool attn_fast_ok(uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot) {
+    const uint32_t g = heads / kv_heads;
+    return (hd == 128 || hd == 256) && n_rot == hd && (g == 1 || g == 2 || g == 4);
 }
 
 // Launch helpers: G heads per warp (the group size, in chunks of at most 4) and
@@ -438,14 +834,14 @@ void launch_chunk(cudaStream_t st, const float *q, const __half *kc, const __hal
                                                                  scale, window);
 }
 
-template <int G, int DPL>
-void launch_decode(cudaStream_t st, const float *q, const float *k, const float *v, const float *qn, const float *kn,
+template <int DPL>
+void launch_decode(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v, const float *qn, const float *kn,
                    const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos,
                    uint32_t *status, uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot, uint32_t cap,
-                   uint32_t window, float eps, float scale, uint32_t group0) {
-    attention_decode_kernel<G, DPL><<<dim3(kvh, (cap + kAttnBlock - 1) / kAttnBlock), 32, 0, st>>>(
-        q, k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, heads, kvh, hd, n_rot, cap, window, eps, scale,
-        group0);
+                   uint32_t window, float eps, float scale) {
+    tm_launch_pdl(ctx, attention_decode_kernel<DPL>, dim3(heads, (cap + kAttnBlock - 1) / kAttnBlock), dim3(32), 0, q,
+                  k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, heads, kvh, hd, n_rot, cap, window, eps,
+                  scale);
 }
 
 #define TM_ATTN_DISPATCH(FN, G, DPL, ...)                                         \
@@ -492,7 +888,8 @@ int tm_cuda_f32_axpy(tm_cuda_ctx *ctx, tm_cuda_buffer *a, tm_cuda_buffer *y, flo
     TM_CHECK_BUF(a, (size_t)n * 4, "a");
     TM_CHECK_BUF(y, (size_t)n * 4, "y");
     TM_OP_BEGIN("f32_axpy");
-    axpy_kernel<<<grid_for(n), 256, 0, ctx->stream>>>((const float *)a->dev, (float *)y->dev, alpha, n);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, axpy_kernel, dim3(grid_for(n)), dim3(256), 0, (const float *)a->dev,
+                              (float *)y->dev, alpha, n));
     TM_OP_END(1);
 }
 
@@ -561,7 +958,7 @@ int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint3
     TM_ENTER();
     TM_CHECK_BUF(buf, ((size_t)index + 1) * 4, "counter");
     TM_OP_BEGIN("u32_add");
-    u32_add_kernel<<<1, 1, 0, ctx->stream>>>((uint32_t *)buf->dev + index, delta);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, u32_add_kernel, dim3(1), dim3(1), 0, (uint32_t *)buf->dev + index, delta));
     TM_OP_END(1);
 }
 
@@ -575,9 +972,8 @@ int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *wei
     TM_CHECK_BUF(y, (size_t)rows * cols * 4, "y");
     TM_CHECK_BUF(weight, (size_t)cols * 4, "norm weight");
     TM_OP_BEGIN("rmsnorm");
-    rmsnorm_kernel<<<rows, kThreads, 0, ctx->stream>>>((const float *)x->dev,
-                                                       (const float *)weight->dev, (float *)y->dev,
-                                                       cols, eps);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, rmsnorm_kernel, dim3(rows), dim3(kThreads), 0, (const float *)x->dev,
+                              (const float *)weight->dev, (float *)y->dev, cols, eps));
     TM_OP_END(1);
 }
 
@@ -590,9 +986,10 @@ static int argmax_common(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cud
     TM_OP_BEGIN("argmax");
     float *pv = (float *)partial->dev;
     uint32_t *pi = (uint32_t *)(partial->dev + 256);
-    argmax_partial_kernel<<<kArgmaxGroups, kThreads, 0, ctx->stream>>>((const float *)x->dev, pv, pi, n);
-    argmax_final_kernel<<<1, kThreads, 0, ctx->stream>>>(pv, pi, (uint32_t *)out->dev, out_index, pos,
-                                                         out_cap, mirror);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_partial_kernel, dim3(kArgmaxGroups), dim3(kThreads), 0,
+                              (const float *)x->dev, pv, pi, n));
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_final_kernel, dim3(1), dim3(kThreads), 0, (const float *)pv,
+                              (const uint32_t *)pi, (uint32_t *)out->dev, out_index, pos, out_cap, mirror));
     TM_OP_END(2);
 }
 
@@ -741,7 +1138,8 @@ size_t tm_cuda_attention_decode_scratch_bytes(uint32_t heads, uint32_t kv_heads,
                                               uint32_t cap) {
     if (heads == 0 || kv_heads == 0 || cap == 0) return 0;
     const size_t nblk = (cap + kAttnBlock - 1) / kAttnBlock;
-    return ((size_t)heads * nblk * (head_dim + 2) + (size_t)kv_heads * 8) * 4;
+    (void)kv_heads;
+    return ((size_t)heads * nblk * (head_dim + 2) + (size_t)heads) * 4;
 }
 
 int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
@@ -751,8 +1149,8 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                                  tm_cuda_buffer *scratch, tm_cuda_buffer *pos_buf,
                                  uint32_t pos_index, tm_cuda_buffer *status, uint32_t heads,
                                  uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
-                                 uint32_t cap, uint32_t window, float eps, float scale, char *err,
-                                 size_t err_cap) {
+                                 uint32_t cap, uint32_t window, float eps, float scale, int exact,
+                                 char *err, size_t err_cap) {
     TM_ENTER();
     if (heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 32 || !attn_shape_ok(head_dim) ||
         n_rot == 0 || n_rot > head_dim || n_rot % 2 != 0 || cap == 0 || cap > 65535u * kAttnBlock)
@@ -774,17 +1172,39 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
     TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
     TM_CHECK_BUF(status, 4, "status");
     TM_OP_BEGIN("attention_decode");
-    const uint32_t group = heads / kv_heads;
-    uint64_t launches = 0;
-    for (uint32_t g0 = 0; g0 < group; g0 += 4) {
-        const uint32_t G = group - g0 < 4 ? group - g0 : 4;
-        TM_ATTN_DISPATCH(launch_decode, G, head_dim / 32, ctx->stream, (const float *)q->dev, (const float *)k->dev,
-                         (const float *)v->dev, (const float *)q_norm->dev, (const float *)k_norm->dev,
-                         (const float *)inv_freq->dev, (__half *)k_cache->dev, (__half *)v_cache->dev,
-                         (float *)out->dev, (float *)scratch->dev, (const uint32_t *)pos_buf->dev + pos_index,
-                         (uint32_t *)status->dev, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, g0);
-        ++launches;
+    const float *qp = (const float *)q->dev, *kp = (const float *)k->dev, *vp = (const float *)v->dev;
+    const float *qn = (const float *)q_norm->dev, *kn = (const float *)k_norm->dev, *fq = (const float *)inv_freq->dev;
+    __half *kcp = (__half *)k_cache->dev, *vcp = (__half *)v_cache->dev;
+    float *op = (float *)out->dev, *sp = (float *)scratch->dev;
+    const uint32_t *pp = (const uint32_t *)pos_buf->dev + pos_index;
+    uint32_t *stp = (uint32_t *)status->dev;
+    if (!exact && attn_fast_ok(heads, kv_heads, head_dim, n_rot)) {
+#define TM_FAST(G, HD)                                                                                       \
+    launch_decode_fast<G, HD>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, kv_heads, n_rot, cap, window, \
+                              eps, scale)
+        switch ((heads / kv_heads) * 1000 + head_dim) {
+            case 1128: TM_FAST(1, 128); break;
+            case 2128: TM_FAST(2, 128); break;
+            case 4128: TM_FAST(4, 128); break;
+            case 1256: TM_FAST(1, 256); break;
+            case 2256: TM_FAST(2, 256); break;
+            default: TM_FAST(4, 256); break;
+        }
+#undef TM_FAST
+        TM_OP_END(1);
     }
+#define TM_DECODE(DPL)                                                                                        \
+    launch_decode<DPL>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads, head_dim, n_rot, \
+                       cap, window, eps, scale)
+    switch (head_dim / 32) {
+        case 1: TM_DECODE(1); break;
+        case 2: TM_DECODE(2); break;
+        case 3: TM_DECODE(3); break;
+        case 4: TM_DECODE(4); break;
+        default: TM_DECODE(8); break;
+    }
+#undef TM_DECODE
+    const uint64_t launches = 1;
     TM_OP_END(launches);
 }
 

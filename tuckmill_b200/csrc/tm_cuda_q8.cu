@@ -87,22 +87,49 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     const uint32_t n_tiles = (rows + 15u) / 16u;
     const uint32_t n_chunks = (cols + kChunkCols - 1u) / kChunkCols;
 
-    // Weights do not depend on the activations: start pulling this warp's
-    // first tile towards L2 while the activations are being staged.
-    {
-        const uint32_t tile = blockIdx.x * tiles_per_cta + my_tile;
-        if (tile < n_tiles) {
-            const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+    // Weights do not depend on the activations: this warp's first batch of
+    // chunks is loaded into registers (and the next batch prefetched towards
+    // L2) before the activations are staged, so the two latencies overlap.
+    constexpr int U = 4;  // chunks whose loads are issued before any is consumed
+    int4 wa[U], wb[U];
+    unsigned short ha[U], hb[U];
+    auto load_batch = [&](uint32_t tile, uint32_t ch0) {
+        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+        const signed char *pa = a.q + (size_t)row_a * cols + t4 * 16u;
+        const signed char *pb = a.q + (size_t)row_b * cols + t4 * 16u;
+        const unsigned short *sa = (const unsigned short *)a.d + (size_t)row_a * nb + (t4 >> 1);
+        const unsigned short *sb = (const unsigned short *)a.d + (size_t)row_b * nb + (t4 >> 1);
 #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j) {
-                const uint32_t c0 = (my_ks + j * ks) * kChunkCols + t4 * 16u;
-                if (c0 < cols) {
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_a * cols + c0));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_b * cols + c0));
-                }
+        for (int u = 0; u < U; ++u) {
+            const uint32_t ch = ch0 + u * ks;
+            const bool inb = ch < n_chunks && ch * kChunkCols + t4 * 16u < cols;
+            wa[u] = wb[u] = make_int4(0, 0, 0, 0);
+            ha[u] = hb[u] = 0;
+            if (inb) {
+                wa[u] = ldg_stream((const int4 *)(pa + (size_t)ch * kChunkCols));
+                wb[u] = ldg_stream((const int4 *)(pb + (size_t)ch * kChunkCols));
+                ha[u] = __ldg(sa + ch * 2u);
+                hb[u] = __ldg(sb + ch * 2u);
+            }
+        }
+    };
+    const uint32_t first_base = blockIdx.x * tiles_per_cta;
+    if (first_base + my_tile < n_tiles) {
+        load_batch(first_base + my_tile, my_ks);
+        const uint32_t tile = first_base + my_tile;
+        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+#pragma unroll
+        for (uint32_t j = U; j < 2 * U; ++j) {
+            const uint32_t c0 = (my_ks + j * ks) * kChunkCols + t4 * 16u;
+            if (c0 < cols) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_a * cols + c0));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_b * cols + c0));
             }
         }
     }
+
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();  // the activations (and y, for the accumulate epilogue) come from the predecessor
 
     // ---- stage the activations: elementwise prologue, then digit planes ----
 #pragma unroll 1
@@ -110,14 +137,18 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
         const float *xm = a.x + (size_t)m * cols;
         signed char *dig = (signed char *)(smem + (size_t)m * tok);
         float *coef = (float *)(smem + (size_t)m * tok + 4u * (size_t)plane);
-        float inv_rms = 0.0f;
-        if (a.prologue == TM_CUDA_PRO_RMSNORM) {
-            const float ss = block_sumsq(xm, cols, red);
-            inv_rms = 1.0f / sqrtf(ss / (float)cols + a.eps);
-        }
         // Each thread takes 4 consecutive columns, so 8 adjacent lanes own one
         // 32-column block; kBatch such quads are loaded before any is digitised.
         constexpr int kBatch = 4;
+        // Up to 4096 columns the whole row sits in one batch of registers and the
+        // RMS norm's sum of squares is taken from them (one trip to memory);
+        // wider rows make a separate pass first.  Same canonical tree either way.
+        const bool one_pass = cols <= (uint32_t)(kThreads * 4 * kBatch);
+        float inv_rms = 0.0f;
+        if (a.prologue == TM_CUDA_PRO_RMSNORM && !one_pass) {
+            const float ss = block_sumsq(xm, cols, red);
+            inv_rms = 1.0f / sqrtf(ss / (float)cols + a.eps);
+        }
         const bool vec_ok = (((size_t)xm | (size_t)a.pro) & 15u) == 0 && (cols & 3u) == 0;
 #pragma unroll 1
         for (uint32_t cb = 0; cb < cols; cb += kThreads * 4 * kBatch) {
@@ -139,6 +170,12 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
                         if (pp) ps[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
                     }
                 }
+            }
+            if (a.prologue == TM_CUDA_PRO_RMSNORM && one_pass) {
+                float sq = 0.0f;  // thread t owns quads t, t+256, ... in this order (zero quads add nothing)
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) sq = tmdev::sumsq_quad(sq, vs[i]);
+                inv_rms = 1.0f / sqrtf(tmdev::block_reduce_sumsq(sq, red) / (float)cols + a.eps);
             }
 #pragma unroll
             for (int i = 0; i < kBatch; ++i) {
@@ -164,23 +201,26 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
                 if (c < cols) {
                     const bool bad = !(amax <= 3.402823466e38f);
                     int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 5;
-                    e = e < -126 ? -126 : e > 122 ? 122 : e;
+                    e = e < -100 ? -100 : e > 122 ? 122 : e;  // blocks below 2^-94 digitise to (near) zero
                     const float inv = __uint_as_float((uint32_t)(127 - e) << 23);
+                    // t = v * 2^-e (|t| < 64, exact) is rounded once to a multiple of 2^-21
+                    // and split into balanced base-128 digits with integer arithmetic:
+                    // T = a0 2^21 + a1 2^14 + a2 2^7 + a3, a1..a3 in [-64, 63].
+                    const float inv21 = inv * 2097152.0f;
                     uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        float r = v[j] * inv;  // |r| < 64, exact
-                        const float a0 = rintf(r);
-                        r = (r - a0) * 128.0f;
-                        const float a1 = rintf(r);
-                        r = (r - a1) * 128.0f;
-                        const float a2 = rintf(r);
-                        r = (r - a2) * 128.0f;
-                        const float a3 = rintf(r);
-                        w0 |= ((uint32_t)(int)a0 & 0xffu) << (8 * j);
-                        w1 |= ((uint32_t)(int)a1 & 0xffu) << (8 * j);
-                        w2 |= ((uint32_t)(int)a2 & 0xffu) << (8 * j);
-                        w3 |= ((uint32_t)(int)a3 & 0xffu) << (8 * j);
+                        int T = __float2int_rn(v[j] * inv21);
+                        const int a3 = (int)((uint32_t)T << 25) >> 25;
+                        T = (T - a3) >> 7;
+                        const int a2 = (int)((uint32_t)T << 25) >> 25;
+                        T = (T - a2) >> 7;
+                        const int a1 = (int)((uint32_t)T << 25) >> 25;
+                        const int a0 = (T - a1) >> 7;
+                        w0 |= ((uint32_t)a0 & 0xffu) << (8 * j);
+                        w1 |= ((uint32_t)a1 & 0xffu) << (8 * j);
+                        w2 |= ((uint32_t)a2 & 0xffu) << (8 * j);
+                        w3 |= ((uint32_t)a3 & 0xffu) << (8 * j);
                     }
                     *(uint32_t *)(dig + c) = w0;
                     *(uint32_t *)(dig + plane + c) = w1;
@@ -205,35 +245,14 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     for (uint32_t base = blockIdx.x * tiles_per_cta; base < n_tiles; base += gridDim.x * tiles_per_cta) {
         const uint32_t tile = base + my_tile;
         const bool tile_ok = tile < n_tiles;
-        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
         float acc[M][2];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m][0] = acc[m][1] = 0.0f;
 
         if (tile_ok) {
-            // Per-lane bases; a chunk advances them by 64 quants / 2 scales.
-            const signed char *pa = a.q + (size_t)row_a * cols + t4 * 16u;
-            const signed char *pb = a.q + (size_t)row_b * cols + t4 * 16u;
-            const unsigned short *sa = (const unsigned short *)a.d + (size_t)row_a * nb + (t4 >> 1);
-            const unsigned short *sb = (const unsigned short *)a.d + (size_t)row_b * nb + (t4 >> 1);
-            constexpr int U = 4;  // chunks whose loads are issued before any is consumed
 #pragma unroll 1
             for (uint32_t ch0 = my_ks; ch0 < n_chunks; ch0 += ks * U) {
-                int4 wa[U], wb[U];
-                unsigned short ha[U], hb[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t ch = ch0 + u * ks;
-                    const bool inb = ch < n_chunks && ch * kChunkCols + t4 * 16u < cols;
-                    wa[u] = wb[u] = make_int4(0, 0, 0, 0);
-                    ha[u] = hb[u] = 0;
-                    if (inb) {
-                        wa[u] = ldg_stream((const int4 *)(pa + (size_t)ch * kChunkCols));
-                        wb[u] = ldg_stream((const int4 *)(pb + (size_t)ch * kChunkCols));
-                        ha[u] = __ldg(sa + ch * 2u);
-                        hb[u] = __ldg(sb + ch * 2u);
-                    }
-                }
+                if (base != first_base || ch0 != my_ks) load_batch(tile, ch0);  // the first batch is already here
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const uint32_t ch = ch0 + u * ks;
@@ -319,8 +338,7 @@ cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t s
         if (e != cudaSuccess) return e;
         attr_set[ctx->device] = true;
     }
-    q8_gemv_kernel<M><<<grid, kThreads, smem, ctx->stream>>>(a);
-    return cudaGetLastError();
+    return tm_launch_pdl(ctx, q8_gemv_kernel<M>, dim3(grid), dim3(kThreads), smem, a);
 }
 
 uint32_t digit_plane_bytes(uint32_t cols) {
@@ -335,9 +353,9 @@ cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
     const size_t smem = (size_t)m * token_smem(a.cols, a.plane);
     const uint32_t n_tiles = (a.rows + 15u) / 16u;
     const uint32_t n_chunks = (a.cols + kChunkCols - 1u) / kChunkCols;
-    const uint32_t want = (uint32_t)ctx->sm_count * 32u;  // warps that fill the machine
+    const uint32_t want = (uint32_t)ctx->sm_count * 2u * kWarps;  // warps of one resident wave (2 CTAs per SM)
     uint32_t ks = 1;
-    while (ks < (uint32_t)kWarps && n_tiles * ks < want && ks * 2u <= n_chunks) ks <<= 1;
+    while (ks < (uint32_t)kWarps && n_tiles * ks * 2u <= want && ks * 2u <= n_chunks) ks <<= 1;
     a.ks = ks;
     const uint32_t tiles_per_cta = kWarps / ks;
     uint32_t ctas = (n_tiles + tiles_per_cta - 1u) / tiles_per_cta;
@@ -436,6 +454,8 @@ __global__ void q8_row_indirect_kernel(const signed char *q, const __half *d, ui
                                        uint32_t cols, const uint32_t *ids, uint32_t slot,
                                        const uint32_t *pos, int bias, uint32_t ids_len, float scale,
                                        float *out) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
     uint32_t s = slot;
     if (pos) s = slot + *pos + (uint32_t)bias;
     long row = -1;
@@ -635,10 +655,10 @@ static int row_indirect(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint
         pos = (const uint32_t *)pos_buf->dev + pos_index;
     }
     TM_OP_BEGIN("row_indirect");
-    q8_row_indirect_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(
-        (const signed char *)w->qp, (const __half *)w->dp, rows,
-        cols, (const uint32_t *)ids->dev, slot, pos, bias, (uint32_t)(ids->len / 4), scale,
-        (float *)out->dev);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, q8_row_indirect_kernel, dim3((cols + 255) / 256), dim3(256), 0,
+                              (const signed char *)w->qp, (const __half *)w->dp, rows, cols,
+                              (const uint32_t *)ids->dev, slot, pos, (int)bias, (uint32_t)(ids->len / 4), scale,
+                              (float *)out->dev));
     TM_OP_END(1);
 }
 

@@ -75,7 +75,7 @@ _OPS = {
     "qwen35_kv_store_f16_chunk": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
     "qwen35_attention_f16": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F],
     "qwen35_attention_f16_chunk": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
-    "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F],
+    "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
 }
 
 
@@ -343,10 +343,10 @@ class CudaContext:
         self._call("qwen35_attention_f16_chunk", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos0, cap, head_dim, group, scale, n, window)
 
     def attention_decode_dev(self, q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, out, scratch, pos_buf,
-                             pos_index, status, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale):
+                             pos_index, status, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, exact=True):
         self._call("attention_decode_dev", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle,
                    inv_freq.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, pos_buf.handle,
-                   pos_index, status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale)
+                   pos_index, status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, int(exact))
 
     def u32_add(self, buf, index, delta): self._call("u32_add", buf.handle, index, delta)
 

@@ -167,6 +167,15 @@ int tm_cuda_q8_0_gemm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm
 int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x,
                           tm_cuda_buffer *y, uint32_t rows, uint32_t cols, uint32_t batch,
                           uint32_t x_off, uint32_t y_off, char *err, size_t err_cap);
+/* No counterpart: the tensor-core GEMM reads an f16 copy of X through TMA; the
+ * copy lives in a workspace owned by the context (cols * batch * 2 bytes,
+ * counted in tm_cuda_allocated_bytes).  It grows on demand, except inside an
+ * open dispatch group, where it must have been reserved beforehand. */
+size_t tm_cuda_mma_workspace_bytes(uint32_t cols, uint32_t batch);
+int tm_cuda_mma_workspace_reserve(tm_cuda_ctx *ctx, size_t bytes, char *err, size_t err_cap);
+/* No counterpart: 1 when a tensor-core GEMM of this context gave up one of its
+ * bounded pipeline waits (its output is then undefined); waits for the stream. */
+int tm_cuda_mma_aborted(tm_cuda_ctx *ctx);
 /* tm_metal.h:151 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
 int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
                          uint32_t cols, uint32_t out_off, char *err, size_t err_cap);

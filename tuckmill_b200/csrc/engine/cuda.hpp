@@ -176,6 +176,10 @@ public:
                        uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off) const {
         TM_CALL(tm_cuda_q8_0_gemm_mma, w.raw(), x.raw(), y.raw(), rows, cols, batch, x_off, y_off);
     }
+    void mma_workspace_reserve(size_t bytes) const {
+        char e[256] = "";
+        cuda_check(tm_cuda_mma_workspace_reserve(ctx_, bytes, e, sizeof e), e);
+    }
     void q8_0_row(const CudaBuffer &w, const CudaBuffer &out, uint32_t row, uint32_t cols, uint32_t out_off) const {
         TM_CALL(tm_cuda_q8_0_row_f32, w.raw(), out.raw(), row, cols, out_off);
     }

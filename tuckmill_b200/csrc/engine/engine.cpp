@@ -137,6 +137,13 @@ struct Matrix {
 // token-major, `n` = prefill batch.
 struct PrefillScratch {
     CudaBuffer x, h, a, b, c, e, proj, h2, g, u, d2, ascr;
+    // f16 copy of the widest GEMM input of a chunk (the tensor-core GEMM's TMA source).
+    static size_t mma_workspace(const ModelGraph &g, size_t n) {
+        size_t widest = g.hidden;
+        for (const LayerSpec &l : g.layers)
+            widest = std::max(widest, std::max(l.mixer.heads * l.mixer.head_dim, l.ffn.width));
+        return tm_cuda_mma_workspace_bytes((uint32_t)widest, (uint32_t)n);
+    }
     static void plan(const ModelGraph &g, size_t cap, size_t n, Plan &p) {
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
         for (const LayerSpec &l : g.layers) {
@@ -407,6 +414,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     p.scratch_bytes(16);                      // device position
     p.scratch_bytes(16);                      // status word
     PrefillScratch::plan(graph, capacity, std::min<size_t>(opts.prefill_batch, capacity), p);
+    if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, std::min<size_t>(opts.prefill_batch, capacity)));
     GpuAllocPlan out;
     out.weights = p.weights;
     out.state = p.state;
@@ -449,6 +457,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     I.pos_buf = c.zeros(16);
     I.status = c.zeros(16, true);
     I.scratch = PrefillScratch::alloc(c, graph, capacity, std::min<size_t>(opts.prefill_batch, capacity));
+    if (!opts.exact) c.mma_workspace_reserve(PrefillScratch::mma_workspace(graph, std::min<size_t>(opts.prefill_batch, capacity)));
     m->graph_ = std::move(graph);
     const ModelGraph &g = m->graph_;
 

@@ -110,6 +110,12 @@ def load_library() -> C.CDLL:
     L.tm_cuda_buffer_device_ptr.argtypes = [_P, _P]
     L.tm_cuda_buffer_len.restype = _SZ
     L.tm_cuda_buffer_len.argtypes = [_P, _P]
+    L.tm_cuda_mma_workspace_bytes.restype = _SZ
+    L.tm_cuda_mma_workspace_bytes.argtypes = [_U32, _U32]
+    L.tm_cuda_mma_workspace_reserve.restype = C.c_int
+    L.tm_cuda_mma_workspace_reserve.argtypes = [_P, _SZ] + _ERR
+    L.tm_cuda_mma_aborted.restype = C.c_int
+    L.tm_cuda_mma_aborted.argtypes = [_P]
     L.tm_cuda_q8_0_packed_bytes.restype = _SZ
     L.tm_cuda_q8_0_packed_bytes.argtypes = [_U32, _U32]
     L.tm_cuda_graph_free.argtypes = [_P, _P]
@@ -315,6 +321,9 @@ class CudaContext:
 
     def q8_0_gemm_mma(self, w, x, y, rows, cols, batch, x_off=0, y_off=0):
         self._call("q8_0_gemm_mma", w.handle, x.handle, y.handle, rows, cols, batch, x_off, y_off)
+
+    def mma_workspace_reserve(self, nbytes: int): self._call("mma_workspace_reserve", nbytes)
+    def mma_aborted(self) -> bool: return bool(self._l.tm_cuda_mma_aborted(self.handle))
 
     def q8_0_gemv_fused(self, w, x, y, rows, cols, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
         self._call("q8_0_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)

@@ -318,6 +318,36 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                                  uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
                                  uint32_t cap, uint32_t window, float eps, float scale, int exact,
                                  char *err, size_t err_cap);
+/* No counterpart in the reference.  tm_cuda_attention_decode_dev for callers that
+ * must not allocate: a serving process that has handed every byte of HBM to its
+ * own arena at start-up, so that a later cudaMalloc fails or forces the driver
+ * to synchronise the whole device in the middle of a token; or a host that is
+ * only allowed to touch memory it was given (a sandboxed plug-in, a worker
+ * whose ledger must equal its plan to the byte).  Such a caller has no buffer
+ * to pass as `scratch`, so this variant takes none: the per-key-block partials
+ * and the arrival counters live in an array built into the library image (one
+ * copy on every device that loads the library, kept until the process exits).
+ * Limit: tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap)
+ * must not exceed tm_cuda_attention_decode_static_max_scratch() (9 MiB: e.g. 16
+ * heads x 128 dims up to a capacity of ~36000, 64 heads x 128 up to ~9000); a
+ * larger geometry is refused with TM_CUDA_ERR_BOUNDS and a message naming both
+ * sizes.  The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress); make that first call before any stream capture
+ * begins.  Every call on a device shares the one array and each call clears
+ * the counters it is about to use, so two calls whose kernels overlap on the
+ * GPU (different streams or contexts of one device) race: keep them ordered.
+ * Inputs, outputs and results are those of tm_cuda_attention_decode_dev.  The
+ * call launches directly on the context's stream and is not entered in the
+ * committed / completed dispatch counters or the profile table. */
+size_t tm_cuda_attention_decode_static_max_scratch(void);
+int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
+                                        tm_cuda_buffer *v, tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm,
+                                        tm_cuda_buffer *inv_freq, tm_cuda_buffer *k_cache,
+                                        tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                        tm_cuda_buffer *pos_buf, uint32_t pos_index, tm_cuda_buffer *status,
+                                        uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
+                                        uint32_t cap, uint32_t window, float eps, float scale, int exact,
+                                        char *err, size_t err_cap);
 /* No counterpart: buf[index] += delta (u32), to advance a device position
  * inside a recorded graph. */
 int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint32_t delta,

@@ -1208,4 +1208,108 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
     TM_OP_END(launches);
 }
 
+// ---- decode attention without any allocation ----------------------------------
+// Scratch of the entry point below: lives in the library image, one copy per
+// device that loads it, held until the process exits.
+constexpr size_t kStaticDecodeScratchBytes = 9u << 20;
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticDecodeScratchBytes];
+// Device address of that array per device (the symbol's name is only a host-side
+// stand-in; kernels must be handed the address cudaGetSymbolAddress returns).
+static unsigned char *g_static_decode_scratch_ptr[64] = {};
+
+size_t tm_cuda_attention_decode_static_max_scratch(void) { return kStaticDecodeScratchBytes; }
+
+int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
+                                        tm_cuda_buffer *v, tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm,
+                                        tm_cuda_buffer *inv_freq, tm_cuda_buffer *k_cache,
+                                        tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                        tm_cuda_buffer *pos_buf, uint32_t pos_index, tm_cuda_buffer *status,
+                                        uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
+                                        uint32_t cap, uint32_t window, float eps, float scale, int exact,
+                                        char *err, size_t err_cap) {
+    TM_ENTER();
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 32 || !attn_shape_ok(head_dim) ||
+        n_rot == 0 || n_rot > head_dim || n_rot % 2 != 0 || cap == 0 || cap > 65535u * kAttnBlock)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
+                       "decode attention geometry: heads %u/%u, head_dim %u (32, 64, 96, 128 or 256), n_rot %u, "
+                       "capacity %u", heads, kv_heads, head_dim, n_rot, cap);
+    const size_t need = tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap);
+    if (need > kStaticDecodeScratchBytes)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
+                       "heads %u x capacity %u x head_dim %u needs %zu bytes of scratch; the built-in scratch of the "
+                       "allocation-free entry point holds %zu (use tm_cuda_attention_decode_dev with a caller buffer)",
+                       heads, cap, head_dim, need, (size_t)kStaticDecodeScratchBytes);
+    if (ctx->device < 0 || ctx->device >= 64)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "device index %d outside 0..63", ctx->device);
+    const size_t plane = (size_t)kv_heads * cap * head_dim * 2;
+    TM_CHECK_BUF(q, (size_t)heads * head_dim * 4, "q");
+    TM_CHECK_BUF(k, (size_t)kv_heads * head_dim * 4, "k");
+    TM_CHECK_BUF(v, (size_t)kv_heads * head_dim * 4, "v");
+    TM_CHECK_BUF(q_norm, (size_t)head_dim * 4, "q norm");
+    TM_CHECK_BUF(k_norm, (size_t)head_dim * 4, "k norm");
+    TM_CHECK_BUF(inv_freq, (size_t)(n_rot / 2) * 4, "inv_freq");
+    TM_CHECK_BUF(k_cache, plane, "k cache");
+    TM_CHECK_BUF(v_cache, plane, "v cache");
+    TM_CHECK_BUF(out, (size_t)heads * head_dim * 4, "attention output");
+    TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
+    TM_CHECK_BUF(status, 4, "status");
+    // Set-up, once per device, with that device current (TM_ENTER made it so).
+    if (!g_static_decode_scratch_ptr[ctx->device]) {
+        unsigned char *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_static_decode_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cudaGetSymbolAddress of the built-in scratch failed: %s",
+                           cudaGetErrorString(e));
+        }
+        g_static_decode_scratch_ptr[ctx->device] = p;
+    }
+    float *sp = (float *)g_static_decode_scratch_ptr[ctx->device];
+    // The array keeps whatever the previous call left: the arrival counters (the
+    // tail of the region this geometry uses) must start at zero.  Both kernels
+    // keep their counters inside the last `heads` words of `need`.
+    TM_CUDA_TRY(cudaMemsetAsync((unsigned char *)sp + need - (size_t)heads * 4, 0, (size_t)heads * 4, ctx->stream));
+    const float *qp = (const float *)q->dev, *kp = (const float *)k->dev, *vp = (const float *)v->dev;
+    const float *qn = (const float *)q_norm->dev, *kn = (const float *)k_norm->dev, *fq = (const float *)inv_freq->dev;
+    __half *kcp = (__half *)k_cache->dev, *vcp = (__half *)v_cache->dev;
+    float *op = (float *)out->dev;
+    const uint32_t *pp = (const uint32_t *)pos_buf->dev + pos_index;
+    uint32_t *stp = (uint32_t *)status->dev;
+    if (!exact && attn_fast_ok(heads, kv_heads, head_dim, n_rot)) {
+        // the fast kernel keeps kv_heads counters right after its partials; clear those too
+        const size_t nsplit = (cap + kFastSplit - 1) / kFastSplit;
+        const size_t off = (size_t)heads * nsplit * (head_dim + 2) * 4;
+        TM_CUDA_TRY(cudaMemsetAsync((unsigned char *)sp + off, 0, (size_t)kv_heads * 4, ctx->stream));
+#define TM_FAST(G, HD)                                                                                       \
+    launch_decode_fast<G, HD>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, kv_heads, n_rot, cap, window, \
+                              eps, scale)
+        switch ((heads / kv_heads) * 1000 + head_dim) {
+            case 1128: TM_FAST(1, 128); break;
+            case 2128: TM_FAST(2, 128); break;
+            case 4128: TM_FAST(4, 128); break;
+            case 1256: TM_FAST(1, 256); break;
+            case 2256: TM_FAST(2, 256); break;
+            default: TM_FAST(4, 256); break;
+        }
+#undef TM_FAST
+    } else {
+#define TM_DECODE(DPL)                                                                                        \
+    launch_decode<DPL>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads, head_dim, n_rot, \
+                       cap, window, eps, scale)
+        switch (head_dim / 32) {
+            case 1: TM_DECODE(1); break;
+            case 2: TM_DECODE(2); break;
+            case 3: TM_DECODE(3); break;
+            case 4: TM_DECODE(4); break;
+            default: TM_DECODE(8); break;
+        }
+#undef TM_DECODE
+    }
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "launch failed: %s", cudaGetErrorString(le));
+    ctx->launches.fetch_add(1);
+    return TM_CUDA_OK;
+}
+
 }  // extern "C"

@@ -76,6 +76,7 @@ _OPS = {
     "qwen35_attention_f16": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F],
     "qwen35_attention_f16_chunk": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
     "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
+    "attention_decode_dev_static": [_P] * 11 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
 }
 
 
@@ -148,6 +149,12 @@ def decode_attention_scratch_bytes(heads: int, kv_heads: int, head_dim: int, cap
     L.tm_cuda_attention_decode_scratch_bytes.restype = C.c_size_t
     L.tm_cuda_attention_decode_scratch_bytes.argtypes = [_U32] * 4
     return int(L.tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap))
+
+
+def decode_attention_static_max_scratch() -> int:
+    L = load_library()
+    L.tm_cuda_attention_decode_static_max_scratch.restype = C.c_size_t
+    return int(L.tm_cuda_attention_decode_static_max_scratch())
 
 
 def packed_bytes(rows: int, cols: int) -> int:
@@ -356,6 +363,14 @@ class CudaContext:
         self._call("attention_decode_dev", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle,
                    inv_freq.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, pos_buf.handle,
                    pos_index, status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, int(exact))
+
+    def attention_decode_dev_static(self, q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, out, pos_buf, pos_index,
+                                    status, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, exact=True):
+        """The decode attention core for callers that may not allocate: no scratch
+        argument, the library's built-in scratch array is used instead."""
+        self._call("attention_decode_dev_static", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle,
+                   inv_freq.handle, k_cache.handle, v_cache.handle, out.handle, pos_buf.handle, pos_index,
+                   status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, int(exact))
 
     def u32_add(self, buf, index, delta): self._call("u32_add", buf.handle, index, delta)
 

@@ -368,6 +368,37 @@ int tm_cuda_row_indirect_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t r
                                  uint32_t pos_index, int32_t bias, float scale,
                                  tm_cuda_buffer *out, char *err, size_t err_cap);
 
+/* ---------------- multi-GPU output-row split (no counterpart: the reference is
+ * single-device) ----------------
+ * Rank r of `world` GPUs of one box owns rows [r*N/world, (r+1)*N/world) of every
+ * projection and of the lm_head, runs the operators above on its slice, and an
+ * all-gather over NVLink reassembles each output vector.  NCCL is loaded at run
+ * time; a process that never calls these needs no NCCL. */
+/* 128-byte rendezvous id, created on one rank and handed to the others by the host. */
+int tm_cuda_comm_unique_id(void *out128, char *err, size_t err_cap);
+/* Join the communicator (collective over all ranks; one per context). */
+int tm_cuda_comm_init(tm_cuda_ctx *ctx, const void *id128, int rank, int world, char *err, size_t err_cap);
+int tm_cuda_comm_rank(const tm_cuda_ctx *ctx, int *rank, int *world);
+/* dst[dst_off + r*count + i] = rank r's src[src_off + i]; on the context's stream,
+ * recordable in a dispatch group. */
+int tm_cuda_all_gather_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t src_off, tm_cuda_buffer *dst,
+                           uint32_t dst_off, uint32_t count, char *err, size_t err_cap);
+/* Row-wise form for a chunk of n_rows token rows: dst[t][r*width + c] = rank r's
+ * src[t][c].  `stage` (world*n_rows*width f32) receives NCCL's rank-major result
+ * before the interleave; unused when n_rows == 1. */
+int tm_cuda_all_gather_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *stage, tm_cuda_buffer *dst,
+                                uint32_t n_rows, uint32_t width, char *err, size_t err_cap);
+/* Greedy token of a row-sharded head: argmax of the local logits slice (global
+ * index = local + index_offset), all-gather of the (value, index) pairs (8 bytes
+ * per rank instead of the logits), then the single-device rule over the pairs
+ * (larger value, ties to the lower GLOBAL index), so every rank writes the token
+ * one device would have chosen to out[base + pos_buf[pos_index]] (pos_buf may be
+ * NULL: out[base]).  `pairs` holds (world + 1) * 8 bytes. */
+int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, uint32_t index_offset,
+                               tm_cuda_buffer *partial, tm_cuda_buffer *pairs, tm_cuda_buffer *out, uint32_t base,
+                               tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
+                               tm_cuda_buffer *mirror, char *err, size_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

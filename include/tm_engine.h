@@ -46,7 +46,19 @@ typedef struct {
     uint32_t prefill_batch;   /* 0 = default (512) */
     int exact;                /* 1: batched projections keep the GEMV arithmetic */
     uint64_t budget_bytes;    /* B of R + U + H <= B; 0 = the device's total memory */
+    /* Output-row split over the devices of one node, one process per device.
+     * shard_world 0 or 1 = single device.  Otherwise every process loads the same
+     * artifact with its own shard_rank and the SAME comm_id (128 bytes from
+     * tm_engine_comm_id on rank 0, handed to the others by the launcher); rank r
+     * keeps rows [r*N/world, (r+1)*N/world) of each projection and of the head,
+     * whole attention heads stay on one rank, and every call below becomes a
+     * collective that all ranks make in the same order. */
+    uint32_t shard_rank, shard_world;
+    const void *comm_id;
 } tm_engine_options;
+
+/* 128 opaque bytes naming a new communicator (tm_cuda_comm_unique_id). */
+int tm_engine_comm_id(void *out128, char *err, size_t err_cap);
 
 typedef struct {
     uint32_t vocab, hidden, layers, context, prefill_batch;
@@ -96,6 +108,11 @@ int tm_engine_decode_ungrouped(tm_engine *e, uint32_t steps, char *err, size_t e
  * TM_ENGINE_*_EXCEEDS_BUDGET when the plan does not fit. */
 int tm_engine_plan(const char *gguf_path, uint32_t context, uint64_t budget_bytes, tm_engine_info *out,
                    char *err, size_t err_cap);
+/* The same for one rank of an output-row split: plan_weights / plan_state /
+ * plan_scratch are that rank's exact device bytes (the embedding table is
+ * replicated, every projection and the KV cache are divided). */
+int tm_engine_plan_shard(const char *gguf_path, uint32_t context, uint64_t budget_bytes, uint32_t shard_rank,
+                         uint32_t shard_world, tm_engine_info *out, char *err, size_t err_cap);
 
 #ifdef __cplusplus
 }

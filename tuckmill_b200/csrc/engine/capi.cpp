@@ -103,6 +103,14 @@ int tm_engine_load(const tm_engine_options *o, tm_engine **out, char *err, size_
         EngineOptions eo;
         eo.prefill_batch = o->prefill_batch ? o->prefill_batch : kPrefillBatchDefault;
         eo.exact = o->exact != 0;
+        eo.shard_world = o->shard_world ? o->shard_world : 1;
+        eo.shard_rank = o->shard_rank;
+        if (eo.shard_world > 1) {
+            if (!o->comm_id) throw TuckmillError(ErrorCode::InvalidRequest, "a row split needs a communicator id");
+            if (eo.shard_rank >= eo.shard_world)
+                throw TuckmillError(ErrorCode::InvalidRequest, "shard rank outside the split");
+            e->ctx->comm_init(o->comm_id, (int)eo.shard_rank, (int)eo.shard_world);
+        }
         e->prefill_batch = eo.prefill_batch;
         // Exact preflight, then every class against its reservation BEFORE any
         // allocation (crates/tuckcore/src/executor.rs:1543-1562).
@@ -121,6 +129,13 @@ int tm_engine_load(const tm_engine_options *o, tm_engine **out, char *err, size_
                                     "Rebuild the plan for this executor; understated reservations are never loaded.");
         e->model = EngineModel::load_with(e->ctx, std::move(graph), *e->weights, o->context, alloc.total(), eo);
         *out = e.release();
+    })
+}
+
+int tm_engine_comm_id(void *out128, char *err, size_t err_cap) {
+    GUARD({
+        char e[256] = {0};
+        if (tm_cuda_comm_unique_id(out128, e, sizeof e) != TM_CUDA_OK) throw TuckmillError(ErrorCode::Unavailable, e);
     })
 }
 
@@ -203,7 +218,13 @@ int tm_engine_decode_ungrouped(tm_engine *e, uint32_t steps, char *err, size_t e
 
 int tm_engine_plan(const char *gguf_path, uint32_t context, uint64_t budget_bytes, tm_engine_info *out,
                    char *err, size_t err_cap) {
+    return tm_engine_plan_shard(gguf_path, context, budget_bytes, 0, 1, out, err, err_cap);
+}
+
+int tm_engine_plan_shard(const char *gguf_path, uint32_t context, uint64_t budget_bytes, uint32_t shard_rank,
+                         uint32_t shard_world, tm_engine_info *out, char *err, size_t err_cap) {
     GUARD({
+        if (!gguf_path || !out) throw TuckmillError(ErrorCode::InvalidRequest, "null plan arguments");
         GgufInspection insp = GgufInspection::open(gguf_path);
         GgufWeights w(insp);
         ModelGraph g = adapt(insp);
@@ -213,6 +234,8 @@ int tm_engine_plan(const char *gguf_path, uint32_t context, uint64_t budget_byte
         out->layers = (uint32_t)g.layers.size();
         out->context = context;
         EngineOptions eo;
+        eo.shard_rank = shard_rank;
+        eo.shard_world = shard_world ? shard_world : 1;
         const GpuAllocPlan alloc = alloc_plan_with(g, w, context, eo);
         out->plan_weights = alloc.weights;
         out->plan_state = alloc.state;

@@ -249,6 +249,22 @@ public:
                 n_rot, cap, window, eps, scale, exact ? 1 : 0);
     }
 
+    // ---- multi-GPU row split ----
+    void comm_init(const void *id128, int rank, int world) const {
+        char e[256] = "";
+        cuda_check(tm_cuda_comm_init(ctx_, id128, rank, world, e, sizeof e), e);
+    }
+    void all_gather_rows(const CudaBuffer &src, const CudaBuffer &stage, const CudaBuffer &dst, uint32_t n_rows,
+                         uint32_t width) const {
+        TM_CALL(tm_cuda_all_gather_rows_f32, src.raw(), stage.raw(), dst.raw(), n_rows, width);
+    }
+    void argmax_sharded(const CudaBuffer &x, uint32_t n, uint32_t index_offset, const CudaBuffer &partial,
+                        const CudaBuffer &pairs, const CudaBuffer &out, uint32_t base, const CudaBuffer *pos,
+                        uint32_t pos_index, uint32_t out_cap, const CudaBuffer *mirror) const {
+        TM_CALL(tm_cuda_argmax_sharded_dev, x.raw(), n, index_offset, partial.raw(), pairs.raw(), out.raw(), base,
+                pos ? pos->raw() : nullptr, pos_index, out_cap, mirror ? mirror->raw() : nullptr);
+    }
+
     // ---- grouping / measurement (crates/tuckcore/src/qwen35_gpu.rs:62-86) ----
     void begin_group() const {
         char e[256] = "";

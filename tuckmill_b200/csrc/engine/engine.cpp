@@ -41,6 +41,12 @@ std::vector<float> rope_inv_freq(size_t rope_dims, float base) {
     return out;
 }
 
+// Output-row split: this rank owns rows [rank*n/world, (rank+1)*n/world) of every
+// projection (each output element needs one weight row and the whole input).
+struct Shard {
+    uint32_t rank = 0, world = 1;
+};
+
 // A device matrix: one or more Q8_0 tensors of equal width, rows concatenated,
 // repacked into the two-plane form at upload (crates/tuckcore/src/engine/
 // metal.rs:107-226 uploads the GGUF bytes verbatim; the row concatenation and
@@ -51,7 +57,8 @@ struct Matrix {
     std::vector<uint32_t> part_rows;
     uint32_t rows = 0, cols = 0;
 
-    static void geometry(const WeightSource &src, const std::vector<Tensor> &ts, uint32_t *rows, uint32_t *cols) {
+    static void geometry(const WeightSource &src, const std::vector<Tensor> &ts, Shard sh, uint32_t *rows,
+                         uint32_t *cols) {
         *rows = 0;
         *cols = 0;
         for (Tensor t : ts) {
@@ -68,20 +75,25 @@ struct Matrix {
                 throw TuckmillError(ErrorCode::InvalidArtifact, "Q8_0 tensor rows are not block aligned");
             if (*cols != 0 && *cols != (uint32_t)d.first)
                 throw TuckmillError(ErrorCode::Internal, "fused projections differ in input width");
+            if (d.second % sh.world != 0)
+                throw TuckmillError(ErrorCode::InvalidRequest,
+                                    "tensor " + std::to_string(t.index) + " has " + std::to_string(d.second) +
+                                        " rows, not divisible by the " + std::to_string(sh.world) + " devices of the split");
             *cols = (uint32_t)d.first;
-            *rows += (uint32_t)d.second;
+            *rows += (uint32_t)(d.second / sh.world);
         }
     }
 
-    static uint64_t plan(const WeightSource &src, const std::vector<Tensor> &ts) {
+    static uint64_t plan(const WeightSource &src, const std::vector<Tensor> &ts, Shard sh = Shard()) {
         uint32_t rows, cols;
-        geometry(src, ts, &rows, &cols);
+        geometry(src, ts, sh, &rows, &cols);
         return tm_cuda_q8_0_packed_bytes(rows, cols);
     }
 
-    static Matrix load(const CudaContext &ctx, const WeightSource &src, const std::vector<Tensor> &ts) {
+    static Matrix load(const CudaContext &ctx, const WeightSource &src, const std::vector<Tensor> &ts,
+                       Shard sh = Shard()) {
         Matrix m;
-        geometry(src, ts, &m.rows, &m.cols);
+        geometry(src, ts, sh, &m.rows, &m.cols);
         m.buf = ctx.buffer(tm_cuda_q8_0_packed_bytes(m.rows, m.cols));
         const size_t row_bytes = (size_t)m.cols / 32 * 34;
         const size_t step = std::max<size_t>(1, kStagingChunkBytes / row_bytes);
@@ -89,10 +101,11 @@ struct Matrix {
         std::vector<unsigned char> host(step * row_bytes);
         uint32_t row0 = 0;
         for (Tensor t : ts) {
-            const uint32_t n = (uint32_t)src.tensor_dims(t.index).second;
+            const uint32_t n = (uint32_t)(src.tensor_dims(t.index).second / sh.world);
+            const uint64_t first = (uint64_t)sh.rank * n;  // this rank's first row of the tensor
             for (uint32_t r = 0; r < n; r += (uint32_t)step) {
                 const uint32_t k = std::min<uint32_t>((uint32_t)step, n - r);
-                src.read_tensor_into(t.index, (uint64_t)r * row_bytes, host.data(), (size_t)k * row_bytes);
+                src.read_tensor_into(t.index, (first + r) * row_bytes, host.data(), (size_t)k * row_bytes);
                 stage.upload(0, host.data(), (size_t)k * row_bytes);
                 ctx.q8_0_pack(m.buf, m.rows, m.cols, stage, 0, row0 + r, k);
             }
@@ -137,6 +150,12 @@ struct Matrix {
 // token-major, `n` = prefill batch.
 struct PrefillScratch {
     CudaBuffer x, h, a, b, c, e, proj, h2, g, u, d2, ascr;
+    CudaBuffer loc, loc2, stage, efull;  // row-split only: local GEMM outputs, NCCL staging, gathered attention
+    static size_t widest(const ModelGraph &g) {
+        size_t w = g.hidden;
+        for (const LayerSpec &l : g.layers) w = std::max(w, std::max(l.mixer.heads * l.mixer.head_dim, l.ffn.width));
+        return w;
+    }
     // f16 copy of the widest GEMM input of a chunk (the tensor-core GEMM's TMA source).
     static size_t mma_workspace(const ModelGraph &g, size_t n) {
         size_t widest = g.hidden;
@@ -144,7 +163,13 @@ struct PrefillScratch {
             widest = std::max(widest, std::max(l.mixer.heads * l.mixer.head_dim, l.ffn.width));
         return tm_cuda_mma_workspace_bytes((uint32_t)widest, (uint32_t)n);
     }
-    static void plan(const ModelGraph &g, size_t cap, size_t n, Plan &p) {
+    static void plan(const ModelGraph &g, size_t cap, size_t n, Shard sh, Plan &p) {
+        if (sh.world > 1) {
+            size_t awf = 0;
+            for (const LayerSpec &l : g.layers) awf = std::max(awf, l.mixer.heads * l.mixer.head_dim);
+            for (int i = 0; i < 3; ++i) p.scratch_f32(n * widest(g));
+            p.scratch_f32(n * awf);
+        }
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
         for (const LayerSpec &l : g.layers) {
             aw = std::max(aw, l.mixer.heads * l.mixer.head_dim);
@@ -158,7 +183,7 @@ struct PrefillScratch {
         (void)cap;
         p.scratch_f32(1);  // the chunk attention streams key blocks; its scratch argument is a placeholder
     }
-    static PrefillScratch alloc(const CudaContext &ctx, const ModelGraph &g, size_t cap, size_t n) {
+    static PrefillScratch alloc(const CudaContext &ctx, const ModelGraph &g, size_t cap, size_t n, Shard sh) {
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
         for (const LayerSpec &l : g.layers) {
             aw = std::max(aw, l.mixer.heads * l.mixer.head_dim);
@@ -181,45 +206,81 @@ struct PrefillScratch {
         (void)heads;
         (void)cap;
         s.ascr = zeros_f32(ctx, 1);
+        if (sh.world > 1) {
+            s.loc = zeros_f32(ctx, n * widest(g));
+            s.loc2 = zeros_f32(ctx, n * widest(g));
+            s.stage = zeros_f32(ctx, n * widest(g));
+            s.efull = zeros_f32(ctx, n * aw);
+        }
         return s;
     }
 };
 
 // Gated FFN: down(act(gate x) * up x), optional RMS norm on the output before
-// the residual add (engine/metal.rs:431-535).  gate|up are one matrix.
+// the residual add (engine/metal.rs:431-535).  gate|up are one matrix.  With a
+// row split every rank owns width/world gate and up rows and hidden/world down
+// rows; the activated slice and the down output are all-gathered.
 struct SwiGluBlock {
     Matrix gate_up, down;
     GluActivation act = GluActivation::Silu;
     CudaBuffer out_norm;  // empty unless the artifact has it
     float eps = 0;
     CudaBuffer gu, g_view, u_view, out;
-    size_t width = 0;
+    CudaBuffer h_full, out_local;  // row split only
+    size_t width = 0, wl = 0;      // full and per-rank FFN width
+    Shard sh;
 
-    static void plan(const FfnSpec &f, bool has_norm, Tensor norm, size_t hidden, const WeightSource &src, Plan &p) {
-        p.weights += Matrix::plan(src, {f.gate, f.up}) + Matrix::plan(src, {f.down});
+    static void plan(const FfnSpec &f, bool has_norm, Tensor norm, size_t hidden, const WeightSource &src, Shard sh,
+                     Plan &p) {
+        p.weights += Matrix::plan(src, {f.gate, f.up}, sh) + Matrix::plan(src, {f.down}, sh);
         if (has_norm) p.weights_f32(vector_len(src, norm));
-        p.scratch_f32(2 * f.width);
+        p.scratch_f32(2 * f.width / sh.world);
         p.scratch_f32(hidden);
+        if (sh.world > 1) {
+            p.scratch_f32(f.width);
+            p.scratch_f32(hidden / sh.world);
+        }
     }
     static SwiGluBlock load(const CudaContext &ctx, const WeightSource &src, const FfnSpec &f, bool has_norm,
-                            Tensor norm, size_t hidden, float eps) {
+                            Tensor norm, size_t hidden, float eps, Shard sh) {
         SwiGluBlock b;
-        b.gate_up = Matrix::load(ctx, src, {f.gate, f.up});
-        b.down = Matrix::load(ctx, src, {f.down});
+        b.sh = sh;
+        b.gate_up = Matrix::load(ctx, src, {f.gate, f.up}, sh);
+        b.down = Matrix::load(ctx, src, {f.down}, sh);
         b.act = f.act;
         if (has_norm) b.out_norm = vector(ctx, src, norm);
         b.eps = eps;
         b.width = f.width;
-        b.gu = zeros_f32(ctx, 2 * f.width);
-        b.g_view = b.gu.view(0, f.width * 4);
-        b.u_view = b.gu.view(f.width * 4, f.width * 4);
+        b.wl = f.width / sh.world;
+        if (f.width % sh.world != 0 || hidden % sh.world != 0 || (b.wl * 4) % 16 != 0)
+            throw TuckmillError(ErrorCode::InvalidRequest, "FFN width does not divide over the devices of the split");
+        b.gu = zeros_f32(ctx, 2 * b.wl);
+        b.g_view = b.gu.view(0, b.wl * 4);
+        b.u_view = b.gu.view(b.wl * 4, b.wl * 4);
         b.out = zeros_f32(ctx, hidden);
+        if (sh.world > 1) {
+            b.h_full = zeros_f32(ctx, f.width);
+            b.out_local = zeros_f32(ctx, hidden / sh.world);
+        }
         return b;
+    }
+    void act_mul(const CudaContext &ctx, const CudaBuffer &g, const CudaBuffer &u, uint32_t n) const {
+        if (act == GluActivation::Silu) ctx.silu_mul(g, u, g, n);
+        else ctx.gelu_tanh_mul(g, u, g, n);
     }
     // x += ffn(norm(x, post_norm)) for one token: 2 launches (3 more with an output norm).
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &post_norm, size_t hidden) const {
         ctx.q8_0_gemv_fused(gate_up.buf, x, gu, gate_up.rows, gate_up.cols, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
                             TM_CUDA_EPI_STORE);
+        if (sh.world > 1) {
+            act_mul(ctx, g_view, u_view, (uint32_t)wl);
+            ctx.all_gather_rows(g_view, h_full, h_full, 1, (uint32_t)wl);
+            ctx.q8_0_gemv(down.buf, h_full, out_local, down.rows, down.cols);
+            ctx.all_gather_rows(out_local, out, out, 1, (uint32_t)(hidden / sh.world));
+            if (out_norm) ctx.rmsnorm(out, out_norm, out, 1, (uint32_t)hidden, eps);
+            ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
+            return;
+        }
         const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
         if (out_norm) {
             ctx.q8_0_gemv_fused(down.buf, g_view, out, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
@@ -232,11 +293,19 @@ struct SwiGluBlock {
     // x += ffn(h2) for the n chunk rows of s.h2 / s.x (engine/metal.rs:514-534).
     void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, size_t hidden, bool exact) const {
         const uint32_t nn = (uint32_t)n;
-        gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
-        gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
-        if (act == GluActivation::Silu) ctx.silu_mul(s.g, s.u, s.g, (uint32_t)(n * width));
-        else ctx.gelu_tanh_mul(s.g, s.u, s.g, (uint32_t)(n * width));
-        down.gemm_all(ctx, s.g, s.d2, nn, exact);
+        if (sh.world > 1) {
+            gate_up.gemm_part(ctx, 0, s.h2, s.loc, nn, exact);
+            gate_up.gemm_part(ctx, 1, s.h2, s.loc2, nn, exact);
+            act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
+            ctx.all_gather_rows(s.loc, s.stage, s.g, nn, (uint32_t)wl);
+            down.gemm_all(ctx, s.g, s.loc, nn, exact);
+            ctx.all_gather_rows(s.loc, s.stage, s.d2, nn, (uint32_t)(hidden / sh.world));
+        } else {
+            gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
+            gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
+            act_mul(ctx, s.g, s.u, (uint32_t)(n * width));
+            down.gemm_all(ctx, s.g, s.d2, nn, exact);
+        }
         if (out_norm) ctx.rmsnorm(s.d2, out_norm, s.d2, nn, (uint32_t)hidden, eps);
         ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
     }
@@ -244,55 +313,77 @@ struct SwiGluBlock {
 
 // Grouped-query attention with per-head Q/K RMS norms, RoPE, packed f16 KV and
 // an optional sliding window (engine/metal.rs:989-1364).  q|k|v are one matrix.
+// With a row split every rank owns heads/world query heads and kv_heads/world
+// KV heads (and only their cache planes); attention is local to the rank, its
+// output and the o projection's output are all-gathered.
 struct AttentionBlock {
     AttentionSpec spec;
     float eps = 0;
     Matrix qkv, o;
     CudaBuffer q_norm, k_norm, inv_freq, k_cache, v_cache;
     CudaBuffer qkv_out, q_view, k_view, v_view, attn, kv_scratch;
-    size_t cap = 0;
+    CudaBuffer attn_full, proj_local;  // row split only
+    size_t cap = 0, heads_l = 0, kv_l = 0;
+    Shard sh;
 
-    static uint64_t kv_plane_bytes(const AttentionSpec &s, size_t cap) { return (uint64_t)s.kv_heads * cap * s.head_dim * 2; }
-
-    static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, Plan &p) {
-        p.weights += Matrix::plan(src, {s.q, s.k, s.v}) + Matrix::plan(src, {s.o});
+    static uint64_t kv_plane_bytes(const AttentionSpec &s, size_t cap, Shard sh) {
+        return (uint64_t)(s.kv_heads / sh.world) * cap * s.head_dim * 2;
+    }
+    static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, size_t hidden, Shard sh, Plan &p) {
+        p.weights += Matrix::plan(src, {s.q, s.k, s.v}, sh) + Matrix::plan(src, {s.o}, sh);
         p.weights_f32(vector_len(src, s.q_norm));
         p.weights_f32(vector_len(src, s.k_norm));
         // The RoPE table is derived by the engine, not artifact bytes: scratch.
         p.scratch_f32(s.rope_dims / 2);
-        p.state += 2 * kv_plane_bytes(s, cap);
-        const size_t hd = s.heads * s.head_dim, kv = s.kv_heads * s.head_dim;
-        p.scratch_f32(hd + 2 * kv);
-        p.scratch_f32(hd);
-        p.scratch_bytes(tm_cuda_attention_decode_scratch_bytes((uint32_t)s.heads, (uint32_t)s.kv_heads,
-                                                               (uint32_t)s.head_dim, (uint32_t)cap));
+        p.state += 2 * kv_plane_bytes(s, cap, sh);
+        const size_t hl = s.heads / sh.world, kl = s.kv_heads / sh.world;
+        p.scratch_f32((hl + 2 * kl) * s.head_dim);
+        p.scratch_f32(hl * s.head_dim);
+        p.scratch_bytes(tm_cuda_attention_decode_scratch_bytes((uint32_t)hl, (uint32_t)kl, (uint32_t)s.head_dim,
+                                                               (uint32_t)cap));
+        if (sh.world > 1) {
+            p.scratch_f32(s.heads * s.head_dim);
+            p.scratch_f32(hidden / sh.world);
+        }
     }
     static AttentionBlock load(const CudaContext &ctx, const WeightSource &src, const AttentionSpec &s, float eps,
-                               size_t cap) {
+                               size_t cap, size_t hidden, Shard sh) {
         if (s.head_dim % 32 != 0 || (s.head_dim / 32 > 4 && s.head_dim != 256) || s.rope_dims % 2 != 0)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture,
                                 "attention head size " + std::to_string(s.head_dim) + " has no CUDA block");
+        if (s.heads % sh.world != 0 || s.kv_heads % sh.world != 0 || hidden % sh.world != 0)
+            throw TuckmillError(ErrorCode::InvalidRequest,
+                                std::to_string(s.heads) + " query / " + std::to_string(s.kv_heads) +
+                                    " KV heads do not divide over " + std::to_string(sh.world) + " devices");
         AttentionBlock b;
         b.spec = s;
         b.eps = eps;
         b.cap = cap;
-        b.qkv = Matrix::load(ctx, src, {s.q, s.k, s.v});
-        b.o = Matrix::load(ctx, src, {s.o});
-        const size_t hd = s.heads * s.head_dim, kv = s.kv_heads * s.head_dim;
-        if (b.qkv.part_rows[0] != hd || b.qkv.part_rows[1] != kv || b.qkv.part_rows[2] != kv || b.o.cols != hd)
+        b.sh = sh;
+        b.heads_l = s.heads / sh.world;
+        b.kv_l = s.kv_heads / sh.world;
+        b.qkv = Matrix::load(ctx, src, {s.q, s.k, s.v}, sh);
+        b.o = Matrix::load(ctx, src, {s.o}, sh);
+        const size_t hd = b.heads_l * s.head_dim, kv = b.kv_l * s.head_dim;
+        if (b.qkv.part_rows[0] != hd || b.qkv.part_rows[1] != kv || b.qkv.part_rows[2] != kv ||
+            b.o.cols != s.heads * s.head_dim)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture, "attention projection shapes do not match the head geometry");
         b.q_norm = vector(ctx, src, s.q_norm);
         b.k_norm = vector(ctx, src, s.k_norm);
         b.inv_freq = ctx.floats(rope_inv_freq(s.rope_dims, s.rope_base));
-        b.k_cache = ctx.buffer(kv_plane_bytes(s, cap));
-        b.v_cache = ctx.buffer(kv_plane_bytes(s, cap));
+        b.k_cache = ctx.buffer(kv_plane_bytes(s, cap, sh));
+        b.v_cache = ctx.buffer(kv_plane_bytes(s, cap, sh));
         b.qkv_out = zeros_f32(ctx, hd + 2 * kv);
         b.q_view = b.qkv_out.view(0, hd * 4);
         b.k_view = b.qkv_out.view(hd * 4, kv * 4);
         b.v_view = b.qkv_out.view((hd + kv) * 4, kv * 4);
         b.attn = zeros_f32(ctx, hd);
-        b.kv_scratch = ctx.zeros(tm_cuda_attention_decode_scratch_bytes((uint32_t)s.heads, (uint32_t)s.kv_heads,
+        b.kv_scratch = ctx.zeros(tm_cuda_attention_decode_scratch_bytes((uint32_t)b.heads_l, (uint32_t)b.kv_l,
                                                                         (uint32_t)s.head_dim, (uint32_t)cap));
+        if (sh.world > 1) {
+            b.attn_full = zeros_f32(ctx, s.heads * s.head_dim);
+            b.proj_local = zeros_f32(ctx, hidden / sh.world);
+        }
         return b;
     }
     void reset() const {
@@ -307,15 +398,20 @@ struct AttentionBlock {
         ctx.q8_0_gemv_fused(qkv.buf, x, qkv_out, qkv.rows, qkv.cols, TM_CUDA_PRO_RMSNORM, &pre_norm, eps,
                             TM_CUDA_EPI_STORE);
         ctx.attention_decode_dev(q_view, k_view, v_view, q_norm, k_norm, inv_freq, k_cache, v_cache, attn, kv_scratch,
-                                 pos_buf, 0, status, (uint32_t)spec.heads, (uint32_t)spec.kv_heads,
-                                 (uint32_t)spec.head_dim, (uint32_t)spec.rope_dims, (uint32_t)cap,
-                                 (uint32_t)spec.window, eps, scale(), exact);
+                                 pos_buf, 0, status, (uint32_t)heads_l, (uint32_t)kv_l, (uint32_t)spec.head_dim,
+                                 (uint32_t)spec.rope_dims, (uint32_t)cap, (uint32_t)spec.window, eps, scale(), exact);
+    }
+    // Row split: proj = all_gather(o_local * all_gather(attn_local)), one token.
+    void project_sharded(const CudaContext &ctx, const CudaBuffer &proj, size_t hidden) const {
+        ctx.all_gather_rows(attn, attn_full, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
+        ctx.q8_0_gemv(o.buf, attn_full, proj_local, o.rows, o.cols);
+        ctx.all_gather_rows(proj_local, proj, proj, 1, (uint32_t)(hidden / sh.world));
     }
     // Chunk core over n queries at pos0.. (engine/metal.rs:1170-1233): every
     // chunk K/V row is stored before any chunk query attends.
-    void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, bool exact) const {
-        const uint32_t nn = (uint32_t)n, heads = (uint32_t)spec.heads, kv = (uint32_t)spec.kv_heads,
-                       hd = (uint32_t)spec.head_dim;
+    void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, size_t hidden,
+                 bool exact) const {
+        const uint32_t nn = (uint32_t)n, heads = (uint32_t)heads_l, kv = (uint32_t)kv_l, hd = (uint32_t)spec.head_dim;
         qkv.gemm_part(ctx, 0, s.h, s.a, nn, exact);
         qkv.gemm_part(ctx, 1, s.h, s.b, nn, exact);
         qkv.gemm_part(ctx, 2, s.h, s.c, nn, exact);
@@ -325,7 +421,13 @@ struct AttentionBlock {
         ctx.kv_store_chunk(s.b, s.c, k_cache, v_cache, pos0, (uint32_t)cap, hd, kv, nn);
         ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
                             (uint32_t)spec.window);
-        o.gemm_all(ctx, s.e, s.proj, nn, exact);
+        if (sh.world > 1) {
+            ctx.all_gather_rows(s.e, s.stage, s.efull, nn, heads * hd);
+            o.gemm_all(ctx, s.efull, s.loc, nn, exact);
+            ctx.all_gather_rows(s.loc, s.stage, s.proj, nn, (uint32_t)(hidden / sh.world));
+        } else {
+            o.gemm_all(ctx, s.e, s.proj, nn, exact);
+        }
     }
 };
 
@@ -335,31 +437,32 @@ struct Layer {
     AttentionBlock mixer;
     SwiGluBlock ffn;
 
-    static void plan(const LayerSpec &l, const ModelGraph &g, const WeightSource &src, size_t cap, Plan &p) {
+    static void plan(const LayerSpec &l, const ModelGraph &g, const WeightSource &src, size_t cap, Shard sh, Plan &p) {
         p.weights_f32(vector_len(src, l.pre_norm));
         p.weights_f32(vector_len(src, l.post_norm));
         if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
         p.scratch_f32(g.hidden);  // proj
-        AttentionBlock::plan(l.mixer, src, cap, p);
-        SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, p);
+        AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p);
+        SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, sh, p);
     }
     static Layer load(const CudaContext &ctx, const WeightSource &src, const LayerSpec &l, const ModelGraph &g,
-                      size_t cap) {
+                      size_t cap, Shard sh) {
         Layer L;
         L.pre_norm = vector(ctx, src, l.pre_norm);
         if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
         L.post_norm = vector(ctx, src, l.post_norm);
         L.proj = zeros_f32(ctx, g.hidden);
-        L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap);
-        L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps);
+        L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh);
+        L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps, sh);
         return L;
     }
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pos_buf, const CudaBuffer &status,
                 size_t hidden, float eps, bool exact) const {
         mixer.decode(ctx, x, pre_norm, pos_buf, status, exact);
-        if (mixer_out_norm) {
-            ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
-            ctx.rmsnorm(proj, mixer_out_norm, proj, 1, (uint32_t)hidden, eps);
+        if (mixer.sh.world > 1 || mixer_out_norm) {
+            if (mixer.sh.world > 1) mixer.project_sharded(ctx, proj, hidden);
+            else ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
+            if (mixer_out_norm) ctx.rmsnorm(proj, mixer_out_norm, proj, 1, (uint32_t)hidden, eps);
             ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
         } else {
             ctx.q8_0_gemv_fused(mixer.o.buf, mixer.attn, x, mixer.o.rows, mixer.o.cols, TM_CUDA_PRO_NONE, nullptr, 0.0f,
@@ -371,7 +474,7 @@ struct Layer {
                  bool exact) const {
         const uint32_t nn = (uint32_t)n;
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
-        mixer.prefill(ctx, s, n, pos0, exact);
+        mixer.prefill(ctx, s, n, pos0, hidden, exact);
         if (mixer_out_norm) ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
         ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
         ctx.rmsnorm(s.x, post_norm, s.h2, nn, (uint32_t)hidden, eps);
@@ -390,31 +493,57 @@ uint64_t now_ns() {
 struct EngineModel::Impl {
     Matrix embedding, head_own;
     bool tied = false;
+    Shard sh;
+    CudaBuffer tied_view;  // row split of a tied head: this rank's rows of the (replicated) embedding
+    uint32_t head_rows = 0;  // rows of the head this rank multiplies (vocab / world)
     CudaBuffer final_norm, x, logits, partial, tokens, tokens_mirror, pos_buf, status;
+    CudaBuffer logits_full, pairs;  // row split only
     std::vector<Layer> layers;
     PrefillScratch scratch;
     CudaGraph decode_graph;
-    const Matrix &head() const { return tied ? embedding : head_own; }
+    const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
+    uint32_t head_cols() const { return embedding.cols; }
 };
 
 GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, size_t capacity,
                              const EngineOptions &opts) {
-    if (opts.shard_world != 1)
-        throw TuckmillError(ErrorCode::InvalidRequest, "row-sharded loading goes through the sharded engine entry point");
+    if (opts.shard_world == 0 || opts.shard_rank >= opts.shard_world)
+        throw TuckmillError(ErrorCode::InvalidRequest, "shard rank outside the split");
+    const Shard sh{opts.shard_rank, opts.shard_world};
+    // Whole attention heads stay on one rank, and every row range is N/world.
+    auto divides = [&](size_t v, const char *what) {
+        if (v % sh.world != 0)
+            throw TuckmillError(ErrorCode::InvalidRequest,
+                                std::string(what) + " = " + std::to_string(v) + " does not divide over " +
+                                    std::to_string(sh.world) + " devices",
+                                "Choose a device count that divides the head counts, the FFN width and the vocabulary.");
+    };
+    divides(graph.vocab, "vocabulary");
+    divides(graph.hidden, "hidden size");
+    for (const LayerSpec &l : graph.layers) {
+        divides(l.mixer.heads, "query heads");
+        divides(l.mixer.kv_heads, "KV heads");
+        divides(l.ffn.width, "FFN width");
+    }
     Plan p;
-    for (const LayerSpec &l : graph.layers) Layer::plan(l, graph, src, capacity, p);
-    p.weights += Matrix::plan(src, {graph.embedding});
-    if (graph.head != graph.embedding) p.weights += Matrix::plan(src, {graph.head});
+    for (const LayerSpec &l : graph.layers) Layer::plan(l, graph, src, capacity, sh, p);
+    p.weights += Matrix::plan(src, {graph.embedding});  // the embedding table is replicated
+    if (graph.head != graph.embedding) p.weights += Matrix::plan(src, {graph.head}, sh);
     p.weights_f32(vector_len(src, graph.final_norm));
     p.scratch_f32(graph.hidden);              // x
-    p.scratch_f32(graph.vocab);               // logits
+    p.scratch_f32(graph.vocab / sh.world);    // logits (this rank's slice)
     p.scratch_bytes(kArgmaxPartialBytes);     // argmax partials
     p.scratch_bytes((capacity + 1) * 4);      // device token log
     p.scratch_bytes((capacity + 1) * 4);      // its host-visible mirror
     p.scratch_bytes(16);                      // device position
     p.scratch_bytes(16);                      // status word
-    PrefillScratch::plan(graph, capacity, std::min<size_t>(opts.prefill_batch, capacity), p);
-    if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, std::min<size_t>(opts.prefill_batch, capacity)));
+    if (sh.world > 1) {
+        p.scratch_f32(graph.vocab);           // gathered logits (only when a caller asks for them)
+        p.scratch_bytes((sh.world + 1) * 8);  // (value, index) pairs of the sharded argmax
+    }
+    const size_t n = std::min<size_t>(opts.prefill_batch, capacity);
+    PrefillScratch::plan(graph, capacity, n, sh, p);
+    if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, n));
     GpuAllocPlan out;
     out.weights = p.weights;
     out.state = p.state;
@@ -442,21 +571,31 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     Impl &I = *m->impl_;
     const CudaContext &c = *ctx;
     I.layers.reserve(graph.layers.size());
-    for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity));
+    const Shard sh{opts.shard_rank, opts.shard_world};
+    I.sh = sh;
+    for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity, sh));
     I.embedding = Matrix::load(c, src, {graph.embedding});
     I.tied = graph.head == graph.embedding;
-    if (!I.tied) I.head_own = Matrix::load(c, src, {graph.head});
-    if (I.embedding.cols != graph.hidden || I.head().cols != graph.hidden || I.head().rows != graph.vocab)
+    I.head_rows = (uint32_t)(graph.vocab / sh.world);
+    if (!I.tied) I.head_own = Matrix::load(c, src, {graph.head}, sh);
+    else if (sh.world > 1)
+        I.tied_view = c.row_view(I.embedding.buf, I.embedding.rows, I.embedding.cols, sh.rank * I.head_rows, I.head_rows);
+    if (I.embedding.cols != graph.hidden || I.embedding.rows != graph.vocab ||
+        (!I.tied && (I.head_own.cols != graph.hidden || I.head_own.rows != I.head_rows)))
         throw TuckmillError(ErrorCode::UnsupportedArchitecture, "embedding / head shapes do not match the graph");
     I.final_norm = vector(c, src, graph.final_norm);
     I.x = zeros_f32(c, graph.hidden);
-    I.logits = zeros_f32(c, graph.vocab);
+    I.logits = zeros_f32(c, I.head_rows);
+    if (sh.world > 1) {
+        I.logits_full = zeros_f32(c, graph.vocab);
+        I.pairs = c.zeros((sh.world + 1) * 8);
+    }
     I.partial = c.zeros(kArgmaxPartialBytes);
     I.tokens = c.zeros((capacity + 1) * 4);
     I.tokens_mirror = c.zeros((capacity + 1) * 4, true);
     I.pos_buf = c.zeros(16);
     I.status = c.zeros(16, true);
-    I.scratch = PrefillScratch::alloc(c, graph, capacity, std::min<size_t>(opts.prefill_batch, capacity));
+    I.scratch = PrefillScratch::alloc(c, graph, capacity, std::min<size_t>(opts.prefill_batch, capacity), sh);
     if (!opts.exact) c.mma_workspace_reserve(PrefillScratch::mma_workspace(graph, std::min<size_t>(opts.prefill_batch, capacity)));
     m->graph_ = std::move(graph);
     const ModelGraph &g = m->graph_;
@@ -491,10 +630,14 @@ void EngineModel::encode_decode_step() {
     c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
                        g.embedding_scale, I.x);
     for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
-    c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
-                      &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
-    c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity_ + 1,
-                 &I.tokens_mirror);
+    c.q8_0_gemv_fused(I.head_buf(), I.x, I.logits, I.head_rows, I.head_cols(), TM_CUDA_PRO_RMSNORM, &I.final_norm,
+                      g.eps, TM_CUDA_EPI_STORE);
+    if (I.sh.world > 1)
+        c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens, 1, &I.pos_buf, 0,
+                         (uint32_t)capacity_ + 1, &I.tokens_mirror);
+    else
+        c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity_ + 1,
+                     &I.tokens_mirror);
     c.u32_add(I.pos_buf, 0, 1);
 }
 
@@ -548,9 +691,13 @@ void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) {
             if (last && want_token) {
                 // Vocabulary projection for the last row only (engine/metal.rs:2610-2617).
                 c.copy_f32(I.scratch.x, (uint32_t)((k - 1) * graph_.hidden), I.x, 0, (uint32_t)graph_.hidden);
-                c.q8_0_gemv_fused(I.head().buf, I.x, I.logits, I.head().rows, I.head().cols, TM_CUDA_PRO_RMSNORM,
+                c.q8_0_gemv_fused(I.head_buf(), I.x, I.logits, I.head_rows, I.head_cols(), TM_CUDA_PRO_RMSNORM,
                                   &I.final_norm, graph_.eps, TM_CUDA_EPI_STORE);
-                c.argmax_f32(I.logits, (uint32_t)graph_.vocab, I.partial, I.tokens, pos0 + (uint32_t)k);
+                if (I.sh.world > 1)
+                    c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens,
+                                     pos0 + (uint32_t)k, nullptr, 0, (uint32_t)capacity_ + 1, nullptr);
+                else
+                    c.argmax_f32(I.logits, (uint32_t)graph_.vocab, I.partial, I.tokens, pos0 + (uint32_t)k);
             }
         });
     }
@@ -578,7 +725,16 @@ void EngineModel::step(uint32_t token) {
     pos_ += 1;
 }
 
-void EngineModel::logits(float *out) { impl_->logits.download(0, out, graph_.vocab * 4); }
+// With a row split this is a collective: every rank must call it.
+void EngineModel::logits(float *out) {
+    Impl &I = *impl_;
+    if (I.sh.world > 1) {
+        ctx_->all_gather_rows(I.logits, I.logits_full, I.logits_full, 1, I.head_rows);
+        I.logits_full.download(0, out, graph_.vocab * 4);
+    } else {
+        I.logits.download(0, out, graph_.vocab * 4);
+    }
+}
 
 EngineModel::Ticket EngineModel::submit_greedy() {
     if (pos_ >= capacity_)

@@ -1,4 +1,259 @@
-// Multi-GPU row split: communicator state of a context.
-#include "tm_cuda_internal.cuh"
+// Multi-GPU output-row split: the exchange step.  Every projection is split by
+// output rows across the GPUs of one box (each output element needs one weight
+// row and the whole input vector: crates/tuckcore/src/kernels.rs:186-204), each
+// rank runs the single-GPU kernels on its slice, and one all-gather over
+// NVLink/NVSwitch reassembles the vector.  The reference is single-device; this
+// file has no counterpart there.
+//
+// NCCL is loaded at run time (dlopen of libnccl.so.2: the copy a host process
+// such as torch already mapped, else the system one), so single-GPU users of
+// the library need no NCCL at all.  Collectives are enqueued on the context's
+// stream and can be recorded in a dispatch group like any operator.
+#include <dlfcn.h>
 
-extern "C" void tm_cuda_comm_release(tm_cuda_ctx *ctx) { (void)ctx; }
+#include "tm_cuda_internal.cuh"
+#include "tm_cuda_device.cuh"
+
+namespace {
+
+// The slice of the NCCL ABI this file uses (nccl.h: stable since 2.x).
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;  // ncclSuccess == 0
+enum { ncclChar = 0, ncclFloat32 = 7 };
+
+struct nccl_api {
+    void *lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+nccl_api *nccl() {
+    static nccl_api api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        // TM_CUDA_NCCL_LIB names a specific copy; otherwise the loader's search order decides.
+        const char *named = getenv("TM_CUDA_NCCL_LIB");
+        void *h = named && *named ? dlopen(named, RTLD_NOW | RTLD_GLOBAL) : nullptr;
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h) {
+            api.lib = h;
+            api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+            api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
+            api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
+            api.AllGather = (decltype(api.AllGather))dlsym(h, "ncclAllGather");
+            api.GetErrorString = (decltype(api.GetErrorString))dlsym(h, "ncclGetErrorString");
+            if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather) api.lib = nullptr;
+        }
+    }
+    return api.lib ? &api : nullptr;
+}
+
+struct comm_state {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+// dst[t][r * w + c] = src[r][t][c]: NCCL concatenates whole per-rank buffers, a
+// chunk of n token rows wants the ranks' slices side by side inside each row.
+__global__ void interleave_kernel(const float *src, float *dst, uint32_t world, uint32_t n, uint32_t w) {
+    const size_t total = (size_t)world * n * w;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = (uint32_t)(i % w);
+        const uint32_t t = (uint32_t)((i / w) % n);
+        const uint32_t r = (uint32_t)(i / ((size_t)w * n));
+        dst[((size_t)t * world + r) * w + c] = src[i];
+    }
+}
+
+constexpr uint32_t kNone = 0xFFFFFFFFu;
+
+// One CTA: greedy choice among `world` (value, global index) pairs with the
+// single-device rule -- larger value wins, equal values go to the lower global
+// index, an index of 0xFFFFFFFF (all-NaN slice) never wins
+// (crates/backend/src/sampling.rs:68-82).
+__global__ void argmax_pairs_final_kernel(const float *pairs, uint32_t world, uint32_t *out, uint32_t base,
+                                          const uint32_t *pos, uint32_t out_cap, uint32_t *mirror) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    if (threadIdx.x != 0) return;
+    float bv = 0.0f;
+    uint32_t bi = kNone;
+    for (uint32_t r = 0; r < world; ++r) {
+        const float v = pairs[2 * r];
+        const uint32_t i = __float_as_uint(pairs[2 * r + 1]);
+        if (i == kNone) continue;
+        if (bi == kNone || v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    const uint32_t slot = pos ? base + *pos : base;
+    if (slot < out_cap) {
+        out[slot] = bi;
+        if (mirror) mirror[slot] = bi;
+    }
+}
+
+// (value, global index) of this rank's slice from the 64 partials of argmax_partial.
+__global__ void argmax_pair_kernel(const float *pv, const uint32_t *pi, float *pair, uint32_t index_offset) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    if (threadIdx.x != 0) return;
+    float bv = 0.0f;
+    uint32_t bi = kNone;
+    for (int g = 0; g < 64; ++g) {
+        const uint32_t i = pi[g];
+        const float v = pv[g];
+        if (i == kNone) continue;
+        if (bi == kNone || v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    pair[0] = bv;
+    pair[1] = __uint_as_float(bi == kNone ? kNone : bi + index_offset);
+}
+
+}  // namespace
+
+extern "C" {
+
+void tm_cuda_comm_release(tm_cuda_ctx *ctx) {
+    if (!ctx || !ctx->comm) return;
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *n = nccl();
+    if (n && c->comm) n->CommDestroy(c->comm);
+    delete c;
+    ctx->comm = nullptr;
+}
+
+int tm_cuda_comm_unique_id(void *out128, char *err, size_t err_cap) {
+    nccl_api *n = nccl();
+    if (!n) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "libnccl.so.2 could not be loaded: %s", dlerror());
+    if (!out128) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null id buffer");
+    ncclUniqueId id;
+    const ncclResult_t r = n->GetUniqueId(&id);
+    if (r != 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclGetUniqueId failed: %s",
+                       n->GetErrorString ? n->GetErrorString(r) : "?");
+    memcpy(out128, &id, sizeof id);
+    return TM_CUDA_OK;
+}
+
+int tm_cuda_comm_init(tm_cuda_ctx *ctx, const void *id128, int rank, int world, char *err, size_t err_cap) {
+    TM_ENTER();
+    nccl_api *n = nccl();
+    if (!n) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "libnccl.so.2 could not be loaded");
+    if (!id128 || world < 1 || world > 64 || rank < 0 || rank >= world)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "rank %d of %d", rank, world);
+    if (ctx->comm) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the context already has a communicator");
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof id);
+    comm_state *c = new comm_state();
+    c->rank = rank;
+    c->world = world;
+    const ncclResult_t r = n->CommInitRank(&c->comm, world, id, rank);
+    if (r != 0) {
+        delete c;
+        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclCommInitRank failed: %s",
+                       n->GetErrorString ? n->GetErrorString(r) : "?");
+    }
+    ctx->comm = c;
+    return TM_CUDA_OK;
+}
+
+int tm_cuda_comm_rank(const tm_cuda_ctx *ctx, int *rank, int *world) {
+    if (!ctx || !ctx->comm) return TM_CUDA_ERR_UNSUPPORTED;
+    const comm_state *c = (const comm_state *)ctx->comm;
+    if (rank) *rank = c->rank;
+    if (world) *world = c->world;
+    return TM_CUDA_OK;
+}
+
+int tm_cuda_all_gather_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t src_off, tm_cuda_buffer *dst,
+                           uint32_t dst_off, uint32_t count, char *err, size_t err_cap) {
+    TM_ENTER();
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *n = nccl();
+    if (!c || !n) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the context has no communicator");
+    if (count == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "empty all-gather");
+    TM_CHECK_BUF(src, ((size_t)src_off + count) * 4, "all-gather source");
+    TM_CHECK_BUF(dst, ((size_t)dst_off + (size_t)count * c->world) * 4, "all-gather target");
+    TM_OP_BEGIN("all_gather");
+    const ncclResult_t r = n->AllGather((const float *)src->dev + src_off, (float *)dst->dev + dst_off, count,
+                                        ncclFloat32, c->comm, ctx->stream);
+    if (r != 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclAllGather failed: %s",
+                       n->GetErrorString ? n->GetErrorString(r) : "?");
+    TM_OP_END(1);
+}
+
+int tm_cuda_all_gather_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *stage, tm_cuda_buffer *dst,
+                                uint32_t n_rows, uint32_t width, char *err, size_t err_cap) {
+    TM_ENTER();
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *n = nccl();
+    if (!c || !n) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the context has no communicator");
+    if (n_rows == 0 || width == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "empty all-gather");
+    const size_t per = (size_t)n_rows * width;
+    TM_CHECK_BUF(src, per * 4, "all-gather source");
+    TM_CHECK_BUF(stage, per * c->world * 4, "all-gather staging");
+    TM_CHECK_BUF(dst, per * c->world * 4, "all-gather target");
+    TM_OP_BEGIN("all_gather_rows");
+    const ncclResult_t r = n->AllGather(src->dev, n_rows == 1 ? dst->dev : stage->dev, per, ncclFloat32, c->comm,
+                                        ctx->stream);
+    if (r != 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclAllGather failed: %s",
+                       n->GetErrorString ? n->GetErrorString(r) : "?");
+    uint64_t kernels = 1;
+    if (n_rows > 1) {
+        const size_t total = per * c->world;
+        const int grid = (int)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
+        interleave_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)stage->dev, (float *)dst->dev,
+                                                          (uint32_t)c->world, n_rows, width);
+        kernels = 2;
+    }
+    TM_OP_END(kernels);
+}
+
+int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, uint32_t index_offset,
+                               tm_cuda_buffer *partial, tm_cuda_buffer *pairs, tm_cuda_buffer *out, uint32_t base,
+                               tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
+                               tm_cuda_buffer *mirror, char *err, size_t err_cap) {
+    // local slice -> (value, global index); all-gather of the pairs; the single-device rule over them
+    TM_ENTER();
+    if (n == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "argmax over zero elements");
+    TM_CHECK_BUF(x, (size_t)n * 4, "logits");
+    TM_CHECK_BUF(partial, 512, "argmax partials");
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *nc = nccl();
+    if (!c || !nc) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the context has no communicator");
+    TM_CHECK_BUF(pairs, (size_t)(c->world + 1) * 8, "argmax pairs");
+    TM_CHECK_BUF(out, (size_t)out_cap * 4, "token log");
+    if (mirror) TM_CHECK_BUF(mirror, (size_t)out_cap * 4, "token log mirror");
+    const uint32_t *pos = nullptr;
+    if (pos_buf) {
+        TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
+        pos = (const uint32_t *)pos_buf->dev + pos_index;
+    }
+    TM_OP_BEGIN("argmax_sharded");
+    float *mine = (float *)pairs->dev + 2 * c->world;  // own pair after the gathered block
+    TM_CUDA_TRY(tm_argmax_partial_launch(ctx, (const float *)x->dev, n, (float *)partial->dev,
+                                         (uint32_t *)(partial->dev + 256)));
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_pair_kernel, dim3(1), dim3(32), 0, (const float *)partial->dev,
+                              (const uint32_t *)(partial->dev + 256), mine, index_offset));
+    const ncclResult_t r = nc->AllGather(mine, pairs->dev, 2, ncclFloat32, c->comm, ctx->stream);
+    if (r != 0) return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclAllGather failed");
+    argmax_pairs_final_kernel<<<1, 32, 0, ctx->stream>>>((const float *)pairs->dev, (uint32_t)c->world,
+                                                         (uint32_t *)out->dev, base, pos, out_cap,
+                                                         mirror ? (uint32_t *)mirror->dev : nullptr);
+    TM_OP_END(4);
+}
+
+}  // extern "C"

@@ -170,3 +170,5 @@ inline cudaError_t tm_launch_pdl(tm_cuda_ctx *ctx, void (*kernel)(KArgs...), dim
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi);

@@ -865,6 +865,12 @@ inline bool attn_shape_ok(uint32_t hd) { return hd % 32 == 0 && (hd / 32 <= 4 ||
 
 }  // namespace
 
+// Pass 1 of the greedy argmax alone (64 partial (value, index) pairs), for callers
+// that finish the reduction themselves (the row-sharded head).
+cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi) {
+    return tm_launch_pdl(ctx, argmax_partial_kernel, dim3(kArgmaxGroups), dim3(kThreads), 0, x, pv, pi, n);
+}
+
 #define TM_EW_CHECK_N()                                                                      \
     if (n == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "element count must be positive")
 

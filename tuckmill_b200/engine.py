@@ -32,7 +32,8 @@ class EngineError(RuntimeError):
 
 class _Options(C.Structure):
     _fields_ = [("gguf_path", C.c_char_p), ("kernels", C.c_char_p), ("device", C.c_int), ("context", C.c_uint32),
-                ("prefill_batch", C.c_uint32), ("exact", C.c_int), ("budget_bytes", C.c_uint64)]
+                ("prefill_batch", C.c_uint32), ("exact", C.c_int), ("budget_bytes", C.c_uint64),
+                ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32), ("comm_id", C.c_void_p)]
 
 
 class Info(C.Structure):
@@ -59,6 +60,7 @@ def load_library() -> C.CDLL:
     P = C.c_void_p
     L.tm_engine_load.argtypes = [C.POINTER(_Options), C.POINTER(P)] + E
     L.tm_engine_free.argtypes = [P]
+    L.tm_engine_comm_id.argtypes = [P] + E
     L.tm_engine_get_info.argtypes = [P, C.POINTER(Info)]
     L.tm_engine_cuda_ctx.restype = P
     L.tm_engine_cuda_ctx.argtypes = [P]
@@ -72,6 +74,7 @@ def load_library() -> C.CDLL:
     L.tm_engine_decode_steps.argtypes = [P, C.c_uint32] + E
     L.tm_engine_decode_ungrouped.argtypes = [P, C.c_uint32] + E
     L.tm_engine_plan.argtypes = [C.c_char_p, C.c_uint32, C.c_uint64, C.POINTER(Info)] + E
+    L.tm_engine_plan_shard.argtypes = [C.c_char_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.POINTER(Info)] + E
     _lib = L
     return L
 
@@ -81,21 +84,38 @@ def _check(rc: int, err) -> None:
         raise EngineError(rc, err.value.decode(errors="replace"))
 
 
-def plan(gguf_path, context: int, budget_bytes: int) -> Info:
-    """Admission arithmetic only (no device): raises when R + U + H > B."""
+def plan(gguf_path, context: int, budget_bytes: int, shard_rank: int = 0, shard_world: int = 1) -> Info:
+    """Admission arithmetic only (no device): raises when R + U + H > B.  With
+    shard_world > 1 the byte classes are those of one rank of the row split."""
     L = load_library()
     info, err = Info(), C.create_string_buffer(1024)
-    _check(L.tm_engine_plan(str(gguf_path).encode(), context, budget_bytes, C.byref(info), err, 1024), err)
+    _check(L.tm_engine_plan_shard(str(gguf_path).encode(), context, budget_bytes, shard_rank, shard_world,
+                                  C.byref(info), err, 1024), err)
     return info
+
+
+def comm_id() -> bytes:
+    """128 opaque bytes naming a new communicator; rank 0 makes them and the
+    launcher hands them to the other ranks."""
+    L = load_library()
+    out, err = C.create_string_buffer(128), C.create_string_buffer(1024)
+    _check(L.tm_engine_comm_id(out, err, 1024), err)
+    return out.raw
 
 
 class Engine:
     def __init__(self, gguf_path, context: int, kernels: str = "cuda", device: int = 0, prefill_batch: int = 0,
-                 exact: bool = False, budget_bytes: int = 0):
+                 exact: bool = False, budget_bytes: int = 0, shard_rank: int = 0, shard_world: int = 1,
+                 comm_id: bytes | None = None):
+        """With shard_world > 1 every rank constructs its Engine with the same
+        128-byte `comm_id` (from `comm_id()` on one rank) and then makes the same
+        calls in the same order; each call is a collective."""
         self._l = load_library()
         self._path = str(gguf_path).encode()
         self._kernels = kernels.encode()
-        o = _Options(self._path, self._kernels, device, context, prefill_batch, int(exact), budget_bytes)
+        self._comm_id = C.create_string_buffer(comm_id, 128) if comm_id is not None else None
+        o = _Options(self._path, self._kernels, device, context, prefill_batch, int(exact), budget_bytes,
+                     shard_rank, shard_world, C.cast(self._comm_id, C.c_void_p) if self._comm_id is not None else None)
         h, err = C.c_void_p(), C.create_string_buffer(1024)
         _check(self._l.tm_engine_load(C.byref(o), C.byref(h), err, 1024), err)
         self.handle = h

@@ -1,0 +1,70 @@
+"""Host arithmetic of the output-row split (one process per device).
+
+Every Q8_0 row is an independent byte range and every output element depends on
+one weight row and the whole input vector, so rank r of W owns rows
+[r*N/W, (r+1)*N/W) of each projection and of the head, and an all-gather
+reassembles the output.  Attention stays local by keeping whole heads on one
+rank.  The reference runs on one device; this module states the rules the C++
+engine (csrc/engine/engine.cpp) and the collectives (csrc/tm_cuda_comm.cu)
+follow, so launchers and tests can share them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+
+def row_range(rank: int, world: int, rows: int) -> tuple[int, int]:
+    """Half-open global row range of `rank`; rows must divide evenly."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a split of {world}")
+    if rows % world:
+        raise ValueError(f"{rows} rows do not divide over {world} devices")
+    per = rows // world
+    return rank * per, (rank + 1) * per
+
+
+@dataclass(frozen=True)
+class ShardGeometry:
+    """Per-rank sizes of a dense decoder under the split."""
+
+    world: int
+    heads: int      # query heads on this rank
+    kv_heads: int   # KV heads on this rank (the KV cache is divided with them)
+    ffn: int        # gate / up rows on this rank
+    hidden: int     # o / down rows on this rank
+    vocab: int      # head rows on this rank
+
+
+def shard_geometry(shape, world: int) -> ShardGeometry:
+    """Refuses what the engine refuses: a head count, FFN width, hidden size or
+    vocabulary that does not divide, or a split that would cut a KV group."""
+    for name in ("heads", "kv_heads", "ffn", "hidden", "vocab"):
+        if getattr(shape, name) % world:
+            raise ValueError(f"{name} = {getattr(shape, name)} does not divide over {world} devices")
+    return ShardGeometry(world, shape.heads // world, shape.kv_heads // world, shape.ffn // world,
+                         shape.hidden // world, shape.vocab // world)
+
+
+def interleave_rows(gathered: np.ndarray, world: int, n_rows: int, width: int) -> np.ndarray:
+    """An all-gather of per-rank [n_rows][width] slices arrives rank-major,
+    [world][n_rows][width]; the activation layout is [n_rows][world * width]."""
+    g = np.asarray(gathered).reshape(world, n_rows, width)
+    return np.ascontiguousarray(g.transpose(1, 0, 2)).reshape(n_rows, world * width)
+
+
+def local_argmax(x: np.ndarray, index_offset: int) -> tuple[np.float32, int]:
+    """(value, global index) of the first maximum of one rank's slice."""
+    i = int(np.argmax(x))
+    return np.float32(x[i]), index_offset + i
+
+
+def merge_argmax(pairs) -> int:
+    """The larger value wins; equal values go to the lower GLOBAL index, so the
+    sharded choice equals the single-device one (first maximum)."""
+    best_v, best_i = None, None
+    for v, i in pairs:
+        if best_v is None or v > best_v or (v == best_v and i < best_i):
+            best_v, best_i = v, i
+    return int(best_i)

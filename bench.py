@@ -273,6 +273,9 @@ def run_cuda(args):
     value = world * dec_tokens / (decode_ms / 1e3)
     e2e = world * gen / (span_ms / 1e3)
 
+    split = row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n,
+                          tokens) if world > 1 else None
+
     if rank == 0:
         roof = gemv_roofline(eng, shape, hbm_gbs)
         roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"
@@ -302,10 +305,72 @@ def run_cuda(args):
             "wall_s": wall,
             "tokens_head": [int(t) for t in tokens[:8]],
         }
+        if split is not None:
+            line["row_split"] = split
         print(json.dumps(line), flush=True)
     eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n, replica_tokens):
+    """The same session with ONE model split by output rows over all ranks (each
+    rank holds 1/world of every projection, of the head and of the KV cache; four
+    NCCL all-gathers per layer inside the replayed decode graph).  Strong scaling
+    of a single sequence: reported beside the replica figure, not as `value`."""
+    try:
+        from tuckmill_b200 import sharding as S
+        S.shard_geometry(shape, world)
+    except ValueError as e:
+        return {"unavailable": str(e)}
+    ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        ident.copy_(torch.frombuffer(bytearray(E.comm_id()), dtype=torch.uint8))
+    dist.broadcast(ident, 0)
+    eng = E.Engine(path, context=context, device=local, shard_rank=rank, shard_world=world,
+                   comm_id=bytes(ident.cpu().numpy().tobytes()))
+    stream = torch.cuda.ExternalStream(eng.stream(), device=local)
+    prompt = T.token_ids(args.seed, prompt_n, shape.vocab)  # rank 0's prompt of the replica arm, on every rank
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e.record()
+        return e
+
+    def session():
+        eng.reset()
+        e0 = ev()
+        eng.prefill(prompt, want_token=True)
+        e1 = ev()
+        eng.decode_steps(decode_n - 1)
+        e2 = ev()
+        return e0, e1, e2
+
+    for _ in range(args.warmup):
+        session()
+    dist.barrier()
+    eng.fence()
+    evs = [session() for _ in range(args.steps)]
+    eng.fence()
+    torch.cuda.synchronize()
+    tokens, st = eng.generate(prompt, decode_n)
+    vals = torch.tensor([sum(a.elapsed_time(b) for a, b, c in evs), sum(b.elapsed_time(c) for a, b, c in evs),
+                         st.decode_span_ns / 1e6], dtype=torch.float64, device="cuda")
+    dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms, span_ms = vals.tolist()
+    info = eng.refresh_info()
+    out = {
+        "parallelism": f"output-row split x{world}, ncclAllGather on the compute stream", "scaling": "strong",
+        "decode_tok_s": args.steps * (decode_n - 1) / (decode_ms / 1e3),
+        "decode_us_per_token": 1e3 * decode_ms / (args.steps * (decode_n - 1)),
+        "prefill_tok_s": args.steps * prompt_n / (prefill_ms / 1e3),
+        "e2e_decode_tok_s": (st.generated - 1) / (span_ms / 1e3),
+        "per_rank_weight_bytes": int(info.plan_weights), "per_rank_kv_bytes": int(info.plan_state),
+        "tokens_equal_single_device": bool(replica_tokens is not None and list(tokens) == list(replica_tokens)),
+    }
+    eng.close()
+    return out
 
 
 def _launches(eng) -> int:

@@ -7,14 +7,29 @@
 // operand profile instead: x and d*q are rounded to binary16 (each once, to
 // nearest even), products accumulate in f32 in tensor memory.
 //
-// One CTA computes a 128 (weight rows) x BN (tokens) tile of Y^T:
-//   warps 0-3  producers: each thread owns one weight row of the tile, loads 64
-//              int8 quants + 2 scales per K block straight from the packed
-//              planes, converts to f16 (byte permute into 1024+u, subtract
-//              1152, multiply by d) and writes the row into the 128-byte
-//              swizzled K-major layout the MMA reads; later the epilogue
-//   warp 4     one thread issues the TMA loads of the token tile (f16 copy of X)
-//   warp 5     allocates tensor memory; one thread issues tcgen05.mma
+// Persistent kernel, one CTA per SM, tiles of 128 (weight rows) x 2*BN (tokens)
+// of Y^T handed out round-robin.  Three facts measured on this part shape it:
+//  * the thread that issues tcgen05.mma cannot hide its own barrier waits and
+//    commits behind a K step of four MMAs, so TWO threads issue, each into its
+//    own BN-column accumulator (two token sub-tiles against the same weight
+//    rows): while one waits, the other's MMAs keep the tensor pipe busy;
+//  * staging both operands in shared memory saturates the shared-memory data
+//    path before the tensor pipe, so the dequantised weight tile is the MMA's A
+//    operand IN TENSOR MEMORY and never touches shared memory;
+//  * a weight tile converted once now serves 2*BN tokens.
+// Tensor memory: two BN-column accumulators + (512 - 2*BN)/32 A stages of 32 columns.
+// Roles by warp:
+//   0-7    converters: warps q and q+4 own tensor-memory lanes 32q..32q+31 and
+//          take alternate K steps; a thread reads its row's 64 raw bytes (TMA,
+//          64-byte swizzle), turns them into f16 d*q (byte permute into 1024+u,
+//          subtract 1152, multiply by d) and writes them with tcgen05.st; block
+//          scales come straight from global memory, several K steps ahead
+//   8-15   epilogue: tensor memory -> registers -> Y; four warps (one lane quarter each) per accumulator
+//   16     one thread issues the TMA loads of the raw weight tile
+//   17     one thread issues the TMA loads of the two token sub-tiles (f16 copy of X)
+//   18,19  one thread each issues tcgen05.mma for its sub-tile; warp 18 allocates tensor memory
+// The accumulators are single-buffered (tensor memory is full), so a tile's epilogue is not hidden
+// behind the next tile's MMAs: eight warps keep it short.
 // Stages are handed over with mbarriers; every wait is bounded and raises an
 // abort flag instead of spinning forever.
 #include <cuda.h>
@@ -25,8 +40,11 @@ namespace {
 
 constexpr int kBM = 128;        // weight rows per tile (UMMA M)
 constexpr int kBK = 64;         // K per stage: 64 f16 = one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kMmaThreads = 192;
+constexpr int kRawStages = 4;   // raw int8 weight tiles in flight (8 KB each)
+constexpr int kConvWarps = 8, kIssuers = 2, kEpiWarps = 4 * kIssuers;
+constexpr int kWarpRaw = kConvWarps + kEpiWarps, kWarpTok = kWarpRaw + 1, kWarpMma = kWarpRaw + 2;
+constexpr int kMmaThreads = (kWarpMma + kIssuers) * 32;
+constexpr int kScaleAhead = 4;  // a converter's own steps (every other K step) between a scale's load and its use
 constexpr uint32_t kSpinLimit = 1u << 20;  // a healthy wait is microseconds; this is ~seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -75,12 +93,21 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem] over one K step of 64: four MMAs of K = 16 in a single block (one
+// predicate set-up for all four).  A is 128 lanes x 8 tensor-memory columns per MMA (16 f16 per row, two per column); B advances 32 bytes = 2 descriptor units, in the low word only.
+__device__ __forceinline__ void umma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n .reg .pred p, q;\n .reg .b64 b0, b1, b2, b3;\n .reg .b32 a1, a2, a3, l1, l2, l3;\n"
+        " setp.ne.b32 p, %5, 0;\n setp.eq.b32 q, 0, 0;\n"
+        " add.u32 a1, %1, 8;\n add.u32 a2, %1, 16;\n add.u32 a3, %1, 24;\n"
+        " add.u32 l1, %2, 2;\n add.u32 l2, %2, 4;\n add.u32 l3, %2, 6;\n"
+        " mov.b64 b0, {%2, %3};\n mov.b64 b1, {l1, %3};\n mov.b64 b2, {l2, %3};\n mov.b64 b3, {l3, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, p;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, q;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, q;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, q;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -96,9 +123,8 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 }
 
 // Eight quants (two 32-bit words) -> eight f16 values d*q, as four half2 words.
-__device__ __forceinline__ int4 dequant8(uint32_t w0, uint32_t w1, __half2 d2) {
+__device__ __forceinline__ void dequant8(uint32_t w0, uint32_t w1, __half2 d2, uint32_t *out) {
     const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));  // 1152.0
-    uint32_t out[4];
     const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;  // q + 128 as unsigned bytes
     // byte b of u -> f16 bits 0x6400 | b == 1024 + b, two lanes per permute
     const uint32_t h[4] = {__byte_perm(u0, 0x64646464u, 0x4140), __byte_perm(u0, 0x64646464u, 0x4342),
@@ -109,47 +135,87 @@ __device__ __forceinline__ int4 dequant8(uint32_t w0, uint32_t w1, __half2 d2) {
         const __half2 v = __hmul2(qh, d2);                          // one rounding: RN(d * q)
         out[i] = *(const uint32_t *)&v;
     }
-    return make_int4((int)out[0], (int)out[1], (int)out[2], (int)out[3]);
 }
 
 struct mma_args {
-    const signed char *q;  // [rows][cols]
-    const __half *d;       // [rows][cols/32]
+    const __half *d;       // [rows][cols/32] block scales
     float *y;              // Y[t * rows + r]
     uint32_t rows, cols, batch;
     uint32_t *abort_flag;  // set when a bounded wait gave up
 };
 
+// Ring bookkeeping over a running step count g: stage g % D, the consumer waits
+// for fill number g / D (parity of it), the producer for drain number g / D - 1.
+template <int D>
+struct ring {
+    static __device__ __forceinline__ uint32_t stage(uint32_t g) { return g % D; }
+    static __device__ __forceinline__ uint32_t full_parity(uint32_t g) { return (g / D) & 1u; }
+    static __device__ __forceinline__ bool must_wait_empty(uint32_t g) { return g >= (uint32_t)D; }
+    static __device__ __forceinline__ uint32_t empty_parity(uint32_t g) { return (g / D - 1u) & 1u; }
+};
+
 template <int BN>
-__global__ void __launch_bounds__(kMmaThreads, 1) q8_gemm_mma_kernel(const __grid_constant__ CUtensorMap xmap,
-                                                                     const mma_args a) {
+struct mma_smem {
+    // One ring hands both operands of a K step to the issuers: stage s holds the converted weight tile
+    // (tensor-memory columns kACol0 + 32 s) and the token sub-tiles (shared memory), behind ONE full
+    // barrier (converter arrivals + the TMA's bytes) and ONE empty barrier (the issuers' commits), so
+    // an issuer pays one wait and one commit per step.
+    static constexpr int kATmemStages = (512 - kIssuers * BN) / 32;  // what the accumulators leave
+    static constexpr int kStages = BN > 128 ? 4 : 6;
+    static constexpr uint32_t kRawBytes = kBM * kBK;             // int8
+    static constexpr uint32_t kSubBytes = BN * kBK * 2;          // one token sub-tile, f16
+    static constexpr uint32_t kBBytes = kIssuers * kSubBytes;    // a stage
+    static constexpr uint32_t kBOff = 0;
+    static constexpr uint32_t kRawOff = kBOff + kStages * kBBytes;
+    static constexpr uint32_t kBarOff = kRawOff + kRawStages * kRawBytes;
+    static constexpr uint32_t kBars = 2 * kRawStages + 2 * kStages + kIssuers + 1;
+    static constexpr uint32_t kBytes = 1024 + kBarOff + kBars * 8 + 16;
+    static constexpr uint32_t kACol0 = kIssuers * BN;  // tensor-memory column of A stage 0, after the accumulators
+    static constexpr uint32_t kTmemCols = 512;
+    static_assert(kStages % 2 == 0 && kStages <= kATmemStages, "each converter set needs its own A stages");
+    static_assert(kBytes <= 232448, "shared memory per CTA");
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kMmaThreads, 1)
+    q8_gemm_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                       const mma_args a) {
+    using L = mma_smem<BN>;
+    constexpr int kStages = L::kStages;
+    constexpr uint32_t kTB = kIssuers * BN;  // tokens per tile
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte aligned stage buffers (swizzle atoms), then the barriers.
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2;
-    unsigned char *sA = smem, *sB = smem + kStages * kABytes;
-    uint64_t *full_a = (uint64_t *)(sB + kStages * kBBytes);
-    uint64_t *full_b = full_a + kStages, *empty = full_b + kStages, *accum = empty + kStages;
-    uint32_t *tmem_slot = (uint32_t *)(accum + 1);
+    unsigned char *sB = smem + L::kBOff, *sRaw = smem + L::kRawOff;
+    uint64_t *raw_full = (uint64_t *)(smem + L::kBarOff), *raw_empty = raw_full + kRawStages;
+    uint64_t *full = raw_empty + kRawStages, *empty = full + kStages;
+    uint64_t *acc_full = empty + kStages, *acc_empty = acc_full + kIssuers;
+    uint32_t *tmem_slot = (uint32_t *)(acc_empty + 1);
     volatile uint32_t *abort_s = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t row0 = blockIdx.x * kBM, tok0 = blockIdx.y * BN;
     const uint32_t nkb = (a.cols + kBK - 1) / kBK, nb = a.cols / 32u;
+    const uint32_t row_tiles = (a.rows + kBM - 1) / kBM, tok_tiles = (a.batch + kTB - 1) / kTB;
+    const uint32_t n_tiles = row_tiles * tok_tiles;
+    // Consecutive tiles share a token tile, so CTAs running side by side read the same X.
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_a[s], 4);  // one arrival per producer warp
-            mbar_init(&full_b[s], 1);  // the TMA thread's expect_tx arrival
-            mbar_init(&empty[s], 1);   // tcgen05.commit
+        for (int s = 0; s < kRawStages; ++s) {
+            mbar_init(&raw_full[s], 1);            // the TMA thread's expect_tx arrival
+            mbar_init(&raw_empty[s], kConvWarps / 2);  // one arrival per converter warp of the set that read it
         }
-        mbar_init(accum, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], kConvWarps / 2 + 1);  // the converter set's warps + the TMA thread's expect_tx arrival
+            mbar_init(&empty[s], kIssuers);           // one tcgen05.commit per issuer
+        }
+        for (int s = 0; s < kIssuers; ++s) mbar_init(&acc_full[s], 1);  // tcgen05.commit after a tile's last MMA
+        mbar_init(acc_empty, kEpiWarps);                                    // one arrival per epilogue warp
         *abort_s = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kWarpMma) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
+                     "r"(L::kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -158,54 +224,116 @@ __global__ void __launch_bounds__(kMmaThreads, 1) q8_gemm_mma_kernel(const __gri
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
-        // ---------------- producers: dequantise one weight row per thread ----------------
-        const uint32_t r = min(row0 + (uint32_t)tid, a.rows - 1u);  // rows past the end repeat the last (masked later)
-        const signed char *qrow = a.q + (size_t)r * a.cols;
-        const __half *drow = a.d + (size_t)r * nb;
-        int4 raw[4];
-        __half sc[2];
-        auto fetch = [&](uint32_t kb) {
-            const uint32_t k0 = kb * kBK;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                raw[c] = k0 + c * 16 < a.cols ? *(const int4 *)(qrow + k0 + c * 16) : make_int4(0, 0, 0, 0);
-            sc[0] = k0 < a.cols ? drow[k0 / 32] : __ushort_as_half((unsigned short)0);
-            sc[1] = k0 + 32 < a.cols ? drow[k0 / 32 + 1] : __ushort_as_half((unsigned short)0);
+    if (warp < kConvWarps) {
+        // ---------------- converters ----------------
+        // Warps q and q + 4 reach tensor-memory lanes 32q..32q+31; set 0 (warps 0-3) converts the even K
+        // steps of the running count, set 1 the odd ones.  A thread owns tile row 32q + lane.
+        const uint32_t set = (uint32_t)warp >> 2, quarter = (uint32_t)warp & 3u;
+        const uint32_t trow = quarter * 32u + (uint32_t)lane;
+        const uint32_t rsw = (trow >> 1) & 3u;  // the TMA's 64-byte swizzle: 16-byte piece c of row r sits at c ^ ((r >> 1) & 3)
+        const bool pair_load = (nb & 1u) == 0u;  // both scales of a K step in one aligned 4-byte load
+        // Scale look-ahead: the position (tile, kb) of this set's step kScaleAhead own-steps in front.
+        uint32_t la_tile = blockIdx.x, la_kb = 0;
+        auto la_advance = [&](uint32_t n) {
+            for (uint32_t i = 0; i < n; ++i)
+                if (++la_kb == nkb) {
+                    la_kb = 0;
+                    la_tile += gridDim.x;
+                }
         };
-        fetch(0);
-        bool ok = true;
-        for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-            const uint32_t s = kb % kStages, it = kb / kStages;
-            if (it > 0) ok = mbar_wait(&empty[s], (it - 1) & 1, abort_s);
-            if (!ok) break;
-            unsigned char *rowp = sA + s * kABytes + (uint32_t)tid * 128u;
+        auto scale_load = [&]() -> uint32_t {
+            if (la_tile >= n_tiles) return 0u;
+            const uint32_t r = min((la_tile % row_tiles) * kBM + trow, a.rows - 1u);
+            const uint32_t blk = la_kb * 2u;
+            const unsigned short *p = (const unsigned short *)a.d + (size_t)r * nb + blk;
+            if (pair_load) return __ldg((const uint32_t *)p);
+            const uint32_t lo = __ldg(p), hi = blk + 1u < nb ? (uint32_t)__ldg(p + 1) : 0u;
+            return lo | (hi << 16);
+        };
+        la_advance(set);
+        // The look-ahead values live in registers with STATIC indices (the loop below is unrolled by
+        // the ring length): a rotating copy would read each register right after its load was issued
+        // and wait out the whole memory latency every step.
+        uint32_t ring_d[kScaleAhead];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {  // chunk c = k 8c..8c+7 of this K block
-                const int4 w = raw[c >> 1];
-                const uint32_t w0 = (c & 1) ? (uint32_t)w.z : (uint32_t)w.x, w1 = (c & 1) ? (uint32_t)w.w : (uint32_t)w.y;
-                const int4 v = dequant8(w0, w1, __half2half2(sc[c >> 2]));
-                *(int4 *)(rowp + ((c ^ (tid & 7)) << 4)) = v;
-            }
-            if (kb + 1 < nkb) fetch(kb + 1);  // next block's bytes travel while the MMA consumes this one
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> async proxy (UMMA)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_a[s]);
+        for (int i = 0; i < kScaleAhead; ++i) {
+            ring_d[i] = scale_load();
+            la_advance(2);
         }
-        // ---------------- epilogue: TMEM -> registers -> Y ----------------
-        if (ok) ok = mbar_wait(accum, 0, abort_s);
-        ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const uint32_t rr = row0 + (uint32_t)tid;
+        // This set's steps, flat over the CTA's tiles: own step j is running step g = 2j + set.
+        const uint32_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1u - blockIdx.x) / gridDim.x + 1u : 0u;
+        const uint32_t total = my_tiles * nkb, n_own = total > set ? (total - set + 1u) / 2u : 0u;
+        bool ok = true;
+        for (uint32_t j0 = 0; j0 < n_own && ok; j0 += kScaleAhead) {
+#pragma unroll
+            for (int u = 0; u < kScaleAhead; ++u) {
+                if (j0 + (uint32_t)u >= n_own || !ok) break;
+                const uint32_t g = 2u * (j0 + (uint32_t)u) + set;
+                const uint32_t sr = ring<kRawStages>::stage(g), sa = ring<kStages>::stage(g);
+                // Convert into registers first; the A stage is needed only for the store.
+                ok = mbar_wait(&raw_full[sr], ring<kRawStages>::full_parity(g), abort_s);
+                const unsigned char *raw = sRaw + sr * L::kRawBytes + trow * kBK;
+                const uint32_t dd = ring_d[u];
+                const __half2 d_lo = __half2half2(__ushort_as_half((unsigned short)(dd & 0xffffu)));
+                const __half2 d_hi = __half2half2(__ushort_as_half((unsigned short)(dd >> 16)));
+                uint32_t v[32];
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {  // piece c = k 16c..16c+15 of this K step
+                    const int4 w = *(const int4 *)(raw + ((c ^ rsw) << 4));
+                    const __half2 d2 = c < 2 ? d_lo : d_hi;
+                    dequant8((uint32_t)w.x, (uint32_t)w.y, d2, v + 8 * c);
+                    dequant8((uint32_t)w.z, (uint32_t)w.w, d2, v + 8 * c + 4);
+                }
+                ring_d[u] = scale_load();
+                la_advance(2);
+                if (ok && ring<kStages>::must_wait_empty(g))
+                    ok = mbar_wait(&empty[sa], ring<kStages>::empty_parity(g), abort_s);
+                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory store below is warp-collective
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // Register i -> column i of this thread's lane: k = 2i (low half), 2i + 1 (high half).
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + L::kACol0 + sa * 32u;
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                    "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
+                    "%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+                    "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+                    "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
+                    "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+                    "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                    : "memory");
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full[sa]);
+                    mbar_arrive(&raw_empty[sr]);  // every lane's reads of the raw tile are done
+                }
+            }
+        }
+    } else if (warp < kWarpRaw) {
+        // ---------------- epilogue: tensor memory -> registers -> Y ----------------
+        const uint32_t quarter = (uint32_t)warp & 3u;  // a warp reaches tensor-memory lanes 32*(warp%4)..+31
+        const uint32_t sub = (uint32_t)(warp - kConvWarps) >> 2;  // the accumulator this warp drains
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+            const uint32_t rr = (tile % row_tiles) * kBM + quarter * 32u + (uint32_t)lane;
+            const uint32_t tok0 = (tile / row_tiles) * kTB + sub * BN;
+            if (ok) ok = mbar_wait(&acc_full[sub], it & 1u, abort_s);
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
+                const uint32_t t0 = tok0 + (uint32_t)c0;
+                if (t0 >= a.batch) break;  // uniform: the rest of the sub-tile is past the batch
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + sub * BN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
-                    "%26,%27,%28,%29,%30,%31}, [%32];"
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+                    "%25,%26,%27,%28,%29,%30,%31}, [%32];"
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
                       "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
@@ -215,52 +343,111 @@ __global__ void __launch_bounds__(kMmaThreads, 1) q8_gemm_mma_kernel(const __gri
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (rr < a.rows) {
+                    // Lane = row: for a fixed token the warp writes 128 contiguous bytes.
+                    float *p = a.y + (size_t)t0 * a.rows + rr;
+                    const size_t stride = a.rows;  // independent addresses: no add chain between the stores
+                    if (t0 + 32u <= a.batch) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t t = tok0 + (uint32_t)(c0 + j);
-                        if (t < a.batch) a.y[(size_t)t * a.rows + rr] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) p[(size_t)j * stride] = __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (t0 + (uint32_t)j < a.batch) p[(size_t)j * stride] = __uint_as_float(v[j]);
                     }
                 }
             }
+            // The accumulator may be overwritten once every warp has its values in registers.
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
         }
-    } else if (warp == 4) {
-        // ---------------- TMA producer of the token tile ----------------
+    } else if (warp == kWarpRaw) {
+        // ---------------- TMA producer of the raw weight tile ----------------
         if (lane == 0) {
+            uint32_t g = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const uint32_t s = kb % kStages, it = kb / kStages;
-                if (it > 0) ok = mbar_wait(&empty[s], (it - 1) & 1, abort_s);
-                if (!ok) break;
-                mbar_expect_tx(&full_b[s], kBBytes);
-                tma_load_2d(sB + s * kBBytes, &xmap, (int)(kb * kBK), (int)tok0, &full_b[s]);
+            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int row0 = (int)((tile % row_tiles) * kBM);
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const uint32_t s = ring<kRawStages>::stage(g);
+                    if (ring<kRawStages>::must_wait_empty(g))
+                        ok = mbar_wait(&raw_empty[s], ring<kRawStages>::empty_parity(g), abort_s);
+                    if (!ok) break;
+                    mbar_expect_tx(&raw_full[s], L::kRawBytes);
+                    tma_load_2d(sRaw + s * L::kRawBytes, &wmap, (int)(kb * kBK), row0, &raw_full[s]);
+                }
             }
+            // Giving up with copies still in flight: let them land before the CTA's memory goes away.
+            if (!ok)
+                for (uint32_t i = 0; i < (uint32_t)kRawStages && i < g; ++i)
+                    mbar_wait(&raw_full[ring<kRawStages>::stage(g - 1 - i)], ring<kRawStages>::full_parity(g - 1 - i),
+                              abort_s);
+        }
+    } else if (warp == kWarpTok) {
+        // ---------------- TMA producer of the token sub-tiles ----------------
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const uint32_t tok0 = (tile / row_tiles) * kTB;
+                // A sub-tile wholly past the batch is neither loaded nor multiplied.
+                const uint32_t subs = tok0 + BN < a.batch ? (uint32_t)kIssuers : 1u;
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const uint32_t s = ring<kStages>::stage(g);
+                    if (ring<kStages>::must_wait_empty(g))
+                        ok = mbar_wait(&empty[s], ring<kStages>::empty_parity(g), abort_s);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], subs * L::kSubBytes);
+                    for (uint32_t sub = 0; sub < subs; ++sub)
+                        tma_load_2d(sB + s * L::kBBytes + sub * L::kSubBytes, &xmap, (int)(kb * kBK),
+                                    (int)(tok0 + sub * BN), &full[s]);
+                }
+            }
+            if (!ok)
+                for (uint32_t i = 0; i < (uint32_t)kStages && i < g; ++i)
+                    mbar_wait(&full[ring<kStages>::stage(g - 1 - i)], ring<kStages>::full_parity(g - 1 - i), abort_s);
         }
     } else {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuers ----------------
+        // Issuer `sub` multiplies the shared A stage by its own token sub-tile into its own accumulator.
+        // Stage indices and parities advance by increment: no divisions, no descriptor built from scratch.
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(kBM, BN);
+            const uint32_t sub = (uint32_t)(warp - kWarpMma);
+            const uint64_t db0 = umma_desc(smem_u32(sB + sub * L::kSubBytes));
+            const uint32_t db_lo = (uint32_t)db0, db_hi = (uint32_t)(db0 >> 32);
+            const uint32_t ta0 = tmem_base + L::kACol0, d_tmem = tmem_base + sub * BN;
+            uint32_t it = 0, st = 0, par = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const uint32_t s = kb % kStages, it = kb / kStages;
-                ok = mbar_wait(&full_a[s], it & 1, abort_s) && mbar_wait(&full_b[s], it & 1, abort_s);
+            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+                const bool live = (tile / row_tiles) * kTB + sub * BN < a.batch;  // else: the barrier protocol only
+                if (it >= 1u) ok = mbar_wait(acc_empty, (it - 1u) & 1u, abort_s);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = umma_desc(smem_u32(sA + s * kABytes)), db = umma_desc(smem_u32(sB + s * kBBytes));
-#pragma unroll
-                for (uint32_t k = 0; k < kBK / 16; ++k)  // 16 f16 = 32 bytes = 2 descriptor units per step
-                    umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+                uint32_t accumulate = 0u;
+                for (uint32_t kb = 0; kb < nkb; ++kb) {
+                    ok = mbar_wait(&full[st], par, abort_s);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (live) umma_f16_ts_x4(d_tmem, ta0 + st * 32u, db_lo + st * (L::kBBytes >> 4), db_hi, idesc, accumulate);
+                    accumulate = 1u;
+                    umma_commit(&empty[st]);  // frees the stage once this issuer's MMAs have read it
+                    if (++st == (uint32_t)kStages) {
+                        st = 0;
+                        par ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(&acc_full[sub]);  // fires when every MMA of the tile has completed
             }
-            if (ok) umma_commit(accum);  // fires when every MMA above has completed
         }
     }
     // ---------------- teardown: everyone meets, tensor memory goes back ----------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0 && *abort_s) atomicOr(a.abort_flag, 1u);
-    if (warp == 5) {
+    if (warp == kWarpMma) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols)
                      : "memory");
     }
 }
@@ -299,8 +486,18 @@ encode_tiled_fn get_encode_tiled() {
 }
 
 template <int BN>
-size_t mma_smem_bytes() {
-    return 1024 + (size_t)kStages * (kBM * kBK * 2 + BN * kBK * 2) + (3 * kStages + 1) * 8 + 16;
+cudaError_t launch_mma(const CUtensorMap &wmap, const CUtensorMap &xmap, const mma_args &a, int grid, int device,
+                       cudaStream_t stream) {
+    static bool attr_done[16] = {};
+    const int dev = device >= 0 && device < 16 ? device : 0;
+    if (!attr_done[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(q8_gemm_mma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)mma_smem<BN>::kBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    q8_gemm_mma_kernel<BN><<<grid, kMmaThreads, mma_smem<BN>::kBytes, stream>>>(wmap, xmap, a);
+    return cudaGetLastError();
 }
 
 }  // namespace
@@ -367,19 +564,50 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
         return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "the driver does not export cuTensorMapEncodeTiled");
     __half *xh = (__half *)ctx->mma_scratch;
     uint32_t *abort_flag = (uint32_t *)(ctx->mma_scratch + tm_round_up(ctx->mma_scratch_bytes, 256));
-    const int bn = batch > 128 ? 256 : 128;
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {cols, batch};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)bn};
+    // Sub-tile width BN (a tile is 128 rows x 2*BN tokens): the one whose rounds of the persistent
+    // grid cost the fewest cycles.  Measured: a K step takes the larger of the tensor-pipe time
+    // (4*BN cycles for the two issuers' eight MMAs) and the issuing threads' own ~440 cycles; the
+    // unhidden epilogue adds about 30 cycles per token column.
+    const uint32_t row_tiles = (rows + kBM - 1) / kBM, sms = (uint32_t)ctx->sm_count;
+    int bn = 64;
+    {
+        const uint64_t nkb = (cols + kBK - 1) / kBK;
+        uint64_t best = ~0ull;
+        for (int cand : {192, 128, 64}) {
+            const uint32_t tiles = row_tiles * ((batch + 2 * cand - 1) / (2 * cand));
+            const uint64_t step = 4 * cand > 440 ? 4 * cand : 440;
+            const uint64_t cost = (uint64_t)((tiles + sms - 1) / sms) * (nkb * step + 30ull * 2 * cand);
+            if (cost < best) {
+                best = cost;
+                bn = cand;
+            }
+        }
+    }
+    if (getenv("TM_MMA_BN")) bn = atoi(getenv("TM_MMA_BN"));
+    CUtensorMap xmap, wmap;
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)xh, gdim, gstride, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS)
-        return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    {
+        const cuuint64_t gdim[2] = {cols, batch};
+        const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)bn};
+        const CUresult cr = encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)xh, gdim, gstride, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS)
+            return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cuTensorMapEncodeTiled (tokens) failed (%d)", (int)cr);
+    }
+    {
+        // The int8 plane as bytes, 64 x 128 boxes, 64-byte swizzle; rows and columns past the end read as zero.
+        const cuuint64_t gdim[2] = {cols, rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)cols};
+        const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+        const CUresult cr = encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w->qp, gdim, gstride, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS)
+            return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
+    }
     mma_args a;
-    a.q = (const signed char *)w->qp;
     a.d = (const __half *)w->dp;
     a.y = (float *)y->dev + y_off;
     a.rows = rows;
@@ -390,24 +618,12 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
     const size_t n = (size_t)batch * cols;
     const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
     x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev + x_off, xh, n);
-    const dim3 grid((rows + kBM - 1) / kBM, (batch + bn - 1) / bn);
-    static bool attr_done[2][16] = {};
-    const int dev = ctx->device < 16 ? ctx->device : 0;
-    if (bn == 256) {
-        if (!attr_done[1][dev]) {
-            TM_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)mma_smem_bytes<256>()));
-            attr_done[1][dev] = true;
-        }
-        q8_gemm_mma_kernel<256><<<grid, kMmaThreads, mma_smem_bytes<256>(), ctx->stream>>>(map, a);
-    } else {
-        if (!attr_done[0][dev]) {
-            TM_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)mma_smem_bytes<128>()));
-            attr_done[0][dev] = true;
-        }
-        q8_gemm_mma_kernel<128><<<grid, kMmaThreads, mma_smem_bytes<128>(), ctx->stream>>>(map, a);
-    }
+    const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn));
+    int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
+    if (getenv("TM_MMA_GRID") && atoi(getenv("TM_MMA_GRID")) < grid) grid = atoi(getenv("TM_MMA_GRID"));
+    TM_CUDA_TRY(bn == 192   ? launch_mma<192>(wmap, xmap, a, grid, ctx->device, ctx->stream)
+                : bn == 128 ? launch_mma<128>(wmap, xmap, a, grid, ctx->device, ctx->stream)
+                            : launch_mma<64>(wmap, xmap, a, grid, ctx->device, ctx->stream));
     TM_OP_END(2);
 }
 

@@ -41,7 +41,7 @@ namespace {
 constexpr int kBM = 128;        // weight rows per tile (UMMA M)
 constexpr int kBK = 64;         // K per stage: 64 f16 = one 128-byte swizzle row
 constexpr int kRawStages = 4;   // raw int8 weight tiles in flight (8 KB each)
-constexpr int kConvWarps = 8, kIssuers = 2, kEpiWarps = 4 * kIssuers;
+constexpr int kConvWarps = 8, kIssuers = 2, kEpiWarps = 4;
 constexpr int kWarpRaw = kConvWarps + kEpiWarps, kWarpTok = kWarpRaw + 1, kWarpMma = kWarpRaw + 2;
 constexpr int kMmaThreads = (kWarpMma + kIssuers) * 32;
 constexpr int kScaleAhead = 4;  // a converter's own steps (every other K step) between a scale's load and its use
@@ -314,10 +314,10 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     } else if (warp < kWarpRaw) {
         // ---------------- epilogue: tensor memory -> registers -> Y ----------------
         const uint32_t quarter = (uint32_t)warp & 3u;  // a warp reaches tensor-memory lanes 32*(warp%4)..+31
-        const uint32_t sub = (uint32_t)(warp - kConvWarps) >> 2;  // the accumulator this warp drains
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+          for (uint32_t sub = 0; sub < (uint32_t)kIssuers && ok; ++sub) {
             const uint32_t rr = (tile % row_tiles) * kBM + quarter * 32u + (uint32_t)lane;
             const uint32_t tok0 = (tile / row_tiles) * kTB + sub * BN;
             if (ok) ok = mbar_wait(&acc_full[sub], it & 1u, abort_s);
@@ -356,6 +356,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     }
                 }
             }
+          }
+            if (!ok) break;
             // The accumulator may be overwritten once every warp has its values in registers.
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -565,9 +567,9 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
     __half *xh = (__half *)ctx->mma_scratch;
     uint32_t *abort_flag = (uint32_t *)(ctx->mma_scratch + tm_round_up(ctx->mma_scratch_bytes, 256));
     // Sub-tile width BN (a tile is 128 rows x 2*BN tokens): the one whose rounds of the persistent
-    // grid cost the fewest cycles.  Measured: a K step takes the larger of the tensor-pipe time
-    // (4*BN cycles for the two issuers' eight MMAs) and the issuing threads' own ~440 cycles; the
-    // unhidden epilogue adds about 30 cycles per token column.
+    // grid cost the fewest cycles.  Fitted to measurements: a K step takes the larger of the
+    // tensor-pipe time plus hand-over (4*BN + 94 cycles for the two issuers' eight MMAs) and the
+    // issuing threads' own 669 cycles; the unhidden epilogue adds about 30 cycles per token column.
     const uint32_t row_tiles = (rows + kBM - 1) / kBM, sms = (uint32_t)ctx->sm_count;
     int bn = 64;
     {
@@ -575,7 +577,7 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
         uint64_t best = ~0ull;
         for (int cand : {192, 128, 64}) {
             const uint32_t tiles = row_tiles * ((batch + 2 * cand - 1) / (2 * cand));
-            const uint64_t step = 4 * cand > 440 ? 4 * cand : 440;
+            const uint64_t step = 4 * cand + 94 > 669 ? 4 * cand + 94 : 669;
             const uint64_t cost = (uint64_t)((tiles + sms - 1) / sms) * (nkb * step + 30ull * 2 * cand);
             if (cost < best) {
                 best = cost;

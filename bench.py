@@ -158,10 +158,14 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def gemv_roofline(eng, shape, hbm_gbs):
-    """Time the decode step's operators one dispatch each and attribute."""
-    from tuckmill_b200 import engine as E  # noqa: F401
+def gemv_roofline(eng, shape, hbm_gbs, us_per_token):
+    """Roofline of the dominant kernel of the timed region, the Q8_0 GEMV (every
+    projection and the lm_head of a decode step are launches of it).
 
+    Inside the replayed graph single launches cannot be bracketed by events, so
+    the kernel's time within a step is the step's device time (measured over the
+    timed region) times the GEMV's share of the step, the share taken from a
+    pass that dispatches each operator on its own with events around it."""
     eng.reset()
     eng.prefill(T.token_ids(1, 64, shape.vocab), want_token=True)
     eng.decode_ungrouped(3)
@@ -175,20 +179,65 @@ def gemv_roofline(eng, shape, hbm_gbs):
     gemv_ns = sum(ns for n, (ns, c) in rows.items() if n.startswith("q8_0_gemv"))
     gemv_launches = sum(c for n, (ns, c) in rows.items() if n.startswith("q8_0_gemv"))
     total_ns = sum(ns for ns, c in rows.values())
+    share = gemv_ns / total_ns
     # algorithmic bytes of the GEMV launches of one step: weights once, f32 in, f32 out
     per_step = shape.decode_weight_bytes()
     act = 0
     for _, o, i in shape.matrices(0):
         act += 4 * i + 4 * o
     per_step += act * shape.layers + 4 * shape.hidden + 4 * shape.vocab
-    achieved = per_step * steps / gemv_ns  # bytes/ns == GB/s
+    launches = gemv_launches / steps
+    us_in_step = us_per_token * share
+    achieved = per_step / (us_in_step * 1e3)  # bytes / ns == GB/s
     return {
         "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-        "traffic": None, "kernel": "q8_gemv_kernel", "launches_per_step": gemv_launches / steps,
-        "bytes_per_launch": per_step / (gemv_launches / steps), "us_per_launch": gemv_ns / gemv_launches / 1e3,
-        "gemv_share_of_step": gemv_ns / total_ns,
-        "by_operator_us_per_step": {n: round(ns / steps / 1e3, 2) for n, (ns, c) in sorted(rows.items())},
+        "traffic": None, "kernel": "q8_gemv_kernel", "launches_per_step": launches,
+        "bytes_per_launch": per_step / launches, "us_per_launch": us_in_step / launches,
+        "gemv_share_of_step": share,
+        "note": "0.6B-scale projections are 2-6 MB each: a launch is latency-bound, not bandwidth-bound; "
+                "lm_head below is the one launch of the step that streams long enough to be",
+        "by_operator_us_per_step_ungrouped": {n: round(ns / steps / 1e3, 2) for n, (ns, c) in sorted(rows.items())},
     }
+
+
+def lm_head_roofline(device, shape, hbm_gbs, torch):
+    """The step's largest launch alone: the vocab x hidden GEMV, 20 launches in one
+    replayed graph with events on its stream either side (the weights, 1.0625
+    bytes per element, exceed L2, so every launch streams them from HBM)."""
+    from tuckmill_b200 import cuda
+
+    ctx = cuda.CudaContext(device)
+    rows, cols = shape.vocab, shape.hidden
+    base = T.q8_0_matrix(0, 99, 2048, cols)
+    raw = np.tile(base, ((rows + 2047) // 2048, 1, 1))[:rows]
+    w = ctx.q8_0_matrix(raw, rows, cols)
+    x = ctx.floats(T.activations(0, 98, cols))
+    y = ctx.buffer(rows * 4)
+    st = torch.cuda.ExternalStream(ctx.stream(), device=device)
+    n = 20
+    ctx.begin_group()  # one replayed graph of n launches: no host gap between them
+    for _ in range(n):
+        ctx.q8_0_gemv(w, x, y, rows, cols)
+    graph = ctx.end_group_retain()
+    graph.launch()
+    ctx.fence()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st):
+        e0.record()
+    graph.launch()
+    with torch.cuda.stream(st):
+        e1.record()
+    ctx.fence()
+    torch.cuda.synchronize()
+    graph.free()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    nbytes = rows * cols + rows * (cols // 32) * 2 + 4 * cols + 4 * rows
+    out = {"rows": rows, "cols": cols, "us_per_launch": us, "bytes_per_launch": nbytes,
+           "achieved": nbytes / (us * 1e3), "unit": "GB/s", "frac": nbytes / (us * 1e3) / hbm_gbs}
+    for b in (w, x, y):
+        b.free()
+    ctx.close()
+    return out
 
 
 def run_cuda(args):
@@ -277,7 +326,8 @@ def run_cuda(args):
                           tokens) if world > 1 else None
 
     if rank == 0:
-        roof = gemv_roofline(eng, shape, hbm_gbs)
+        roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens)
+        roof["lm_head"] = lm_head_roofline(local, shape, hbm_gbs, torch)
         roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"
         step_bytes = shape.decode_weight_bytes()
         cpu = None

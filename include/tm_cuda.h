@@ -294,6 +294,18 @@ int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
                                        uint32_t head_dim, uint32_t group, float scale, uint32_t n,
                                        uint32_t window, char *err, size_t err_cap);
 
+/* No counterpart: the same operator as tm_cuda_qwen35_attention_f16_chunk on the
+ * tensor cores (mma.sync m16n8k16: Q and the softmax weights rounded to binary16,
+ * f32 accumulation, keys visited in tiles of 64 with a running maximum), hence
+ * tolerance-qualified (about 1e-3 of the output scale) instead of bit-identical
+ * to the per-token form.  The engine uses it for batched prefill unless `exact`
+ * is asked.  head_dim 32, 64, 128 or 256; buffers 16-byte aligned; no scratch. */
+int tm_cuda_attention_chunk_mma_supported(uint32_t head_dim);
+int tm_cuda_attention_chunk_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache,
+                                tm_cuda_buffer *v_cache, tm_cuda_buffer *out, uint32_t heads,
+                                uint32_t pos0, uint32_t cap, uint32_t head_dim, uint32_t group,
+                                float scale, uint32_t n, uint32_t window, char *err, size_t err_cap);
+
 /* No counterpart: the per-token attention core with the position read from
  * device memory (u32 pos_buf[pos_index]), so one recorded decode graph serves
  * every step: per-head q/k RMS norm, RoPE, f16 KV store and (windowed) causal

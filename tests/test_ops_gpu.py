@@ -304,3 +304,37 @@ def test_profile_table(ctx):
     assert rows["f32_scale"][1] == 3
     ctx.set_profiling(False)
     assert ctx.profile_snapshot() == []
+
+
+@pytest.mark.parametrize("heads,kvh,hd,window,cap,pos0,n", [
+    (16, 8, 128, 0, 600, 0, 512),      # the benchmark's prefill geometry
+    (16, 8, 128, 0, 700, 130, 200),    # a later chunk: earlier keys plus the causal part
+    (4, 1, 256, 512, 900, 300, 333),   # Gemma-style: wide heads (two value halves), sliding window, ragged n
+    (4, 1, 256, 40, 300, 0, 130),      # window shorter than a key tile
+    (4, 2, 32, 0, 100, 57, 6),         # the small test models' head size
+    (12, 2, 64, 17, 150, 3, 70),
+])
+def test_tensor_core_chunk_attention_within_tolerance(ctx, oracle, heads, kvh, hd, window, cap, pos0, n):
+    """The mma.sync prefill form against the blockwise kernel (itself pinned to
+    the scalar executor above) and, on sampled rows, against the oracle: binary16
+    Q / softmax weights cost about 1e-3 of the output scale."""
+    group = heads // kvh
+    kf = T.activations(0, 10, kvh * cap * hd).astype(np.float16).reshape(kvh, cap, hd)
+    vf = T.activations(0, 11, kvh * cap * hd).astype(np.float16).reshape(kvh, cap, hd)
+    q = T.activations(0, 12, n * heads * hd).reshape(n, heads, hd)
+    kc, vc, qb = ctx.from_array(kf), ctx.from_array(vf), ctx.floats(q)
+    ob, o2, sb = ctx.buffer(q.size * 4), ctx.buffer(q.size * 4), ctx.buffer(16)
+    scale = 1.0 / np.sqrt(np.float32(hd))
+    ctx.qwen35_attention_chunk(qb, kc, vc, ob, sb, heads, pos0, cap, hd, group, scale, n, window)
+    ctx.attention_chunk_mma(qb, kc, vc, o2, heads, pos0, cap, hd, group, scale, n, window)
+    ref = f32(ob, q.size).reshape(n, heads, hd)
+    got = f32(o2, q.size).reshape(n, heads, hd)
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - ref)) <= 2e-3 * max(1.0, float(np.max(np.abs(ref))))
+    k32, v32 = kf.astype(np.float32), vf.astype(np.float32)
+    for t in sorted({0, n // 2, n - 1}):
+        seq = pos0 + t + 1
+        start = seq - window if (window and seq > window) else 0
+        for h in (0, heads - 1):
+            cpu = oracle.attend_head(q[t, h], k32[h // group], v32[h // group], start, seq, scale)
+            assert rel_err(got[t, h], cpu) <= 3e-3

@@ -238,6 +238,12 @@ public:
         TM_CALL(tm_cuda_qwen35_attention_f16_chunk, q.raw(), kc.raw(), vc.raw(), out.raw(), scratch.raw(), heads,
                 pos0, cap, hd, group, scale, n, window);
     }
+    void attention_chunk_mma(const CudaBuffer &q, const CudaBuffer &kc, const CudaBuffer &vc, const CudaBuffer &out,
+                             uint32_t heads, uint32_t pos0, uint32_t cap, uint32_t hd, uint32_t group, float scale,
+                             uint32_t n, uint32_t window) const {
+        TM_CALL(tm_cuda_attention_chunk_mma, q.raw(), kc.raw(), vc.raw(), out.raw(), heads, pos0, cap, hd, group, scale,
+                n, window);
+    }
     void attention_decode_dev(const CudaBuffer &q, const CudaBuffer &k, const CudaBuffer &v, const CudaBuffer &qn,
                               const CudaBuffer &kn, const CudaBuffer &inv_freq, const CudaBuffer &kc,
                               const CudaBuffer &vc, const CudaBuffer &out, const CudaBuffer &scratch,

@@ -419,8 +419,13 @@ struct AttentionBlock {
         ctx.rmsnorm(s.b, k_norm, s.b, nn * kv, hd, eps);
         ctx.rope_partial_chunk(s.a, s.b, inv_freq, pos0, heads, kv, hd, (uint32_t)spec.rope_dims, nn);
         ctx.kv_store_chunk(s.b, s.c, k_cache, v_cache, pos0, (uint32_t)cap, hd, kv, nn);
-        ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
-                            (uint32_t)spec.window);
+        // Tolerance-qualified tensor-core form unless bit identity with the per-token path is asked.
+        if (!exact && tm_cuda_attention_chunk_mma_supported(hd))
+            ctx.attention_chunk_mma(s.a, k_cache, v_cache, s.e, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
+                                    (uint32_t)spec.window);
+        else
+            ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(),
+                                nn, (uint32_t)spec.window);
         if (sh.world > 1) {
             ctx.all_gather_rows(s.e, s.stage, s.efull, nn, heads * hd);
             o.gemm_all(ctx, s.efull, s.loc, nn, exact);

@@ -75,6 +75,7 @@ _OPS = {
     "qwen35_kv_store_f16_chunk": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
     "qwen35_attention_f16": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F],
     "qwen35_attention_f16_chunk": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
+    "attention_chunk_mma": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
     "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
     "attention_decode_dev_static": [_P] * 11 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
 }
@@ -354,6 +355,9 @@ class CudaContext:
 
     def qwen35_attention_f16(self, q, k_cache, v_cache, out, scratch, heads, pos, cap, head_dim, group, scale):
         self._call("qwen35_attention_f16", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos, cap, head_dim, group, scale)
+
+    def attention_chunk_mma(self, q, k_cache, v_cache, out, heads, pos0, cap, head_dim, group, scale, n, window):
+        self._call("attention_chunk_mma", q.handle, k_cache.handle, v_cache.handle, out.handle, heads, pos0, cap, head_dim, group, scale, n, window)
 
     def qwen35_attention_chunk(self, q, k_cache, v_cache, out, scratch, heads, pos0, cap, head_dim, group, scale, n, window):
         self._call("qwen35_attention_f16_chunk", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos0, cap, head_dim, group, scale, n, window)

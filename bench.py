@@ -423,6 +423,39 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
     return out
 
 
+def run_op(args):
+    """Small fixed cases for profiler captures (`--op`): a few launches of one
+    kernel at a stated shape, or one prefill plus three decode steps of the
+    workload.  Prints what ran; no JSON line, not a measurement."""
+    from tuckmill_b200 import cuda, engine as E
+
+    if args.op == "slice":
+        shape, prompt_n, decode_n = WORKLOADS[args.workload]
+        eng = E.Engine(artifact(args.workload, args.seed), context=prompt_n + decode_n + 16)
+        for _ in range(2):
+            eng.reset()
+            eng.prefill(T.token_ids(args.seed, prompt_n, shape.vocab), want_token=True)
+            eng.decode_steps(3)
+            eng.fence()
+        print("slice: 2 x (prefill %d + 3 decode steps), %d launches" % (prompt_n, _launches(eng)))
+        eng.close()
+        return
+    ctx = cuda.CudaContext(0)
+    rows, cols, m = args.rows, args.cols, args.batch
+    base = T.q8_0_matrix(0, 1, min(rows, 1024), cols)
+    w = ctx.q8_0_matrix(np.tile(base, ((rows + base.shape[0] - 1) // base.shape[0], 1, 1))[:rows], rows, cols)
+    x = ctx.buffer(m * cols * 4)
+    x.upload(0, T.activations(0, 2, min(m * cols, 1 << 22)))
+    y = ctx.buffer(m * rows * 4)
+    for _ in range(3):
+        if args.op == "gemm":
+            ctx.q8_0_gemm_mma(w, x, y, rows, cols, m)
+        else:
+            ctx.q8_0_gemv(w, x, y, rows, cols)
+    ctx.fence()
+    print("%s %dx%d batch %d: 3 launches, aborted=%s" % (args.op, rows, cols, m, ctx.mma_aborted()))
+
+
 def _launches(eng) -> int:
     from tuckmill_b200 import cuda as C
 
@@ -438,8 +471,14 @@ def main():
     ap.add_argument("--workload", default="qwen3-0.6b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--op", choices=["gemv", "gemm", "slice"], help="profiler case instead of the benchmark")
+    ap.add_argument("--rows", type=int, default=12288)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=2048)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.op:
+        run_op(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_cuda(args)

@@ -425,6 +425,123 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
     return out
 
 
+SWEEP_SHAPES = [(4096, 4096), (12288, 4096), (4096, 12288), (151936, 4096)]
+SWEEP_BATCHES = [1, 8, 32, 128, 512, 2048, 8192]
+
+
+def run_sweep(args):
+    """The Q8_0 projection sweep at Qwen3-8B shapes, split by output rows over the
+    ranks: every rank multiplies its N/G rows with the single-device kernel (GEMV at
+    M = 1, the bit-identical batched form up to 8, the tensor-core GEMM above) and an
+    all-gather reassembles Y.  Per case: device time of the multiply alone, of the
+    all-gather alone, and of both back to back (each a replayed graph, CUDA events,
+    max over ranks).  Rank 0 prints one JSON line; a profiling aid, not `value`."""
+    import torch
+    import torch.distributed as dist
+
+    from tuckmill_b200 import cuda
+
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = cuda.CudaContext(local)
+    if world > 1:
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            ident.copy_(torch.frombuffer(bytearray(cuda.comm_unique_id()), dtype=torch.uint8))
+        dist.broadcast(ident, 0)
+        ctx.comm_init(bytes(ident.cpu().numpy().tobytes()), rank, world)
+    st = torch.cuda.ExternalStream(ctx.stream(), device=local)
+    hbm_gbs, _ = measured_peaks()
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+
+    def timed(record, reps):
+        ctx.begin_group()
+        for _ in range(reps):
+            record()
+        g = ctx.end_group_retain()
+        g.launch()
+        ctx.fence()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(st):
+            e0.record()
+        g.launch()
+        with torch.cuda.stream(st):
+            e1.record()
+        ctx.fence()
+        torch.cuda.synchronize()
+        g.free()
+        v = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    cases = []
+    for rows, cols in SWEEP_SHAPES:
+        local_rows = rows // world
+        base = T.q8_0_matrix(args.seed, 1, min(local_rows, 1024), cols)
+        copies = 2 if local_rows * cols < 200e6 else 1  # small slices alternate so they are not L2-resident
+        ws = [ctx.q8_0_matrix(np.tile(base, ((local_rows + base.shape[0] - 1) // base.shape[0], 1, 1))[:local_rows],
+                              local_rows, cols) for _ in range(copies)]
+        for m in SWEEP_BATCHES:
+            if m * rows * 4 > 3 << 30:
+                continue  # a gathered Y above 3 GiB is left out
+            x = ctx.buffer(m * cols * 4)
+            x.upload(0, T.activations(args.seed, 2, min(m * cols, 1 << 22)))
+            y_loc = ctx.buffer(m * local_rows * 4)
+            y = ctx.buffer(m * rows * 4) if world > 1 else y_loc
+            stage = ctx.buffer(m * rows * 4) if world > 1 and m > 1 else y
+            if m > 8:
+                ctx.mma_workspace_reserve(m * cols * 2)
+            turn = [0]
+
+            def multiply():
+                w = ws[turn[0] % copies]
+                turn[0] += 1
+                if m == 1:
+                    ctx.q8_0_gemv(w, x, y_loc, local_rows, cols)
+                elif m <= 8:
+                    ctx.q8_0_gemm(w, x, y_loc, local_rows, cols, m)
+                else:
+                    ctx.q8_0_gemm_mma(w, x, y_loc, local_rows, cols, m)
+
+            def gather():
+                ctx.all_gather_rows_f32(y_loc, stage, y, m, local_rows)
+
+            def both():
+                multiply()
+                gather()
+
+            reps = 20 if m * rows * cols < 2e11 else 4
+            t_mul = timed(multiply, reps)
+            t_ag = timed(gather, reps) if world > 1 else 0.0
+            t_both = timed(both, reps) if world > 1 else t_mul
+            nbytes = rows * (cols // 32) * 34 + 4 * m * cols * world + 4 * m * rows
+            case = {"rows": rows, "cols": cols, "batch": m, "us_multiply": round(t_mul, 2),
+                    "us_all_gather": round(t_ag, 2), "us_both": round(t_both, 2),
+                    "tflops": round(2.0 * m * rows * cols / t_both / 1e6, 1),
+                    "gbs": round(nbytes / t_both / 1e3, 1)}
+            case["frac"] = round(case["gbs"] / (hbm_gbs * world), 3) if m <= 8 else round(case["tflops"] / (tf_peak * world), 3)
+            case["bound"] = "hbm" if m <= 8 else "tensor"
+            cases.append(case)
+            for b in {id(b): b for b in (x, y_loc, y, stage)}.values():
+                b.free()
+        for w in ws:
+            w.free()
+    if rank == 0:
+        print(json.dumps({"workload": "q8_0 projection sweep, output rows split over the ranks", "n_gpus": world,
+                          "peaks": {"hbm_gbs": hbm_gbs, "tflops": tf_peak, "per": "GPU; frac is of n_gpus x peak"},
+                          "cases": cases}), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_op(args):
     """Small fixed cases for profiler captures (`--op`): a few launches of one
     kernel at a stated shape, or one prefill plus three decode steps of the
@@ -473,12 +590,15 @@ def main():
     ap.add_argument("--workload", default="qwen3-0.6b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--op", choices=["gemv", "gemm", "slice"], help="profiler case instead of the benchmark")
+    ap.add_argument("--op", choices=["gemv", "gemm", "slice", "sweep"],
+                    help="profiler case / projection sweep instead of the benchmark")
     ap.add_argument("--rows", type=int, default=12288)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=2048)
     args = ap.parse_args()
-    if args.op:
+    if args.op == "sweep":
+        run_sweep(args)
+    elif args.op:
         run_op(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -294,6 +294,29 @@ int tm_cuda_qwen35_attention_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q,
                                        uint32_t head_dim, uint32_t group, float scale, uint32_t n,
                                        uint32_t window, char *err, size_t err_cap);
 
+/* No counterpart: the batched-prefill forms that fold the surrounding elementwise
+ * launches into the tensor-core GEMM (tolerance-qualified like tm_cuda_q8_0_gemm_mma).
+ * One call = the f16 copy of X with `prologue` applied (TM_CUDA_PRO_NONE; _RMSNORM:
+ * x * rsqrt(mean x^2 + eps) * pro[cols]; _SILU_MUL / _GELU_MUL: act(x) * pro[batch][cols])
+ * + ONE GEMM launch over the whole matrix whose rows are cut into n_parts (1..3)
+ * consecutive parts -- q | k | v, gate | up -- each written densely to its own
+ * y_parts[p][t * part_rows[p] + r]; every part but the last must be a multiple of 128
+ * rows.  epilogue TM_CUDA_EPI_ADD accumulates into y (the residual add). */
+int tm_cuda_q8_0_gemm_mma_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, uint32_t rows,
+                                uint32_t cols, uint32_t batch, uint32_t n_parts,
+                                tm_cuda_buffer *const *y_parts, const uint32_t *part_rows, int prologue,
+                                tm_cuda_buffer *pro, float eps, int epilogue, char *err, size_t err_cap);
+/* No counterpart: tm_cuda_rmsnorm_f32 (q heads), tm_cuda_rmsnorm_f32 (k heads),
+ * tm_cuda_qwen35_rope_partial_chunk and tm_cuda_qwen35_kv_store_f16_chunk as one
+ * launch for a chunk of n token rows at pos0: q [n][heads][head_dim] is normed and
+ * rotated in place; k is normed, rotated and stored to the f16 cache with v (k and v
+ * themselves are not modified).  Warp-level sums: tolerance-qualified. */
+int tm_cuda_qk_prep_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k, tm_cuda_buffer *v,
+                          tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm, tm_cuda_buffer *inv_freq,
+                          tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, uint32_t heads,
+                          uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot, uint32_t pos0, uint32_t cap,
+                          uint32_t n, float eps, char *err, size_t err_cap);
+
 /* No counterpart: the same operator as tm_cuda_qwen35_attention_f16_chunk on the
  * tensor cores (mma.sync m16n8k16: Q and the softmax weights rounded to binary16,
  * f32 accumulation, keys visited in tiles of 64 with a running maximum), hence
@@ -400,6 +423,22 @@ int tm_cuda_all_gather_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t src_o
  * before the interleave; unused when n_rows == 1. */
 int tm_cuda_all_gather_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *stage, tm_cuda_buffer *dst,
                                 uint32_t n_rows, uint32_t width, char *err, size_t err_cap);
+/* The same exchange through PEER MEMORY instead of a library collective.  A
+ * symmetric buffer is the same allocation on every rank, each mapped into every
+ * other rank's address space (CUDA IPC; collective call, outside dispatch groups,
+ * after tm_cuda_comm_init).  tm_cuda_push_rows_f32 is then the all-gather as a
+ * push: one kernel stores this rank's n_rows x width slice straight into every
+ * rank's copy at dst[t][rank*width + c] (plain stores over NVLink), raises a
+ * per-sender sequence flag on every rank and waits, with an iteration limit, until
+ * every sender's flag on this rank has reached the same number -- when the kernel
+ * ends, dst holds all ranks' slices.  Recordable in a dispatch group.  The same
+ * symmetric buffer must not be the target of two consecutive pushes (a peer may
+ * still be reading the previous contents); alternate between at least two.  Bit 0
+ * of tm_cuda_symm_status: a wait ran out (the consumer read stale rows). */
+tm_cuda_buffer *tm_cuda_symm_alloc(tm_cuda_ctx *ctx, size_t bytes, char *err, size_t err_cap);
+int tm_cuda_push_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *dst, uint32_t n_rows, uint32_t width,
+                          char *err, size_t err_cap);
+int tm_cuda_symm_status(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t *status, char *err, size_t err_cap);
 /* Greedy token of a row-sharded head: argmax of the local logits slice (global
  * index = local + index_offset), all-gather of the (value, index) pairs (8 bytes
  * per rank instead of the logits), then the single-device rule over the pairs

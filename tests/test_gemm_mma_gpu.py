@@ -75,3 +75,79 @@ def test_mma_gemm_limits(ctx):
         assert e.value.code == -5
     finally:
         ctx.abort_group()
+
+
+@pytest.mark.parametrize("parts,cols,batch,prologue,add", [
+    ((2048, 1024, 1024), 1024, 512, cuda.PRO_RMSNORM, False),   # Qwen3-0.6B q | k | v with the input norm folded in
+    ((3072, 3072), 1024, 300, cuda.PRO_RMSNORM, False),         # gate | up
+    ((1024,), 3072, 200, cuda.PRO_SILU_MUL, True),              # down: silu(gate) * up in, residual add out
+    ((1152,), 640, 77, cuda.PRO_GELU_MUL, True),                # Gemma-style activation, ragged sizes
+    ((256, 100), 256, 40, cuda.PRO_NONE, False),                # a last part that is not a multiple of 128
+])
+def test_fused_prefill_gemm_equals_operator_sequence(ctx, oracle, parts, cols, batch, prologue, add):
+    """One prologue-fused f16 copy + one multi-part launch against the launches it
+    replaces (rmsnorm / silu_mul, one GEMM per part, axpy) and against the oracle."""
+    rows = sum(parts)
+    raw = T.q8_0_matrix(2, rows + cols, rows, cols)
+    w = ctx.q8_0_matrix(raw, rows, cols)
+    X = T.activations(2, 5, batch * cols).reshape(batch, cols)
+    eps = 1e-6
+    if prologue == cuda.PRO_RMSNORM:
+        pro = (1 + 0.1 * T.activations(2, 6, cols)).astype(np.float32)
+        xin = (X / np.sqrt((X.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + eps) * pro).astype(np.float32)
+    elif prologue == cuda.PRO_NONE:
+        pro, xin = None, X
+    else:
+        pro = T.activations(2, 7, batch * cols).reshape(batch, cols)
+        x64 = X.astype(np.float64)
+        act = x64 / (1 + np.exp(-x64)) if prologue == cuda.PRO_SILU_MUL else \
+            0.5 * x64 * (1 + np.tanh(0.7978845608028654 * (x64 + 0.044715 * x64 ** 3)))
+        xin = (act * pro).astype(np.float32)
+    ref = oracle.matmul_q8_0(raw, rows, cols, xin)
+    before = [T.activations(2, 20 + i, batch * p).reshape(batch, p) for i, p in enumerate(parts)]
+    ys = [ctx.floats(b) for b in before]
+    ctx.q8_0_gemm_mma_fused(w, ctx.floats(X), rows, cols, batch, ys, list(parts), prologue,
+                            ctx.floats(pro) if pro is not None else None, eps, cuda.EPI_ADD if add else cuda.EPI_STORE)
+    assert not ctx.mma_aborted()
+    r0 = 0
+    for y, p, b in zip(ys, parts, before):
+        got = y.download(0, batch * p * 4, np.float32).reshape(batch, p)
+        want = ref[:, r0:r0 + p] + (b if add else 0)
+        scale = max(1.0, float(np.max(np.abs(want))))
+        assert float(np.max(np.abs(got - want))) <= 2e-2 * scale, f"part at row {r0}"
+        r0 += p
+    with pytest.raises(cuda.CudaError):  # a middle part that would let a tile straddle two outputs
+        ctx.q8_0_gemm_mma_fused(w, ctx.floats(X), rows, cols, batch, [ys[0], ys[0]], [100, rows - 100])
+
+
+@pytest.mark.parametrize("heads,kvh,hd,n_rot,pos0,n,cap", [(16, 8, 128, 128, 0, 70, 100), (4, 1, 256, 256, 33, 50, 90),
+                                                         (4, 2, 32, 32, 5, 9, 40), (12, 2, 64, 32, 7, 21, 64)])
+def test_qk_prep_chunk_equals_operator_sequence(ctx, heads, kvh, hd, n_rot, pos0, n, cap):
+    """rmsnorm (q heads), rmsnorm (k heads), rope, kv_store as one launch: same values to a few ulp."""
+    eps = 1e-6
+    q = T.activations(3, 1, n * heads * hd)
+    k = T.activations(3, 2, n * kvh * hd)
+    v = T.activations(3, 3, n * kvh * hd)
+    qn = (1 + 0.1 * T.activations(3, 4, hd)).astype(np.float32)
+    kn = (1 + 0.1 * T.activations(3, 5, hd)).astype(np.float32)
+    inv = (1e4 ** (-np.arange(n_rot // 2, dtype=np.float64) * 2 / n_rot)).astype(np.float32)
+    qnb, knb, ib = ctx.floats(qn), ctx.floats(kn), ctx.floats(inv)
+    plane = kvh * cap * hd * 2
+    caches = [[ctx.buffer(plane), ctx.buffer(plane)] for _ in range(2)]
+    for pair in caches:
+        for c in pair:
+            c.zero()
+    qa, ka, va = ctx.floats(q), ctx.floats(k), ctx.floats(v)
+    ctx.rmsnorm(qa, qnb, qa, n * heads, hd, eps)
+    ctx.rmsnorm(ka, knb, ka, n * kvh, hd, eps)
+    ctx.qwen35_rope_partial_chunk(qa, ka, ib, pos0, heads, kvh, hd, n_rot, n)
+    ctx.qwen35_kv_store_chunk(ka, va, caches[0][0], caches[0][1], pos0, cap, hd, kvh, n)
+    qb, kb, vb = ctx.floats(q), ctx.floats(k), ctx.floats(v)
+    ctx.qk_prep_chunk(qb, kb, vb, qnb, knb, ib, caches[1][0], caches[1][1], heads, kvh, hd, n_rot, pos0, cap, n, eps)
+    qa_h, qb_h = qa.download(0, q.size * 4, np.float32), qb.download(0, q.size * 4, np.float32)
+    assert rel_err(qb_h, qa_h) <= 2e-6
+    np.testing.assert_array_equal(kb.download(0, k.size * 4, np.float32), k)  # k itself is left alone
+    for a_, b_ in zip(caches[0], caches[1]):
+        ca = a_.download(0, plane, np.float16).astype(np.float32)
+        cb = b_.download(0, plane, np.float16).astype(np.float32)
+        assert np.max(np.abs(ca - cb)) <= 2e-3 * max(1.0, float(np.max(np.abs(ca))))  # one f16 ulp at most

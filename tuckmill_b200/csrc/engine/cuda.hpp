@@ -3,6 +3,7 @@
 // per operator, MetalBuffer handles freed on drop, ABI codes mapped to typed
 // errors :732-747).  Header-only; calls nothing but the C ABI.
 #pragma once
+#include <initializer_list>
 #include <cstdint>
 #include <cstring>
 #include <memory>
@@ -143,6 +144,14 @@ public:
         b.zero();
         return b;
     }
+    // A zeroed exchange buffer mapped on every rank of the communicator (collective).
+    CudaBuffer symm_zeros(size_t bytes) const {
+        char e[256] = "";
+        tm_cuda_buffer *b = tm_cuda_symm_alloc(ctx_, bytes, e, sizeof e);
+        if (!b) throw TuckmillError(ErrorCode::Unavailable, std::string("peer-memory exchange buffer: ") + e,
+                                    "The GPUs of a row split must be able to map one another's memory (CUDA IPC, peer access).");
+        return CudaBuffer(ctx_, b);
+    }
     CudaBuffer floats(const std::vector<float> &v) const {
         CudaBuffer b = buffer(v.size() * 4);
         b.upload(0, v.data(), v.size() * 4);
@@ -175,6 +184,26 @@ public:
     void q8_0_gemm_mma(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows,
                        uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off) const {
         TM_CALL(tm_cuda_q8_0_gemm_mma, w.raw(), x.raw(), y.raw(), rows, cols, batch, x_off, y_off);
+    }
+    // One prologue-fused f16 copy + one GEMM launch over up to three row parts (include/tm_cuda.h).
+    void q8_0_gemm_mma_fused(const CudaBuffer &w, const CudaBuffer &x, uint32_t rows, uint32_t cols, uint32_t batch,
+                             std::initializer_list<const CudaBuffer *> ys, std::initializer_list<uint32_t> part_rows,
+                             int prologue, const CudaBuffer *pro, float eps, int epilogue) const {
+        tm_cuda_buffer *yp[3] = {nullptr, nullptr, nullptr};
+        uint32_t pr[3] = {0, 0, 0};
+        uint32_t n = 0;
+        for (const CudaBuffer *b : ys) yp[n++] = b->raw();
+        n = 0;
+        for (uint32_t r : part_rows) pr[n++] = r;
+        TM_CALL(tm_cuda_q8_0_gemm_mma_fused, w.raw(), x.raw(), rows, cols, batch, n, yp, pr, prologue,
+                pro ? pro->raw() : nullptr, eps, epilogue);
+    }
+    void qk_prep_chunk(const CudaBuffer &q, const CudaBuffer &k, const CudaBuffer &v, const CudaBuffer &qn,
+                       const CudaBuffer &kn, const CudaBuffer &inv_freq, const CudaBuffer &kc, const CudaBuffer &vc,
+                       uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot, uint32_t pos0, uint32_t cap, uint32_t n,
+                       float eps) const {
+        TM_CALL(tm_cuda_qk_prep_chunk, q.raw(), k.raw(), v.raw(), qn.raw(), kn.raw(), inv_freq.raw(), kc.raw(), vc.raw(),
+                heads, kvh, hd, n_rot, pos0, cap, n, eps);
     }
     void mma_workspace_reserve(size_t bytes) const {
         char e[256] = "";
@@ -263,6 +292,10 @@ public:
     void all_gather_rows(const CudaBuffer &src, const CudaBuffer &stage, const CudaBuffer &dst, uint32_t n_rows,
                          uint32_t width) const {
         TM_CALL(tm_cuda_all_gather_rows_f32, src.raw(), stage.raw(), dst.raw(), n_rows, width);
+    }
+    // The all-gather as a push into a symmetric buffer (include/tm_cuda.h): dst[t][rank*width + c] on every rank.
+    void push_rows(const CudaBuffer &src, const CudaBuffer &dst, uint32_t n_rows, uint32_t width) const {
+        TM_CALL(tm_cuda_push_rows_f32, src.raw(), dst.raw(), n_rows, width);
     }
     void argmax_sharded(const CudaBuffer &x, uint32_t n, uint32_t index_offset, const CudaBuffer &partial,
                         const CudaBuffer &pairs, const CudaBuffer &out, uint32_t base, const CudaBuffer *pos,

@@ -12,8 +12,19 @@ uint64_t f32_bytes(size_t elems) { return 4ull * (elems ? elems : 1); }
 
 // Allocation accumulator mirroring every buffer a block creates
 // (crates/tuckcore/src/engine/metal.rs:254-272).
+inline size_t gather_bytes(size_t n) { return (f32_bytes(n) + 255) / 256 * 256; }
+
 struct Plan {
-    uint64_t weights = 0, state = 0, scratch = 0;
+    uint64_t weights = 0, state = 0, scratch = 0, gather = 0;
+    // A buffer other ranks store into when the model is split, an ordinary one otherwise.
+    void target_f32(size_t n, uint32_t world) {
+        if (world > 1) {
+            scratch += gather_bytes(n);
+            gather += gather_bytes(n);
+        } else {
+            scratch += f32_bytes(n);
+        }
+    }
     void weights_f32(size_t n) { weights += f32_bytes(n); }
     void scratch_f32(size_t n) { scratch += f32_bytes(n); }
     void scratch_bytes(size_t n) { scratch += n ? n : 4; }
@@ -22,6 +33,28 @@ struct Plan {
 size_t vector_len(const WeightSource &src, Tensor t) {
     auto d = src.tensor_dims(t.index);
     return (size_t)(d.first * (d.second ? d.second : 1));
+}
+
+// With a row split the gather targets of every exchange live in ONE buffer that all ranks map
+// (peer memory); blocks take 256-byte aligned views of it in plan order.
+struct GatherArena {
+    CudaBuffer buf;
+    size_t off = 0;
+};
+
+struct Shard {
+    uint32_t rank = 0, world = 1;
+    GatherArena *arena = nullptr;  // set while loading a split model
+};
+
+// Gather targets of a row split are exchange buffers every rank can store into.
+CudaBuffer gather_target_f32(const CudaContext &ctx, size_t n, const Shard &sh) {
+    if (sh.world <= 1) return ctx.zeros(f32_bytes(n));
+    if (!sh.arena || sh.arena->off + gather_bytes(n) > sh.arena->buf.len())
+        throw TuckmillError(ErrorCode::Internal, "exchange arena smaller than the plan");
+    CudaBuffer v = sh.arena->buf.view(sh.arena->off, f32_bytes(n));
+    sh.arena->off += gather_bytes(n);
+    return v;
 }
 
 CudaBuffer vector(const CudaContext &ctx, const WeightSource &src, Tensor t) {
@@ -43,10 +76,6 @@ std::vector<float> rope_inv_freq(size_t rope_dims, float base) {
 
 // Output-row split: this rank owns rows [rank*n/world, (rank+1)*n/world) of every
 // projection (each output element needs one weight row and the whole input).
-struct Shard {
-    uint32_t rank = 0, world = 1;
-};
-
 // A device matrix: one or more Q8_0 tensors of equal width, rows concatenated,
 // repacked into the two-plane form at upload (crates/tuckcore/src/engine/
 // metal.rs:107-226 uploads the GGUF bytes verbatim; the row concatenation and
@@ -150,7 +179,7 @@ struct Matrix {
 // token-major, `n` = prefill batch.
 struct PrefillScratch {
     CudaBuffer x, h, a, b, c, e, proj, h2, g, u, d2, ascr;
-    CudaBuffer loc, loc2, stage, efull;  // row-split only: local GEMM outputs, NCCL staging, gathered attention
+    CudaBuffer loc, loc2, efull;  // row-split only: local GEMM outputs, gathered attention
     static size_t widest(const ModelGraph &g) {
         size_t w = g.hidden;
         for (const LayerSpec &l : g.layers) w = std::max(w, std::max(l.mixer.heads * l.mixer.head_dim, l.ffn.width));
@@ -167,8 +196,8 @@ struct PrefillScratch {
         if (sh.world > 1) {
             size_t awf = 0;
             for (const LayerSpec &l : g.layers) awf = std::max(awf, l.mixer.heads * l.mixer.head_dim);
-            for (int i = 0; i < 3; ++i) p.scratch_f32(n * widest(g));
-            p.scratch_f32(n * awf);
+            for (int i = 0; i < 2; ++i) p.scratch_f32(n * widest(g));
+            p.target_f32(n * awf, sh.world);  // efull
         }
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
         for (const LayerSpec &l : g.layers) {
@@ -177,8 +206,9 @@ struct PrefillScratch {
             ffn = std::max(ffn, l.ffn.width);
             heads = std::max(heads, l.mixer.heads);
         }
-        for (size_t e : {g.hidden, g.hidden, aw, kvw, kvw, aw, g.hidden, g.hidden, ffn, ffn, g.hidden})
+        for (size_t e : {g.hidden, g.hidden, aw, kvw, kvw, aw, g.hidden, ffn})  // x h a b c e h2 u
             p.scratch_f32(n * e);
+        for (size_t e : {g.hidden, ffn, g.hidden}) p.target_f32(n * e, sh.world);  // proj g d2: gathered when split
         (void)heads;
         (void)cap;
         p.scratch_f32(1);  // the chunk attention streams key blocks; its scratch argument is a placeholder
@@ -198,19 +228,18 @@ struct PrefillScratch {
         s.b = zeros_f32(ctx, n * kvw);
         s.c = zeros_f32(ctx, n * kvw);
         s.e = zeros_f32(ctx, n * aw);
-        s.proj = zeros_f32(ctx, n * g.hidden);
+        s.proj = gather_target_f32(ctx, n * g.hidden, sh);
         s.h2 = zeros_f32(ctx, n * g.hidden);
-        s.g = zeros_f32(ctx, n * ffn);
+        s.g = gather_target_f32(ctx, n * ffn, sh);
         s.u = zeros_f32(ctx, n * ffn);
-        s.d2 = zeros_f32(ctx, n * g.hidden);
+        s.d2 = gather_target_f32(ctx, n * g.hidden, sh);
         (void)heads;
         (void)cap;
         s.ascr = zeros_f32(ctx, 1);
         if (sh.world > 1) {
             s.loc = zeros_f32(ctx, n * widest(g));
             s.loc2 = zeros_f32(ctx, n * widest(g));
-            s.stage = zeros_f32(ctx, n * widest(g));
-            s.efull = zeros_f32(ctx, n * aw);
+            s.efull = gather_target_f32(ctx, n * aw, sh);
         }
         return s;
     }
@@ -235,9 +264,9 @@ struct SwiGluBlock {
         p.weights += Matrix::plan(src, {f.gate, f.up}, sh) + Matrix::plan(src, {f.down}, sh);
         if (has_norm) p.weights_f32(vector_len(src, norm));
         p.scratch_f32(2 * f.width / sh.world);
-        p.scratch_f32(hidden);
+        p.target_f32(hidden, sh.world);  // out
         if (sh.world > 1) {
-            p.scratch_f32(f.width);
+            p.target_f32(f.width, sh.world);  // h_full
             p.scratch_f32(hidden / sh.world);
         }
     }
@@ -257,9 +286,9 @@ struct SwiGluBlock {
         b.gu = zeros_f32(ctx, 2 * b.wl);
         b.g_view = b.gu.view(0, b.wl * 4);
         b.u_view = b.gu.view(b.wl * 4, b.wl * 4);
-        b.out = zeros_f32(ctx, hidden);
+        b.out = gather_target_f32(ctx, hidden, sh);
         if (sh.world > 1) {
-            b.h_full = zeros_f32(ctx, f.width);
+            b.h_full = gather_target_f32(ctx, f.width, sh);
             b.out_local = zeros_f32(ctx, hidden / sh.world);
         }
         return b;
@@ -274,9 +303,9 @@ struct SwiGluBlock {
                             TM_CUDA_EPI_STORE);
         if (sh.world > 1) {
             act_mul(ctx, g_view, u_view, (uint32_t)wl);
-            ctx.all_gather_rows(g_view, h_full, h_full, 1, (uint32_t)wl);
+            ctx.push_rows(g_view, h_full, 1, (uint32_t)wl);
             ctx.q8_0_gemv(down.buf, h_full, out_local, down.rows, down.cols);
-            ctx.all_gather_rows(out_local, out, out, 1, (uint32_t)(hidden / sh.world));
+            ctx.push_rows(out_local, out, 1, (uint32_t)(hidden / sh.world));
             if (out_norm) ctx.rmsnorm(out, out_norm, out, 1, (uint32_t)hidden, eps);
             ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
             return;
@@ -290,6 +319,26 @@ struct SwiGluBlock {
             ctx.q8_0_gemv_fused(down.buf, g_view, x, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_ADD);
         }
     }
+    // The tolerance-qualified batched form: norm and activation folded into the GEMMs' f16 copies,
+    // gate|up as one launch, the residual add in the down projection's epilogue (5 launches -> 4).
+    bool fusable() const { return sh.world == 1 && width % 128 == 0; }
+    void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
+                       size_t hidden) const {
+        const uint32_t nn = (uint32_t)n;
+        ctx.q8_0_gemm_mma_fused(gate_up.buf, s.x, gate_up.rows, gate_up.cols, nn, {&s.g, &s.u},
+                                {(uint32_t)width, (uint32_t)width}, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
+                                TM_CUDA_EPI_STORE);
+        const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        if (out_norm) {
+            ctx.q8_0_gemm_mma_fused(down.buf, s.g, down.rows, down.cols, nn, {&s.d2}, {down.rows}, pro, &s.u, 0.0f,
+                                    TM_CUDA_EPI_STORE);
+            ctx.rmsnorm(s.d2, out_norm, s.d2, nn, (uint32_t)hidden, eps);
+            ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+        } else {
+            ctx.q8_0_gemm_mma_fused(down.buf, s.g, down.rows, down.cols, nn, {&s.x}, {down.rows}, pro, &s.u, 0.0f,
+                                    TM_CUDA_EPI_ADD);
+        }
+    }
     // x += ffn(h2) for the n chunk rows of s.h2 / s.x (engine/metal.rs:514-534).
     void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, size_t hidden, bool exact) const {
         const uint32_t nn = (uint32_t)n;
@@ -297,9 +346,9 @@ struct SwiGluBlock {
             gate_up.gemm_part(ctx, 0, s.h2, s.loc, nn, exact);
             gate_up.gemm_part(ctx, 1, s.h2, s.loc2, nn, exact);
             act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
-            ctx.all_gather_rows(s.loc, s.stage, s.g, nn, (uint32_t)wl);
+            ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
             down.gemm_all(ctx, s.g, s.loc, nn, exact);
-            ctx.all_gather_rows(s.loc, s.stage, s.d2, nn, (uint32_t)(hidden / sh.world));
+            ctx.push_rows(s.loc, s.d2, nn, (uint32_t)(hidden / sh.world));
         } else {
             gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
             gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
@@ -342,7 +391,7 @@ struct AttentionBlock {
         p.scratch_bytes(tm_cuda_attention_decode_scratch_bytes((uint32_t)hl, (uint32_t)kl, (uint32_t)s.head_dim,
                                                                (uint32_t)cap));
         if (sh.world > 1) {
-            p.scratch_f32(s.heads * s.head_dim);
+            p.target_f32(s.heads * s.head_dim, sh.world);  // attn_full
             p.scratch_f32(hidden / sh.world);
         }
     }
@@ -381,7 +430,7 @@ struct AttentionBlock {
         b.kv_scratch = ctx.zeros(tm_cuda_attention_decode_scratch_bytes((uint32_t)b.heads_l, (uint32_t)b.kv_l,
                                                                         (uint32_t)s.head_dim, (uint32_t)cap));
         if (sh.world > 1) {
-            b.attn_full = zeros_f32(ctx, s.heads * s.head_dim);
+            b.attn_full = gather_target_f32(ctx, s.heads * s.head_dim, sh);
             b.proj_local = zeros_f32(ctx, hidden / sh.world);
         }
         return b;
@@ -403,9 +452,26 @@ struct AttentionBlock {
     }
     // Row split: proj = all_gather(o_local * all_gather(attn_local)), one token.
     void project_sharded(const CudaContext &ctx, const CudaBuffer &proj, size_t hidden) const {
-        ctx.all_gather_rows(attn, attn_full, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
+        ctx.push_rows(attn, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
         ctx.q8_0_gemv(o.buf, attn_full, proj_local, o.rows, o.cols);
-        ctx.all_gather_rows(proj_local, proj, proj, 1, (uint32_t)(hidden / sh.world));
+        ctx.push_rows(proj_local, proj, 1, (uint32_t)(hidden / sh.world));
+    }
+    // The tolerance-qualified batched form: input norm folded into the f16 copy, q|k|v as one GEMM
+    // launch, the four launches before attention as one, tensor-core attention (9 launches -> 4).
+    bool fusable() const {
+        return sh.world == 1 && qkv.part_rows.size() == 3 && qkv.part_rows[0] % 128 == 0 && qkv.part_rows[1] % 128 == 0 &&
+               tm_cuda_attention_chunk_mma_supported((uint32_t)spec.head_dim);
+    }
+    void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0,
+                       const CudaBuffer &pre_norm) const {
+        const uint32_t nn = (uint32_t)n, heads = (uint32_t)heads_l, kv = (uint32_t)kv_l, hd = (uint32_t)spec.head_dim;
+        ctx.q8_0_gemm_mma_fused(qkv.buf, s.x, qkv.rows, qkv.cols, nn, {&s.a, &s.b, &s.c},
+                                {qkv.part_rows[0], qkv.part_rows[1], qkv.part_rows[2]}, TM_CUDA_PRO_RMSNORM, &pre_norm,
+                                eps, TM_CUDA_EPI_STORE);
+        ctx.qk_prep_chunk(s.a, s.b, s.c, q_norm, k_norm, inv_freq, k_cache, v_cache, heads, kv, hd,
+                          (uint32_t)spec.rope_dims, pos0, (uint32_t)cap, nn, eps);
+        ctx.attention_chunk_mma(s.a, k_cache, v_cache, s.e, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
+                                (uint32_t)spec.window);
     }
     // Chunk core over n queries at pos0.. (engine/metal.rs:1170-1233): every
     // chunk K/V row is stored before any chunk query attends.
@@ -427,9 +493,9 @@ struct AttentionBlock {
             ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(),
                                 nn, (uint32_t)spec.window);
         if (sh.world > 1) {
-            ctx.all_gather_rows(s.e, s.stage, s.efull, nn, heads * hd);
+            ctx.push_rows(s.e, s.efull, nn, heads * hd);
             o.gemm_all(ctx, s.efull, s.loc, nn, exact);
-            ctx.all_gather_rows(s.loc, s.stage, s.proj, nn, (uint32_t)(hidden / sh.world));
+            ctx.push_rows(s.loc, s.proj, nn, (uint32_t)(hidden / sh.world));
         } else {
             o.gemm_all(ctx, s.e, s.proj, nn, exact);
         }
@@ -446,7 +512,7 @@ struct Layer {
         p.weights_f32(vector_len(src, l.pre_norm));
         p.weights_f32(vector_len(src, l.post_norm));
         if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
-        p.scratch_f32(g.hidden);  // proj
+        p.target_f32(g.hidden, sh.world);  // proj
         AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p);
         SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, sh, p);
     }
@@ -456,7 +522,7 @@ struct Layer {
         L.pre_norm = vector(ctx, src, l.pre_norm);
         if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
         L.post_norm = vector(ctx, src, l.post_norm);
-        L.proj = zeros_f32(ctx, g.hidden);
+        L.proj = gather_target_f32(ctx, g.hidden, sh);
         L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh);
         L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps, sh);
         return L;
@@ -478,6 +544,19 @@ struct Layer {
     void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, size_t hidden, float eps,
                  bool exact) const {
         const uint32_t nn = (uint32_t)n;
+        if (!exact && mixer.fusable() && ffn.fusable()) {
+            mixer.prefill_fused(ctx, s, n, pos0, pre_norm);
+            if (mixer_out_norm) {
+                mixer.o.gemm_all(ctx, s.e, s.proj, nn, false);
+                ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
+                ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+            } else {
+                ctx.q8_0_gemm_mma_fused(mixer.o.buf, s.e, mixer.o.rows, mixer.o.cols, nn, {&s.x}, {mixer.o.rows},
+                                        TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_ADD);
+            }
+            ffn.prefill_fused(ctx, s, n, post_norm, hidden);
+            return;
+        }
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
         mixer.prefill(ctx, s, n, pos0, hidden, exact);
         if (mixer_out_norm) ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
@@ -499,6 +578,7 @@ struct EngineModel::Impl {
     Matrix embedding, head_own;
     bool tied = false;
     Shard sh;
+    GatherArena arena;  // declared before the blocks that hold views of it (views are released first)
     CudaBuffer tied_view;  // row split of a tied head: this rank's rows of the (replicated) embedding
     uint32_t head_rows = 0;  // rows of the head this rank multiplies (vocab / world)
     CudaBuffer final_norm, x, logits, partial, tokens, tokens_mirror, pos_buf, status;
@@ -553,6 +633,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     out.weights = p.weights;
     out.state = p.state;
     out.scratch = p.scratch;
+    out.gather = p.gather;
     return out;
 }
 
@@ -576,7 +657,10 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     Impl &I = *m->impl_;
     const CudaContext &c = *ctx;
     I.layers.reserve(graph.layers.size());
-    const Shard sh{opts.shard_rank, opts.shard_world};
+    // Split model: the exchange arena first (one collective allocation every rank maps), then the
+    // blocks take their gather targets from it in plan order.
+    if (opts.shard_world > 1) I.arena.buf = c.symm_zeros(m->plan_.gather);
+    const Shard sh{opts.shard_rank, opts.shard_world, opts.shard_world > 1 ? &I.arena : nullptr};
     I.sh = sh;
     for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity, sh));
     I.embedding = Matrix::load(c, src, {graph.embedding});

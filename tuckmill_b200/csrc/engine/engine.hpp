@@ -37,6 +37,7 @@ struct EngineOptions {
 // Exact device bytes by class (crates/tuckcore/src/qwen35_gpu.rs:1181-1193).
 struct GpuAllocPlan {
     uint64_t weights = 0, state = 0, scratch = 0;
+    uint64_t gather = 0;  // part of `scratch`: the peer-mapped exchange arena of a row split
     uint64_t total() const { return weights + state + scratch; }
 };
 

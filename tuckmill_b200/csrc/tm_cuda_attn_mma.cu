@@ -243,6 +243,88 @@ __global__ void __launch_bounds__(kThreads) attention_chunk_mma_kernel(const att
     }
 }
 
+// Per-head RMS norm of q and k, split-half RoPE at pos0 + t, f16 K/V store: the four launches that
+// precede chunk attention (rmsnorm x2, rope, kv_store) as one.  One warp per (token, vector),
+// vectors = query heads, then KV heads; q is normed and rotated in place, k is normed, rotated and
+// written to the cache together with v (k itself is left as it was).  Warp-shuffle sum of squares,
+// so the low bits differ from the one-CTA-per-row norm: part of the tolerance-qualified prefill.
+__global__ void __launch_bounds__(256) qk_prep_chunk_kernel(float *q, const float *k, const float *v,
+                                                             const float *q_norm, const float *k_norm,
+                                                             const float *inv_freq, __half *kc, __half *vc,
+                                                             uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot,
+                                                             uint32_t pos0, uint32_t cap, uint32_t n, float eps) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t vec = blockIdx.x * 8u + (threadIdx.x >> 5), per_tok = heads + kvh;
+    if (vec >= n * per_tok) return;
+    const uint32_t t = vec / per_tok, h = vec % per_tok;
+    const bool is_k = h >= heads;
+    const uint32_t kh = h - heads;
+    float *qrow = q + ((size_t)t * heads + h) * hd;
+    const float *src = is_k ? k + ((size_t)t * kvh + kh) * hd : qrow;
+    const float *nw = is_k ? k_norm : q_norm;
+    constexpr int kMax = 8;  // head dims up to 256
+    float x[kMax];
+    float ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kMax; ++r) {
+        const uint32_t e = lane + 32u * r;
+        x[r] = e < hd ? src[e] : 0.0f;
+        ss = fmaf(x[r], x[r], ss);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+    for (int r = 0; r < kMax; ++r) {
+        const uint32_t e = lane + 32u * r;
+        if (e < hd) x[r] = x[r] * inv * nw[e];
+    }
+    // Pairs (i, i + n_rot/2): with lane-strided elements the partner sits r_half registers away in the
+    // same lane when n_rot/2 is a multiple of 32, otherwise it is fetched from another lane.
+    const uint32_t half = n_rot / 2u, pos = pos0 + t;
+    float y[kMax];
+#pragma unroll
+    for (int r = 0; r < kMax; ++r) y[r] = x[r];
+#pragma unroll
+    for (int r = 0; r < kMax; ++r) {
+        const uint32_t e = lane + 32u * r;
+        // partner element index and whether e is the first or the second member of its pair
+        const bool first = e < half, second = e >= half && e < n_rot;
+        const uint32_t pe = first ? e + half : e - half;
+        float partner = 0.0f;
+        // the partner lives at register (pe / 32) of lane (pe % 32); half % 32 == 0 keeps it in this lane
+#pragma unroll
+        for (int rr = 0; rr < kMax; ++rr) {
+            const float cand = __shfl_sync(0xffffffffu, x[rr], (int)(pe & 31u));
+            if ((first || second) && (uint32_t)rr == (pe >> 5)) partner = cand;
+        }
+        if (first || second) {
+            const uint32_t i = first ? e : e - half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            y[r] = first ? x[r] * cs - partner * sn : partner * sn + x[r] * cs;
+        }
+    }
+    if (!is_k) {
+#pragma unroll
+        for (int r = 0; r < kMax; ++r) {
+            const uint32_t e = lane + 32u * r;
+            if (e < hd) qrow[e] = y[r];
+        }
+    } else {
+        const float *vsrc = v + ((size_t)t * kvh + kh) * hd;
+        const size_t dst = ((size_t)kh * cap + pos) * hd;
+#pragma unroll
+        for (int r = 0; r < kMax; ++r) {
+            const uint32_t e = lane + 32u * r;
+            if (e < hd) {
+                kc[dst + e] = __float2half_rn(y[r]);
+                vc[dst + e] = __float2half_rn(vsrc[e]);
+            }
+        }
+    }
+}
+
 template <int HD>
 cudaError_t launch_attn(const attn_args &a, int device, cudaStream_t stream) {
     using C = attn_cfg<HD>;
@@ -265,6 +347,35 @@ extern "C" {
 
 int tm_cuda_attention_chunk_mma_supported(uint32_t head_dim) {
     return head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
+}
+
+int tm_cuda_qk_prep_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k, tm_cuda_buffer *v,
+                          tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm, tm_cuda_buffer *inv_freq,
+                          tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, uint32_t heads, uint32_t kv_heads,
+                          uint32_t head_dim, uint32_t n_rot, uint32_t pos0, uint32_t cap, uint32_t n, float eps,
+                          char *err, size_t err_cap) {
+    TM_ENTER();
+    if (heads == 0 || kv_heads == 0 || head_dim == 0 || head_dim > 256 || n_rot == 0 || n_rot > head_dim ||
+        n_rot % 2 != 0 || n == 0 || (size_t)pos0 + n > cap)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
+                       "q/k preparation: heads %u/%u, head_dim %u (<= 256), n_rot %u, rows %u..%u of capacity %u", heads,
+                       kv_heads, head_dim, n_rot, pos0, pos0 + n, cap);
+    const size_t plane = (size_t)kv_heads * cap * head_dim * 2;
+    TM_CHECK_BUF(q, (size_t)n * heads * head_dim * 4, "q");
+    TM_CHECK_BUF(k, (size_t)n * kv_heads * head_dim * 4, "k");
+    TM_CHECK_BUF(v, (size_t)n * kv_heads * head_dim * 4, "v");
+    TM_CHECK_BUF(q_norm, (size_t)head_dim * 4, "q norm");
+    TM_CHECK_BUF(k_norm, (size_t)head_dim * 4, "k norm");
+    TM_CHECK_BUF(inv_freq, (size_t)(n_rot / 2) * 4, "inv_freq");
+    TM_CHECK_BUF(k_cache, plane, "K cache");
+    TM_CHECK_BUF(v_cache, plane, "V cache");
+    TM_OP_BEGIN("qk_prep_chunk");
+    const uint32_t vecs = n * (heads + kv_heads);
+    qk_prep_chunk_kernel<<<(vecs + 7) / 8, 256, 0, ctx->stream>>>(
+        (float *)q->dev, (const float *)k->dev, (const float *)v->dev, (const float *)q_norm->dev,
+        (const float *)k_norm->dev, (const float *)inv_freq->dev, (__half *)k_cache->dev, (__half *)v_cache->dev, heads,
+        kv_heads, head_dim, n_rot, pos0, cap, n, eps);
+    TM_OP_END(1);
 }
 
 int tm_cuda_attention_chunk_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache,

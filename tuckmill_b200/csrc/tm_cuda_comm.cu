@@ -11,6 +11,8 @@
 // stream and can be recorded in a dispatch group like any operator.
 #include <dlfcn.h>
 
+#include <vector>
+
 #include "tm_cuda_internal.cuh"
 #include "tm_cuda_device.cuh"
 
@@ -118,6 +120,90 @@ __global__ void argmax_pair_kernel(const float *pv, const uint32_t *pi, float *p
     }
     pair[0] = bv;
     pair[1] = __uint_as_float(bi == kNone ? kNone : bi + index_offset);
+}
+
+
+// ---- exchange through peer memory --------------------------------------------
+// A symmetric buffer is the same allocation on every rank, each mapped into every
+// other rank's address space (CUDA IPC).  An all-gather is then a PUSH: the producer
+// stores its slice straight into every rank's copy (plain stores over NVLink, no
+// multicast, no library kernel touching peer memory), the last block of the push
+// raises a per-sender sequence flag on every rank and waits -- bounded -- until
+// every sender's flag on THIS rank has reached the same sequence number.
+constexpr int kSymmMaxWorld = 16;
+constexpr uint32_t kSymmTail = 512;        // u32 flags[16] | u32 seq @64 | u32 block counter @68 | u32 status @72
+constexpr uint32_t kSymmSpinLimit = 1u << 24;
+
+struct symm_state {
+    int world = 1, rank = 0;
+    size_t payload = 0;                    // bytes before the flag tail
+    void *peer[kSymmMaxWorld] = {};        // this buffer on every rank (own entry = local pointer)
+    void **d_peer = nullptr;               // the same table in device memory
+};
+
+struct push_args {
+    const float *src;        // [n_rows][width] local slice
+    float *const *peer;      // device table: the target buffer on every rank
+    uint32_t world, rank, n_rows, width;
+    uint32_t tail_off;       // float offset of the flag tail inside the buffer
+    uint32_t dst_off;        // float offset of the target view inside the buffer
+};
+
+__global__ void __launch_bounds__(256) push_rows_kernel(const push_args a) {
+    __shared__ uint32_t s_last, s_seq;
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const size_t total = (size_t)a.n_rows * a.width;
+    const bool vec = (a.width & 3u) == 0u;
+    if (vec) {
+        const size_t quads = total / 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+            const float4 v = *(const float4 *)(a.src + i * 4);
+            const size_t t = (i * 4) / a.width, c = (i * 4) % a.width;
+            const size_t dst = a.dst_off + (t * a.world + a.rank) * a.width + c;
+            for (uint32_t r = 0; r < a.world; ++r) *(float4 *)(a.peer[r] + dst) = v;
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t t = i / a.width, c = i % a.width;
+            const size_t dst = a.dst_off + (t * a.world + a.rank) * a.width + c;
+            const float v = a.src[i];
+            for (uint32_t r = 0; r < a.world; ++r) a.peer[r][dst] = v;
+        }
+    }
+    // Every block's stores are fenced to system scope before it counts itself in; the block that
+    // counts last therefore signals after ALL of this launch's stores.
+    __threadfence_system();
+    __syncthreads();
+    uint32_t *tail = (uint32_t *)(a.peer[a.rank] + a.tail_off);
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(tail + 68, 1u);
+        s_last = prev == gridDim.x - 1u ? 1u : 0u;
+        if (s_last) {
+            tail[68] = 0u;                 // ready for the next launch
+            s_seq = tail[64] + 1u;
+            tail[64] = s_seq;
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    const uint32_t seq = s_seq;
+    if (threadIdx.x < a.world) {
+        __threadfence_system();
+        uint32_t *remote = (uint32_t *)(a.peer[threadIdx.x] + a.tail_off) + a.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
+        // wait for sender threadIdx.x on this rank; sequence numbers only grow
+        const uint32_t *mine = tail + threadIdx.x;
+        uint32_t spin = 0, v = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if ((int32_t)(v - seq) >= 0) break;
+            if (++spin > kSymmSpinLimit) {
+                atomicOr(tail + 72, 1u);   // gave up: the consumer will read stale rows; the host sees the status
+                break;
+            }
+        }
+    }
 }
 
 }  // namespace
@@ -254,6 +340,123 @@ int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, 
                                                          (uint32_t *)out->dev, base, pos, out_cap,
                                                          mirror ? (uint32_t *)mirror->dev : nullptr);
     TM_OP_END(4);
+}
+
+
+void tm_cuda_symm_release(tm_cuda_buffer *b) {
+    if (!b || !b->symm) return;
+    symm_state *st = (symm_state *)b->symm;
+    for (int r = 0; r < st->world; ++r)
+        if (r != st->rank && st->peer[r]) cudaIpcCloseMemHandle(st->peer[r]);
+    if (st->d_peer) cudaFree(st->d_peer);
+    delete st;
+    b->symm = nullptr;
+}
+
+tm_cuda_buffer *tm_cuda_symm_alloc(tm_cuda_ctx *ctx, size_t bytes, char *err, size_t err_cap) {
+    if (!ctx) {
+        tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null context");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *n = nccl();
+    if (!c || !n || c->world < 2 || c->world > kSymmMaxWorld || bytes == 0) {
+        tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "a symmetric buffer needs a communicator of 2..%d ranks", kSymmMaxWorld);
+        return nullptr;
+    }
+    if (ctx->group_open) {
+        tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "symmetric buffers are allocated outside dispatch groups");
+        return nullptr;
+    }
+    cudaSetDevice(ctx->device);
+    const size_t payload = tm_round_up(bytes, 256), total = payload + kSymmTail;
+    unsigned char *dev = nullptr, *hbuf = nullptr;
+    symm_state *st = new symm_state();
+    st->world = c->world;
+    st->rank = c->rank;
+    st->payload = payload;
+    cudaIpcMemHandle_t mine;
+    std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
+    bool ok = cudaMalloc(&dev, total) == cudaSuccess && cudaMemset(dev, 0, total) == cudaSuccess &&
+              cudaIpcGetMemHandle(&mine, dev) == cudaSuccess &&
+              cudaMalloc(&hbuf, sizeof(mine) * (size_t)(c->world + 1)) == cudaSuccess;
+    if (ok) {
+        // every rank's handle, gathered through the communicator
+        ok = cudaMemcpy(hbuf + sizeof(mine) * (size_t)c->world, &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess &&
+             n->AllGather(hbuf + sizeof(mine) * (size_t)c->world, hbuf, sizeof(mine), ncclChar, c->comm, ctx->stream) == 0 &&
+             cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+             cudaMemcpy(all.data(), hbuf, sizeof(mine) * (size_t)c->world, cudaMemcpyDeviceToHost) == cudaSuccess;
+    }
+    for (int r = 0; ok && r < c->world; ++r) {
+        if (r == c->rank) st->peer[r] = dev;
+        else ok = cudaIpcOpenMemHandle(&st->peer[r], all[(size_t)r], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+    }
+    if (ok)
+        ok = cudaMalloc(&st->d_peer, sizeof(void *) * kSymmMaxWorld) == cudaSuccess &&
+             cudaMemcpy(st->d_peer, st->peer, sizeof(void *) * kSymmMaxWorld, cudaMemcpyHostToDevice) == cudaSuccess;
+    if (hbuf) cudaFree(hbuf);
+    if (!ok) {
+        const cudaError_t e = cudaGetLastError();
+        tm_fail(err, err_cap, TM_CUDA_ERR_ALLOC, "symmetric buffer of %zu bytes could not be set up: %s", bytes,
+                cudaGetErrorString(e));
+        tm_cuda_buffer tmp;
+        tmp.symm = st;
+        tm_cuda_symm_release(&tmp);
+        if (dev) cudaFree(dev);
+        return nullptr;
+    }
+    tm_cuda_buffer *b = new tm_cuda_buffer();
+    b->owner = ctx;
+    b->dev = dev;
+    b->len = bytes;  // the ledger counts what was asked for; rounding and the flag tail are bookkeeping
+    b->symm = st;
+    ctx->live.insert(b);
+    ctx->allocated.fetch_add(bytes);
+    return b;
+}
+
+int tm_cuda_push_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *dst, uint32_t n_rows, uint32_t width,
+                          char *err, size_t err_cap) {
+    TM_ENTER();
+    if (n_rows == 0 || width == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "empty push");
+    // The target is a symmetric buffer or a view into one (same offset on every rank).
+    tm_cuda_buffer *root = dst && dst->parent ? dst->parent : dst;
+    if (!dst || ctx->live.find(dst) == ctx->live.end() || !root || !root->symm)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the push target is not (a view of) a symmetric buffer of this context");
+    symm_state *st = (symm_state *)root->symm;
+    const size_t dst_off = (size_t)(dst->dev - root->dev);
+    if (dst_off % 16 != 0) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "push target view is not 16-byte aligned");
+    const size_t per = (size_t)n_rows * width;
+    TM_CHECK_BUF(src, per * 4, "push source");
+    TM_CHECK_BUF(dst, per * (size_t)st->world * 4, "push target");
+    if (src == dst) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "push in place");
+    TM_OP_BEGIN("push_rows");
+    push_args a;
+    a.src = (const float *)src->dev;
+    a.peer = (float *const *)st->d_peer;
+    a.world = (uint32_t)st->world;
+    a.rank = (uint32_t)st->rank;
+    a.n_rows = n_rows;
+    a.width = width;
+    a.tail_off = (uint32_t)(st->payload / 4);
+    a.dst_off = (uint32_t)(dst_off / 4);
+    const size_t work = (width & 3u) == 0u ? per / 4 : per;
+    int grid = (int)((work + 255) / 256);
+    grid = grid < 1 ? 1 : grid > ctx->sm_count * 2 ? ctx->sm_count * 2 : grid;
+    TM_CUDA_TRY(tm_launch_pdl(ctx, push_rows_kernel, dim3(grid), dim3(256), 0, a));
+    TM_OP_END(1);
+}
+
+// Bit 0 set: a push on this buffer gave up waiting for a peer (its consumer read stale rows).
+int tm_cuda_symm_status(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t *status, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (!buf || ctx->live.find(buf) == ctx->live.end() || !buf->symm || !status)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "not a symmetric buffer of this context");
+    symm_state *st = (symm_state *)buf->symm;
+    TM_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    TM_CUDA_TRY(cudaMemcpy(status, buf->dev + st->payload + 72 * 4, 4, cudaMemcpyDeviceToHost));
+    return TM_CUDA_OK;
 }
 
 }  // extern "C"

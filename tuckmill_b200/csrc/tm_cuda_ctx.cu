@@ -268,6 +268,7 @@ void tm_cuda_buffer_free(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer) {
         // Committed work may still read the storage: wait for it (the Metal
         // original leases the storage to its pending command buffers instead).
         cudaStreamSynchronize(ctx->stream);
+        if (buffer->symm) tm_cuda_symm_release(buffer);
         if (buffer->shared) cudaFreeHost(buffer->dev); else cudaFree(buffer->dev);
         ctx->allocated.fetch_sub(buffer->len);
     }

@@ -31,7 +31,11 @@ struct tm_cuda_buffer {
     uint32_t rows = 0, cols = 0;       // geometry of a packed matrix
     const unsigned char *qp = nullptr; // packed: int8 quant plane of row 0
     const unsigned char *dp = nullptr; // packed: f16 scale plane of row 0
+    void *symm = nullptr;              // peer mappings of a symmetric exchange buffer (tm_cuda_comm.cu)
 };
+
+// Closes the peer mappings of a symmetric buffer (no-op for ordinary buffers).
+extern "C" void tm_cuda_symm_release(tm_cuda_buffer *b);
 
 struct tm_cuda_graph {
     tm_cuda_ctx *owner = nullptr;

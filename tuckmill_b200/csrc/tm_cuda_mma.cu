@@ -35,6 +35,7 @@
 #include <cuda.h>
 
 #include "tm_cuda_internal.cuh"
+#include "tm_cuda_device.cuh"
 
 namespace {
 
@@ -139,7 +140,12 @@ __device__ __forceinline__ void dequant8(uint32_t w0, uint32_t w1, __half2 d2, u
 
 struct mma_args {
     const __half *d;       // [rows][cols/32] block scales
-    float *y;              // Y[t * rows + r]
+    // The rows may be cut into up to three consecutive parts (q | k | v, gate | up), each with its own
+    // dense output Y_p[t * part_rows + r]; every part but the last is a multiple of 128 rows, so a
+    // tile never straddles two parts.
+    float *y[3];
+    uint32_t part_end[3];  // exclusive row bound of each part (the last one is `rows`)
+    uint32_t accumulate;   // 1: Y += W X (the residual add folded into the epilogue)
     uint32_t rows, cols, batch;
     uint32_t *abort_flag;  // set when a bounded wait gave up
 };
@@ -318,8 +324,15 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
           for (uint32_t sub = 0; sub < (uint32_t)kIssuers && ok; ++sub) {
-            const uint32_t rr = (tile % row_tiles) * kBM + quarter * 32u + (uint32_t)lane;
+            const uint32_t tile_row0 = (tile % row_tiles) * kBM;
+            const uint32_t rr = tile_row0 + quarter * 32u + (uint32_t)lane;
             const uint32_t tok0 = (tile / row_tiles) * kTB + sub * BN;
+            // (selects, not indexing: the arrays are kernel parameters)
+            const bool p0 = tile_row0 < a.part_end[0], p1 = tile_row0 < a.part_end[1];
+            const uint32_t part_row0 = p0 ? 0u : p1 ? a.part_end[0] : a.part_end[1];
+            const uint32_t part_row1 = p0 ? a.part_end[0] : p1 ? a.part_end[1] : a.part_end[2];
+            const size_t stride = part_row1 - part_row0;  // rows of this part = token stride of its output
+            float *ybase = (p0 ? a.y[0] : p1 ? a.y[1] : a.y[2]) + (rr - part_row0);
             if (ok) ok = mbar_wait(&acc_full[sub], it & 1u, abort_s);
             ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
             if (!ok) break;
@@ -343,10 +356,14 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (rr < a.rows) {
-                    // Lane = row: for a fixed token the warp writes 128 contiguous bytes.
-                    float *p = a.y + (size_t)t0 * a.rows + rr;
-                    const size_t stride = a.rows;  // independent addresses: no add chain between the stores
-                    if (t0 + 32u <= a.batch) {
+                    // Lane = row: for a fixed token the warp writes 128 contiguous bytes; the addresses
+                    // are independent (no add chain between the stores).
+                    float *p = ybase + (size_t)t0 * stride;
+                    if (a.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (t0 + (uint32_t)j < a.batch) p[(size_t)j * stride] += __uint_as_float(v[j]);
+                    } else if (t0 + 32u <= a.batch) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) p[(size_t)j * stride] = __uint_as_float(v[j]);
                     } else {
@@ -467,6 +484,36 @@ __global__ void x_to_f16_kernel(const float *x, __half *out, size_t n) {
     }
 }
 
+// The same copy with the producer's elementwise step folded in, one CTA per token row:
+// RMS norm times a weight vector, or activation(x) * up (the gated-FFN product).
+template <int PRO>
+__global__ void __launch_bounds__(256) x_prep_f16_kernel(const float *x, const float *pro, __half *out, uint32_t cols,
+                                                          float eps) {
+    __shared__ float red[8];
+    const float *xr = x + (size_t)blockIdx.x * cols;
+    __half *orow = out + (size_t)blockIdx.x * cols;
+    float inv = 1.0f;
+    if (PRO == TM_CUDA_PRO_RMSNORM) {
+        float ss = 0.0f;
+        for (uint32_t c = threadIdx.x; c < cols; c += 256) ss = fmaf(xr[c], xr[c], ss);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        inv = 1.0f / sqrtf(tot / (float)cols + eps);
+    }
+    for (uint32_t c = threadIdx.x; c < cols; c += 256) {
+        float v = xr[c];
+        if (PRO == TM_CUDA_PRO_RMSNORM) v = v * inv * pro[c];
+        else if (PRO == TM_CUDA_PRO_SILU_MUL) v = tmdev::silu_f(v) * pro[(size_t)blockIdx.x * cols + c];
+        else if (PRO == TM_CUDA_PRO_GELU_MUL) v = tmdev::gelu_tanh_f(v) * pro[(size_t)blockIdx.x * cols + c];
+        orow[c] = __float2half_rn(v);
+    }
+}
+
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                     const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -535,32 +582,21 @@ int tm_cuda_mma_workspace_reserve(tm_cuda_ctx *ctx, size_t bytes, char *err, siz
 
 size_t tm_cuda_mma_workspace_bytes(uint32_t cols, uint32_t batch) { return (size_t)cols * batch * 2; }
 
-int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
-                          uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off, char *err, size_t err_cap) {
-    if (batch >= 1 && batch < 9) {
-        // A handful of tokens is HBM-bound: the exact integer-tensor-core path serves it (and is tighter).
-        return tm_cuda_q8_0_gemm(ctx, w, x, y, rows, cols, batch, x_off, y_off, err, err_cap);
-    }
+// Grows the f16 workspace when the call needs more (outside a dispatch group only).
+static int mma_ensure_workspace(tm_cuda_ctx *ctx, uint32_t cols, uint32_t batch, char *err, size_t err_cap) {
+    const size_t need = tm_cuda_mma_workspace_bytes(cols, batch);
+    bool small;
     {
-        const size_t need = tm_cuda_mma_workspace_bytes(cols, batch);
-        bool small;
-        {
-            if (!ctx) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null context");
-            std::lock_guard<std::mutex> lock(ctx->mu);
-            small = ctx->mma_scratch_bytes < need;
-        }
-        if (small) {
-            int rc = tm_cuda_mma_workspace_reserve(ctx, need, err, err_cap);
-            if (rc != TM_CUDA_OK) return rc;
-        }
+        if (!ctx) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "null context");
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        small = ctx->mma_scratch_bytes < need;
     }
-    TM_ENTER();
-    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
-    if (rc != TM_CUDA_OK) return rc;
-    if (batch == 0 || batch > TM_CUDA_GEMM_MMA_MAX_BATCH)
-        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "batch %u outside 1..%u", batch, TM_CUDA_GEMM_MMA_MAX_BATCH);
-    TM_CHECK_BUF(x, ((size_t)x_off + (size_t)batch * cols) * 4, "activation");
-    TM_CHECK_BUF(y, ((size_t)y_off + (size_t)batch * rows) * 4, "output");
+    return small ? tm_cuda_mma_workspace_reserve(ctx, need, err, err_cap) : TM_CUDA_OK;
+}
+
+// The GEMM launch proper: the f16 copy of X is already in the workspace.  Called with the context locked.
+static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, uint32_t cols, uint32_t batch,
+                      float *const y[3], const uint32_t part_end[3], int accumulate, char *err, size_t err_cap) {
     encode_tiled_fn encode = get_encode_tiled();
     if (!encode)
         return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "the driver does not export cuTensorMapEncodeTiled");
@@ -585,7 +621,6 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
             }
         }
     }
-    if (getenv("TM_MMA_BN")) bn = atoi(getenv("TM_MMA_BN"));
     CUtensorMap xmap, wmap;
     const cuuint32_t estr[2] = {1, 1};
     {
@@ -611,21 +646,103 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
     }
     mma_args a;
     a.d = (const __half *)w->dp;
-    a.y = (float *)y->dev + y_off;
+    for (int p = 0; p < 3; ++p) {
+        a.y[p] = y[p];
+        a.part_end[p] = part_end[p];
+    }
+    a.accumulate = accumulate ? 1u : 0u;
     a.rows = rows;
     a.cols = cols;
     a.batch = batch;
     a.abort_flag = abort_flag;
-    TM_OP_BEGIN("q8_0_gemm_mma");
-    const size_t n = (size_t)batch * cols;
-    const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
-    x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev + x_off, xh, n);
     const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn));
-    int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
-    if (getenv("TM_MMA_GRID") && atoi(getenv("TM_MMA_GRID")) < grid) grid = atoi(getenv("TM_MMA_GRID"));
+    const int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
     TM_CUDA_TRY(bn == 192   ? launch_mma<192>(wmap, xmap, a, grid, ctx->device, ctx->stream)
                 : bn == 128 ? launch_mma<128>(wmap, xmap, a, grid, ctx->device, ctx->stream)
                             : launch_mma<64>(wmap, xmap, a, grid, ctx->device, ctx->stream));
+    return TM_CUDA_OK;
+}
+
+int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                          uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off, char *err, size_t err_cap) {
+    if (batch >= 1 && batch < 9) {
+        // A handful of tokens is HBM-bound: the exact integer-tensor-core path serves it (and is tighter).
+        return tm_cuda_q8_0_gemm(ctx, w, x, y, rows, cols, batch, x_off, y_off, err, err_cap);
+    }
+    {
+        const int rc = mma_ensure_workspace(ctx, cols, batch, err, err_cap);
+        if (rc != TM_CUDA_OK) return rc;
+    }
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (batch == 0 || batch > TM_CUDA_GEMM_MMA_MAX_BATCH)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "batch %u outside 1..%u", batch, TM_CUDA_GEMM_MMA_MAX_BATCH);
+    TM_CHECK_BUF(x, ((size_t)x_off + (size_t)batch * cols) * 4, "activation");
+    TM_CHECK_BUF(y, ((size_t)y_off + (size_t)batch * rows) * 4, "output");
+    TM_OP_BEGIN("q8_0_gemm_mma");
+    const size_t n = (size_t)batch * cols;
+    const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
+    x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev + x_off,
+                                                                      (__half *)ctx->mma_scratch, n);
+    float *const ys[3] = {(float *)y->dev + y_off, nullptr, nullptr};
+    const uint32_t ends[3] = {rows, rows, rows};
+    rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, 0, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    TM_OP_END(2);
+}
+
+int tm_cuda_q8_0_gemm_mma_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, uint32_t rows, uint32_t cols,
+                                uint32_t batch, uint32_t n_parts, tm_cuda_buffer *const *y_parts,
+                                const uint32_t *part_rows, int prologue, tm_cuda_buffer *pro, float eps, int epilogue,
+                                char *err, size_t err_cap) {
+    {
+        const int rc = mma_ensure_workspace(ctx, cols, batch, err, err_cap);
+        if (rc != TM_CUDA_OK) return rc;
+    }
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (batch == 0 || batch > TM_CUDA_GEMM_MMA_MAX_BATCH)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "batch %u outside 1..%u", batch, TM_CUDA_GEMM_MMA_MAX_BATCH);
+    if (n_parts < 1 || n_parts > 3 || !y_parts || !part_rows)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "1 to 3 output parts, got %u", n_parts);
+    if (prologue < TM_CUDA_PRO_NONE || prologue > TM_CUDA_PRO_GELU_MUL ||
+        (epilogue != TM_CUDA_EPI_STORE && epilogue != TM_CUDA_EPI_ADD))
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "unknown prologue %d / epilogue %d", prologue, epilogue);
+    float *ys[3] = {nullptr, nullptr, nullptr};
+    uint32_t ends[3] = {rows, rows, rows}, sum = 0;
+    for (uint32_t p = 0; p < n_parts; ++p) {
+        if (part_rows[p] == 0 || (p + 1 < n_parts && part_rows[p] % kBM != 0))
+            return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
+                           "part %u has %u rows: every part but the last must be a multiple of %d", p, part_rows[p], kBM);
+        TM_CHECK_BUF(y_parts[p], (size_t)batch * part_rows[p] * 4, "output part");
+        ys[p] = (float *)y_parts[p]->dev;
+        sum += part_rows[p];
+        ends[p] = sum;
+    }
+    if (sum != rows) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "parts cover %u of %u rows", sum, rows);
+    TM_CHECK_BUF(x, (size_t)batch * cols * 4, "activation");
+    if (prologue == TM_CUDA_PRO_RMSNORM) TM_CHECK_BUF(pro, (size_t)cols * 4, "norm weight");
+    else if (prologue != TM_CUDA_PRO_NONE) TM_CHECK_BUF(pro, (size_t)batch * cols * 4, "gate operand");
+    TM_OP_BEGIN("q8_0_gemm_mma_fused");
+    __half *xh = (__half *)ctx->mma_scratch;
+    const float *xp = (const float *)x->dev, *pp = pro ? (const float *)pro->dev : nullptr;
+    switch (prologue) {
+        case TM_CUDA_PRO_RMSNORM:
+            x_prep_f16_kernel<TM_CUDA_PRO_RMSNORM><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            break;
+        case TM_CUDA_PRO_SILU_MUL:
+            x_prep_f16_kernel<TM_CUDA_PRO_SILU_MUL><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            break;
+        case TM_CUDA_PRO_GELU_MUL:
+            x_prep_f16_kernel<TM_CUDA_PRO_GELU_MUL><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            break;
+        default:
+            x_prep_f16_kernel<TM_CUDA_PRO_NONE><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+    }
+    rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, epilogue == TM_CUDA_EPI_ADD, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
     TM_OP_END(2);
 }
 

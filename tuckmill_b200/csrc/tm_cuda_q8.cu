@@ -7,6 +7,8 @@
 // free (tolerance-registered against the scalar CPU order,
 // crates/tuckcore/src/kernels.rs:186-204).  The design is not the Metal
 // kernel's; it is described at q8_gemv_kernel below.
+#include <type_traits>
+
 #include "tm_cuda_internal.cuh"
 #include "tm_cuda_device.cuh"
 
@@ -72,7 +74,7 @@ __host__ __device__ inline size_t token_smem(uint32_t cols, uint32_t plane) {
  * matrix shape, never on the batch, which keeps a (row, token) result
  * bit-identical between the GEMV and any batched call.
  */
-template <int M>
+template <int M, int kSlots, int H>
 __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float red[kWarps];
@@ -87,40 +89,58 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     const uint32_t n_tiles = (rows + 15u) / 16u;
     const uint32_t n_chunks = (cols + kChunkCols - 1u) / kChunkCols;
 
-    // Weights do not depend on the activations: this warp's first batch of
-    // chunks is loaded into registers (and the next batch prefetched towards
-    // L2) before the activations are staged, so the two latencies overlap.
-    constexpr int U = 4;  // chunks whose loads are issued before any is consumed
+    // Weights do not depend on the activations, so they stream through registers on their own
+    // schedule: the warp's (tile, chunk) work is one flat sequence of groups of H chunks, held in
+    // kSlots register slots.  While one slot is multiplied the other slots' loads are in flight, and
+    // a slot is refilled (with the group kSlots ahead, possibly of the warp's NEXT tile) as soon as it
+    // has been consumed -- loads never stop at a tile boundary.  The first kSlots groups are
+    // requested before the activations are staged, so both latencies overlap.
+    // kSlots x H is chosen per shape by the host: three slots of two chunks keep the small and
+    // mid-size projections streaming; one slot of four (a plain load / multiply alternation with
+    // wider bursts per row) measured best on the very large ks = 1 matrices.
+    constexpr int U = kSlots * H;  // chunks in registers
     int4 wa[U], wb[U];
     unsigned short ha[U], hb[U];
-    auto load_batch = [&](uint32_t tile, uint32_t ch0) {
-        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+    const uint32_t tile_stride = gridDim.x * tiles_per_cta;
+    uint32_t ld_tile = blockIdx.x * tiles_per_cta + my_tile, ld_ch = my_ks;  // next group to request
+    auto load_half = [&](auto half_c) {
+        constexpr int half = decltype(half_c)::value;
+        if (ld_tile >= n_tiles) return;
+        const uint32_t row_a = min(ld_tile * 16u + g, rows - 1u), row_b = min(ld_tile * 16u + g + 8u, rows - 1u);
         const signed char *pa = a.q + (size_t)row_a * cols + t4 * 16u;
         const signed char *pb = a.q + (size_t)row_b * cols + t4 * 16u;
         const unsigned short *sa = (const unsigned short *)a.d + (size_t)row_a * nb + (t4 >> 1);
         const unsigned short *sb = (const unsigned short *)a.d + (size_t)row_b * nb + (t4 >> 1);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t ch = ch0 + u * ks;
+        for (int u = 0; u < H; ++u) {
+            const uint32_t ch = ld_ch + u * ks;
             const bool inb = ch < n_chunks && ch * kChunkCols + t4 * 16u < cols;
-            wa[u] = wb[u] = make_int4(0, 0, 0, 0);
-            ha[u] = hb[u] = 0;
+            wa[half * H + u] = wb[half * H + u] = make_int4(0, 0, 0, 0);
+            ha[half * H + u] = hb[half * H + u] = 0;
             if (inb) {
-                wa[u] = ldg_stream((const int4 *)(pa + (size_t)ch * kChunkCols));
-                wb[u] = ldg_stream((const int4 *)(pb + (size_t)ch * kChunkCols));
-                ha[u] = __ldg(sa + ch * 2u);
-                hb[u] = __ldg(sb + ch * 2u);
+                wa[half * H + u] = ldg_stream((const int4 *)(pa + (size_t)ch * kChunkCols));
+                wb[half * H + u] = ldg_stream((const int4 *)(pb + (size_t)ch * kChunkCols));
+                ha[half * H + u] = __ldg(sa + ch * 2u);
+                hb[half * H + u] = __ldg(sb + ch * 2u);
             }
         }
+        ld_ch += H * ks;
+        if (ld_ch >= n_chunks) {
+            ld_ch = my_ks;
+            ld_tile += tile_stride;
+        }
     };
-    const uint32_t first_base = blockIdx.x * tiles_per_cta;
-    if (first_base + my_tile < n_tiles) {
-        load_batch(first_base + my_tile, my_ks);
-        const uint32_t tile = first_base + my_tile;
-        const uint32_t row_a = min(tile * 16u + g, rows - 1u), row_b = min(tile * 16u + g + 8u, rows - 1u);
+    using half0 = std::integral_constant<int, 0>;
+    using half1 = std::integral_constant<int, 1>;
+    using half2 = std::integral_constant<int, 2>;
+    load_half(half0{});
+    if constexpr (kSlots > 1) load_half(half1{});
+    if constexpr (kSlots > 2) load_half(half2{});
+    if (ld_tile < n_tiles) {  // the groups after those: towards L2
+        const uint32_t row_a = min(ld_tile * 16u + g, rows - 1u), row_b = min(ld_tile * 16u + g + 8u, rows - 1u);
 #pragma unroll
-        for (uint32_t j = U; j < 2 * U; ++j) {
-            const uint32_t c0 = (my_ks + j * ks) * kChunkCols + t4 * 16u;
+        for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t c0 = (ld_ch + j * ks) * kChunkCols + t4 * 16u;
             if (c0 < cols) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_a * cols + c0));
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(a.q + (size_t)row_b * cols + c0));
@@ -242,6 +262,39 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
 
     const bool b_live = (t4 >> 1) == (g >> 2);  // this lane's k-slots belong to column n = g's block
 
+    uint32_t cur_half = 0;  // the slot holding the next group to multiply
+    auto multiply_half = [&](auto half_c, uint32_t ch0, float (&acc)[M][2]) {
+        constexpr int half = decltype(half_c)::value;
+#pragma unroll
+        for (int u = 0; u < H; ++u) {
+            const uint32_t ch = ch0 + u * ks;
+            const uint32_t c0 = ch * kChunkCols + t4 * 16u;
+            const bool inb = ch < n_chunks && c0 < cols;
+            if (ch >= n_chunks) break;
+            const float da = __half2float(__ushort_as_half(ha[half * H + u]));
+            const float db = __half2float(__ushort_as_half(hb[half * H + u]));
+            const int4 qa = wa[half * H + u], qb = wb[half * H + u];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const unsigned char *tokp = smem + (size_t)m * tok;
+                int4 bx = make_int4(0, 0, 0, 0);
+                if (b_live) bx = *(const int4 *)(tokp + (size_t)(g & 3) * plane + c0);
+                int dd[4] = {0, 0, 0, 0};
+                mma_s8(dd, qa.x, qb.x, qa.y, qb.y, bx.x, bx.y);
+                mma_s8(dd, qa.z, qb.z, qa.w, qb.w, bx.z, bx.w);
+                if (inb) {
+                    const float2 cx = *(const float2 *)(tokp + 4u * (size_t)plane +
+                                                        ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
+                    const float va = fmaf((float)dd[1], cx.y, (float)dd[0] * cx.x);
+                    const float vb = fmaf((float)dd[3], cx.y, (float)dd[2] * cx.x);
+                    acc[m][0] = fmaf(da, va, acc[m][0]);
+                    acc[m][1] = fmaf(db, vb, acc[m][1]);
+                }
+            }
+        }
+        load_half(half_c);  // refill with the group kSlots ahead
+    };
+
     for (uint32_t base = blockIdx.x * tiles_per_cta; base < n_tiles; base += gridDim.x * tiles_per_cta) {
         const uint32_t tile = base + my_tile;
         const bool tile_ok = tile < n_tiles;
@@ -251,34 +304,14 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
 
         if (tile_ok) {
 #pragma unroll 1
-            for (uint32_t ch0 = my_ks; ch0 < n_chunks; ch0 += ks * U) {
-                if (base != first_base || ch0 != my_ks) load_batch(tile, ch0);  // the first batch is already here
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint32_t ch = ch0 + u * ks;
-                    const uint32_t c0 = ch * kChunkCols + t4 * 16u;
-                    const bool inb = ch < n_chunks && c0 < cols;
-                    if (ch >= n_chunks) break;
-                    const float da = __half2float(__ushort_as_half(ha[u]));
-                    const float db = __half2float(__ushort_as_half(hb[u]));
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        const unsigned char *tokp = smem + (size_t)m * tok;
-                        int4 bx = make_int4(0, 0, 0, 0);
-                        if (b_live) bx = *(const int4 *)(tokp + (size_t)(g & 3) * plane + c0);
-                        int dd[4] = {0, 0, 0, 0};
-                        mma_s8(dd, wa[u].x, wb[u].x, wa[u].y, wb[u].y, bx.x, bx.y);
-                        mma_s8(dd, wa[u].z, wb[u].z, wa[u].w, wb[u].w, bx.z, bx.w);
-                        if (inb) {
-                            const float2 cx = *(const float2 *)(tokp + 4u * (size_t)plane +
-                                                                ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
-                            const float va = fmaf((float)dd[1], cx.y, (float)dd[0] * cx.x);
-                            const float vb = fmaf((float)dd[3], cx.y, (float)dd[2] * cx.x);
-                            acc[m][0] = fmaf(da, va, acc[m][0]);
-                            acc[m][1] = fmaf(db, vb, acc[m][1]);
-                        }
-                    }
+            for (uint32_t ch0 = my_ks; ch0 < n_chunks; ch0 += ks * H) {
+                if (cur_half == 0 || kSlots == 1) multiply_half(half0{}, ch0, acc);
+                else if (cur_half == 1 || kSlots == 2) {
+                    if constexpr (kSlots > 1) multiply_half(half1{}, ch0, acc);
+                } else {
+                    if constexpr (kSlots > 2) multiply_half(half2{}, ch0, acc);
                 }
+                cur_half = cur_half == (uint32_t)(kSlots - 1) ? 0u : cur_half + 1u;
             }
         }
         // ---- add the four lanes of each row, then the ks column splits ----
@@ -328,17 +361,17 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     }
 }
 
-template <int M>
+template <int M, int kSlots, int H>
 cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
     static bool attr_set[16] = {};  // per device
     if (ctx->device < 16 && !attr_set[ctx->device]) {
-        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M>,
+        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M, kSlots, H>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)ctx->smem_optin - 8192);
         if (e != cudaSuccess) return e;
         attr_set[ctx->device] = true;
     }
-    return tm_launch_pdl(ctx, q8_gemv_kernel<M>, dim3(grid), dim3(kThreads), smem, a);
+    return tm_launch_pdl(ctx, q8_gemv_kernel<M, kSlots, H>, dim3(grid), dim3(kThreads), smem, a);
 }
 
 uint32_t digit_plane_bytes(uint32_t cols) {
@@ -361,10 +394,11 @@ cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
     uint32_t ctas = (n_tiles + tiles_per_cta - 1u) / tiles_per_cta;
     if (ctas > 1u << 20) ctas = 1u << 20;  // the kernel strides over any remainder
     switch (m) {
-        case 8: return launch_gemv<8>(ctx, a, (int)ctas, smem);
-        case 4: return launch_gemv<4>(ctx, a, (int)ctas, smem);
-        case 2: return launch_gemv<2>(ctx, a, (int)ctas, smem);
-        default: return launch_gemv<1>(ctx, a, (int)ctas, smem);
+        case 8: return launch_gemv<8, 2, 2>(ctx, a, (int)ctas, smem);
+        case 4: return launch_gemv<4, 2, 2>(ctx, a, (int)ctas, smem);
+        case 2: return launch_gemv<2, 2, 2>(ctx, a, (int)ctas, smem);
+        default:
+            return ks == 1 ? launch_gemv<1, 1, 4>(ctx, a, (int)ctas, smem) : launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
     }
 }
 

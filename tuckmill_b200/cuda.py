@@ -75,6 +75,11 @@ _OPS = {
     "qwen35_kv_store_f16_chunk": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
     "qwen35_attention_f16": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F],
     "qwen35_attention_f16_chunk": [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
+    "comm_init": [_P, C.c_void_p, _I, _I],
+    "all_gather_f32": [_P, _P, _U32, _P, _U32, _U32],
+    "all_gather_rows_f32": [_P, _P, _P, _P, _U32, _U32],
+    "q8_0_gemm_mma_fused": [_P, _P, _P, _U32, _U32, _U32, _U32, C.POINTER(C.c_void_p), C.POINTER(C.c_uint32), _I, _P, _F, _I],
+    "qk_prep_chunk": [_P] * 9 + [_U32] * 7 + [_F],
     "attention_chunk_mma": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
     "attention_decode_dev": [_P] * 12 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
     "attention_decode_dev_static": [_P] * 11 + [_U32, _P] + [_U32] * 6 + [_F, _F, _I],
@@ -139,6 +144,15 @@ def load_library() -> C.CDLL:
 
 def available() -> int:
     return int(load_library().tm_cuda_available())
+
+
+def comm_unique_id() -> bytes:
+    """128 opaque bytes naming a new communicator (made on one rank, handed to the others)."""
+    out, err = C.create_string_buffer(128), C.create_string_buffer(512)
+    rc = load_library().tm_cuda_comm_unique_id(out, err, 512)
+    if rc != 0:
+        raise CudaError(rc, err.value.decode())
+    return out.raw
 
 
 def runtime_info() -> str:
@@ -356,6 +370,18 @@ class CudaContext:
     def qwen35_attention_f16(self, q, k_cache, v_cache, out, scratch, heads, pos, cap, head_dim, group, scale):
         self._call("qwen35_attention_f16", q.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, heads, pos, cap, head_dim, group, scale)
 
+    def q8_0_gemm_mma_fused(self, w, x, rows, cols, batch, ys, part_rows, prologue=PRO_NONE, pro=None, eps=0.0,
+                            epilogue=EPI_STORE):
+        yp = (C.c_void_p * len(ys))(*[y.handle for y in ys])
+        pr = (C.c_uint32 * len(ys))(*part_rows)
+        self._call("q8_0_gemm_mma_fused", w.handle, x.handle, rows, cols, batch, len(ys), yp, pr, prologue,
+                   self._h(pro), eps, epilogue)
+
+    def qk_prep_chunk(self, q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, heads, kv_heads, head_dim, n_rot, pos0,
+                      cap, n, eps):
+        self._call("qk_prep_chunk", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle, inv_freq.handle,
+                   k_cache.handle, v_cache.handle, heads, kv_heads, head_dim, n_rot, pos0, cap, n, eps)
+
     def attention_chunk_mma(self, q, k_cache, v_cache, out, heads, pos0, cap, head_dim, group, scale, n, window):
         self._call("attention_chunk_mma", q.handle, k_cache.handle, v_cache.handle, out.handle, heads, pos0, cap, head_dim, group, scale, n, window)
 
@@ -377,6 +403,18 @@ class CudaContext:
                    status.handle, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, int(exact))
 
     def u32_add(self, buf, index, delta): self._call("u32_add", buf.handle, index, delta)
+
+    # -- output-row split across devices (one process per device) ---------------
+    def comm_init(self, ident: bytes, rank: int, world: int):
+        """Collective: every rank passes the same 128-byte id (`comm_unique_id()` of one rank)."""
+        self._comm_id = C.create_string_buffer(ident, 128)
+        self._call("comm_init", C.cast(self._comm_id, C.c_void_p), rank, world)
+
+    def all_gather_f32(self, src, src_off, dst, dst_off, count):
+        self._call("all_gather_f32", src.handle, src_off, dst.handle, dst_off, count)
+
+    def all_gather_rows_f32(self, src, stage, dst, n_rows, width):
+        self._call("all_gather_rows_f32", src.handle, stage.handle, dst.handle, n_rows, width)
 
     # -- grouping, fences, measurement ---------------------------------------
     def begin_group(self): self._call("begin_group")

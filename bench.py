@@ -200,6 +200,26 @@ def gemv_roofline(eng, shape, hbm_gbs, us_per_token):
     }
 
 
+def copy_bandwidth(torch, device):
+    """Device-to-device copy of 1 GiB on THIS GPU (read + write bytes / time), the same kind of
+    measurement the peak in MEASURED_PEAKS.json comes from: GPUs of this pool differ by 10-20 %."""
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.uint8, device=f"cuda:{device}")
+    b = torch.empty_like(a)
+    for _ in range(2):
+        b.copy_(a)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        b.copy_(a)
+    e1.record()
+    torch.cuda.synchronize()
+    gbs = 2.0 * n * 5 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+    del a, b
+    return gbs
+
+
 def lm_head_roofline(device, shape, hbm_gbs, torch):
     """The step's largest launch alone: the vocab x hidden GEMV, 20 launches in one
     replayed graph with events on its stream either side (the weights, 1.0625
@@ -330,6 +350,8 @@ def run_cuda(args):
     if rank == 0:
         roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens)
         roof["lm_head"] = lm_head_roofline(local, shape, hbm_gbs, torch)
+        roof["copy_gbs_this_gpu"] = copy_bandwidth(torch, local)
+        roof["lm_head"]["frac_of_this_gpu_copy"] = roof["lm_head"]["achieved"] / roof["copy_gbs_this_gpu"]
         roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"
         step_bytes = shape.decode_weight_bytes()
         cpu = None
@@ -368,8 +390,11 @@ def run_cuda(args):
 def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n, replica_tokens):
     """The same session with ONE model split by output rows over all ranks (each
     rank holds 1/world of every projection, of the head and of the KV cache; four
-    NCCL all-gathers per layer inside the replayed decode graph).  Strong scaling
-    of a single sequence: reported beside the replica figure, not as `value`."""
+    exchanges per layer inside the replayed decode graph, pushed through peer
+    memory).  Strong scaling of a single sequence: reported beside the replica
+    figure, not as `value`."""
+    if os.environ.get("TM_BENCH_ROW_SPLIT", "1") == "0":
+        return {"unavailable": "switched off by TM_BENCH_ROW_SPLIT=0"}
     try:
         from tuckmill_b200 import sharding as S
         S.shard_geometry(shape, world)
@@ -413,7 +438,7 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
     prefill_ms, decode_ms, span_ms = vals.tolist()
     info = eng.refresh_info()
     out = {
-        "parallelism": f"output-row split x{world}, ncclAllGather on the compute stream", "scaling": "strong",
+        "parallelism": f"output-row split x{world}, exchanges pushed through peer memory on the compute stream", "scaling": "strong",
         "decode_tok_s": args.steps * (decode_n - 1) / (decode_ms / 1e3),
         "decode_us_per_token": 1e3 * decode_ms / (args.steps * (decode_n - 1)),
         "prefill_tok_s": args.steps * prompt_n / (prefill_ms / 1e3),
@@ -433,9 +458,10 @@ def run_sweep(args):
     """The Q8_0 projection sweep at Qwen3-8B shapes, split by output rows over the
     ranks: every rank multiplies its N/G rows with the single-device kernel (GEMV at
     M = 1, the bit-identical batched form up to 8, the tensor-core GEMM above) and an
-    all-gather reassembles Y.  Per case: device time of the multiply alone, of the
-    all-gather alone, and of both back to back (each a replayed graph, CUDA events,
-    max over ranks).  Rank 0 prints one JSON line; a profiling aid, not `value`."""
+    all-gather reassembles Y -- once as ncclAllGather (+ interleave), once as a push
+    through peer memory.  Per case: device time of the multiply alone, of each
+    exchange alone, and of multiply + exchange back to back (each a replayed graph,
+    CUDA events, max over ranks).  Rank 0 prints one JSON line; a profiling aid, not `value`."""
     import torch
     import torch.distributed as dist
 
@@ -517,20 +543,41 @@ def run_sweep(args):
                 multiply()
                 gather()
 
+            # the same exchange as a push through peer memory (two target views used in turn)
+            arena = ctx.symm_buffer(2 * m * rows * 4) if world > 1 else None
+            views = [arena.view(i * m * rows * 4, m * rows * 4) for i in range(2)] if world > 1 else []
+            pturn = [0]
+
+            def push():
+                ctx.push_rows_f32(y_loc, views[pturn[0] % 2], m, local_rows)
+                pturn[0] += 1
+
+            def both_push():
+                multiply()
+                push()
+
             reps = 20 if m * rows * cols < 2e11 else 4
             t_mul = timed(multiply, reps)
             t_ag = timed(gather, reps) if world > 1 else 0.0
             t_both = timed(both, reps) if world > 1 else t_mul
+            t_push = timed(push, reps) if world > 1 else 0.0
+            t_both_push = timed(both_push, reps) if world > 1 else t_mul
             nbytes = rows * (cols // 32) * 34 + 4 * m * cols * world + 4 * m * rows
             case = {"rows": rows, "cols": cols, "batch": m, "us_multiply": round(t_mul, 2),
                     "us_all_gather": round(t_ag, 2), "us_both": round(t_both, 2),
+                    "us_push": round(t_push, 2), "us_both_push": round(t_both_push, 2),
                     "tflops": round(2.0 * m * rows * cols / t_both / 1e6, 1),
                     "gbs": round(nbytes / t_both / 1e3, 1)}
             case["frac"] = round(case["gbs"] / (hbm_gbs * world), 3) if m <= 8 else round(case["tflops"] / (tf_peak * world), 3)
             case["bound"] = "hbm" if m <= 8 else "tensor"
             cases.append(case)
+            for b in views:
+                b.free()
             for b in {id(b): b for b in (x, y_loc, y, stage)}.values():
                 b.free()
+            if arena is not None:
+                assert ctx.symm_status(arena) == 0, "a peer-memory wait ran out"
+                arena.free()
         for w in ws:
             w.free()
     if rank == 0:

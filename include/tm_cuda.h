@@ -436,6 +436,14 @@ int tm_cuda_all_gather_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_b
  * still be reading the previous contents); alternate between at least two.  Bit 0
  * of tm_cuda_symm_status: a wait ran out (the consumer read stale rows). */
 tm_cuda_buffer *tm_cuda_symm_alloc(tm_cuda_ctx *ctx, size_t bytes, char *err, size_t err_cap);
+/* The tensor-core GEMM and the exchange as ONE kernel: the epilogue of
+ * tm_cuda_q8_0_gemm_mma stores each finished tile of this rank's `rows` output rows
+ * straight into every rank's gathered Y (dst[t][rank*rows + r], dst a symmetric buffer
+ * or a view of one), so the transfer of a tile overlaps the MMAs of the next; the
+ * last CTA ends the exchange like tm_cuda_push_rows_f32 does.  STORE only. */
+int tm_cuda_q8_0_gemm_mma_push(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *dst,
+                               uint32_t rows, uint32_t cols, uint32_t batch, char *err, size_t err_cap);
+
 int tm_cuda_push_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *dst, uint32_t n_rows, uint32_t width,
                           char *err, size_t err_cap);
 int tm_cuda_symm_status(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t *status, char *err, size_t err_cap);

@@ -70,3 +70,24 @@ def test_two_device_split_matches_single_device_and_oracle(oracle, tmp_path, mod
     cpu.reset(96)
     ref_tokens, _ = cpu.generate_greedy(T.token_ids(6, 19, shape.vocab), 40)
     assert list(got["generated"]) == list(ref_tokens)
+
+
+def test_peer_memory_push_all_gather(tmp_path):
+    """tm_cuda_push_rows_f32 over a symmetric arena: every rank receives every rank's
+    rows at the interleaved position, round after round, eagerly and from a replayed
+    dispatch group; no bounded wait ever ran out."""
+    if cuda.available() < 2:
+        pytest.skip("needs two devices")
+    comm = cuda.comm_unique_id().hex()
+    env = {**os.environ, "PYTHONPATH": str(ROOT), "NCCL_NVLS_ENABLE": "0"}
+    procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "_push_worker.py"), str(r), "2", comm], cwd=ROOT,
+                              env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(2)]
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        logs.append(o.decode(errors="replace")[-3000:])
+    assert all(p.returncode == 0 for p in procs), "\n----\n".join(logs)

@@ -297,6 +297,11 @@ public:
     void push_rows(const CudaBuffer &src, const CudaBuffer &dst, uint32_t n_rows, uint32_t width) const {
         TM_CALL(tm_cuda_push_rows_f32, src.raw(), dst.raw(), n_rows, width);
     }
+    // GEMM whose epilogue writes this rank's rows into every rank's gathered output (include/tm_cuda.h).
+    void q8_0_gemm_mma_push(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &dst, uint32_t rows, uint32_t cols,
+                            uint32_t batch) const {
+        TM_CALL(tm_cuda_q8_0_gemm_mma_push, w.raw(), x.raw(), dst.raw(), rows, cols, batch);
+    }
     void argmax_sharded(const CudaBuffer &x, uint32_t n, uint32_t index_offset, const CudaBuffer &partial,
                         const CudaBuffer &pairs, const CudaBuffer &out, uint32_t base, const CudaBuffer *pos,
                         uint32_t pos_index, uint32_t out_cap, const CudaBuffer *mirror) const {

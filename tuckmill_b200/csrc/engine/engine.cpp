@@ -347,8 +347,12 @@ struct SwiGluBlock {
             gate_up.gemm_part(ctx, 1, s.h2, s.loc2, nn, exact);
             act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
             ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
-            down.gemm_all(ctx, s.g, s.loc, nn, exact);
-            ctx.push_rows(s.loc, s.d2, nn, (uint32_t)(hidden / sh.world));
+            if (exact) {
+                down.gemm_all(ctx, s.g, s.loc, nn, exact);
+                ctx.push_rows(s.loc, s.d2, nn, (uint32_t)(hidden / sh.world));
+            } else {  // multiply and exchange as one kernel
+                ctx.q8_0_gemm_mma_push(down.buf, s.g, s.d2, down.rows, down.cols, nn);
+            }
         } else {
             gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
             gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
@@ -494,8 +498,12 @@ struct AttentionBlock {
                                 nn, (uint32_t)spec.window);
         if (sh.world > 1) {
             ctx.push_rows(s.e, s.efull, nn, heads * hd);
-            o.gemm_all(ctx, s.efull, s.loc, nn, exact);
-            ctx.push_rows(s.loc, s.proj, nn, (uint32_t)(hidden / sh.world));
+            if (exact) {
+                o.gemm_all(ctx, s.efull, s.loc, nn, exact);
+                ctx.push_rows(s.loc, s.proj, nn, (uint32_t)(hidden / sh.world));
+            } else {  // multiply and exchange as one kernel
+                ctx.q8_0_gemm_mma_push(o.buf, s.efull, s.proj, o.rows, o.cols, nn);
+            }
         } else {
             o.gemm_all(ctx, s.e, s.proj, nn, exact);
         }

@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "tm_cuda_internal.cuh"
+#include "tm_cuda_symm.cuh"
 #include "tm_cuda_device.cuh"
 
 namespace {
@@ -130,16 +131,7 @@ __global__ void argmax_pair_kernel(const float *pv, const uint32_t *pi, float *p
 // multicast, no library kernel touching peer memory), the last block of the push
 // raises a per-sender sequence flag on every rank and waits -- bounded -- until
 // every sender's flag on THIS rank has reached the same sequence number.
-constexpr int kSymmMaxWorld = 16;
-constexpr uint32_t kSymmTail = 512;        // u32 flags[16] | u32 seq @64 | u32 block counter @68 | u32 status @72
-constexpr uint32_t kSymmSpinLimit = 1u << 24;
-
-struct symm_state {
-    int world = 1, rank = 0;
-    size_t payload = 0;                    // bytes before the flag tail
-    void *peer[kSymmMaxWorld] = {};        // this buffer on every rank (own entry = local pointer)
-    void **d_peer = nullptr;               // the same table in device memory
-};
+using symm_state = tm_symm_state;
 
 struct push_args {
     const float *src;        // [n_rows][width] local slice
@@ -150,7 +142,7 @@ struct push_args {
 };
 
 __global__ void __launch_bounds__(256) push_rows_kernel(const push_args a) {
-    __shared__ uint32_t s_last, s_seq;
+    __shared__ uint32_t s_flag[2];
     tmdev::pdl_trigger();
     tmdev::pdl_wait();
     const size_t total = (size_t)a.n_rows * a.width;
@@ -175,35 +167,7 @@ __global__ void __launch_bounds__(256) push_rows_kernel(const push_args a) {
     // counts last therefore signals after ALL of this launch's stores.
     __threadfence_system();
     __syncthreads();
-    uint32_t *tail = (uint32_t *)(a.peer[a.rank] + a.tail_off);
-    if (threadIdx.x == 0) {
-        const uint32_t prev = atomicAdd(tail + 68, 1u);
-        s_last = prev == gridDim.x - 1u ? 1u : 0u;
-        if (s_last) {
-            tail[68] = 0u;                 // ready for the next launch
-            s_seq = tail[64] + 1u;
-            tail[64] = s_seq;
-        }
-    }
-    __syncthreads();
-    if (!s_last) return;
-    const uint32_t seq = s_seq;
-    if (threadIdx.x < a.world) {
-        __threadfence_system();
-        uint32_t *remote = (uint32_t *)(a.peer[threadIdx.x] + a.tail_off) + a.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
-        // wait for sender threadIdx.x on this rank; sequence numbers only grow
-        const uint32_t *mine = tail + threadIdx.x;
-        uint32_t spin = 0, v = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-            if ((int32_t)(v - seq) >= 0) break;
-            if (++spin > kSymmSpinLimit) {
-                atomicOr(tail + 72, 1u);   // gave up: the consumer will read stale rows; the host sees the status
-                break;
-            }
-        }
-    }
+    tm_symm_finish(a.peer, a.tail_off, a.world, a.rank, s_flag);
 }
 
 }  // namespace

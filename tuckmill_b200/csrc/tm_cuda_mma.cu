@@ -36,6 +36,7 @@
 
 #include "tm_cuda_internal.cuh"
 #include "tm_cuda_device.cuh"
+#include "tm_cuda_symm.cuh"
 
 namespace {
 
@@ -146,6 +147,11 @@ struct mma_args {
     float *y[3];
     uint32_t part_end[3];  // exclusive row bound of each part (the last one is `rows`)
     uint32_t accumulate;   // 1: Y += W X (the residual add folded into the epilogue)
+    // Row split: the epilogue stores this rank's rows straight into EVERY rank's gathered
+    // Y[t][rank * rows + r] (peer memory, plain stores over NVLink), so the all-gather overlaps the
+    // MMAs of later tiles; the last CTA ends the exchange (tm_symm_finish).  push_world = 0: off.
+    float *const *peer;
+    uint32_t push_world, push_rank, push_off, push_tail;
     uint32_t rows, cols, batch;
     uint32_t *abort_flag;  // set when a bounded wait gave up
 };
@@ -359,7 +365,16 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     // Lane = row: for a fixed token the warp writes 128 contiguous bytes; the addresses
                     // are independent (no add chain between the stores).
                     float *p = ybase + (size_t)t0 * stride;
-                    if (a.accumulate) {
+                    if (a.push_world) {
+                        const size_t wide = (size_t)a.push_world * a.rows;  // token stride of the gathered Y
+                        const size_t at = a.push_off + (size_t)t0 * wide + (size_t)a.push_rank * a.rows + rr;
+                        for (uint32_t pr = 0; pr < a.push_world; ++pr) {
+                            float *q = a.peer[pr] + at;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (t0 + (uint32_t)j < a.batch) q[(size_t)j * wide] = __uint_as_float(v[j]);
+                        }
+                    } else if (a.accumulate) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (t0 + (uint32_t)j < a.batch) p[(size_t)j * stride] += __uint_as_float(v[j]);
@@ -380,6 +395,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty);
         }
+        if (a.push_world) __threadfence_system();  // this thread's peer stores, before the CTA counts itself in
     } else if (warp == kWarpRaw) {
         // ---------------- TMA producer of the raw weight tile ----------------
         if (lane == 0) {
@@ -464,6 +480,10 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0 && *abort_s) atomicOr(a.abort_flag, 1u);
+    if (a.push_world) {
+        __shared__ uint32_t s_flag[2];
+        tm_symm_finish(a.peer, a.push_tail, a.push_world, a.push_rank, s_flag);
+    }
     if (warp == kWarpMma) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::kTmemCols)
@@ -595,8 +615,14 @@ static int mma_ensure_workspace(tm_cuda_ctx *ctx, uint32_t cols, uint32_t batch,
 }
 
 // The GEMM launch proper: the f16 copy of X is already in the workspace.  Called with the context locked.
+struct mma_push {
+    float *const *peer = nullptr;
+    uint32_t world = 0, rank = 0, off = 0, tail = 0;
+};
+
 static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, uint32_t cols, uint32_t batch,
-                      float *const y[3], const uint32_t part_end[3], int accumulate, char *err, size_t err_cap) {
+                      float *const y[3], const uint32_t part_end[3], int accumulate, char *err, size_t err_cap,
+                      const mma_push &push = mma_push()) {
     encode_tiled_fn encode = get_encode_tiled();
     if (!encode)
         return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "the driver does not export cuTensorMapEncodeTiled");
@@ -651,6 +677,11 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
         a.part_end[p] = part_end[p];
     }
     a.accumulate = accumulate ? 1u : 0u;
+    a.peer = push.peer;
+    a.push_world = push.world;
+    a.push_rank = push.rank;
+    a.push_off = push.off;
+    a.push_tail = push.tail;
     a.rows = rows;
     a.cols = cols;
     a.batch = batch;
@@ -742,6 +773,42 @@ int tm_cuda_q8_0_gemm_mma_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buf
             x_prep_f16_kernel<TM_CUDA_PRO_NONE><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
     }
     rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, epilogue == TM_CUDA_EPI_ADD, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    TM_OP_END(2);
+}
+
+int tm_cuda_q8_0_gemm_mma_push(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *dst,
+                               uint32_t rows, uint32_t cols, uint32_t batch, char *err, size_t err_cap) {
+    {
+        const int rc = mma_ensure_workspace(ctx, cols, batch, err, err_cap);
+        if (rc != TM_CUDA_OK) return rc;
+    }
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (batch == 0 || batch > TM_CUDA_GEMM_MMA_MAX_BATCH)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "batch %u outside 1..%u", batch, TM_CUDA_GEMM_MMA_MAX_BATCH);
+    tm_cuda_buffer *root = dst && dst->parent ? dst->parent : dst;
+    if (!dst || ctx->live.find(dst) == ctx->live.end() || !root || !root->symm)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the target is not (a view of) a symmetric buffer of this context");
+    const tm_symm_state *st = (const tm_symm_state *)root->symm;
+    TM_CHECK_BUF(x, (size_t)batch * cols * 4, "activation");
+    TM_CHECK_BUF(dst, (size_t)batch * rows * (size_t)st->world * 4, "gathered output");
+    const size_t dst_off = (size_t)(dst->dev - root->dev);
+    if (dst_off % 16 != 0) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "target view is not 16-byte aligned");
+    TM_OP_BEGIN("q8_0_gemm_mma_push");
+    const size_t n = (size_t)batch * cols;
+    const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
+    x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev, (__half *)ctx->mma_scratch, n);
+    float *const ys[3] = {(float *)dst->dev, nullptr, nullptr};  // unused by the pushing epilogue
+    const uint32_t ends[3] = {rows, rows, rows};
+    mma_push push;
+    push.peer = (float *const *)st->d_peer;
+    push.world = (uint32_t)st->world;
+    push.rank = (uint32_t)st->rank;
+    push.off = (uint32_t)(dst_off / 4);
+    push.tail = (uint32_t)(st->payload / 4);
+    rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, 0, err, err_cap, push);
     if (rc != TM_CUDA_OK) return rc;
     TM_OP_END(2);
 }

@@ -45,6 +45,7 @@ struct gemv_args {
     float *y;               // [M][rows] (token stride = rows)
     const float *pro;       // norm weight [cols] or the `up` operand [M][cols]
     uint32_t rows, cols;
+    uint32_t y_stride;      // floats between the outputs of consecutive tokens (the whole matrix's rows)
     float eps;
     int prologue, epilogue;
     uint32_t plane;         // bytes between digit planes (== 64 mod 128)
@@ -95,9 +96,10 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     // a slot is refilled (with the group kSlots ahead, possibly of the warp's NEXT tile) as soon as it
     // has been consumed -- loads never stop at a tile boundary.  The first kSlots groups are
     // requested before the activations are staged, so both latencies overlap.
-    // kSlots x H is chosen per shape by the host: three slots of two chunks keep the small and
-    // mid-size projections streaming; one slot of four (a plain load / multiply alternation with
-    // wider bursts per row) measured best on the very large ks = 1 matrices.
+    // kSlots x H is chosen per shape by the host: three slots of two chunks keep the short column
+    // ranges of the small projections streaming; one slot of six (a load / multiply alternation with
+    // wide bursts per row: the most bytes in flight two CTAs per SM allow) measured best wherever a
+    // warp streams six chunks or more per tile.
     constexpr int U = kSlots * H;  // chunks in registers
     int4 wa[U], wb[U];
     unsigned short ha[U], hb[U];
@@ -332,7 +334,7 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t row = tile * 16u + g + 8u * h;
                         if (row < rows) {
-                            float *yp = a.y + (size_t)m * rows + row;
+                            float *yp = a.y + (size_t)m * a.y_stride + row;
                             *yp = a.epilogue == TM_CUDA_EPI_ADD ? *yp + acc[m][h] : acc[m][h];
                         }
                     }
@@ -353,7 +355,7 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
                 if (base + tl < n_tiles && row < rows) {
                     float v = 0.0f;
                     for (uint32_t k = 0; k < ks; ++k) v += partial[tl * ks + k][m][r16];
-                    float *yp = a.y + (size_t)m * rows + row;
+                    float *yp = a.y + (size_t)m * a.y_stride + row;
                     *yp = a.epilogue == TM_CUDA_EPI_ADD ? *yp + v : v;
                 }
             }
@@ -379,9 +381,9 @@ uint32_t digit_plane_bytes(uint32_t cols) {
     return pad % 128u == 0 ? pad + 64u : pad;
 }
 
-// One launch for `m` tokens (m in {1,2,4,8}).  The column split comes from
-// the matrix shape alone, so small projections still fill the machine.
-cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
+// One launch for `m` tokens (m in {1,2,4,8}) over a.rows rows.  The column split comes from the
+// matrix shape alone, so small projections still fill the machine.
+cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
     a.plane = digit_plane_bytes(a.cols);
     const size_t smem = (size_t)m * token_smem(a.cols, a.plane);
     const uint32_t n_tiles = (a.rows + 15u) / 16u;
@@ -398,8 +400,39 @@ cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
         case 4: return launch_gemv<4, 2, 2>(ctx, a, (int)ctas, smem);
         case 2: return launch_gemv<2, 2, 2>(ctx, a, (int)ctas, smem);
         default:
-            return ks == 1 ? launch_gemv<1, 1, 4>(ctx, a, (int)ctas, smem) : launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
+            // Measured on the 8B-scale shapes and both lm_heads: one slot of six chunks (the most loads
+            // a warp can hold in flight at two CTAs per SM) wins whenever a warp has at least six chunks
+            // of a tile to stream; shorter column ranges do best with three slots of two.
+            return n_chunks / ks >= 6u ? launch_gemv<1, 1, 6>(ctx, a, (int)ctas, smem)
+                                       : launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
     }
+}
+
+// `m` tokens over the whole matrix.  A very tall matrix whose CTAs (8 row tiles each, no column
+// split) do not fill a whole number of resident waves would spend up to a full CTA time on a nearly
+// empty last wave (151936 rows: 4.01 waves).  Its rows are cut instead: the bulk that fills whole
+// waves keeps ks = 1, the remaining rows go to a second launch that takes its own, much wider
+// column split and slots into the SMs the bulk's last wave frees.  The cut depends on the shape
+// only, so a (row, token) result is still the same for every batch size.
+cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
+    a.y_stride = a.rows;
+    const uint32_t slots = (uint32_t)ctx->sm_count * 2u;       // resident CTAs
+    const uint32_t rows_per_cta = (uint32_t)kWarps * 16u;
+    const uint32_t ctas = (a.rows + rows_per_cta - 1u) / rows_per_cta;
+    const uint32_t rem = ctas % slots;
+    if (ctas > 2u * slots && rem != 0u && rem * 2u < slots) {
+        const uint32_t bulk_rows = (ctas - rem) * rows_per_cta;
+        gemv_args bulk = a, rest = a;
+        bulk.rows = bulk_rows;
+        cudaError_t e = gemv_part(ctx, bulk, m);
+        if (e != cudaSuccess) return e;
+        rest.q = a.q + (size_t)bulk_rows * a.cols;
+        rest.d = a.d + (size_t)bulk_rows * (a.cols / 32u);
+        rest.y = a.y + bulk_rows;
+        rest.rows = a.rows - bulk_rows;
+        return gemv_part(ctx, rest, m);
+    }
+    return gemv_part(ctx, a, m);
 }
 
 // Whole batch in slices of 8/4/2/1 tokens that fit shared memory.

@@ -78,6 +78,9 @@ _OPS = {
     "comm_init": [_P, C.c_void_p, _I, _I],
     "all_gather_f32": [_P, _P, _U32, _P, _U32, _U32],
     "all_gather_rows_f32": [_P, _P, _P, _P, _U32, _U32],
+    "push_rows_f32": [_P, _P, _P, _U32, _U32],
+    "q8_0_gemm_mma_push": [_P, _P, _P, _P, _U32, _U32, _U32],
+    "symm_status": [_P, _P, C.POINTER(C.c_uint32)],
     "q8_0_gemm_mma_fused": [_P, _P, _P, _U32, _U32, _U32, _U32, C.POINTER(C.c_void_p), C.POINTER(C.c_uint32), _I, _P, _F, _I],
     "qk_prep_chunk": [_P] * 9 + [_U32] * 7 + [_F],
     "attention_chunk_mma": [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _U32, _U32],
@@ -106,6 +109,8 @@ def load_library() -> C.CDLL:
     L.tm_cuda_destroy.argtypes = [_P]
     L.tm_cuda_buffer_new.restype = _P
     L.tm_cuda_buffer_new.argtypes = [_P, _SZ, _I] + _ERR
+    L.tm_cuda_symm_alloc.restype = _P
+    L.tm_cuda_symm_alloc.argtypes = [_P, _SZ] + _ERR
     L.tm_cuda_buffer_view.restype = _P
     L.tm_cuda_buffer_view.argtypes = [_P, _P, _SZ, _SZ] + _ERR
     L.tm_cuda_buffer_free.argtypes = [_P, _P]
@@ -412,6 +417,27 @@ class CudaContext:
 
     def all_gather_f32(self, src, src_off, dst, dst_off, count):
         self._call("all_gather_f32", src.handle, src_off, dst.handle, dst_off, count)
+
+    def symm_buffer(self, nbytes: int) -> CudaBuffer:
+        """Collective: the same zeroed allocation on every rank, mapped into every other rank."""
+        err = C.create_string_buffer(512)
+        h = self._l.tm_cuda_symm_alloc(self.handle, nbytes, err, 512)
+        if not h:
+            raise CudaError(-2, err.value.decode())
+        return CudaBuffer(self, h)
+
+    def push_rows_f32(self, src, dst, n_rows, width):
+        """All-gather as a push: dst[t][rank*width + c] on every rank (dst: a symmetric buffer or a view of one)."""
+        self._call("push_rows_f32", src.handle, dst.handle, n_rows, width)
+
+    def q8_0_gemm_mma_push(self, w, x, dst, rows, cols, batch):
+        """The tensor-core GEMM whose epilogue writes this rank's rows into every rank's gathered output."""
+        self._call("q8_0_gemm_mma_push", w.handle, x.handle, dst.handle, rows, cols, batch)
+
+    def symm_status(self, buf) -> int:
+        v = C.c_uint32(0)
+        self._call("symm_status", buf.handle, C.byref(v))
+        return int(v.value)
 
     def all_gather_rows_f32(self, src, stage, dst, n_rows, width):
         self._call("all_gather_rows_f32", src.handle, stage.handle, dst.handle, n_rows, width)

@@ -98,9 +98,15 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     // requested before the activations are staged, so both latencies overlap.
     // kSlots x H is chosen per shape by the host: three slots of two chunks keep the short column
     // ranges of the small projections streaming; one slot of six (a load / multiply alternation with
-    // wide bursts per row: the most bytes in flight two CTAs per SM allow) measured best wherever a
-    // warp streams six chunks or more per tile.
-    constexpr int U = kSlots * H;  // chunks in registers
+    // wide bursts per row: the most bytes in flight the register file allows at two CTAs per SM) is the
+    // register form for long ranges.
+    // kSlots == 0 selects the third form, used for the tall matrices: the stream goes through a
+    // per-warp ring of H chunk slots in SHARED memory filled with cp.async (every lane copies, and
+    // later reads back, its own 16 bytes of rows g and g+8; the chunk's scale pairs ride along as
+    // 4-byte copies).  Bytes in flight then cost no registers: H = 8..12 chunks per warp.
+    constexpr bool kAsync = kSlots == 0;
+    constexpr int U = kAsync ? 1 : kSlots * H;  // chunks in registers
+    constexpr uint32_t kRingSlot = 1024u + 64u;  // 2 x 512 bytes of quants + 16 rows x 2 scales
     int4 wa[U], wb[U];
     unsigned short ha[U], hb[U];
     const uint32_t tile_stride = gridDim.x * tiles_per_cta;
@@ -135,9 +141,40 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     using half0 = std::integral_constant<int, 0>;
     using half1 = std::integral_constant<int, 1>;
     using half2 = std::integral_constant<int, 2>;
-    load_half(half0{});
-    if constexpr (kSlots > 1) load_half(half1{});
-    if constexpr (kSlots > 2) load_half(half2{});
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + (uint32_t)(((size_t)M * tok + 15u) & ~(size_t)15u) +
+                          (uint32_t)warp * (uint32_t)(H > 0 ? H : 1) * kRingSlot;
+    // One chunk of the flat sequence into ring slot `slot` (always commits a group, so exactly H
+    // groups are outstanding at any time and wait_group H-1 means "the oldest has landed").
+    auto async_issue = [&](uint32_t slot) {
+        if (ld_tile < n_tiles) {
+            const uint32_t row_a = min(ld_tile * 16u + g, rows - 1u), row_b = min(ld_tile * 16u + g + 8u, rows - 1u);
+            const uint32_t dst = ring + slot * kRingSlot;
+            const size_t col = (size_t)ld_ch * kChunkCols + t4 * 16u;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)lane * 16u),
+                         "l"(a.q + (size_t)row_a * cols + col) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512u + (uint32_t)lane * 16u),
+                         "l"(a.q + (size_t)row_b * cols + col) : "memory");
+            if (t4 < 2) {  // the two block scales of this chunk for row g (t4 = 0) / g + 8 (t4 = 1)
+                const uint32_t r16 = (uint32_t)g + 8u * (uint32_t)t4;
+                const unsigned short *sp = (const unsigned short *)a.d + (size_t)(t4 == 0 ? row_a : row_b) * nb + ld_ch * 2u;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 1024u + r16 * 4u), "l"(sp) : "memory");
+            }
+            ld_ch += ks;
+            if (ld_ch >= n_chunks) {
+                ld_ch = my_ks;
+                ld_tile += tile_stride;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if constexpr (kAsync) {
+#pragma unroll
+        for (int i = 0; i < H; ++i) async_issue((uint32_t)i);
+    } else {
+        load_half(half0{});
+        if constexpr (kSlots > 1) load_half(half1{});
+        if constexpr (kSlots > 2) load_half(half2{});
+    }
     if (ld_tile < n_tiles) {  // the groups after those: towards L2
         const uint32_t row_a = min(ld_tile * 16u + g, rows - 1u), row_b = min(ld_tile * 16u + g + 8u, rows - 1u);
 #pragma unroll
@@ -304,7 +341,43 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m][0] = acc[m][1] = 0.0f;
 
-        if (tile_ok) {
+        if constexpr (kAsync) {
+            if (tile_ok) {
+#pragma unroll 1
+                for (uint32_t ch = my_ks; ch < n_chunks; ch += ks) {
+                    asm volatile("cp.async.wait_group %0;" ::"n"(H > 0 ? H - 1 : 0) : "memory");
+                    __syncwarp();  // the scale pairs were copied by other lanes
+                    const uint32_t src = ring + cur_half * kRingSlot;
+                    int4 qa, qb;
+                    unsigned short sa16, sb16;
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(qa.x), "=r"(qa.y), "=r"(qa.z), "=r"(qa.w) : "r"(src + (uint32_t)lane * 16u));
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(qb.x), "=r"(qb.y), "=r"(qb.z), "=r"(qb.w) : "r"(src + 512u + (uint32_t)lane * 16u));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sa16) : "r"(src + 1024u + (uint32_t)g * 4u + (uint32_t)(t4 >> 1) * 2u));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sb16) : "r"(src + 1024u + (uint32_t)(g + 8) * 4u + (uint32_t)(t4 >> 1) * 2u));
+                    const uint32_t c0 = ch * kChunkCols + t4 * 16u;
+                    const float da = __half2float(__ushort_as_half(sa16));
+                    const float db = __half2float(__ushort_as_half(sb16));
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const unsigned char *tokp = smem + (size_t)m * tok;
+                        int4 bx = make_int4(0, 0, 0, 0);
+                        if (b_live) bx = *(const int4 *)(tokp + (size_t)(g & 3) * plane + c0);
+                        int dd[4] = {0, 0, 0, 0};
+                        mma_s8(dd, qa.x, qb.x, qa.y, qb.y, bx.x, bx.y);
+                        mma_s8(dd, qa.z, qb.z, qa.w, qb.w, bx.z, bx.w);
+                        const float2 cx = *(const float2 *)(tokp + 4u * (size_t)plane +
+                                                            ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
+                        const float va = fmaf((float)dd[1], cx.y, (float)dd[0] * cx.x);
+                        const float vb = fmaf((float)dd[3], cx.y, (float)dd[2] * cx.x);
+                        acc[m][0] = fmaf(da, va, acc[m][0]);
+                        acc[m][1] = fmaf(db, vb, acc[m][1]);
+                    }
+                    __syncwarp();  // every lane has read the slot before it is refilled
+                    async_issue(cur_half);
+                    cur_half = cur_half + 1u == (uint32_t)H ? 0u : cur_half + 1u;
+                }
+            }
+        } else if (tile_ok) {
 #pragma unroll 1
             for (uint32_t ch0 = my_ks; ch0 < n_chunks; ch0 += ks * H) {
                 if (cur_half == 0 || kSlots == 1) multiply_half(half0{}, ch0, acc);
@@ -400,11 +473,19 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
         case 4: return launch_gemv<4, 2, 2>(ctx, a, (int)ctas, smem);
         case 2: return launch_gemv<2, 2, 2>(ctx, a, (int)ctas, smem);
         default:
-            // Measured on the 8B-scale shapes and both lm_heads: one slot of six chunks (the most loads
-            // a warp can hold in flight at two CTAs per SM) wins whenever a warp has at least six chunks
-            // of a tile to stream; shorter column ranges do best with three slots of two.
-            return n_chunks / ks >= 6u ? launch_gemv<1, 1, 6>(ctx, a, (int)ctas, smem)
-                                       : launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
+            // Measured on the 8B-scale shapes and both lm_heads (same-box A/B): wherever a warp streams at
+            // least six chunks per tile the shared-memory ring of eight chunks wins (64 registers, three
+            // CTAs per SM, 192 KB of loads in flight per SM); it needs whole 64-column chunks, otherwise
+            // one register slot of six chunks is next best; short column ranges do best with three
+            // slots of two.
+            if (n_chunks / ks >= 6u) {
+                constexpr int kRingDepth = 8;
+                const size_t total = ((smem + 15u) & ~(size_t)15u) + (size_t)kWarps * kRingDepth * 1088u;
+                if (a.cols % 64u == 0u && total <= ctx->smem_optin - 8192u)
+                    return launch_gemv<1, 0, kRingDepth>(ctx, a, (int)ctas, total);
+                return launch_gemv<1, 1, 6>(ctx, a, (int)ctas, smem);
+            }
+            return launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
     }
 }
 

@@ -497,7 +497,19 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
 // only, so a (row, token) result is still the same for every batch size.
 cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
     a.y_stride = a.rows;
-    const uint32_t slots = (uint32_t)ctx->sm_count * 2u;       // resident CTAs
+    // Resident CTAs per SM of the form gemv_part will pick for a tall matrix: the register forms fit
+    // two; the shared-memory ring is limited by its shared memory (staged activations + 8 warps x 8
+    // slots + 1 KB the system reserves per CTA), at most four by registers.
+    uint32_t per_sm = 2u;
+    if (m == 1 && a.cols % 64u == 0u) {
+        const size_t cta = (((size_t)token_smem(a.cols, digit_plane_bytes(a.cols)) + 15u) & ~(size_t)15u) +
+                           (size_t)kWarps * 8u * 1088u + 1024u;
+        if (cta - 1024u <= ctx->smem_optin - 8192u) {
+            const size_t fit = (228u * 1024u) / cta;
+            per_sm = (uint32_t)(fit > 4u ? 4u : fit < 1u ? 1u : fit);
+        }
+    }
+    const uint32_t slots = (uint32_t)ctx->sm_count * per_sm;   // resident CTAs
     const uint32_t rows_per_cta = (uint32_t)kWarps * 16u;
     const uint32_t ctas = (a.rows + rows_per_cta - 1u) / rows_per_cta;
     const uint32_t rem = ctas % slots;

@@ -41,6 +41,7 @@ from tuckmill_b200 import testing as T  # noqa: E402
 WORKLOADS = {
     "qwen3-0.6b": (T.QWEN3_0_6B, 512, 256),
     "gemma3-1b": (T.GEMMA3_1B, 512, 256),
+    "qwen3-8b": (T.QWEN3_8B, 2048, 256),  # one sequence of the 8-GPU configuration's model (8.7 GB of Q8_0)
     "tiny-qwen3": (T.TINY_QWEN3, 32, 16),
 }
 METRIC = "q8_0_decode_tok_s"
@@ -74,26 +75,32 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+        self.index, self.samples, self._p, self._t = index, [], None, None
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-                self.samples.append([c.strip() for c in out.strip().split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.2)
+        for line in self._p.stdout:  # one line every 100 ms until the process is ended
+            self.samples.append([c.strip() for c in line.strip().split(",")])
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        try:
+            self._p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                        "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                       stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+            time.sleep(0.3)  # the first sample is there before the timed region starts
+        except OSError:
+            self._p = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        self._t.join(timeout=6)
+        if self._p is not None:
+            self._p.terminate()  # this process only
+            try:
+                self._p.wait(timeout=3)
+            except subprocess.TimeoutExpired:
+                self._p.kill()
+            self._t.join(timeout=3)
 
     def summary(self):
         mhz, mx, reasons = [], [], set()

@@ -454,6 +454,18 @@ uint32_t digit_plane_bytes(uint32_t cols) {
     return pad % 128u == 0 ? pad + 64u : pad;
 }
 
+// Resident CTAs per SM of the form the launcher picks for long column ranges: the register forms
+// fit two; the shared-memory ring is limited by its shared memory (staged activations + 8 warps x 8
+// slots + 1 KB the system reserves per CTA), at most four by registers.
+uint32_t resident_ctas_per_sm(const tm_cuda_ctx *ctx, uint32_t cols, int m) {
+    if (m != 1 || cols % 64u != 0u) return 2u;
+    const size_t cta = (((size_t)token_smem(cols, digit_plane_bytes(cols)) + 15u) & ~(size_t)15u) +
+                       (size_t)kWarps * 8u * 1088u + 1024u;
+    if (cta - 1024u > ctx->smem_optin - 8192u) return 2u;
+    const size_t fit = (228u * 1024u) / cta;
+    return (uint32_t)(fit > 4u ? 4u : fit < 1u ? 1u : fit);
+}
+
 // One launch for `m` tokens (m in {1,2,4,8}) over a.rows rows.  The column split comes from the
 // matrix shape alone, so small projections still fill the machine.
 cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
@@ -461,7 +473,9 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
     const size_t smem = (size_t)m * token_smem(a.cols, a.plane);
     const uint32_t n_tiles = (a.rows + 15u) / 16u;
     const uint32_t n_chunks = (a.cols + kChunkCols - 1u) / kChunkCols;
-    const uint32_t want = (uint32_t)ctx->sm_count * 2u * kWarps;  // warps of one resident wave (2 CTAs per SM)
+    // warps of one resident wave: the column split grows only while the grid stays within it
+    // (taken from the one-token form whatever m is: the split must depend on the shape alone)
+    const uint32_t want = (uint32_t)ctx->sm_count * resident_ctas_per_sm(ctx, a.cols, 1) * kWarps;
     uint32_t ks = 1;
     while (ks < (uint32_t)kWarps && n_tiles * ks * 2u <= want && ks * 2u <= n_chunks) ks <<= 1;
     a.ks = ks;
@@ -479,10 +493,18 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
             // one register slot of six chunks is next best; short column ranges do best with three
             // slots of two.
             if (n_chunks / ks >= 6u) {
-                constexpr int kRingDepth = 8;
-                const size_t total = ((smem + 15u) & ~(size_t)15u) + (size_t)kWarps * kRingDepth * 1088u;
-                if (a.cols % 64u == 0u && total <= ctx->smem_optin - 8192u)
-                    return launch_gemv<1, 0, kRingDepth>(ctx, a, (int)ctas, total);
+                // Ring depth: 8 chunks per warp leaves room for three CTAs per SM; a grid that puts at
+                // most one CTA on an SM anyway (the mid-size projections) takes the deepest ring that
+                // fits instead, so that its few warps still keep enough bytes in flight.
+                const size_t base = (smem + 15u) & ~(size_t)15u, budget = ctx->smem_optin - 8192u;
+                auto ring_bytes = [&](int depth) { return base + (size_t)kWarps * (size_t)depth * 1088u; };
+                if (a.cols % 64u == 0u && ring_bytes(8) <= budget) {
+                    if (ctas <= (uint32_t)ctx->sm_count && n_chunks / ks >= 24u && ring_bytes(24) <= budget)
+                        return launch_gemv<1, 0, 24>(ctx, a, (int)ctas, ring_bytes(24));
+                    if (ctas <= (uint32_t)ctx->sm_count && n_chunks / ks >= 16u && ring_bytes(16) <= budget)
+                        return launch_gemv<1, 0, 16>(ctx, a, (int)ctas, ring_bytes(16));
+                    return launch_gemv<1, 0, 8>(ctx, a, (int)ctas, ring_bytes(8));
+                }
                 return launch_gemv<1, 1, 6>(ctx, a, (int)ctas, smem);
             }
             return launch_gemv<1, 3, 2>(ctx, a, (int)ctas, smem);
@@ -497,18 +519,7 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
 // only, so a (row, token) result is still the same for every batch size.
 cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
     a.y_stride = a.rows;
-    // Resident CTAs per SM of the form gemv_part will pick for a tall matrix: the register forms fit
-    // two; the shared-memory ring is limited by its shared memory (staged activations + 8 warps x 8
-    // slots + 1 KB the system reserves per CTA), at most four by registers.
-    uint32_t per_sm = 2u;
-    if (m == 1 && a.cols % 64u == 0u) {
-        const size_t cta = (((size_t)token_smem(a.cols, digit_plane_bytes(a.cols)) + 15u) & ~(size_t)15u) +
-                           (size_t)kWarps * 8u * 1088u + 1024u;
-        if (cta - 1024u <= ctx->smem_optin - 8192u) {
-            const size_t fit = (228u * 1024u) / cta;
-            per_sm = (uint32_t)(fit > 4u ? 4u : fit < 1u ? 1u : fit);
-        }
-    }
+    const uint32_t per_sm = resident_ctas_per_sm(ctx, a.cols, 1);  // shape only, like the column split
     const uint32_t slots = (uint32_t)ctx->sm_count * per_sm;   // resident CTAs
     const uint32_t rows_per_cta = (uint32_t)kWarps * 16u;
     const uint32_t ctas = (a.rows + rows_per_cta - 1u) / rows_per_cta;

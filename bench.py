@@ -288,7 +288,9 @@ def run_cuda(args):
         dist.barrier()
     path = artifact(args.workload, args.seed)
     context = prompt_n + decode_n + 16
-    eng = E.Engine(path, context=context, device=local)
+    # 8B-scale projections want wider prefill chunks (the GEMM reaches its rate from M = 2048)
+    prefill_batch = 2048 if shape.hidden >= 4096 else 0
+    eng = E.Engine(path, context=context, device=local, prefill_batch=prefill_batch)
     stream = torch.cuda.ExternalStream(eng.stream(), device=local)
     prompt = T.token_ids(args.seed + 1000 * rank, prompt_n, shape.vocab)
     hbm_gbs, peak_kind = measured_peaks()
@@ -372,6 +374,7 @@ def run_cuda(args):
             "data": "synthetic",
             "config": {"workload": args.workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1,
                        "kv": "f16", "weights": "Q8_0 random-init, seed %d" % args.seed,
+                       "prefill_chunk": prefill_batch or 512,
                        "parallelism": f"replicas x{world}" if world > 1 else "single",
                        "l2": "per-token weight stream %.0f MB exceeds the 126 MB L2" % (step_bytes / 1e6)},
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
@@ -412,7 +415,7 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
         ident.copy_(torch.frombuffer(bytearray(E.comm_id()), dtype=torch.uint8))
     dist.broadcast(ident, 0)
     eng = E.Engine(path, context=context, device=local, shard_rank=rank, shard_world=world,
-                   comm_id=bytes(ident.cpu().numpy().tobytes()))
+                   comm_id=bytes(ident.cpu().numpy().tobytes()), prefill_batch=2048 if shape.hidden >= 4096 else 0)
     stream = torch.cuda.ExternalStream(eng.stream(), device=local)
     prompt = T.token_ids(args.seed, prompt_n, shape.vocab)  # rank 0's prompt of the replica arm, on every rank
 

@@ -359,6 +359,10 @@ def run_cuda(args):
     if rank == 0:
         roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens)
         roof["lm_head"] = lm_head_roofline(local, shape, hbm_gbs, torch)
+        if args.workload == "qwen3-0.6b":
+            # dram__bytes_read.sum + dram__bytes_write.sum of this launch in the committed ncu capture
+            roof["lm_head"]["traffic"] = 164954112 + 7096576
+            roof["lm_head"]["traffic_source"] = "profiles/q8_gemv_lm_head.md (one ncu capture of the same shape)"
         roof["copy_gbs_this_gpu"] = copy_bandwidth(torch, local)
         roof["lm_head"]["frac_of_this_gpu_copy"] = roof["lm_head"]["achieved"] / roof["copy_gbs_this_gpu"]
         roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"

@@ -292,11 +292,18 @@ __global__ void __launch_bounds__(256) qk_prep_chunk_kernel(float *q, const floa
         const bool first = e < half, second = e >= half && e < n_rot;
         const uint32_t pe = first ? e + half : e - half;
         float partner = 0.0f;
-        // the partner lives at register (pe / 32) of lane (pe % 32); half % 32 == 0 keeps it in this lane
+        // the partner lives at register (pe / 32) of lane (pe % 32); when half the rotated width is a
+        // multiple of 32 (head sizes 64 and up, fully rotated) that is this lane: no shuffles
+        if ((half & 31u) == 0u) {
 #pragma unroll
-        for (int rr = 0; rr < kMax; ++rr) {
-            const float cand = __shfl_sync(0xffffffffu, x[rr], (int)(pe & 31u));
-            if ((first || second) && (uint32_t)rr == (pe >> 5)) partner = cand;
+            for (int rr = 0; rr < kMax; ++rr)
+                if ((first || second) && (uint32_t)rr == (pe >> 5)) partner = x[rr];
+        } else {
+#pragma unroll
+            for (int rr = 0; rr < kMax; ++rr) {
+                const float cand = __shfl_sync(0xffffffffu, x[rr], (int)(pe & 31u));
+                if ((first || second) && (uint32_t)rr == (pe >> 5)) partner = cand;
+            }
         }
         if (first || second) {
             const uint32_t i = first ? e : e - half;

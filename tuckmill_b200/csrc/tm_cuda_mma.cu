@@ -377,18 +377,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     } else if (a.accumulate) {
                         // all 32 loads first: a load after a store to the same array cannot be hoisted by
                         // the compiler, and 32 dependent round trips cost more than the tile's main loop
-                        // (four groups of 8 keep the epilogue inside its register budget)
+                        float old[32];
 #pragma unroll
-                        for (int h = 0; h < 4; ++h) {
-                            float old[8];
+                        for (int j = 0; j < 32; ++j)
+                            old[j] = t0 + (uint32_t)j < a.batch ? __ldcg(p + (size_t)j * stride) : 0.0f;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                old[j] = t0 + (uint32_t)(8 * h + j) < a.batch ? __ldcg(p + (size_t)(8 * h + j) * stride) : 0.0f;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (t0 + (uint32_t)(8 * h + j) < a.batch)
-                                    p[(size_t)(8 * h + j) * stride] = old[j] + __uint_as_float(v[8 * h + j]);
-                        }
+                        for (int j = 0; j < 32; ++j)
+                            if (t0 + (uint32_t)j < a.batch) p[(size_t)j * stride] = old[j] + __uint_as_float(v[j]);
                     } else if (t0 + 32u <= a.batch) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) p[(size_t)j * stride] = __uint_as_float(v[j]);

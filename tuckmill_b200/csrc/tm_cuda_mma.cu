@@ -531,12 +531,22 @@ __global__ void __launch_bounds__(256) x_prep_f16_kernel(const float *x, const f
         for (int w = 0; w < 8; ++w) tot += red[w];
         inv = 1.0f / sqrtf(tot / (float)cols + eps);
     }
-    for (uint32_t c = threadIdx.x; c < cols; c += 256) {
-        float v = xr[c];
-        if (PRO == TM_CUDA_PRO_RMSNORM) v = v * inv * pro[c];
-        else if (PRO == TM_CUDA_PRO_SILU_MUL) v = tmdev::silu_f(v) * pro[(size_t)blockIdx.x * cols + c];
-        else if (PRO == TM_CUDA_PRO_GELU_MUL) v = tmdev::gelu_tanh_f(v) * pro[(size_t)blockIdx.x * cols + c];
-        orow[c] = __float2half_rn(v);
+    const float *pr = PRO == TM_CUDA_PRO_RMSNORM ? pro : PRO == TM_CUDA_PRO_NONE ? xr : pro + (size_t)blockIdx.x * cols;
+    auto one = [&](float v, float p) -> float {
+        if (PRO == TM_CUDA_PRO_RMSNORM) return v * inv * p;
+        if (PRO == TM_CUDA_PRO_SILU_MUL) return tmdev::silu_f(v) * p;
+        if (PRO == TM_CUDA_PRO_GELU_MUL) return tmdev::gelu_tanh_f(v) * p;
+        return v;
+    };
+    if ((cols & 3u) == 0u && ((((size_t)xr) | ((size_t)pr) | ((size_t)orow << 1)) & 15u) == 0u) {
+        for (uint32_t c = threadIdx.x * 4u; c < cols; c += 1024u) {  // four columns per thread and trip
+            const float4 v = *(const float4 *)(xr + c), p = *(const float4 *)(pr + c);
+            const __half2 lo = __floats2half2_rn(one(v.x, p.x), one(v.y, p.y));
+            const __half2 hi = __floats2half2_rn(one(v.z, p.z), one(v.w, p.w));
+            *(uint2 *)(orow + c) = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < cols; c += 256) orow[c] = __float2half_rn(one(xr[c], pr[c]));
     }
 }
 

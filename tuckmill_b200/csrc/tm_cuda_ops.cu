@@ -586,6 +586,23 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     }
     tmdev::pdl_trigger();
     tmdev::pdl_wait();
+    // The first vector this warp will normalise (q_warp, or k for warp G) does not depend on the
+    // position: its loads are issued together with the position's, one memory trip instead of two.
+    constexpr int EPL0 = HD / 32;
+    float x0[EPL0], w0[EPL0], v0[EPL0], f0[EPL0 / 2];
+    {
+        const bool pre_k = warp == G;
+        const float *src = pre_k ? k + (size_t)blockIdx.x * HD : q + ((size_t)blockIdx.x * G + (warp < G ? warp : 0)) * HD;
+        const float *nw = pre_k ? k_norm : q_norm;
+#pragma unroll
+        for (int r = 0; r < EPL0; ++r) {
+            x0[r] = src[lane + 32 * r];
+            w0[r] = nw[lane + 32 * r];
+            v0[r] = pre_k ? v[(size_t)blockIdx.x * HD + lane + 32 * r] : 0.0f;
+        }
+#pragma unroll
+        for (int r = 0; r < EPL0 / 2; ++r) f0[r] = inv_freq[lane + 32 * r];
+    }
     const uint32_t pos = *pos_p;
     if (pos >= cap) {
         if (tid == 0 && split == 0 && kvh == 0) atomicOr(status, 1u);
@@ -603,10 +620,11 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
         const float *src = is_k ? k + (size_t)kvh * HD : q + ((size_t)kvh * G + vec) * HD;
         const float *nw = is_k ? k_norm : q_norm;
         float x[EPL], w[EPL];
+        const bool preloaded = vec == warp;  // the loop's first trip: the values are already here
 #pragma unroll
         for (int r = 0; r < EPL; ++r) {
-            x[r] = src[lane + 32 * r];
-            w[r] = nw[lane + 32 * r];
+            x[r] = preloaded ? x0[r] : src[lane + 32 * r];
+            w[r] = preloaded ? w0[r] : nw[lane + 32 * r];
         }
         float ss = 0.0f;
 #pragma unroll
@@ -621,7 +639,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
 #pragma unroll
         for (int r = 0; r < EPL / 2; ++r) {
             float sn, cs;
-            sincosf((float)pos * inv_freq[lane + 32 * r], &sn, &cs);
+            sincosf((float)pos * f0[r], &sn, &cs);
             const float a0 = x[r], b0 = x[r + EPL / 2];
             x[r] = a0 * cs - b0 * sn;
             x[r + EPL / 2] = a0 * sn + b0 * cs;
@@ -631,7 +649,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
 #pragma unroll
             for (int r = 0; r < EPL; ++r) {
                 const uint32_t e = lane + 32 * r;
-                const __half hk = __float2half_rn(x[r]), hv = __float2half_rn(vsrc[e]);
+                const __half hk = __float2half_rn(x[r]), hv = __float2half_rn(preloaded ? v0[r] : vsrc[e]);
                 kh[e] = hk;
                 vh[e] = hv;
                 kc[((size_t)kvh * cap + pos) * HD + e] = hk;

@@ -584,6 +584,17 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
             asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(vp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
         }
     }
+    // This thread's half of key row split*64 + tid/2: written by an earlier step's kernel (or is a row past
+    // the sequence, masked below; or the current position's row, replaced below by the fresh one), so it
+    // is read before the predecessor finishes.
+    constexpr int NL0 = HD / 16;  // 16-byte loads per thread
+    int4 kraw[NL0];
+    {
+        const uint32_t j = min(split * kFastSplit + ((uint32_t)tid >> 1), cap - 1u);
+        const __half *kr = kp + (size_t)j * HD + (tid & 1) * (HD / 2);
+#pragma unroll
+        for (int c = 0; c < NL0; ++c) kraw[c] = *(const int4 *)(kr + c * 8);
+    }
     tmdev::pdl_trigger();
     tmdev::pdl_wait();
     // The first vector this warp will normalise (q_warp, or k for warp G) does not depend on the
@@ -669,11 +680,11 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
 #pragma unroll
         for (int g = 0; g < G; ++g) dot[g][0] = dot[g][1] = 0.0f;
         if (valid) {
-            const __half *kr = (owns_new && j == pos ? kh : kp + (size_t)j * HD) + hsel * (HD / 2);
             constexpr int NL = HD / 16;  // 16-byte loads per thread
             int4 raw[NL];
+            const bool fresh = owns_new && j == pos;  // this step's own key: from shared memory
 #pragma unroll
-            for (int c = 0; c < NL; ++c) raw[c] = *(const int4 *)(kr + c * 8);
+            for (int c = 0; c < NL; ++c) raw[c] = fresh ? *(const int4 *)(kh + hsel * (HD / 2) + c * 8) : kraw[c];
 #pragma unroll
             for (int c = 0; c < NL; ++c) {
                 const __half2 *h2 = (const __half2 *)&raw[c];

@@ -108,6 +108,11 @@ int tm_cuda_argmax_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cuda_
 int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *weight,
                         tm_cuda_buffer *y, uint32_t rows, uint32_t cols, float eps, char *err,
                         size_t err_cap);
+/* No counterpart: x[row] += rmsnorm(p[row]) * weight, i.e. tm_cuda_rmsnorm_f32 followed by
+ * tm_cuda_f32_axpy(alpha = 1) as one launch, bit for bit (the output norm plus residual add of
+ * Gemma-style layers). */
+int tm_cuda_rmsnorm_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *p, tm_cuda_buffer *weight, tm_cuda_buffer *x,
+                            uint32_t rows, uint32_t cols, float eps, char *err, size_t err_cap);
 /* tm_metal.h:202 tm_metal_silu_mul_f32 / :206 tm_metal_gelu_tanh_mul_f32. */
 int tm_cuda_silu_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_buffer *up,
                          tm_cuda_buffer *out, uint32_t n, char *err, size_t err_cap);

@@ -338,3 +338,19 @@ def test_tensor_core_chunk_attention_within_tolerance(ctx, oracle, heads, kvh, h
         for h in (0, heads - 1):
             cpu = oracle.attend_head(q[t, h], k32[h // group], v32[h // group], start, seq, scale)
             assert rel_err(got[t, h], cpu) <= 3e-3
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1152), (7, 1024), (300, 640), (3, 4097)])
+def test_rmsnorm_add_equals_rmsnorm_then_axpy(ctx, rows, cols):
+    """The fused output norm + residual add is the two launches it replaces, bit for bit."""
+    p = T.activations(5, 1, rows * cols)
+    x = T.activations(5, 2, rows * cols)
+    w = (1 + 0.1 * T.activations(5, 3, cols)).astype(np.float32)
+    wb = ctx.floats(w)
+    pa, xa = ctx.floats(p), ctx.floats(x)
+    ctx.rmsnorm(pa, wb, pa, rows, cols, 1e-6)
+    ctx.f32_axpy(pa, xa, 1.0, rows * cols)
+    pb, xb = ctx.floats(p), ctx.floats(x)
+    ctx.rmsnorm_add(pb, wb, xb, rows, cols, 1e-6)
+    np.testing.assert_array_equal(f32(xb, rows * cols), f32(xa, rows * cols))
+    np.testing.assert_array_equal(f32(pb, rows * cols), p)  # the input is left alone

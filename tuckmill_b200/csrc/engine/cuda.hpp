@@ -222,6 +222,10 @@ public:
         TM_CALL(tm_cuda_row_indirect_f32_dev, w.raw(), rows, cols, ids.raw(), base, pos.raw(), pos_index, bias,
                 scale, out.raw());
     }
+    void rmsnorm_add(const CudaBuffer &p, const CudaBuffer &w, const CudaBuffer &x, uint32_t rows, uint32_t cols,
+                     float eps) const {
+        TM_CALL(tm_cuda_rmsnorm_add_f32, p.raw(), w.raw(), x.raw(), rows, cols, eps);
+    }
     void rmsnorm(const CudaBuffer &x, const CudaBuffer &w, const CudaBuffer &y, uint32_t rows, uint32_t cols,
                  float eps) const {
         TM_CALL(tm_cuda_rmsnorm_f32, x.raw(), w.raw(), y.raw(), rows, cols, eps);

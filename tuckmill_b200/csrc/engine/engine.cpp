@@ -306,15 +306,14 @@ struct SwiGluBlock {
             ctx.push_rows(g_view, h_full, 1, (uint32_t)wl);
             ctx.q8_0_gemv(down.buf, h_full, out_local, down.rows, down.cols);
             ctx.push_rows(out_local, out, 1, (uint32_t)(hidden / sh.world));
-            if (out_norm) ctx.rmsnorm(out, out_norm, out, 1, (uint32_t)hidden, eps);
-            ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
+            if (out_norm) ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
+            else ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
             return;
         }
         const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
         if (out_norm) {
             ctx.q8_0_gemv_fused(down.buf, g_view, out, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
-            ctx.rmsnorm(out, out_norm, out, 1, (uint32_t)hidden, eps);
-            ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
+            ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
         } else {
             ctx.q8_0_gemv_fused(down.buf, g_view, x, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_ADD);
         }
@@ -332,8 +331,7 @@ struct SwiGluBlock {
         if (out_norm) {
             ctx.q8_0_gemm_mma_fused(down.buf, s.g, down.rows, down.cols, nn, {&s.d2}, {down.rows}, pro, &s.u, 0.0f,
                                     TM_CUDA_EPI_STORE);
-            ctx.rmsnorm(s.d2, out_norm, s.d2, nn, (uint32_t)hidden, eps);
-            ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+            ctx.rmsnorm_add(s.d2, out_norm, s.x, nn, (uint32_t)hidden, eps);
         } else {
             ctx.q8_0_gemm_mma_fused(down.buf, s.g, down.rows, down.cols, nn, {&s.x}, {down.rows}, pro, &s.u, 0.0f,
                                     TM_CUDA_EPI_ADD);
@@ -359,8 +357,8 @@ struct SwiGluBlock {
             act_mul(ctx, s.g, s.u, (uint32_t)(n * width));
             down.gemm_all(ctx, s.g, s.d2, nn, exact);
         }
-        if (out_norm) ctx.rmsnorm(s.d2, out_norm, s.d2, nn, (uint32_t)hidden, eps);
-        ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+        if (out_norm) ctx.rmsnorm_add(s.d2, out_norm, s.x, nn, (uint32_t)hidden, eps);
+        else ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
     }
 };
 
@@ -541,8 +539,8 @@ struct Layer {
         if (mixer.sh.world > 1 || mixer_out_norm) {
             if (mixer.sh.world > 1) mixer.project_sharded(ctx, proj, hidden);
             else ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
-            if (mixer_out_norm) ctx.rmsnorm(proj, mixer_out_norm, proj, 1, (uint32_t)hidden, eps);
-            ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
+            if (mixer_out_norm) ctx.rmsnorm_add(proj, mixer_out_norm, x, 1, (uint32_t)hidden, eps);
+            else ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
         } else {
             ctx.q8_0_gemv_fused(mixer.o.buf, mixer.attn, x, mixer.o.rows, mixer.o.cols, TM_CUDA_PRO_NONE, nullptr, 0.0f,
                                 TM_CUDA_EPI_ADD);
@@ -556,8 +554,7 @@ struct Layer {
             mixer.prefill_fused(ctx, s, n, pos0, pre_norm);
             if (mixer_out_norm) {
                 mixer.o.gemm_all(ctx, s.e, s.proj, nn, false);
-                ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
-                ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+                ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
             } else {
                 ctx.q8_0_gemm_mma_fused(mixer.o.buf, s.e, mixer.o.rows, mixer.o.cols, nn, {&s.x}, {mixer.o.rows},
                                         TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_ADD);
@@ -567,8 +564,8 @@ struct Layer {
         }
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
         mixer.prefill(ctx, s, n, pos0, hidden, exact);
-        if (mixer_out_norm) ctx.rmsnorm(s.proj, mixer_out_norm, s.proj, nn, (uint32_t)hidden, eps);
-        ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+        if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
+        else ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
         ctx.rmsnorm(s.x, post_norm, s.h2, nn, (uint32_t)hidden, eps);
         ffn.prefill(ctx, s, n, hidden, exact);
     }

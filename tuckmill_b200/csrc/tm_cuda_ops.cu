@@ -70,6 +70,22 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const float *x, const
     for (uint32_t i = threadIdx.x; i < cols; i += kThreads) yr[i] = xr[i] * inv * w[i];
 }
 
+// x[row] += p[row] * rsqrt(mean(p^2) + eps) * w: the output norm and the residual add of a layer as one
+// launch, rounded exactly like rmsnorm_kernel followed by axpy_kernel(alpha = 1): the product is
+// formed with two multiplies and added with one rounding.
+__global__ void __launch_bounds__(kThreads) rmsnorm_add_kernel(const float *p, const float *w, float *x,
+                                                               uint32_t cols, float eps) {
+    __shared__ float red[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const float *pr = p + (size_t)blockIdx.x * cols;
+    float *xr = x + (size_t)blockIdx.x * cols;
+    const float ss = tmdev::block_sumsq(pr, cols, red);
+    const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
+    for (uint32_t i = threadIdx.x; i < cols; i += kThreads)
+        xr[i] = __fadd_rn(xr[i], __fmul_rn(__fmul_rn(pr[i], inv), w[i]));
+}
+
 // ---- greedy argmax (crates/backend/src/sampling.rs:68-82) -------------------
 __device__ __forceinline__ bool better(float av, uint32_t ai, float bv, uint32_t bi) {
     if (ai == kArgmaxNone) return false;
@@ -1009,6 +1025,21 @@ int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *wei
     TM_OP_BEGIN("rmsnorm");
     TM_CUDA_TRY(tm_launch_pdl(ctx, rmsnorm_kernel, dim3(rows), dim3(kThreads), 0, (const float *)x->dev,
                               (const float *)weight->dev, (float *)y->dev, cols, eps));
+    TM_OP_END(1);
+}
+
+int tm_cuda_rmsnorm_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *p, tm_cuda_buffer *weight, tm_cuda_buffer *x,
+                            uint32_t rows, uint32_t cols, float eps, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (rows == 0 || cols == 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "rmsnorm geometry %u x %u", rows, cols);
+    TM_CHECK_BUF(p, (size_t)rows * cols * 4, "p");
+    TM_CHECK_BUF(x, (size_t)rows * cols * 4, "x");
+    TM_CHECK_BUF(weight, (size_t)cols * 4, "norm weight");
+    if (p == x) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "rmsnorm_add in place");
+    TM_OP_BEGIN("rmsnorm_add");
+    TM_CUDA_TRY(tm_launch_pdl(ctx, rmsnorm_add_kernel, dim3(rows), dim3(kThreads), 0, (const float *)p->dev,
+                              (const float *)weight->dev, (float *)x->dev, cols, eps));
     TM_OP_END(1);
 }
 

@@ -50,6 +50,7 @@ _OPS = {
     "argmax_f32": [_P, _P, _U32, _P, _P, _U32],
     "argmax_f32_dev": [_P, _P, _U32, _P, _P, _U32, _P, _U32, _U32, _P],
     "rmsnorm_f32": [_P, _P, _P, _P, _U32, _U32, _F],
+    "rmsnorm_add_f32": [_P, _P, _P, _P, _U32, _U32, _F],
     "silu_mul_f32": [_P, _P, _P, _P, _U32],
     "gelu_tanh_mul_f32": [_P, _P, _P, _P, _U32],
     "q8_0_pack": [_P, _P, _U32, _U32, _P, _SZ, _U32, _U32],
@@ -338,6 +339,7 @@ class CudaContext:
     def cast_f16_f32(self, x, y, n): self._call("cast_f16_f32", x.handle, y.handle, n)
     def cast_f32_f16(self, x, y, n): self._call("cast_f32_f16", x.handle, y.handle, n)
     def argmax_f32(self, x, n, partial, out, out_index): self._call("argmax_f32", x.handle, n, partial.handle, out.handle, out_index)
+    def rmsnorm_add(self, p, weight, x, rows, cols, eps): self._call("rmsnorm_add_f32", p.handle, weight.handle, x.handle, rows, cols, eps)
     def rmsnorm(self, x, weight, y, rows, cols, eps): self._call("rmsnorm_f32", x.handle, weight.handle, y.handle, rows, cols, eps)
     def silu_mul(self, gate, up, out, n): self._call("silu_mul_f32", gate.handle, up.handle, out.handle, n)
     def gelu_tanh_mul(self, gate, up, out, n): self._call("gelu_tanh_mul_f32", gate.handle, up.handle, out.handle, n)

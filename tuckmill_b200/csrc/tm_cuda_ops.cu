@@ -611,6 +611,18 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
 #pragma unroll
         for (int c = 0; c < NL0; ++c) kraw[c] = *(const int4 *)(kr + c * 8);
     }
+    // The same for this thread's value elements (one dim pair of up to 32 cached rows), when they fit.
+    constexpr int KEYS0 = kFastSplit / KP;
+    constexpr bool kHoistV = PPT == 1 && KEYS0 <= 32;
+    __half2 vpre[kHoistV ? KEYS0 : 1];
+    if constexpr (kHoistV) {
+        const uint32_t kpart0 = tid / PAIRS < KP ? tid / PAIRS : 0, dp00 = tid % PAIRS;
+#pragma unroll
+        for (int c = 0; c < KEYS0; ++c) {
+            const uint32_t j = min(split * kFastSplit + kpart0 * KEYS0 + (uint32_t)c, cap - 1u);
+            vpre[c] = *(const __half2 *)(vp + (size_t)j * HD + 2 * dp00);
+        }
+    }
     tmdev::pdl_trigger();
     tmdev::pdl_wait();
     // The first vector this warp will normalise (q_warp, or k for warp G) does not depend on the
@@ -758,6 +770,23 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
         for (int pp = 0; pp < PPT; ++pp)
 #pragma unroll
             for (int g = 0; g < G; ++g) acc[pp][g][0] = acc[pp][g][1] = 0.0f;
+        if constexpr (kHoistV) {
+#pragma unroll
+            for (int c = 0; c < KEYS; ++c) {
+                const uint32_t j = jbase + (uint32_t)c;
+                __half2 hv = vpre[c];
+                if (owns_new && j == pos) hv = *(const __half2 *)(vh + 2 * dp0);  // this step's own row
+                if (j >= seq) hv = __float2half2_rn(0.0f);  // weight 0 there; never multiply stale bytes
+                const float2 f = __half22float2(hv);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pj = sc[g][kpart * KEYS + c];
+                    acc[0][g][0] = fmaf(pj, f.x, acc[0][g][0]);
+                    acc[0][g][1] = fmaf(pj, f.y, acc[0][g][1]);
+                }
+            }
+        }
+        if constexpr (!kHoistV) {
 #pragma unroll 1
         for (int kb = 0; kb < KEYS; kb += 8) {
             __half2 vv[8][PPT];
@@ -783,6 +812,7 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
                 }
             }
         }
+        }  // !kHoistV
 #pragma unroll
         for (int pp = 0; pp < PPT; ++pp)
 #pragma unroll

@@ -88,23 +88,23 @@ void *tm_cuda_buffer_device_ptr(tm_cuda_ctx *ctx, tm_cuda_buffer *buffer);
 /* tm_metal.h:88 tm_metal_f32_scale: y[i] = x[i] * factor. */
 int tm_cuda_f32_scale(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, float factor,
                       uint32_t n, char *err, size_t err_cap);
-/* tm_metal.h:121 tm_metal_f32_axpy: y[i] += alpha * a[i]. */
+/* tm_metal.h:115 tm_metal_f32_axpy: y[i] += alpha * a[i]. */
 int tm_cuda_f32_axpy(tm_cuda_ctx *ctx, tm_cuda_buffer *a, tm_cuda_buffer *y, float alpha,
                      uint32_t n, char *err, size_t err_cap);
-/* tm_metal.h:117 tm_metal_copy_f32: dst[dst_off+i] = src[src_off+i]. */
+/* tm_metal.h:111 tm_metal_copy_f32: dst[dst_off+i] = src[src_off+i]. */
 int tm_cuda_copy_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t src_off, tm_cuda_buffer *dst,
                      uint32_t dst_off, uint32_t n, char *err, size_t err_cap);
-/* tm_metal.h:125,129 casts between binary16 and f32 (encode rounds to
+/* tm_metal.h:119,123 casts between binary16 and f32 (encode rounds to
  * nearest even and saturates to infinity). */
 int tm_cuda_cast_f16_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t n,
                          char *err, size_t err_cap);
 int tm_cuda_cast_f32_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t n,
                          char *err, size_t err_cap);
-/* tm_metal.h:99 tm_metal_argmax_f32 -- NaN skipped, largest wins, ties to the
+/* tm_metal.h:96 tm_metal_argmax_f32 -- NaN skipped, largest wins, ties to the
  * lowest index, 0xFFFFFFFF when every entry is NaN; `partial` is 512 bytes. */
 int tm_cuda_argmax_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cuda_buffer *partial,
                        tm_cuda_buffer *out, uint32_t out_index, char *err, size_t err_cap);
-/* tm_metal.h:161 tm_metal_rmsnorm_f32. */
+/* tm_metal.h:147 tm_metal_rmsnorm_f32. */
 int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *weight,
                         tm_cuda_buffer *y, uint32_t rows, uint32_t cols, float eps, char *err,
                         size_t err_cap);
@@ -113,7 +113,7 @@ int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *wei
  * Gemma-style layers). */
 int tm_cuda_rmsnorm_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *p, tm_cuda_buffer *weight, tm_cuda_buffer *x,
                             uint32_t rows, uint32_t cols, float eps, char *err, size_t err_cap);
-/* tm_metal.h:202 tm_metal_silu_mul_f32 / :206 tm_metal_gelu_tanh_mul_f32. */
+/* tm_metal.h:189 tm_metal_silu_mul_f32 / :193 tm_metal_gelu_tanh_mul_f32. */
 int tm_cuda_silu_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_buffer *up,
                          tm_cuda_buffer *out, uint32_t n, char *err, size_t err_cap);
 int tm_cuda_gelu_tanh_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_buffer *up,
@@ -122,7 +122,7 @@ int tm_cuda_gelu_tanh_mul_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *gate, tm_cuda_bu
 /* ---------------- Q8_0 weights ---------------- */
 /*
  * Weight layout.  The reference keeps a Q8_0 matrix as the GGUF bytes
- * verbatim (tm_metal.h:209-212: rows * cols/32 blocks of 34 bytes).  A 34-byte
+ * verbatim (tm_metal.h:196-199: rows * cols/32 blocks of 34 bytes).  A 34-byte
  * stride leaves quants 2-byte aligned, which rules out 128-bit loads, so this
  * library keeps the SAME values in two planes inside one buffer:
  *   int8  q[rows][cols]      at byte 0
@@ -154,17 +154,17 @@ int tm_cuda_q8_0_unpack(tm_cuda_ctx *ctx, tm_cuda_buffer *src, uint32_t rows, ui
                         tm_cuda_buffer *raw, size_t raw_off, uint32_t row0, uint32_t nrows,
                         char *err, size_t err_cap);
 
-/* tm_metal.h:213 tm_metal_q8_0_gemv: y[r] = dot(dequant(w_row_r), x), f32. */
+/* tm_metal.h:200 tm_metal_q8_0_gemv: y[r] = dot(dequant(w_row_r), x), f32. */
 int tm_cuda_q8_0_gemv(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y,
                       uint32_t rows, uint32_t cols, char *err, size_t err_cap);
-/* tm_metal.h:176 tm_metal_q8_0_gemm: Y[b,:] = W X[b,:], b < batch (1..32), X
+/* tm_metal.h:165 tm_metal_q8_0_gemm: Y[b,:] = W X[b,:], b < batch (1..32), X
  * at f32 offset x_off, Y at y_off; per-token arithmetic is that of the GEMV,
  * so any batch is bit-identical to `batch` GEMV calls. */
 #define TM_CUDA_GEMM_MAX_BATCH 32u
 int tm_cuda_q8_0_gemm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y,
                       uint32_t rows, uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off,
                       char *err, size_t err_cap);
-/* tm_metal.h:170,187 tm_metal_q8_0_gemm_mma: the same contract on the tensor
+/* tm_metal.h:176 tm_metal_q8_0_gemm_mma: the same contract on the tensor
  * cores (tcgen05, f16 operands: x and d*q are rounded to binary16, f32
  * accumulation in tensor memory); tolerance-qualified, not bit-identical.
  * The batch limit is the reference's 512 raised to what one launch tiles. */
@@ -181,10 +181,14 @@ int tm_cuda_mma_workspace_reserve(tm_cuda_ctx *ctx, size_t bytes, char *err, siz
 /* No counterpart: 1 when a tensor-core GEMM of this context gave up one of its
  * bounded pipeline waits (its output is then undefined); waits for the stream. */
 int tm_cuda_mma_aborted(tm_cuda_ctx *ctx);
-/* tm_metal.h:151 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
+/* No counterpart: which instantiation of the tensor-core kernel the context's last GEMM
+ * launch used, as its token sub-tile width (64, 128 or 192; 0 before the first launch).
+ * The launcher picks it from the shape; tests use this to prove each one is covered. */
+int tm_cuda_mma_last_tile(tm_cuda_ctx *ctx);
+/* tm_metal.h:138 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
 int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
                          uint32_t cols, uint32_t out_off, char *err, size_t err_cap);
-/* tm_metal.h:108 tm_metal_row_indirect_f32: row ids[slot] (type 8 only); an
+/* tm_metal.h:104 tm_metal_row_indirect_f32: row ids[slot] (type 8 only); an
  * id >= rows writes zeros. */
 int tm_cuda_row_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t type_id, uint32_t rows,
                              uint32_t cols, tm_cuda_buffer *ids, uint32_t slot,
@@ -213,7 +217,7 @@ int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer 
                             size_t err_cap);
 
 /* ---------------- grouped encoding ---------------- */
-/* tm_metal.h:141-143 begin/end/abort_group: operations between begin and end
+/* tm_metal.h:133-135 begin/end/abort_group: operations between begin and end
  * are captured into one CUDA graph launched at end_group; abort discards
  * them without running anything.  Copies and fence need no open group. */
 int tm_cuda_begin_group(tm_cuda_ctx *ctx, char *err, size_t err_cap);
@@ -227,23 +231,23 @@ int tm_cuda_end_group_retain(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, s
 int tm_cuda_graph_launch(tm_cuda_ctx *ctx, tm_cuda_graph *graph, char *err, size_t err_cap);
 void tm_cuda_graph_free(tm_cuda_ctx *ctx, tm_cuda_graph *graph);
 
-/* tm_metal.h:281 tm_metal_fence. */
+/* tm_metal.h:291 tm_metal_fence. */
 int tm_cuda_fence(tm_cuda_ctx *ctx, char *err, size_t err_cap);
-/* tm_metal.h:284,290 committed / completed dispatch counters. */
+/* tm_metal.h:294,301 committed / completed dispatch counters. */
 uint64_t tm_cuda_committed_dispatches(const tm_cuda_ctx *ctx);
 uint64_t tm_cuda_completed_dispatches(const tm_cuda_ctx *ctx);
-/* tm_metal.h:289 tm_metal_download_after: copy from a SHARED buffer once the
+/* tm_metal.h:299 tm_metal_download_after: copy from a SHARED buffer once the
  * first `completed_target` committed dispatches have completed. */
 int tm_cuda_download_after(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, void *dst,
                            size_t len, uint64_t completed_target, char *err, size_t err_cap);
-/* tm_metal.h:293,296 GPU time of the last completed dispatch / cumulative. */
+/* tm_metal.h:304,307 GPU time of the last completed dispatch / cumulative. */
 double tm_cuda_last_gpu_ms(const tm_cuda_ctx *ctx);
 uint64_t tm_cuda_gpu_nanos_total(const tm_cuda_ctx *ctx);
-/* tm_metal.h:301,304 per-operator attribution (CUDA events per dispatch). */
+/* tm_metal.h:312,315 per-operator attribution (CUDA events per dispatch). */
 int tm_cuda_profile_set(tm_cuda_ctx *ctx, int enabled);
 int tm_cuda_profile_read(tm_cuda_ctx *ctx, uint32_t index, char *name, size_t name_cap,
                          uint64_t *nanos, uint64_t *count);
-/* tm_metal.h:307 live bytes in buffers; :314 bytes leased by pending work
+/* tm_metal.h:318 live bytes in buffers; :325 bytes leased by pending work
  * (always 0 here: tm_cuda_buffer_free waits instead of leasing). */
 uint64_t tm_cuda_allocated_bytes(const tm_cuda_ctx *ctx);
 uint64_t tm_cuda_in_flight_bytes(const tm_cuda_ctx *ctx);
@@ -258,18 +262,18 @@ int tm_cuda_device_memory(tm_cuda_ctx *ctx, uint64_t *free_bytes, uint64_t *tota
 void *tm_cuda_stream(tm_cuda_ctx *ctx);
 
 /* ---------------- attention operators ---------------- */
-/* tm_metal.h:252 tm_metal_qwen35_rope_partial: split-half RoPE on the first
+/* tm_metal.h:257 tm_metal_qwen35_rope_partial: split-half RoPE on the first
  * n_rot dims of every q/k head row, angle (float)pos * inv_freq[i]. */
 int tm_cuda_qwen35_rope_partial(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
                                 tm_cuda_buffer *inv_freq, uint32_t pos, uint32_t n_q_heads,
                                 uint32_t n_kv_heads, uint32_t head_dim, uint32_t n_rot, char *err,
                                 size_t err_cap);
-/* tm_metal.h:357 ..._rope_partial_chunk: token t rotates at pos0 + t. */
+/* tm_metal.h:368 ..._rope_partial_chunk: token t rotates at pos0 + t. */
 int tm_cuda_qwen35_rope_partial_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,
                                       tm_cuda_buffer *inv_freq, uint32_t pos0, uint32_t n_q_heads,
                                       uint32_t n_kv_heads, uint32_t head_dim, uint32_t n_rot,
                                       uint32_t n, char *err, size_t err_cap);
-/* tm_metal.h:259 ..._kv_store_f16 / :362 ..._kv_store_f16_chunk:
+/* tm_metal.h:264 ..._kv_store_f16 / :373 ..._kv_store_f16_chunk:
  * cache[h][pos0+t][d] = (half) src[t][h][d], planes [kv_head][cap][head_dim]. */
 int tm_cuda_qwen35_kv_store_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *k_src, tm_cuda_buffer *v_src,
                                 tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, uint32_t pos,
@@ -280,14 +284,14 @@ int tm_cuda_qwen35_kv_store_f16_chunk(tm_cuda_ctx *ctx, tm_cuda_buffer *k_src,
                                       tm_cuda_buffer *v_cache, uint32_t pos0, uint32_t cap,
                                       uint32_t head_dim, uint32_t kv_heads, uint32_t n, char *err,
                                       size_t err_cap);
-/* tm_metal.h:265 ..._attention_f16: causal GQA attention of one query row
+/* tm_metal.h:270 ..._attention_f16: causal GQA attention of one query row
  * over keys 0..=pos of a packed f16 cache (`scratch`: see the chunk form). */
 int tm_cuda_qwen35_attention_f16(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k_cache,
                                  tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
                                  tm_cuda_buffer *scratch, uint32_t heads, uint32_t pos,
                                  uint32_t cap, uint32_t head_dim, uint32_t group, float scale,
                                  char *err, size_t err_cap);
-/* tm_metal.h:367 ..._attention_f16_chunk: query row t attends keys
+/* tm_metal.h:378 ..._attention_f16_chunk: query row t attends keys
  * [start, pos0+t] where start = seq > window ? seq - window : 0 (window 0 =
  * full causal).  The reference's scratch is n*heads*cap f32 of scores; this
  * implementation streams key blocks through registers and only requires
@@ -346,7 +350,15 @@ int tm_cuda_attention_chunk_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buf
  * `scratch` holds the per-key-block partial results and arrival counters
  * (tm_cuda_attention_decode_scratch_bytes, zero-filled once by the caller;
  * the kernel leaves the counters at zero).  Calls sharing one scratch buffer
- * must be ordered on the stream. */
+ * must be ordered on the stream.
+ * Cache contract: the kernel reads cache rows below `pos` while the kernel
+ * launched before it on the stream may still be running (programmatic
+ * dependent launch).  Row pos - 1 is read again once the predecessor has
+ * finished, so consecutive decode calls at pos, pos + 1 on one cache are safe
+ * however close together they are issued; rows below pos - 1 must have been
+ * written by work that completed before the PREDECESSOR kernel was launched
+ * (true of any earlier dispatch group or graph launch, and of a decode step
+ * two or more positions back). */
 size_t tm_cuda_attention_decode_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                                               uint32_t cap);
 int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,

@@ -39,6 +39,41 @@ def test_mma_gemm_matches_oracle_and_f16_profile(ctx, oracle, rows, cols, batch)
     assert rel_err(Y, ref16) <= 2e-5, "differs from the f16-operand profile by more than accumulation error"
 
 
+# Shapes the launcher serves with its wider instantiations (token sub-tile 128 and 192: a different
+# shared-memory ring and tensor-memory split each) and batches up to the limit of one launch.  The
+# whole GEMM runs on the device; the first, middle and last 256 weight rows of Y (every token) are
+# compared with the oracle and with the f16-operand profile.  The expected instantiation is asserted,
+# so a change of the launcher's choice cannot silently drop the coverage.
+BIG_CASES = [(3072, 1024, 512, 64),        # the single-operator configuration at its batch
+             (12288, 4096, 512, 128), (4096, 4096, 2048, 128),
+             (12288, 4096, 2048, 192), (4096, 4096, 8192, 192), (151936, 4096, 2048, 192)]
+
+
+@pytest.mark.parametrize("rows,cols,batch,tile", BIG_CASES)
+def test_mma_gemm_large_shapes_every_instantiation(ctx, oracle, rows, cols, batch, tile):
+    base_rows = min(rows, 4096)
+    base = T.q8_0_matrix(3, rows + cols, base_rows, cols)
+    raw = np.tile(base, ((rows + base_rows - 1) // base_rows, 1, 1))[:rows]
+    X = T.activations(3, 5, min(batch, 2048) * cols).reshape(-1, cols)
+    X = np.tile(X, ((batch + X.shape[0] - 1) // X.shape[0], 1))[:batch]
+    X = (X * (1 + 0.25 * np.arange(batch, dtype=np.float32)[:, None] / batch)).astype(np.float32)  # rows differ
+    w = ctx.q8_0_matrix(raw, rows, cols)
+    xb, yb = ctx.floats(X), ctx.buffer(batch * rows * 4)
+    ctx.q8_0_gemm_mma(w, xb, yb, rows, cols, batch)
+    Y = yb.download(0, batch * rows * 4, np.float32).reshape(batch, rows)
+    assert not ctx.mma_aborted()
+    assert ctx.mma_last_tile() == tile, f"launcher picked sub-tile {ctx.mma_last_tile()}, the case is meant for {tile}"
+    mid = (rows // 2) // 128 * 128 + 64  # straddles a 128-row tile boundary
+    for r0 in sorted({0, mid, rows - 256}):
+        sub = np.ascontiguousarray(raw[r0:r0 + 256])
+        got = Y[:, r0:r0 + 256]
+        cpu = oracle.matmul_q8_0(sub, 256, cols, X)
+        assert float(np.max(np.abs(got - cpu))) <= 2e-2, f"rows {r0}..{r0 + 256}"
+        assert rel_err(got, f16_profile_reference(sub, X)) <= 2e-5, f"rows {r0}..{r0 + 256}: not the f16-operand profile"
+    for b in (w, xb, yb):
+        b.free()
+
+
 def test_mma_gemm_row_view_and_larger_scales(ctx, oracle):
     """A projection stored inside a fused matrix (row view), scales up to ~1."""
     rows, cols, batch = 384, 512, 200

@@ -213,6 +213,47 @@ def test_decode_attention_core_equals_operator_sequence(ctx, oracle, heads, kvh,
     np.testing.assert_array_equal(caches[1][0].download(0, plane), before)
 
 
+@pytest.mark.parametrize("exact", [True, False])
+def test_consecutive_decode_calls_inside_one_group(ctx, exact):
+    """attention(pos) -> advance -> attention(pos + 1) -> ... on ONE cache inside ONE dispatch group:
+    kernels of a group start while their predecessors still run, so a call must not pick up the row
+    its predecessor-but-one is still storing.  Compared with the same calls issued one by one."""
+    heads, kvh, hd, cap, eps, filled, n = 16, 8, 128, 200, 1e-6, 60, 6
+    scale = 1.0 / np.sqrt(np.float32(hd))
+    qnb = ctx.floats((1 + 0.1 * T.activations(0, 20, hd)).astype(np.float32))
+    knb = ctx.floats((1 + 0.1 * T.activations(0, 21, hd)).astype(np.float32))
+    ib = ctx.floats((1e4 ** (-np.arange(hd // 2, dtype=np.float64) * 2 / hd)).astype(np.float32))
+    kfill = T.activations(1, 1, kvh * cap * hd).astype(np.float16)
+    vfill = T.activations(1, 2, kvh * cap * hd).astype(np.float16)
+    qs = [ctx.floats(T.activations(40 + i, 30, heads * hd)) for i in range(n)]
+    ks = [ctx.floats(T.activations(40 + i, 31, kvh * hd)) for i in range(n)]
+    vs = [ctx.floats(T.activations(40 + i, 32, kvh * hd)) for i in range(n)]
+    status = ctx.buffer(4, shared=True)
+    status.zero()
+    results = []
+    for grouped in (False, True):
+        kc, vc = ctx.from_array(kfill), ctx.from_array(vfill)
+        pos_buf = ctx.from_array(np.array([filled], np.uint32))
+        sb = ctx.buffer(cuda.decode_attention_scratch_bytes(heads, kvh, hd, cap))
+        sb.zero()
+        outs = [ctx.buffer(heads * hd * 4) for _ in range(n)]
+        if grouped:
+            ctx.begin_group()
+        for i in range(n):
+            ctx.attention_decode_dev(qs[i], ks[i], vs[i], qnb, knb, ib, kc, vc, outs[i], sb, pos_buf, 0, status,
+                                     heads, kvh, hd, hd, cap, 0, eps, scale, exact=exact)
+            ctx.u32_add(pos_buf, 0, 1)
+            if not grouped:
+                ctx.fence()
+        if grouped:
+            ctx.end_group()
+        ctx.fence()
+        results.append([f32(o, heads * hd) for o in outs])
+    for i in range(n):
+        np.testing.assert_array_equal(results[1][i], results[0][i], err_msg=f"call {i} of the group")
+    assert int(status.download(0, 4, np.uint32)[0]) == 0
+
+
 def test_buffers_ledger_and_ownership(ctx):
     base = ctx.allocated_bytes()
     a, b = ctx.buffer(1000), ctx.buffer(24, shared=True)

@@ -41,6 +41,22 @@ def test_gemv_matches_oracle_seeded(ctx, oracle, rows, cols):
     assert rel_err(gpu, cpu) <= TOL
 
 
+# The projection and head shapes of the 8B-scale and Gemma configurations: long column ranges and
+# tall matrices, which take the shared-memory ring forms (8, 16 and 24 chunks deep) and the row cut
+# that the small shapes above never reach.  Weights repeat with a period of 4096 rows (generating
+# 600 M seeded elements would dominate the test); the activations do not.
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (12288, 4096), (24576, 4096), (151936, 4096), (262144, 1152)])
+def test_gemv_large_shapes_match_oracle(ctx, oracle, rows, cols):
+    base = T.q8_0_matrix(4, rows + cols, 4096, cols)
+    raw = np.ascontiguousarray(np.tile(base, ((rows + 4095) // 4096, 1, 1))[:rows])
+    x = T.activations(4, 78, cols)
+    cpu = oracle.matmul_q8_0(raw, rows, cols, x)
+    gpu = run_gemv(ctx, raw, rows, cols, x)
+    assert rel_err(gpu, cpu) <= TOL
+    period = gpu[:rows // 4096 * 4096].reshape(-1, 4096)
+    assert np.all(period == period[0]), "equal weight rows gave different results: a row-dependent path"
+
+
 @pytest.mark.parametrize("rows,cols", [(1, 32), (3, 32), (17, 64), (1024, 1024), (2048, 1024)])
 def test_gemv_boundary_weights(ctx, oracle, rows, cols):
     """Adversarial scales (+-65504, subnormal, +-0) and quants (-128, 127, 0)."""

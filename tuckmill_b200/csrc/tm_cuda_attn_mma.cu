@@ -335,13 +335,12 @@ __global__ void __launch_bounds__(256) qk_prep_chunk_kernel(float *q, const floa
 template <int HD>
 cudaError_t launch_attn(const attn_args &a, int device, cudaStream_t stream) {
     using C = attn_cfg<HD>;
-    static bool attr_done[16] = {};
-    const int dev = device >= 0 && device < 16 ? device : 0;
-    if (!attr_done[dev]) {
+    static std::atomic<bool> attr_done[64] = {};  // per device; contexts of a process share it
+    if (device < 0 || device >= 64 || !attr_done[device].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(attention_chunk_mma_kernel<HD>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
+        if (device >= 0 && device < 64) attr_done[device].store(true, std::memory_order_release);
     }
     const dim3 grid((a.n + kBQ - 1) / kBQ, a.heads, HD / C::kDV);
     attention_chunk_mma_kernel<HD><<<grid, kThreads, C::kBytes, stream>>>(a);

@@ -79,6 +79,7 @@ struct tm_cuda_ctx {
     // Scratch owned by the context for the tensor-core GEMM (f16 copy of X).
     unsigned char *mma_scratch = nullptr;
     size_t mma_scratch_bytes = 0;
+    int mma_last_bn = 0;                 // token sub-tile width of the last tensor-core GEMM launch
     void *comm = nullptr;  // multi-GPU communicator state (tm_cuda_comm.cu)
 };
 

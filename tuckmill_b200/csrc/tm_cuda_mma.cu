@@ -573,13 +573,12 @@ encode_tiled_fn get_encode_tiled() {
 template <int BN>
 cudaError_t launch_mma(const CUtensorMap &wmap, const CUtensorMap &xmap, const mma_args &a, int grid, int device,
                        cudaStream_t stream) {
-    static bool attr_done[16] = {};
-    const int dev = device >= 0 && device < 16 ? device : 0;
-    if (!attr_done[dev]) {
+    static std::atomic<bool> attr_done[64] = {};  // per device; contexts of a process share it
+    if (device < 0 || device >= 64 || !attr_done[device].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(q8_gemm_mma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)mma_smem<BN>::kBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
+        if (device >= 0 && device < 64) attr_done[device].store(true, std::memory_order_release);
     }
     q8_gemm_mma_kernel<BN><<<grid, kMmaThreads, mma_smem<BN>::kBytes, stream>>>(wmap, xmap, a);
     return cudaGetLastError();
@@ -702,6 +701,7 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
     a.cols = cols;
     a.batch = batch;
     a.abort_flag = abort_flag;
+    ctx->mma_last_bn = bn;
     const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn));
     const int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
     TM_CUDA_TRY(bn == 192   ? launch_mma<192>(wmap, xmap, a, grid, ctx->device, ctx->stream)
@@ -827,6 +827,13 @@ int tm_cuda_q8_0_gemm_mma_push(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buff
     rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, 0, err, err_cap, push);
     if (rc != TM_CUDA_OK) return rc;
     TM_OP_END(2);
+}
+
+// Token sub-tile width (64, 128 or 192) of the kernel instantiation the last GEMM launch used.
+int tm_cuda_mma_last_tile(tm_cuda_ctx *ctx) {
+    if (!ctx) return 0;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return ctx->mma_last_bn;
 }
 
 // 1 when a tensor-core GEMM on this context ever gave up a bounded wait.

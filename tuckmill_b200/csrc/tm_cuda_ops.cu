@@ -399,11 +399,14 @@ __global__ void __launch_bounds__(32) attention_decode_kernel(
     const __half *kp = kc + (size_t)kvh * cap * hd, *vp = vc + (size_t)kvh * cap * hd;
     // The cache rows of this block do not depend on the predecessor's output
     // (except the new row, taken from shared memory below): pull them close now.
+    // Only as far as L2, which is coherent: a kernel two places back in a chain of
+    // programmatic launches (the previous token's attention) may still be storing
+    // its row, and a copy of that line taken into L1 now would be read stale later.
     {
         const uint32_t j = min(blk * kAttnBlock + lane, cap - 1u);
         for (uint32_t off = 0; off < hd * 2u; off += 128u) {
-            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(kp + (size_t)j * hd) + off));
-            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(vp + (size_t)j * hd) + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(kp + (size_t)j * hd) + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(vp + (size_t)j * hd) + off));
         }
     }
     tmdev::pdl_trigger();
@@ -592,17 +595,18 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t nsplit = (cap + kFastSplit - 1) / kFastSplit;
     const __half *kp = kc + (size_t)kvh * cap * HD, *vp = vc + (size_t)kvh * cap * HD;
-    {   // cache rows of this split: independent of the predecessor, pull them close
+    {   // value rows of this split: towards L2 (coherent; see the note on row pos - 1 below)
         const uint32_t j = min(split * kFastSplit + (tid >> 1), cap - 1u);
         const uint32_t half_bytes = HD;  // half a row of f16
-        for (uint32_t off = 0; off < half_bytes; off += 128u) {
-            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(kp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
-            asm volatile("prefetch.global.L1 [%0];" ::"l"((const char *)(vp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
-        }
+        for (uint32_t off = 0; off < half_bytes; off += 128u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(vp + (size_t)j * HD) + (tid & 1) * half_bytes + off));
     }
     // This thread's half of key row split*64 + tid/2: written by an earlier step's kernel (or is a row past
     // the sequence, masked below; or the current position's row, replaced below by the fresh one), so it
-    // is read before the predecessor finishes.
+    // is read before the predecessor finishes.  One row is the exception: every kernel of a chain of
+    // programmatic launches lets its successor start early, so the attention call of the PREVIOUS token
+    // (two or more kernels back) may still be storing row pos - 1; that row is read again after the wait.
+    // Rows below pos - 1 must be complete before the predecessor kernel is launched.
     constexpr int NL0 = HD / 16;  // 16-byte loads per thread
     int4 kraw[NL0];
     {
@@ -652,6 +656,23 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     if (split < first || split > last) return;
     const bool owns_new = split == last;
     (void)n_rot;
+    if (pos > 0u) {  // the previous token's row, now certainly complete (read past L1)
+        const uint32_t prev = pos - 1u;
+        if (split * kFastSplit + ((uint32_t)tid >> 1) == prev) {
+            const int4 *kr = (const int4 *)(kp + (size_t)prev * HD + (tid & 1) * (HD / 2));
+#pragma unroll
+            for (int c = 0; c < NL0; ++c) kraw[c] = __ldcg(kr + c);
+        }
+        if constexpr (kHoistV) {
+            const uint32_t kpart0 = tid / PAIRS < KP ? tid / PAIRS : 0, dp00 = tid % PAIRS;
+#pragma unroll
+            for (int c = 0; c < KEYS0; ++c)
+                if (split * kFastSplit + kpart0 * KEYS0 + (uint32_t)c == prev) {
+                    const uint32_t raw = __ldcg((const unsigned int *)(vp + (size_t)prev * HD + 2 * dp00));
+                    vpre[c] = *(const __half2 *)&raw;
+                }
+        }
+    }
 
     // ---- vectors q_0..q_{G-1} (and k for the owning split): RMS norm + RoPE, one warp each ----
     for (int vec = warp; vec < G + (owns_new ? 1 : 0); vec += kFastThreads / 32) {
@@ -1311,7 +1332,9 @@ constexpr size_t kStaticDecodeScratchBytes = 9u << 20;
 static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticDecodeScratchBytes];
 // Device address of that array per device (the symbol's name is only a host-side
 // stand-in; kernels must be handed the address cudaGetSymbolAddress returns).
-static unsigned char *g_static_decode_scratch_ptr[64] = {};
+// Contexts of one process share the table (each under its own lock), hence atomic slots; every
+// writer stores the same address.
+static std::atomic<unsigned char *> g_static_decode_scratch_ptr[64] = {};
 
 size_t tm_cuda_attention_decode_static_max_scratch(void) { return kStaticDecodeScratchBytes; }
 
@@ -1350,7 +1373,7 @@ int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_
     TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
     TM_CHECK_BUF(status, 4, "status");
     // Set-up, once per device, with that device current (TM_ENTER made it so).
-    if (!g_static_decode_scratch_ptr[ctx->device]) {
+    if (!g_static_decode_scratch_ptr[ctx->device].load(std::memory_order_acquire)) {
         unsigned char *p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_static_decode_scratch);
         if (e != cudaSuccess || !p) {
@@ -1358,9 +1381,9 @@ int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_
             return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "cudaGetSymbolAddress of the built-in scratch failed: %s",
                            cudaGetErrorString(e));
         }
-        g_static_decode_scratch_ptr[ctx->device] = p;
+        g_static_decode_scratch_ptr[ctx->device].store(p, std::memory_order_release);
     }
-    float *sp = (float *)g_static_decode_scratch_ptr[ctx->device];
+    float *sp = (float *)g_static_decode_scratch_ptr[ctx->device].load(std::memory_order_acquire);
     // The array keeps whatever the previous call left: the arrival counters (the
     // tail of the region this geometry uses) must start at zero.  Both kernels
     // keep their counters inside the last `heads` words of `need`.

@@ -438,13 +438,14 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
 
 template <int M, int kSlots, int H>
 cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
-    static bool attr_set[16] = {};  // per device
-    if (ctx->device < 16 && !attr_set[ctx->device]) {
+    static std::atomic<bool> attr_set[64] = {};  // per device; contexts of a process share it
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M, kSlots, H>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)ctx->smem_optin - 8192);
         if (e != cudaSuccess) return e;
-        attr_set[ctx->device] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     return tm_launch_pdl(ctx, q8_gemv_kernel<M, kSlots, H>, dim3(grid), dim3(kThreads), smem, a);
 }

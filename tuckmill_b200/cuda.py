@@ -129,6 +129,8 @@ def load_library() -> C.CDLL:
     L.tm_cuda_mma_workspace_reserve.argtypes = [_P, _SZ] + _ERR
     L.tm_cuda_mma_aborted.restype = C.c_int
     L.tm_cuda_mma_aborted.argtypes = [_P]
+    L.tm_cuda_mma_last_tile.restype = C.c_int
+    L.tm_cuda_mma_last_tile.argtypes = [_P]
     L.tm_cuda_q8_0_packed_bytes.restype = _SZ
     L.tm_cuda_q8_0_packed_bytes.argtypes = [_U32, _U32]
     L.tm_cuda_graph_free.argtypes = [_P, _P]
@@ -353,6 +355,7 @@ class CudaContext:
 
     def mma_workspace_reserve(self, nbytes: int): self._call("mma_workspace_reserve", nbytes)
     def mma_aborted(self) -> bool: return bool(self._l.tm_cuda_mma_aborted(self.handle))
+    def mma_last_tile(self) -> int: return int(self._l.tm_cuda_mma_last_tile(self.handle))
 
     def q8_0_gemv_fused(self, w, x, y, rows, cols, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
         self._call("q8_0_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)

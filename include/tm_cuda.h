@@ -231,6 +231,55 @@ int tm_cuda_end_group_retain(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, s
 int tm_cuda_graph_launch(tm_cuda_ctx *ctx, tm_cuda_graph *graph, char *err, size_t err_cap);
 void tm_cuda_graph_free(tm_cuda_ctx *ctx, tm_cuda_graph *graph);
 
+/* No counterpart: a decode step as ONE persistent kernel.  Between begin_program and
+ * end_program the operators a step is made of do not launch; they are recorded, in
+ * order, into a program: tm_cuda_q8_0_gemv / _gemv_fused (one token),
+ * tm_cuda_row_indirect_f32(_dev), tm_cuda_attention_decode_dev (exact = 0, a geometry
+ * tm_cuda_program_supports_attention accepts), tm_cuda_rmsnorm_add_f32 (one row),
+ * tm_cuda_argmax_f32(_dev) and tm_cuda_u32_add; any other operator fails with
+ * TM_CUDA_ERR_UNSUPPORTED and the caller falls back to a dispatch group.  The result is
+ * launched and freed like a retained group (tm_cuda_graph_launch / _free; one committed
+ * dispatch, one kernel per launch) and computes what the recorded operators would have
+ * computed one after the other -- same arithmetic per operator, the GEMV's partial sums
+ * added in a different (fixed) order, hence tolerance-qualified like the decode
+ * attention it contains.  A buffer that several operators of the program write (the
+ * residual stream) holds, after a launch, what the last of them wrote.
+ * One CTA per SM walks the program: a producer warp streams the Q8_0 weights of ALL
+ * operators through a shared-memory ring without stopping at operator boundaries, the
+ * other warps multiply; vectors travel between operators as {value, sequence number}
+ * words that consumers poll (no grid barrier), every poll bounded.
+ * Device memory: tm_cuda_program_bytes(max_ops, vector_elems, attention_elems), counted in
+ * tm_cuda_allocated_bytes until the program is freed.  vector_elems >= the sum of the
+ * output lengths of the recorded operators (GEMV rows, embedding columns, attention
+ * heads x head_dim, normed columns); attention_elems >= the largest
+ * tm_cuda_program_attention_elems(heads, head_dim, capacity) of its attention operators.
+ * Bits of tm_cuda_program_status (waits for the stream): 1 a wait for activations ran
+ * out, 2 a weight-stage wait ran out.  A program whose status is non-zero computes
+ * nothing further; free it and record a new one. */
+size_t tm_cuda_program_bytes(uint32_t max_ops, uint64_t vector_elems, uint64_t attention_elems);
+uint64_t tm_cuda_program_attention_elems(uint32_t heads, uint32_t head_dim, uint32_t cap);
+int tm_cuda_program_supports_gemv(uint32_t cols);
+int tm_cuda_program_supports_attention(uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot);
+int tm_cuda_begin_program(tm_cuda_ctx *ctx, uint32_t max_ops, uint64_t vector_elems, uint64_t attention_elems,
+                          char *err, size_t err_cap);
+int tm_cuda_end_program(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, size_t err_cap);
+int tm_cuda_abort_program(tm_cuda_ctx *ctx, char *err, size_t err_cap);
+int tm_cuda_program_status(tm_cuda_ctx *ctx, tm_cuda_graph *program, uint32_t *status, char *err, size_t err_cap);
+/* No counterpart, a profiling aid: time stamps (device global timer, ns) that CTA 0 took in the
+ * program's last launch: out[8*i + 0] = operator i started, [1] = its activations were staged
+ * (GEMV), [2] = its work on this CTA was done, [7] = the weight producer reached it; kinds[i]
+ * (optional) = the operator's kind (1 embedding, 2 GEMV, 3 attention, 4 argmax, 5 norm + add,
+ * 6 position).  The first call switches the stamps on and returns zeros.  `out` holds
+ * 8 * max_ops words. */
+int tm_cuda_program_trace(tm_cuda_ctx *ctx, tm_cuda_graph *program, uint64_t *out, uint32_t max_ops, uint32_t *kinds,
+                          char *err, size_t err_cap);
+/* No counterpart, for tests of the bounded waits: consumers expect sequence numbers
+ * `sequence_skew` higher than producers write (0 = normal), and poll at most `spin_limit`
+ * times (0 = unchanged).  With a skew no wait for activations can be satisfied: the kernel must
+ * raise status bit 1 and return. */
+int tm_cuda_program_debug(tm_cuda_ctx *ctx, tm_cuda_graph *program, uint32_t sequence_skew, uint32_t spin_limit,
+                          char *err, size_t err_cap);
+
 /* tm_metal.h:291 tm_metal_fence. */
 int tm_cuda_fence(tm_cuda_ctx *ctx, char *err, size_t err_cap);
 /* tm_metal.h:294,301 committed / completed dispatch counters. */

@@ -55,6 +55,10 @@ typedef struct {
      * collective that all ranks make in the same order. */
     uint32_t shard_rank, shard_world;
     const void *comm_id;
+    /* 0 (default): a decode step runs as ONE persistent kernel where the model allows it
+     * (single device, not exact, attention shapes the program kernel serves); 1: always
+     * the recorded graph of per-operator kernels. */
+    int step_graph;
 } tm_engine_options;
 
 /* 128 opaque bytes naming a new communicator (tm_cuda_comm_unique_id). */
@@ -80,6 +84,9 @@ void tm_engine_free(tm_engine *e);
 int tm_engine_get_info(tm_engine *e, tm_engine_info *out);
 /* The tm_cuda_ctx the engine runs on (for event timing on its stream). */
 void *tm_engine_cuda_ctx(tm_engine *e);
+/* The tm_cuda_graph of the persistent decode program (tm_cuda_program_status / _trace), or
+ * NULL when a decode step is a graph of per-operator kernels. */
+void *tm_engine_decode_program(tm_engine *e);
 int tm_engine_reset(tm_engine *e, char *err, size_t err_cap);
 int tm_engine_prefill(tm_engine *e, const uint32_t *tokens, uint32_t n, int want_token, char *err,
                       size_t err_cap);

@@ -101,12 +101,13 @@ def test_mma_gemm_limits(ctx):
     assert e.value.code == -4
     with pytest.raises(cuda.CudaError):
         ctx.q8_0_gemm_mma(w, ctx.buffer(16), y, 40, 64, 64)
-    wide = ctx.q8_0_matrix(T.q8_0_matrix(0, 2, 8, 8192), 8, 8192)
-    xw, yw = ctx.buffer(4096 * 8192 * 4), ctx.buffer(4096 * 8 * 4)
+    wide = ctx.q8_0_matrix(T.q8_0_matrix(0, 2, 8, 16384), 8, 16384)
+    xw, yw = ctx.buffer(8192 * 16384 * 4), ctx.buffer(8192 * 8 * 4)
     ctx.begin_group()
     try:
         with pytest.raises(cuda.CudaError) as e:
-            ctx.q8_0_gemm_mma(wide, xw, yw, 8, 8192, 4096)  # the 64 MiB workspace would have to grow inside a group
+            # a 256 MiB workspace, larger than any earlier test needed: it would have to grow inside a group
+            ctx.q8_0_gemm_mma(wide, xw, yw, 8, 16384, 8192)
         assert e.value.code == -5
     finally:
         ctx.abort_group()

@@ -103,6 +103,7 @@ int tm_engine_load(const tm_engine_options *o, tm_engine **out, char *err, size_
         EngineOptions eo;
         eo.prefill_batch = o->prefill_batch ? o->prefill_batch : kPrefillBatchDefault;
         eo.exact = o->exact != 0;
+        eo.persistent = o->step_graph == 0;
         eo.shard_world = o->shard_world ? o->shard_world : 1;
         eo.shard_rank = o->shard_rank;
         if (eo.shard_world > 1) {
@@ -162,6 +163,7 @@ int tm_engine_get_info(tm_engine *e, tm_engine_info *out) {
 }
 
 void *tm_engine_cuda_ctx(tm_engine *e) { return e ? (void *)e->ctx->raw() : nullptr; }
+void *tm_engine_decode_program(tm_engine *e) { return e && e->model ? (void *)e->model->decode_program() : nullptr; }
 
 int tm_engine_reset(tm_engine *e, char *err, size_t err_cap) { GUARD(e->model->reset()) }
 

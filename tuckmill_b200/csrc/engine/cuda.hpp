@@ -102,6 +102,7 @@ public:
         g_ = nullptr;
     }
     explicit operator bool() const { return g_ != nullptr; }
+    tm_cuda_graph *raw() const { return g_; }
     void launch() const {
         char e[256] = "";
         cuda_check(tm_cuda_graph_launch(ctx_, g_, e, sizeof e), e);
@@ -331,6 +332,36 @@ public:
         tm_cuda_graph *g = nullptr;
         cuda_check(tm_cuda_end_group_retain(ctx_, &g, e, sizeof e), e);
         return CudaGraph(ctx_, g);
+    }
+    // A decode step recorded as one persistent kernel (include/tm_cuda.h): the operators called
+    // between begin_program and end_program are recorded, not launched.
+    void begin_program(uint32_t max_ops, uint64_t vector_elems, uint64_t attention_elems) const {
+        char e[256] = "";
+        cuda_check(tm_cuda_begin_program(ctx_, max_ops, vector_elems, attention_elems, e, sizeof e), e);
+    }
+    void abort_program() const {
+        char e[256] = "";
+        tm_cuda_abort_program(ctx_, e, sizeof e);
+    }
+    CudaGraph end_program() const {
+        char e[256] = "";
+        tm_cuda_graph *g = nullptr;
+        cuda_check(tm_cuda_end_program(ctx_, &g, e, sizeof e), e);
+        return CudaGraph(ctx_, g);
+    }
+    // Status words of the bounded waits (each waits for the stream): non-zero = a wait ran out.
+    uint32_t program_status(const CudaGraph &g) const {
+        char e[256] = "";
+        uint32_t st = 0;
+        cuda_check(tm_cuda_program_status(ctx_, g.raw(), &st, e, sizeof e), e);
+        return st;
+    }
+    bool mma_aborted() const { return tm_cuda_mma_aborted(ctx_) != 0; }
+    uint32_t symm_status(const CudaBuffer &b) const {
+        char e[256] = "";
+        uint32_t st = 0;
+        cuda_check(tm_cuda_symm_status(ctx_, b.raw(), &st, e, sizeof e), e);
+        return st;
     }
     // One dispatch per step: a failure inside `encode` aborts the group so no
     // partial work reaches the device.

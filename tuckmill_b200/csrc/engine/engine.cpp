@@ -2,6 +2,7 @@
 
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace tuckmill {
@@ -591,9 +592,41 @@ struct EngineModel::Impl {
     std::vector<Layer> layers;
     PrefillScratch scratch;
     CudaGraph decode_graph;
+    bool persistent = false;  // decode_graph is a persistent program
     const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
     uint32_t head_cols() const { return embedding.cols; }
 };
+
+DecodeProgramSize decode_program_size(const ModelGraph &graph, size_t capacity) {
+    DecodeProgramSize s;
+    s.max_ops = (uint32_t)graph.layers.size() * 8u + 8u;
+    s.vector_elems = graph.hidden + graph.vocab;  // embedding row, logits
+    for (const LayerSpec &l : graph.layers) {
+        const AttentionSpec &m = l.mixer;
+        // q|k|v, attention output, o projection (+ its normed residual form), gate|up, down (+ normed form)
+        s.vector_elems += (m.heads + 2 * m.kv_heads) * m.head_dim + m.heads * m.head_dim + 2 * graph.hidden +
+                          2 * l.ffn.width + 2 * graph.hidden;
+        s.attention_elems = std::max<uint64_t>(
+            s.attention_elems, tm_cuda_program_attention_elems((uint32_t)m.heads, (uint32_t)m.head_dim, (uint32_t)capacity));
+    }
+    return s;
+}
+
+bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opts) {
+    if (!opts.persistent || opts.exact || opts.shard_world > 1) return false;
+    if (const char *e = std::getenv("TM_ENGINE_PERSISTENT"))
+        if (e[0] == '0') return false;
+    if (!tm_cuda_program_supports_gemv((uint32_t)graph.hidden)) return false;
+    for (const LayerSpec &l : graph.layers) {
+        const AttentionSpec &m = l.mixer;
+        if (!tm_cuda_program_supports_attention((uint32_t)m.heads, (uint32_t)m.kv_heads, (uint32_t)m.head_dim,
+                                                (uint32_t)m.rope_dims) ||
+            !tm_cuda_program_supports_gemv((uint32_t)(m.heads * m.head_dim)) ||
+            !tm_cuda_program_supports_gemv((uint32_t)l.ffn.width))
+            return false;
+    }
+    return true;
+}
 
 GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, size_t capacity,
                              const EngineOptions &opts) {
@@ -634,6 +667,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     const size_t n = std::min<size_t>(opts.prefill_batch, capacity);
     PrefillScratch::plan(graph, capacity, n, sh, p);
     if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, n));
+    if (persistent_decode_applies(graph, opts)) p.scratch_bytes(decode_program_size(graph, capacity).bytes());
     GpuAllocPlan out;
     out.weights = p.weights;
     out.state = p.state;
@@ -694,25 +728,39 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     m->graph_ = std::move(graph);
     const ModelGraph &g = m->graph_;
 
+    // Record the decode step once: embedding of the logged token at the device
+    // position, every layer, last norm + head, greedy token appended to the log,
+    // position advanced.  (One command buffer per step in the reference:
+    // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)  Where the
+    // model allows it the step becomes one persistent kernel, else a graph of kernels.
+    I.persistent = persistent_decode_applies(g, opts);
+    if (I.persistent) {
+        const DecodeProgramSize ps = decode_program_size(g, capacity);
+        c.begin_program(ps.max_ops, ps.vector_elems, ps.attention_elems);
+        try {
+            m->encode_decode_step();
+        } catch (...) {
+            c.abort_program();
+            throw;
+        }
+        I.decode_graph = c.end_program();
+    } else {
+        c.begin_group();
+        try {
+            m->encode_decode_step();
+        } catch (...) {
+            c.abort_group();
+            throw;
+        }
+        I.decode_graph = c.end_group_retain();
+    }
+
     // The ledger must equal the preflight (crates/tuckcore/src/executor.rs:1571-1580).
     const uint64_t held = ctx->allocated_bytes() - base;
     if (held != m->plan_.total())
         throw TuckmillError(ErrorCode::Internal, g.architecture + " GPU ledger holds " + std::to_string(held) +
                                                      " but the preflight priced " + std::to_string(m->plan_.total()) +
                                                      "; refusing an unaccounted allocation");
-
-    // Record the decode step once: embedding of the logged token at the device
-    // position, every layer, last norm + head, greedy token appended to the log,
-    // position advanced.  (One command buffer per step in the reference:
-    // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)
-    c.begin_group();
-    try {
-        m->encode_decode_step();
-    } catch (...) {
-        c.abort_group();
-        throw;
-    }
-    I.decode_graph = c.end_group_retain();
     m->reset();
     return m;
 }
@@ -741,6 +789,31 @@ void EngineModel::step_ungrouped() {
                             "position " + std::to_string(pos_) + " exceeds KV capacity " + std::to_string(capacity_));
     encode_decode_step();
     pos_ += 1;
+}
+
+void EngineModel::check_device_status() {
+    Impl &I = *impl_;
+    ctx_->fence();
+    uint32_t st = 0;
+    I.status.download(0, &st, 4);
+    if (st != 0) throw TuckmillError(ErrorCode::Internal, "a decode step ran past the KV capacity on the device");
+    if (!opts_.exact && ctx_->mma_aborted())
+        throw TuckmillError(ErrorCode::Internal,
+                            "a pipeline wait of the tensor-core GEMM ran out; the prefill results are undefined");
+    if (I.sh.world > 1 && ctx_->symm_status(I.arena.buf) != 0)
+        throw TuckmillError(ErrorCode::Internal,
+                            "a peer-memory exchange wait ran out; gathered activations of a step are stale");
+    if (I.persistent) {
+        const uint32_t ps = ctx_->program_status(I.decode_graph);
+        if (ps != 0)
+            throw TuckmillError(ErrorCode::Internal,
+                                std::string("a bounded wait of the persistent decode kernel ran out (") +
+                                    ((ps & 1u) ? "activations" : "weight stage") + "); the step's results are undefined");
+    }
+}
+
+tm_cuda_graph *EngineModel::decode_program() const {
+    return impl_->persistent ? impl_->decode_graph.raw() : nullptr;
 }
 
 EngineModel::~EngineModel() {
@@ -822,6 +895,7 @@ void EngineModel::step(uint32_t token) {
 // With a row split this is a collective: every rank must call it.
 void EngineModel::logits(float *out) {
     Impl &I = *impl_;
+    check_device_status();
     if (I.sh.world > 1) {
         ctx_->all_gather_rows(I.logits, I.logits_full, I.logits_full, 1, I.head_rows);
         I.logits_full.download(0, out, graph_.vocab * 4);
@@ -886,9 +960,7 @@ std::vector<uint32_t> EngineModel::generate(const uint32_t *prompt, size_t n_pro
         }
         ctx_->fence();
     }
-    uint32_t st = 0;
-    impl_->status.download(0, &st, 4);
-    if (st != 0) throw TuckmillError(ErrorCode::Internal, "a decode step ran past the KV capacity on the device");
+    check_device_status();
     if (stats) {
         stats->ttft_ns = t_first - t_start;
         stats->decode_span_ns = t_last - t_first;

@@ -32,7 +32,24 @@ struct EngineOptions {
     // Output-row split of every projection across `world` devices (rank owns
     // rows [rank*N/world, (rank+1)*N/world)); 1 = single device.
     uint32_t shard_rank = 0, shard_world = 1;
+    // Decode steps run as ONE persistent kernel (a recorded program) where the model allows it:
+    // single device, not `exact`, attention geometries and widths the program kernel serves.
+    // false keeps the graph of per-operator kernels.
+    bool persistent = true;
 };
+
+// Whether load_with will record the decode step as a persistent program for this graph and options
+// (the plan prices the program's device memory exactly when this holds).
+bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opts);
+// What the decode program of `graph` at `capacity` positions is opened for: operators at most,
+// elements of all the vectors its operators produce, elements of its largest attention's partials
+// (the arguments of tm_cuda_begin_program / tm_cuda_program_bytes).
+struct DecodeProgramSize {
+    uint32_t max_ops = 0;
+    uint64_t vector_elems = 0, attention_elems = 0;
+    uint64_t bytes() const { return tm_cuda_program_bytes(max_ops, vector_elems, attention_elems); }
+};
+DecodeProgramSize decode_program_size(const ModelGraph &graph, size_t capacity);
 
 // Exact device bytes by class (crates/tuckcore/src/qwen35_gpu.rs:1181-1193).
 struct GpuAllocPlan {
@@ -90,6 +107,14 @@ public:
     // graph): the attribution mode of engine/metal.rs:1964-1968, used with the
     // context's per-operator profile table.
     void step_ungrouped();
+    // Throws Internal naming the wait when a bounded device-side wait ran out (tensor-core GEMM
+    // pipeline, peer-memory exchange, persistent decode program) or a step ran past the KV capacity:
+    // the results of such a dispatch are undefined and must not be returned as tokens.  Waits for
+    // the stream.
+    void check_device_status();
+    // The persistent decode program (for tm_cuda_program_status / _trace), or null when a decode step
+    // is a graph of kernels.
+    tm_cuda_graph *decode_program() const;
     // Token the last prefill(want_token) chose (blocking read).
     uint32_t prefill_token();
     // The reference's run_session loop (crates/tuckcore/src/executor.rs:870-1125)

@@ -79,6 +79,9 @@ int commit_end(tm_cuda_ctx *ctx, tm_commit *c, char *err, size_t err_cap) {
 }  // namespace
 
 int tm_op_begin(tm_cuda_ctx *ctx, const char *label, char *err, size_t err_cap) {
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED,
+                       "operator %s cannot be recorded into a persistent program", label);
     if (ctx->group_open) return TM_CUDA_OK;
     return commit_begin(ctx, &ctx->open_commit, label, err, err_cap);
 }
@@ -365,7 +368,7 @@ int tm_cuda_download_after(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, vo
 
 int tm_cuda_begin_group(tm_cuda_ctx *ctx, char *err, size_t err_cap) {
     TM_ENTER();
-    if (ctx->group_open)
+    if (ctx->group_open || ctx->program)
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "a dispatch group is already open");
     TM_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
     ctx->group_open = true;
@@ -448,6 +451,17 @@ int tm_cuda_graph_launch(tm_cuda_ctx *ctx, tm_cuda_graph *graph, char *err, size
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "graph launch with a dispatch group open");
     if (!graph || ctx->graphs.find(graph) == ctx->graphs.end())
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "graph does not belong to this context");
+    if (graph->program) {  // a persistent program: one kernel launch is the whole dispatch
+        if (ctx->program)
+            return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "program launch with a program open");
+        tm_commit c;
+        int rc = commit_begin(ctx, &c, "program", err, err_cap);
+        if (rc != TM_CUDA_OK) return rc;
+        rc = tm_step_launch(ctx, graph->program, err, err_cap);
+        if (rc != TM_CUDA_OK) return rc;
+        ctx->launches.fetch_add(1);
+        return commit_end(ctx, &c, err, err_cap);
+    }
     return launch_exec(ctx, graph->exec, graph->kernels, "graph", err, err_cap);
 }
 
@@ -457,7 +471,12 @@ void tm_cuda_graph_free(tm_cuda_ctx *ctx, tm_cuda_graph *graph) {
     if (ctx->graphs.find(graph) == ctx->graphs.end()) return;
     ctx->graphs.erase(graph);
     cudaSetDevice(ctx->device);
-    cudaGraphExecDestroy(graph->exec);
+    if (graph->program) {
+        cudaStreamSynchronize(ctx->stream);  // a launch may still be reading the operator table
+        tm_step_free(ctx, graph->program);
+    } else {
+        cudaGraphExecDestroy(graph->exec);
+    }
     delete graph;
 }
 

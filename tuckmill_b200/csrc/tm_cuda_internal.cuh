@@ -37,9 +37,12 @@ struct tm_cuda_buffer {
 // Closes the peer mappings of a symmetric buffer (no-op for ordinary buffers).
 extern "C" void tm_cuda_symm_release(tm_cuda_buffer *b);
 
+struct tm_step_program;  // a recorded decode step run by one persistent kernel (tm_cuda_step.cu)
+
 struct tm_cuda_graph {
     tm_cuda_ctx *owner = nullptr;
-    cudaGraphExec_t exec = nullptr;
+    cudaGraphExec_t exec = nullptr;      // a captured group, or
+    tm_step_program *program = nullptr;  // a persistent program
     uint64_t kernels = 0;
 };
 
@@ -81,6 +84,7 @@ struct tm_cuda_ctx {
     size_t mma_scratch_bytes = 0;
     int mma_last_bn = 0;                 // token sub-tile width of the last tensor-core GEMM launch
     void *comm = nullptr;  // multi-GPU communicator state (tm_cuda_comm.cu)
+    void *program = nullptr;  // the persistent program being recorded (tm_step_program), if any
 };
 
 // ---- error plumbing -------------------------------------------------------
@@ -177,3 +181,25 @@ inline cudaError_t tm_launch_pdl(tm_cuda_ctx *ctx, void (*kernel)(KArgs...), dim
 }
 
 cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi);
+
+// ---- persistent decode program (tm_cuda_step.cu) ----
+// While ctx->program is set, the operators a program can hold record themselves through these
+// instead of launching; every other operator refuses (tm_op_begin).
+int tm_step_record_gemv(tm_cuda_ctx *ctx, const void *q, const void *d, const float *x, float *y, const float *pro,
+                        uint32_t rows, uint32_t cols, int prologue, int epilogue, float eps, uint32_t batch, char *err,
+                        size_t err_cap);
+int tm_step_record_embed(tm_cuda_ctx *ctx, const void *q, const void *d, uint32_t rows, uint32_t cols,
+                         const uint32_t *ids, uint32_t slot, const uint32_t *pos, int bias, uint32_t ids_len,
+                         float scale, float *out, char *err, size_t err_cap);
+int tm_step_record_attention(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v, const float *qn,
+                             const float *kn, const float *inv_freq, void *kc, void *vc, float *out, float *scratch,
+                             const uint32_t *pos, uint32_t *status, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+                             uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale, int exact,
+                             char *err, size_t err_cap);
+int tm_step_record_argmax(tm_cuda_ctx *ctx, const float *x, uint32_t n, uint32_t *out, uint32_t base,
+                          const uint32_t *pos, uint32_t out_cap, uint32_t *mirror, char *err, size_t err_cap);
+int tm_step_record_norm_add(tm_cuda_ctx *ctx, const float *p, const float *w, float *x, uint32_t rows, uint32_t cols,
+                            float eps, char *err, size_t err_cap);
+int tm_step_record_pos_add(tm_cuda_ctx *ctx, uint32_t *counter, uint32_t delta, char *err, size_t err_cap);
+int tm_step_launch(tm_cuda_ctx *ctx, tm_step_program *p, char *err, size_t err_cap);
+void tm_step_free(tm_cuda_ctx *ctx, tm_step_program *p);

@@ -1059,6 +1059,7 @@ int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint3
                     char *err, size_t err_cap) {
     TM_ENTER();
     TM_CHECK_BUF(buf, ((size_t)index + 1) * 4, "counter");
+    if (ctx->program) return tm_step_record_pos_add(ctx, (uint32_t *)buf->dev + index, delta, err, err_cap);
     TM_OP_BEGIN("u32_add");
     TM_CUDA_TRY(tm_launch_pdl(ctx, u32_add_kernel, dim3(1), dim3(1), 0, (uint32_t *)buf->dev + index, delta));
     TM_OP_END(1);
@@ -1088,6 +1089,9 @@ int tm_cuda_rmsnorm_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *p, tm_cuda_buffer 
     TM_CHECK_BUF(x, (size_t)rows * cols * 4, "x");
     TM_CHECK_BUF(weight, (size_t)cols * 4, "norm weight");
     if (p == x) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "rmsnorm_add in place");
+    if (ctx->program)
+        return tm_step_record_norm_add(ctx, (const float *)p->dev, (const float *)weight->dev, (float *)x->dev, rows,
+                                       cols, eps, err, err_cap);
     TM_OP_BEGIN("rmsnorm_add");
     TM_CUDA_TRY(tm_launch_pdl(ctx, rmsnorm_add_kernel, dim3(rows), dim3(kThreads), 0, (const float *)p->dev,
                               (const float *)weight->dev, (float *)x->dev, cols, eps));
@@ -1100,6 +1104,9 @@ static int argmax_common(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, tm_cud
     if (n == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "argmax over zero elements");
     TM_CHECK_BUF(x, (size_t)n * 4, "logits");
     TM_CHECK_BUF(partial, 512, "argmax partials");
+    if (ctx->program)
+        return tm_step_record_argmax(ctx, (const float *)x->dev, n, (uint32_t *)out->dev, out_index, pos, out_cap, mirror,
+                                     err, err_cap);
     TM_OP_BEGIN("argmax");
     float *pv = (float *)partial->dev;
     uint32_t *pi = (uint32_t *)(partial->dev + 256);
@@ -1288,13 +1295,16 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
                  "decode attention scratch");
     TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
     TM_CHECK_BUF(status, 4, "status");
-    TM_OP_BEGIN("attention_decode");
     const float *qp = (const float *)q->dev, *kp = (const float *)k->dev, *vp = (const float *)v->dev;
     const float *qn = (const float *)q_norm->dev, *kn = (const float *)k_norm->dev, *fq = (const float *)inv_freq->dev;
     __half *kcp = (__half *)k_cache->dev, *vcp = (__half *)v_cache->dev;
     float *op = (float *)out->dev, *sp = (float *)scratch->dev;
     const uint32_t *pp = (const uint32_t *)pos_buf->dev + pos_index;
     uint32_t *stp = (uint32_t *)status->dev;
+    if (ctx->program)
+        return tm_step_record_attention(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads, head_dim,
+                                        n_rot, cap, window, eps, scale, exact, err, err_cap);
+    TM_OP_BEGIN("attention_decode");
     if (!exact && attn_fast_ok(heads, kv_heads, head_dim, n_rot)) {
 #define TM_FAST(G, HD)                                                                                       \
     launch_decode_fast<G, HD>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, kv_heads, n_rot, cap, window, \
@@ -1360,6 +1370,8 @@ int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_
                        heads, cap, head_dim, need, (size_t)kStaticDecodeScratchBytes);
     if (ctx->device < 0 || ctx->device >= 64)
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "device index %d outside 0..63", ctx->device);
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "this entry point launches directly; it cannot be recorded");
     const size_t plane = (size_t)kv_heads * cap * head_dim * 2;
     TM_CHECK_BUF(q, (size_t)heads * head_dim * 4, "q");
     TM_CHECK_BUF(k, (size_t)kv_heads * head_dim * 4, "k");

@@ -766,6 +766,8 @@ static int gemv_common(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, t
     a.eps = eps;
     a.prologue = prologue;
     a.epilogue = epilogue;
+    if (ctx->program)
+        return tm_step_record_gemv(ctx, a.q, a.d, a.x, a.y, a.pro, rows, cols, prologue, epilogue, eps, batch, err, err_cap);
     TM_OP_BEGIN(label);
     uint64_t kernels = 0;
     rc = gemv_batch(ctx, a, batch, &kernels, err, err_cap);
@@ -826,6 +828,9 @@ static int row_indirect(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint
         TM_CHECK_BUF(pos_buf, ((size_t)pos_index + 1) * 4, "position");
         pos = (const uint32_t *)pos_buf->dev + pos_index;
     }
+    if (ctx->program)
+        return tm_step_record_embed(ctx, w->qp, w->dp, rows, cols, (const uint32_t *)ids->dev, slot, pos, (int)bias,
+                                    (uint32_t)(ids->len / 4), scale, (float *)out->dev, err, err_cap);
     TM_OP_BEGIN("row_indirect");
     TM_CUDA_TRY(tm_launch_pdl(ctx, q8_row_indirect_kernel, dim3((cols + 255) / 256), dim3(256), 0,
                               (const signed char *)w->qp, (const __half *)w->dp, rows, cols,

@@ -68,6 +68,11 @@ _OPS = {
     "abort_group": [_P],
     "end_group_retain": [_P, C.POINTER(C.c_void_p)],
     "graph_launch": [_P, _P],
+    "begin_program": [_P, _U32, C.c_uint64, C.c_uint64],
+    "end_program": [_P, C.POINTER(C.c_void_p)],
+    "abort_program": [_P],
+    "program_status": [_P, _P, C.POINTER(C.c_uint32)],
+    "program_debug": [_P, _P, _U32, _U32],
     "fence": [_P],
     "u32_add": [_P, _P, _U32, _U32],
     "qwen35_rope_partial": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
@@ -131,6 +136,12 @@ def load_library() -> C.CDLL:
     L.tm_cuda_mma_aborted.argtypes = [_P]
     L.tm_cuda_mma_last_tile.restype = C.c_int
     L.tm_cuda_mma_last_tile.argtypes = [_P]
+    L.tm_cuda_program_bytes.restype = _SZ
+    L.tm_cuda_program_bytes.argtypes = [_U32, C.c_uint64, C.c_uint64]
+    L.tm_cuda_program_attention_elems.restype = C.c_uint64
+    L.tm_cuda_program_attention_elems.argtypes = [_U32, _U32, _U32]
+    L.tm_cuda_program_supports_gemv.argtypes = [_U32]
+    L.tm_cuda_program_supports_attention.argtypes = [_U32, _U32, _U32, _U32]
     L.tm_cuda_q8_0_packed_bytes.restype = _SZ
     L.tm_cuda_q8_0_packed_bytes.argtypes = [_U32, _U32]
     L.tm_cuda_graph_free.argtypes = [_P, _P]
@@ -241,6 +252,15 @@ class CudaGraph:
 
     def launch(self):
         self.ctx._call("graph_launch", self.handle)
+
+    def status(self) -> int:
+        """Status bits of a persistent program (1: a wait for activations ran out, 2: a weight-stage wait)."""
+        st = C.c_uint32()
+        self.ctx._call("program_status", self.handle, C.byref(st))
+        return st.value
+
+    def debug(self, sequence_skew: int = 0, spin_limit: int = 0):
+        self.ctx._call("program_debug", self.handle, sequence_skew, spin_limit)
 
     def free(self):
         if self.handle and self.ctx.handle:
@@ -455,6 +475,21 @@ class CudaContext:
     def end_group_retain(self) -> CudaGraph:
         out = C.c_void_p()
         self._call("end_group_retain", C.byref(out))
+        return CudaGraph(self, out.value)
+
+    def begin_program(self, max_ops: int, vector_elems: int = 1 << 20, attention_elems: int = 0):
+        """Open a program for at most `max_ops` operators whose outputs total `vector_elems` floats;
+        `attention_elems` from program_attention_elems() for its largest attention operator."""
+        self._call("begin_program", max_ops, vector_elems, attention_elems)
+
+    def program_attention_elems(self, heads: int, head_dim: int, cap: int) -> int:
+        return int(self._l.tm_cuda_program_attention_elems(heads, head_dim, cap))
+    def abort_program(self): self._call("abort_program")
+
+    def end_program(self) -> CudaGraph:
+        """The operators recorded since begin_program as one persistent kernel."""
+        out = C.c_void_p()
+        self._call("end_program", C.byref(out))
         return CudaGraph(self, out.value)
 
     def grouped(self, encode):

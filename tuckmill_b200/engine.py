@@ -33,7 +33,8 @@ class EngineError(RuntimeError):
 class _Options(C.Structure):
     _fields_ = [("gguf_path", C.c_char_p), ("kernels", C.c_char_p), ("device", C.c_int), ("context", C.c_uint32),
                 ("prefill_batch", C.c_uint32), ("exact", C.c_int), ("budget_bytes", C.c_uint64),
-                ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32), ("comm_id", C.c_void_p)]
+                ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32), ("comm_id", C.c_void_p),
+                ("step_graph", C.c_int)]
 
 
 class Info(C.Structure):
@@ -64,6 +65,8 @@ def load_library() -> C.CDLL:
     L.tm_engine_get_info.argtypes = [P, C.POINTER(Info)]
     L.tm_engine_cuda_ctx.restype = P
     L.tm_engine_cuda_ctx.argtypes = [P]
+    L.tm_engine_decode_program.restype = P
+    L.tm_engine_decode_program.argtypes = [P]
     L.tm_engine_reset.argtypes = [P] + E
     L.tm_engine_prefill.argtypes = [P, P, C.c_uint32, C.c_int] + E
     L.tm_engine_prefill_token.argtypes = [P, C.POINTER(C.c_uint32)] + E
@@ -106,7 +109,7 @@ def comm_id() -> bytes:
 class Engine:
     def __init__(self, gguf_path, context: int, kernels: str = "cuda", device: int = 0, prefill_batch: int = 0,
                  exact: bool = False, budget_bytes: int = 0, shard_rank: int = 0, shard_world: int = 1,
-                 comm_id: bytes | None = None):
+                 comm_id: bytes | None = None, step_graph: bool = False):
         """With shard_world > 1 every rank constructs its Engine with the same
         128-byte `comm_id` (from `comm_id()` on one rank) and then makes the same
         calls in the same order; each call is a collective."""
@@ -115,7 +118,8 @@ class Engine:
         self._kernels = kernels.encode()
         self._comm_id = C.create_string_buffer(comm_id, 128) if comm_id is not None else None
         o = _Options(self._path, self._kernels, device, context, prefill_batch, int(exact), budget_bytes,
-                     shard_rank, shard_world, C.cast(self._comm_id, C.c_void_p) if self._comm_id is not None else None)
+                     shard_rank, shard_world, C.cast(self._comm_id, C.c_void_p) if self._comm_id is not None else None,
+                     int(step_graph))
         h, err = C.c_void_p(), C.create_string_buffer(1024)
         _check(self._l.tm_engine_load(C.byref(o), C.byref(h), err, 1024), err)
         self.handle = h
@@ -133,6 +137,24 @@ class Engine:
 
     def cuda_ctx(self) -> int:
         return int(self._l.tm_engine_cuda_ctx(self.handle))
+
+    def decode_program(self) -> int:
+        """Handle of the persistent decode program (0 when a step is a graph of kernels)."""
+        return int(self._l.tm_engine_decode_program(self.handle) or 0)
+
+    def program_trace(self):
+        """Per-operator time stamps of the last decode step (tm_cuda_program_trace): (kinds, stamps[n][4])."""
+        L = _cuda.load_library()
+        cap = 4096
+        out = (C.c_uint64 * (cap * 8))()
+        kinds = (C.c_uint32 * cap)()
+        err = C.create_string_buffer(256)
+        L.tm_cuda_program_trace.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_char_p, C.c_size_t]
+        rc = L.tm_cuda_program_trace(self.cuda_ctx(), self.decode_program(), out, cap, kinds, err, 256)
+        if rc:
+            raise _cuda.CudaError(rc, err.value.decode())
+        n = self.info.layers * 8 + 8
+        return np.array(kinds[:n]), np.array(out[:n * 8], dtype=np.uint64).reshape(n, 8)
 
     def stream(self) -> int:
         return int(_cuda.load_library().tm_cuda_stream(self.cuda_ctx()) or 0)

@@ -208,6 +208,11 @@ QWEN3_8B = DecoderShape("qwen3", 36, 4096, 12288, 32, 8, 128, 151936, rope_base=
 TINY_QWEN3 = DecoderShape("qwen3", 2, 128, 256, 4, 2, 32, 512, rope_base=1e6, context=256)
 TINY_GEMMA3 = DecoderShape("gemma3", 6, 64, 128, 4, 1, 32, 256, rope_base=1e6, window=8,
                            tied_head=True, context=256)
+# Small decoders with the head sizes of the benchmark models (128 and 256), which the persistent
+# decode kernel serves; the two above (head size 32) take the per-operator graph.
+SMALL_QWEN3 = DecoderShape("qwen3", 3, 256, 512, 4, 2, 128, 1024, rope_base=1e6, context=512)
+SMALL_GEMMA3 = DecoderShape("gemma3", 6, 128, 320, 4, 1, 256, 512, rope_base=1e6, window=40,
+                            tied_head=True, context=512)
 
 
 def _gguf_str(s: str) -> bytes:

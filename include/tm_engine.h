@@ -55,10 +55,10 @@ typedef struct {
      * collective that all ranks make in the same order. */
     uint32_t shard_rank, shard_world;
     const void *comm_id;
-    /* 0 (default): a decode step runs as ONE persistent kernel where the model allows it
-     * (single device, not exact, attention shapes the program kernel serves); 1: always
-     * the recorded graph of per-operator kernels. */
-    int step_graph;
+    /* 0 (default): a decode step replays the recorded graph of per-operator kernels; 1: it runs
+     * as ONE persistent kernel (tm_cuda_begin_program) where the model allows it (single device,
+     * not exact, attention shapes the program kernel serves), the graph otherwise. */
+    int persistent_step;
 } tm_engine_options;
 
 /* 128 opaque bytes naming a new communicator (tm_cuda_comm_unique_id). */

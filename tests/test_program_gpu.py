@@ -210,8 +210,9 @@ def test_engine_decodes_on_the_program_like_the_graph_and_the_oracle(ctx, oracle
     cpu.reset(256)
     ref, margins = cpu.generate_greedy(prompt, 100, chunk=32)
     runs = {}
-    for name, step_graph in (("program", False), ("graph", True)):
-        eng = E.Engine(path, context=256, prefill_batch=32, step_graph=step_graph)
+    for name, persistent in (("program", True), ("graph", False)):
+        eng = E.Engine(path, context=256, prefill_batch=32, persistent_step=persistent)
+        assert bool(eng.decode_program()) == persistent
         got, stats = eng.generate(prompt, 100)
         assert stats.generated == 100
         # one launch per decode step on the program; several per step on the graph

@@ -103,7 +103,7 @@ int tm_engine_load(const tm_engine_options *o, tm_engine **out, char *err, size_
         EngineOptions eo;
         eo.prefill_batch = o->prefill_batch ? o->prefill_batch : kPrefillBatchDefault;
         eo.exact = o->exact != 0;
-        eo.persistent = o->step_graph == 0;
+        eo.persistent = o->persistent_step != 0;
         eo.shard_world = o->shard_world ? o->shard_world : 1;
         eo.shard_rank = o->shard_rank;
         if (eo.shard_world > 1) {

@@ -613,9 +613,9 @@ DecodeProgramSize decode_program_size(const ModelGraph &graph, size_t capacity) 
 }
 
 bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opts) {
-    if (!opts.persistent || opts.exact || opts.shard_world > 1) return false;
-    if (const char *e = std::getenv("TM_ENGINE_PERSISTENT"))
-        if (e[0] == '0') return false;
+    bool want = opts.persistent;
+    if (const char *e = std::getenv("TM_ENGINE_PERSISTENT")) want = e[0] != '0';  // experiments: overrides the option
+    if (!want || opts.exact || opts.shard_world > 1) return false;
     if (!tm_cuda_program_supports_gemv((uint32_t)graph.hidden)) return false;
     for (const LayerSpec &l : graph.layers) {
         const AttentionSpec &m = l.mixer;

@@ -32,10 +32,11 @@ struct EngineOptions {
     // Output-row split of every projection across `world` devices (rank owns
     // rows [rank*N/world, (rank+1)*N/world)); 1 = single device.
     uint32_t shard_rank = 0, shard_world = 1;
-    // Decode steps run as ONE persistent kernel (a recorded program) where the model allows it:
-    // single device, not `exact`, attention geometries and widths the program kernel serves.
-    // false keeps the graph of per-operator kernels.
-    bool persistent = true;
+    // true: decode steps run as ONE persistent kernel (a recorded program, include/tm_cuda.h) where
+    // the model allows it: single device, not `exact`, attention geometries and widths the program
+    // kernel serves.  Off by default: on the decoders measured so far the recorded graph of
+    // per-operator kernels is the faster of the two.
+    bool persistent = false;
 };
 
 // Whether load_with will record the decode step as a persistent program for this graph and options

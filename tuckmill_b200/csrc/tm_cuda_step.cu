@@ -67,10 +67,11 @@ constexpr uint32_t kMaxSlots = 12;
 constexpr uint32_t kMaxQuads = 12;              // activation quads per consumer thread: cols <= 12288
 constexpr uint32_t kNormQuads = 8;              // ... of a vector that is RMS-normed on the way in: cols <= 8192
 constexpr uint32_t kPollQuads = 4;              // quads a thread polls for at a time
+constexpr uint32_t kUnitBatch = 8;              // units a CTA multiplies between two syncs of its consumer warps
 constexpr uint32_t kAttnSub = 10752;            // shared memory of one attention warp group
 constexpr uint32_t kAttnSplit = 64;             // keys per attention item (the fast decode kernel's split)
 constexpr uint32_t kDescWords = 64;             // a descriptor is copied to shared memory as 64 x 4 bytes
-constexpr uint32_t kTailBytes = 2 * kMaxSlots * 8 + 2 * kCWarps * 16 * 4 + 32 * 4 + 2 * kDescWords * 4 + 64;
+constexpr uint32_t kTailBytes = 2 * kMaxSlots * 8 + 2 * kUnitBatch * kCWarps * 16 * 4 + 32 * 4 + 2 * kDescWords * 4 + 64;
 constexpr uint32_t kArgmaxNone = 0xFFFFFFFFu;
 
 enum : uint32_t { STEP_EMBED = 1, STEP_GEMV = 2, STEP_ATTN = 3, STEP_ARGMAX = 4, STEP_NORM_ADD = 5, STEP_POS_ADD = 6 };
@@ -115,6 +116,7 @@ struct step_params {
     u64 *argmax_ll;         // [2 * grid] flagged per-CTA candidates of the greedy choice
     u64 *attn_ll;           // flagged attention partials, shared by all attention operators
     uint32_t n_slots, xs_bytes, spin_limit;
+    uint32_t l2_ahead;      // stages the L2 prefetch runs ahead of the ring
     u64 *trace;             // optional: [n_ops][8] nanosecond stamps of CTA 0 (tm_cuda_program_trace)
 };
 
@@ -131,7 +133,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
     uint32_t done;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
         : "r"(addr), "r"(parity)
         : "memory");
@@ -277,9 +279,11 @@ __device__ __forceinline__ void digitize_quad(const float (&v)[4], uint32_t c, u
 }
 
 // Polls (or plainly loads) this thread's quads i0 .. i0 + kPollQuads - 1 of one vector.
+template <uint32_t NQ>
 __device__ __forceinline__ void fetch_quads(const step_params &P, const float *plain, const u64 *ll, uint32_t seq,
-                                            uint32_t i0, uint32_t cols, float fill, float4 (&out)[kPollQuads],
+                                            uint32_t i0, uint32_t cols, float fill, float4 (&out)[NQ],
                                             volatile uint32_t *flags) {
+    constexpr uint32_t kPollQuads = NQ;
     const int tid = threadIdx.x;
     ll_quad q[kPollQuads];
     bool need[kPollQuads];
@@ -307,7 +311,7 @@ __device__ __forceinline__ void fetch_quads(const step_params &P, const float *p
     }
 }
 
-__device__ void stage_activations(const step_params &P, const step_op &op, uint32_t oi, unsigned char *xs, float *red,
+__device__ __forceinline__ void stage_activations(const step_params &P, const step_op &op, uint32_t oi, unsigned char *xs, float *red,
                                   volatile uint32_t *flags) {
     const uint32_t cols = op.cols, plane = digit_plane(cols);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -318,28 +322,27 @@ __device__ void stage_activations(const step_params &P, const step_op &op, uint3
     float *coef = (float *)(xs + 3u * (size_t)plane);
     const uint32_t warp_col0 = (tid & ~31u) * 4u;  // first column of this warp's quad 0
     if (prologue == TM_CUDA_PRO_RMSNORM) {
-        // the whole row waits for its sum of squares: kept in registers (at most kNormQuads per thread)
-        float4 kept[kNormQuads];
-        float4 wts[kPollQuads];  // the norm weights of the first quads travel with the activations
+        // The whole row waits for its sum of squares.  A thread keeps its first kKeepQuads quads in
+        // registers (rows up to 2048 columns entirely); further quads are polled for the sum and
+        // fetched again for the digits (valid by then: one more L2 trip, no more registers).
+        constexpr uint32_t kKeepQuads = 2;
+        float4 kept[kKeepQuads], wts[kKeepQuads];
 #pragma unroll
-        for (uint32_t i = 0; i < kPollQuads; ++i) {
+        for (uint32_t i = 0; i < kKeepQuads; ++i) {
             const uint32_t c = (i * kCThreads + tid) * 4u;
             wts[i] = c < cols ? __ldg((const float4 *)(pro + c)) : make_float4(1.f, 1.f, 1.f, 1.f);
         }
         float sq = 0.0f;
+        fetch_quads<kKeepQuads>(P, x, op.in[0], xseq, 0, cols, 0.0f, kept, flags);
 #pragma unroll
-        for (uint32_t i0 = 0; i0 < kNormQuads; i0 += kPollQuads) {
-            float4 vs[kPollQuads];
-            if (i0 * kCThreads * 4u + warp_col0 < cols) fetch_quads(P, x, op.in[0], xseq, i0, cols, 0.0f, vs, flags);
-            else {
+        for (uint32_t j = 0; j < kKeepQuads; ++j) sq = tmdev::sumsq_quad(sq, kept[j]);
+#pragma unroll 1
+        for (uint32_t i0 = kKeepQuads; i0 < kNormQuads; i0 += kKeepQuads) {
+            if (i0 * kCThreads * 4u + warp_col0 >= cols) break;
+            float4 vs[kKeepQuads];
+            fetch_quads<kKeepQuads>(P, x, op.in[0], xseq, i0, cols, 0.0f, vs, flags);
 #pragma unroll
-                for (uint32_t j = 0; j < kPollQuads; ++j) vs[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (uint32_t j = 0; j < kPollQuads; ++j) {
-                kept[i0 + j] = vs[j];
-                sq = tmdev::sumsq_quad(sq, vs[j]);
-            }
+            for (uint32_t j = 0; j < kKeepQuads; ++j) sq = tmdev::sumsq_quad(sq, vs[j]);
         }
         trace_stamp(P, oi, 3);
 #pragma unroll
@@ -351,15 +354,29 @@ __device__ void stage_activations(const step_params &P, const step_op &op, uint3
         for (int w = 0; w < kCWarps; ++w) t += red[w];
         const float inv_rms = 1.0f / sqrtf(t / (float)cols + op.eps);
 #pragma unroll
-        for (uint32_t i = 0; i < kNormQuads; ++i) {
+        for (uint32_t i = 0; i < kKeepQuads; ++i) {
             const uint32_t c = (i * kCThreads + tid) * 4u;
             if (i * kCThreads * 4u + warp_col0 < cols) {  // whole warps digitise together
-                float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (i < kPollQuads) w4 = wts[i];
-                else if (c < cols) w4 = __ldg((const float4 *)(pro + c));
-                const float v[4] = {kept[i].x * inv_rms * w4.x, kept[i].y * inv_rms * w4.y, kept[i].z * inv_rms * w4.z,
-                                    kept[i].w * inv_rms * w4.w};
+                const float v[4] = {kept[i].x * inv_rms * wts[i].x, kept[i].y * inv_rms * wts[i].y,
+                                    kept[i].z * inv_rms * wts[i].z, kept[i].w * inv_rms * wts[i].w};
                 digitize_quad(v, c, cols, plane, dig, coef, lane);
+            }
+        }
+#pragma unroll 1
+        for (uint32_t i0 = kKeepQuads; i0 < kNormQuads; i0 += kKeepQuads) {
+            if (i0 * kCThreads * 4u + warp_col0 >= cols) break;
+            float4 vs[kKeepQuads];
+            fetch_quads<kKeepQuads>(P, x, op.in[0], xseq, i0, cols, 0.0f, vs, flags);
+#pragma unroll
+            for (uint32_t j = 0; j < kKeepQuads; ++j) {
+                const uint32_t c = ((i0 + j) * kCThreads + tid) * 4u;
+                if ((i0 + j) * kCThreads * 4u + warp_col0 < cols) {
+                    float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (c < cols) w4 = __ldg((const float4 *)(pro + c));
+                    const float v[4] = {vs[j].x * inv_rms * w4.x, vs[j].y * inv_rms * w4.y, vs[j].z * inv_rms * w4.z,
+                                        vs[j].w * inv_rms * w4.w};
+                    digitize_quad(v, c, cols, plane, dig, coef, lane);
+                }
             }
         }
     } else {
@@ -368,8 +385,8 @@ __device__ void stage_activations(const step_params &P, const step_op &op, uint3
         for (uint32_t i0 = 0; i0 < kMaxQuads; i0 += kPollQuads) {
             if (i0 * kCThreads * 4u + warp_col0 >= cols) break;  // this warp has no more columns
             float4 vs[kPollQuads], ps[kPollQuads];
-            fetch_quads(P, x, op.in[0], xseq, i0, cols, 0.0f, vs, flags);
-            if (act) fetch_quads(P, pro, op.in[1], pseq, i0, cols, 1.0f, ps, flags);
+            fetch_quads<kPollQuads>(P, x, op.in[0], xseq, i0, cols, 0.0f, vs, flags);
+            if (act) fetch_quads<kPollQuads>(P, pro, op.in[1], pseq, i0, cols, 1.0f, ps, flags);
             if (i0 == 0) trace_stamp(P, oi, 3);
 #pragma unroll
             for (uint32_t j = 0; j < kPollQuads; ++j) {
@@ -393,7 +410,7 @@ __device__ void stage_activations(const step_params &P, const step_op &op, uint3
 // ---- one GEMV operator, consumer side ------------------------------------------------
 // `n` counts the stages this CTA has consumed since the kernel began (the producer counts the same
 // sequence): stage n sits in ring slot n % n_slots with phase parity (n / n_slots) & 1.
-__device__ void gemv_consume(const step_params &P, const step_op &op, uint32_t oi, unsigned char *xs,
+__device__ __forceinline__ void gemv_consume(const step_params &P, const step_op &op, uint32_t oi, unsigned char *xs,
                              unsigned char *slots, uint64_t *full, uint64_t *empty, float *partial,
                              volatile uint32_t *flags, uint32_t &n, uint32_t &pbuf) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
@@ -409,92 +426,106 @@ __device__ void gemv_consume(const step_params &P, const step_op &op, uint32_t o
     const uint32_t seq = P.seq_base + oi, old_seq = P.seq_base + op.in_op[2] + P.seq_skew;
     const unsigned char *coef_base = xs + 3u * (size_t)plane;
     bool first_unit = true;
-    for (uint32_t u = (blockIdx.x + gridDim.x - op.first_cta) % gridDim.x; u < n_units; u += gridDim.x) {
-        // the residual value of this thread's row, if any, travels while the unit is multiplied
+    const uint32_t u_first = (blockIdx.x + gridDim.x - op.first_cta) % gridDim.x;
+    // Units in batches of up to kUnitBatch: every warp leaves its partial row sums of each unit in shared
+    // memory, ONE sync ends the batch, then thread (unit j, row r) adds the warps' partials in order,
+    // adds the residual value if the operator accumulates, and publishes the row.
+    for (uint32_t u0 = u_first; u0 < n_units; u0 += gridDim.x * kUnitBatch) {
+        const uint32_t left = (n_units - u0 + gridDim.x - 1u) / gridDim.x;
+        const uint32_t nbu = left < kUnitBatch ? left : kUnitBatch;
+        // the residual value of this thread's row, if any, travels while the batch is multiplied
         float old = 0.0f;
         u64 oldw = 0;
-        const uint32_t my_row = u * 16u + (uint32_t)tid;
-        if (add && tid < 16 && my_row < rows) {
+        const uint32_t my_row = (u0 + ((uint32_t)tid >> 4) * gridDim.x) * 16u + ((uint32_t)tid & 15u);
+        const bool mine = (uint32_t)tid < nbu * 16u && my_row < rows;
+        if (add && mine) {
             if (oldl) oldw = ll_load(oldl + my_row);
             else old = __ldcg(y + my_row);
         }
-        float acc0 = 0.0f, acc1 = 0.0f;
-        for (uint32_t s = 0; s < n_stages; ++s, ++n) {
-            const uint32_t slot = n % P.n_slots, parity = (n / P.n_slots) & 1u;
-            const bool ok = mbar_wait(&full[slot], parity, flags, P.spin_limit, P.status);
-            if (first_unit && s == 0) trace_stamp(P, oi, 4);
-            const uint32_t base = smem_u32(slots + (size_t)slot * kSlotBytes);
-            // This warp multiplies the chunk pair (2 warp, 2 warp + 1) of the stage.  Rows are dense in shared
-            // memory (a multiple of 128 bytes apart), so rows g and g + 1 of one chunk would meet in the same
-            // banks: even rows fetch the pair's first chunk while odd rows fetch its second, then the other
-            // way round -- every 16-byte read of a quarter warp lands in its own bank group -- and each lane
-            // keeps its own rows' two chunks apart again (no data moves between lanes).
-            const uint32_t lc0 = 2u * (uint32_t)warp, par = (uint32_t)g & 1u;
-            const uint32_t ch_a = s * kStageChunks + lc0;
-            if (ok && ch_a < n_chunks) {
-                const uint32_t ra = base + (uint32_t)g * rs + (uint32_t)t4 * 16u, rb = ra + 8u * rs;
-                const uint32_t first = (lc0 + par) * kChunkCols, second = (lc0 + (par ^ 1u)) * kChunkCols;
-                int4 a1, a2, b1, b2;
-                uint32_t sa, sb;  // the pair's four block scales of rows g and g + 8 (8 bytes each, chunk-major)
-                asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a1.x), "=r"(a1.y), "=r"(a1.z), "=r"(a1.w) : "r"(ra + first));
-                asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b1.x), "=r"(b1.y), "=r"(b1.z), "=r"(b1.w) : "r"(rb + first));
-                asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a2.x), "=r"(a2.y), "=r"(a2.z), "=r"(a2.w) : "r"(ra + second));
-                asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b2.x), "=r"(b2.y), "=r"(b2.z), "=r"(b2.w) : "r"(rb + second));
-                const uint32_t soff = base + kQuantBytes + lc0 * 4u + (uint32_t)(t4 >> 1) * 2u;
-                {   // this lane's block (t4 / 2) of both chunks: two f16 scales 4 bytes apart, for each row
-                    unsigned short s0, s1, s2, s3;
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0) : "r"(soff + (uint32_t)g * kScaleStride));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s1) : "r"(soff + 4u + (uint32_t)g * kScaleStride));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s2) : "r"(soff + (uint32_t)(g + 8) * kScaleStride));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s3) : "r"(soff + 4u + (uint32_t)(g + 8) * kScaleStride));
-                    sa = (uint32_t)s0 | ((uint32_t)s1 << 16);
-                    sb = (uint32_t)s2 | ((uint32_t)s3 << 16);
+        float *pb = partial + pbuf * (kUnitBatch * kCWarps * 16);
+        for (uint32_t j = 0; j < nbu; ++j) {
+            const uint32_t u = u0 + j * gridDim.x;
+            (void)u;
+            float acc0 = 0.0f, acc1 = 0.0f;
+            for (uint32_t s = 0; s < n_stages; ++s, ++n) {
+                const uint32_t slot = n % P.n_slots, parity = (n / P.n_slots) & 1u;
+                const bool ok = mbar_wait(&full[slot], parity, flags, P.spin_limit, P.status);
+                    if (first_unit && s == 0) trace_stamp(P, oi, 4);
+                const uint32_t base = smem_u32(slots + (size_t)slot * kSlotBytes);
+                // This warp multiplies the chunk pair (2 warp, 2 warp + 1) of the stage.  Rows are dense in shared
+                // memory (a multiple of 128 bytes apart), so rows g and g + 1 of one chunk would meet in the same
+                // banks: even rows fetch the pair's first chunk while odd rows fetch its second, then the other
+                // way round -- every 16-byte read of a quarter warp lands in its own bank group -- and each lane
+                // keeps its own rows' two chunks apart again (no data moves between lanes).
+                const uint32_t lc0 = 2u * (uint32_t)warp, par = (uint32_t)g & 1u;
+                const uint32_t ch_a = s * kStageChunks + lc0;
+                if (ok && ch_a < n_chunks) {
+                    const uint32_t ra = base + (uint32_t)g * rs + (uint32_t)t4 * 16u, rb = ra + 8u * rs;
+                    const uint32_t first = (lc0 + par) * kChunkCols, second = (lc0 + (par ^ 1u)) * kChunkCols;
+                    int4 a1, a2, b1, b2;
+                    uint32_t sa, sb;  // the pair's four block scales of rows g and g + 8 (8 bytes each, chunk-major)
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a1.x), "=r"(a1.y), "=r"(a1.z), "=r"(a1.w) : "r"(ra + first));
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b1.x), "=r"(b1.y), "=r"(b1.z), "=r"(b1.w) : "r"(rb + first));
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(a2.x), "=r"(a2.y), "=r"(a2.z), "=r"(a2.w) : "r"(ra + second));
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(b2.x), "=r"(b2.y), "=r"(b2.z), "=r"(b2.w) : "r"(rb + second));
+                    const uint32_t soff = base + kQuantBytes + lc0 * 4u + (uint32_t)(t4 >> 1) * 2u;
+                    {   // this lane's block (t4 / 2) of both chunks: two f16 scales 4 bytes apart, for each row
+                        unsigned short s0, s1, s2, s3;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0) : "r"(soff + (uint32_t)g * kScaleStride));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s1) : "r"(soff + 4u + (uint32_t)g * kScaleStride));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s2) : "r"(soff + (uint32_t)(g + 8) * kScaleStride));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s3) : "r"(soff + 4u + (uint32_t)(g + 8) * kScaleStride));
+                        sa = (uint32_t)s0 | ((uint32_t)s1 << 16);
+                        sb = (uint32_t)s2 | ((uint32_t)s3 << 16);
+                    }
+                    const bool two = ch_a + 1u < n_chunks;
+                    const uint32_t c0 = ch_a * kChunkCols + (uint32_t)t4 * 16u;
+                    int4 bx0 = make_int4(0, 0, 0, 0), bx1 = bx0;
+                    if (b_live) {
+                        bx0 = *(const int4 *)(xs + (size_t)(g & 3) * plane + c0);
+                        if (two) bx1 = *(const int4 *)(xs + (size_t)(g & 3) * plane + c0 + kChunkCols);
+                    }
+                    const float2 cx0 = *(const float2 *)(coef_base + ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
+                    const float2 cx1 = two ? *(const float2 *)(coef_base + ((size_t)((c0 + kChunkCols) >> 5) * 4u + 2u * (t4 & 1)) * 4u)
+                                           : make_float2(0.f, 0.f);
+                    // chunk h of the pair came with load `h == par ? first : second`
+                    const int4 qa0 = par ? a2 : a1, qb0 = par ? b2 : b1, qa1 = par ? a1 : a2, qb1 = par ? b1 : b2;
+                    int d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0}, d3[4] = {0, 0, 0, 0};
+                    mma_s8(d0, qa0.x, qb0.x, qa0.y, qb0.y, bx0.x, bx0.y);
+                    mma_s8(d1, qa0.z, qb0.z, qa0.w, qb0.w, bx0.z, bx0.w);
+                    mma_s8(d2, qa1.x, qb1.x, qa1.y, qb1.y, bx1.x, bx1.y);
+                    mma_s8(d3, qa1.z, qb1.z, qa1.w, qb1.w, bx1.z, bx1.w);
+                    const float va0 = fmaf((float)(d0[1] + d1[1]), cx0.y, (float)(d0[0] + d1[0]) * cx0.x);
+                    const float vb0 = fmaf((float)(d0[3] + d1[3]), cx0.y, (float)(d0[2] + d1[2]) * cx0.x);
+                    const float va1 = fmaf((float)(d2[1] + d3[1]), cx1.y, (float)(d2[0] + d3[0]) * cx1.x);
+                    const float vb1 = fmaf((float)(d2[3] + d3[3]), cx1.y, (float)(d2[2] + d3[2]) * cx1.x);
+                    const float2 fa = __half22float2(*(const __half2 *)&sa), fb = __half22float2(*(const __half2 *)&sb);
+                    acc0 = fmaf(fa.x, va0, acc0);
+                    acc1 = fmaf(fb.x, vb0, acc1);
+                    if (two) {  // past the last chunk the scale bytes are whatever the slot held before
+                        acc0 = fmaf(fa.y, va1, acc0);
+                        acc1 = fmaf(fb.y, vb1, acc1);
+                    }
                 }
-                const bool two = ch_a + 1u < n_chunks;
-                const uint32_t c0 = ch_a * kChunkCols + (uint32_t)t4 * 16u;
-                int4 bx0 = make_int4(0, 0, 0, 0), bx1 = bx0;
-                if (b_live) {
-                    bx0 = *(const int4 *)(xs + (size_t)(g & 3) * plane + c0);
-                    if (two) bx1 = *(const int4 *)(xs + (size_t)(g & 3) * plane + c0 + kChunkCols);
-                }
-                const float2 cx0 = *(const float2 *)(coef_base + ((size_t)(c0 >> 5) * 4u + 2u * (t4 & 1)) * 4u);
-                const float2 cx1 = two ? *(const float2 *)(coef_base + ((size_t)((c0 + kChunkCols) >> 5) * 4u + 2u * (t4 & 1)) * 4u)
-                                       : make_float2(0.f, 0.f);
-                // chunk h of the pair came with load `h == par ? first : second`
-                const int4 qa0 = par ? a2 : a1, qb0 = par ? b2 : b1, qa1 = par ? a1 : a2, qb1 = par ? b1 : b2;
-                int d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0}, d3[4] = {0, 0, 0, 0};
-                mma_s8(d0, qa0.x, qb0.x, qa0.y, qb0.y, bx0.x, bx0.y);
-                mma_s8(d1, qa0.z, qb0.z, qa0.w, qb0.w, bx0.z, bx0.w);
-                mma_s8(d2, qa1.x, qb1.x, qa1.y, qb1.y, bx1.x, bx1.y);
-                mma_s8(d3, qa1.z, qb1.z, qa1.w, qb1.w, bx1.z, bx1.w);
-                const float va0 = fmaf((float)(d0[1] + d1[1]), cx0.y, (float)(d0[0] + d1[0]) * cx0.x);
-                const float vb0 = fmaf((float)(d0[3] + d1[3]), cx0.y, (float)(d0[2] + d1[2]) * cx0.x);
-                const float va1 = fmaf((float)(d2[1] + d3[1]), cx1.y, (float)(d2[0] + d3[0]) * cx1.x);
-                const float vb1 = fmaf((float)(d2[3] + d3[3]), cx1.y, (float)(d2[2] + d3[2]) * cx1.x);
-                const float2 fa = __half22float2(*(const __half2 *)&sa), fb = __half22float2(*(const __half2 *)&sb);
-                acc0 = fmaf(fa.x, va0, acc0);
-                acc1 = fmaf(fb.x, vb0, acc1);
-                acc0 = fmaf(fa.y, va1, acc0);
-                acc1 = fmaf(fb.y, vb1, acc1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);  // this warp is done with the stage (one arrival per warp frees it)
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);  // this warp is done with the stage (one arrival per warp frees it)
-        }
-        if (first_unit) trace_stamp(P, oi, 5);
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-        float *pb = partial + pbuf * (kCWarps * 16);
-        if (t4 == 0) {
-            pb[warp * 16 + g] = acc0;
-            pb[warp * 16 + g + 8] = acc1;
+            if (first_unit) trace_stamp(P, oi, 5);
+            first_unit = false;
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+            if (t4 == 0) {
+                pb[(j * kCWarps + warp) * 16 + g] = acc0;
+                pb[(j * kCWarps + warp) * 16 + g + 8] = acc1;
+            }
         }
         consumer_sync();
-        if (tid < 16 && my_row < rows) {
+        if (mine) {
             float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kCWarps; ++w) v += pb[w * 16 + tid];
+            for (int w = 0; w < kCWarps; ++w) v += pb[(((uint32_t)tid >> 4) * kCWarps + w) * 16 + (tid & 15)];
             if (add) {
                 if (oldl) {
                     uint32_t spin = 0;
@@ -508,79 +539,122 @@ __device__ void gemv_consume(const step_params &P, const step_op &op, uint32_t o
                 if (plain) y[my_row] = v;
             }
         }
-        if (first_unit) trace_stamp(P, oi, 6);
-        first_unit = false;
-        pbuf ^= 1u;  // the next unit writes the other buffer; its sync orders this one's readers
+        if (u0 == u_first) trace_stamp(P, oi, 6);
+        pbuf ^= 1u;  // the next batch writes the other buffer; its sync orders this one's readers
     }
 }
 
 // ---- weight producer -------------------------------------------------------------------
-// Returns the number of stages it requested.
-__device__ uint32_t producer_loop(const step_params &P, unsigned char *slots, uint64_t *full, uint64_t *empty,
+// This CTA's weight stages in program order: (operator, unit, stage of the unit).
+struct stage_cursor {
+    uint32_t oi, u, s, count;  // count: stages before this one
+    uint32_t rows, cols, n_units, n_stages;
+    const step_op *op;
+    __device__ bool seek(const step_params &P) {  // position on the first unit of operator `oi` or a later one
+        for (; oi < P.n_ops; ++oi) {
+            op = P.ops + oi;
+            if (op->kind != STEP_GEMV) continue;
+            rows = op->rows;
+            cols = op->cols;
+            n_units = (rows + 15u) / 16u;
+            n_stages = (cols / kChunkCols + kStageChunks - 1u) / kStageChunks;
+            u = (blockIdx.x + gridDim.x - op->first_cta) % gridDim.x;
+            s = 0;
+            if (u < n_units) return true;
+        }
+        return false;
+    }
+    __device__ bool next(const step_params &P) {
+        ++count;
+        if (++s < n_stages) return true;
+        s = 0;
+        u += gridDim.x;
+        if (u < n_units) return true;
+        ++oi;
+        return seek(P);
+    }
+};
+
+// Stages run through two cursors: the far one asks L2 for a stage (tensor-map prefetch, no shared
+// memory involved) `l2_ahead` stages before the near one copies it into the ring.  The ring alone
+// (ten stages) covers about four microseconds of the HBM stream; while the consumers stage
+// activations or run attention it fills up and the stream would stop -- L2 keeps it going.
+// Returns the number of stages requested into the ring.
+__device__ __forceinline__ uint32_t producer_loop(const step_params &P, unsigned char *slots, uint64_t *full, uint64_t *empty,
                                   volatile uint32_t *flags) {
     const int lane = threadIdx.x & 31;
-    uint32_t n = 0;
-    for (uint32_t oi = 0; oi < P.n_ops && !flags[0]; ++oi) {
-        const step_op &op = P.ops[oi];
-        if (op.kind != STEP_GEMV) continue;
-        const uint32_t rows = op.rows, cols = op.cols, nb = cols / 32u;
-        const uint32_t n_units = (rows + 15u) / 16u, n_chunks = cols / kChunkCols;
-        const uint32_t n_stages = (n_chunks + kStageChunks - 1u) / kStageChunks;
+    stage_cursor near = {}, far = {};
+    bool near_ok = near.seek(P), far_ok = far.seek(P);
+    uint32_t traced = 0xFFFFFFFFu;
+    while (near_ok && !flags[0]) {
+        while (far_ok && far.count < near.count + P.l2_ahead) {
+            const uint32_t ch0 = far.s * kStageChunks;
+            if (lane == 0)
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(far.op->wmap),
+                             "r"((int)(ch0 * (kChunkCols / 4u))), "r"((int)(far.u * 16u))
+                             : "memory");
+            else if ((uint32_t)lane <= 16u && far.u * 16u + (uint32_t)lane - 1u < far.rows)  // the rows' block scales
+                asm volatile("prefetch.global.L2 [%0];" ::"l"((const unsigned char *)far.op->p[1] +
+                                                               ((size_t)(far.u * 16u + (uint32_t)lane - 1u) * (far.cols / 32u) +
+                                                                (size_t)ch0 * 2u) * 2u));
+            far_ok = far.next(P);
+        }
+        const step_op &op = *near.op;
+        const uint32_t n = near.count, u = near.u, cols = near.cols, nb = cols / 32u;
+        const uint32_t n_chunks = cols / kChunkCols;
         const unsigned char *d = (const unsigned char *)op.p[1];
-        if (P.trace != nullptr && blockIdx.x == 0 && lane == 0) {  // when the producer reached this operator
+        const uint32_t unit_rows = min(16u, near.rows - u * 16u);
+        const uint32_t slot = n % P.n_slots, parity = ((n / P.n_slots) & 1u) ^ 1u;
+        // the slot's previous tenant has been read by every consumer warp
+        if (!mbar_wait(&empty[slot], parity, flags, P.spin_limit, P.status)) return n;
+        if (P.trace != nullptr && blockIdx.x == 0 && lane == 0 && traced != near.oi) {  // when the operator's first stage was requested
             u64 t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            P.trace[(size_t)oi * 8 + 7] = t;
+            P.trace[(size_t)near.oi * 8 + 7] = t;
+            traced = near.oi;
         }
-        for (uint32_t u = (blockIdx.x + gridDim.x - op.first_cta) % gridDim.x; u < n_units; u += gridDim.x) {
-            const uint32_t unit_rows = min(16u, rows - u * 16u);
-            for (uint32_t s = 0; s < n_stages; ++s, ++n) {
-                const uint32_t slot = n % P.n_slots, parity = ((n / P.n_slots) & 1u) ^ 1u;
-                // the slot's previous tenant has been read by every consumer warp
-                if (!mbar_wait(&empty[slot], parity, flags, P.spin_limit, P.status)) return n;
-                const uint32_t ch0 = s * kStageChunks, nch = min(kStageChunks, n_chunks - ch0);
-                unsigned char *dst = slots + (size_t)slot * kSlotBytes;
-                if (lane == 0) {
-                    // the whole box arrives (columns and rows past the matrix as zeros), so the stage's
-                    // byte count does not depend on where it sits
-                    mbar_expect_tx(&full[slot], 16u * op.row_stride);
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-                            smem_u32(dst)),
-                        "l"(op.wmap), "r"(smem_u32(&full[slot])), "r"((int)(ch0 * (kChunkCols / 4u))), "r"((int)(u * 16u))
-                        : "memory");
+        const uint32_t ch0 = near.s * kStageChunks, nch = min(kStageChunks, n_chunks - ch0);
+        unsigned char *dst = slots + (size_t)slot * kSlotBytes;
+        if (lane == 0) {
+            // the whole box arrives (columns and rows past the matrix as zeros), so the stage's
+            // byte count does not depend on where it sits
+            mbar_expect_tx(&full[slot], 16u * op.row_stride);
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                    smem_u32(dst)),
+                "l"(op.wmap), "r"(smem_u32(&full[slot])), "r"((int)(ch0 * (kChunkCols / 4u))), "r"((int)(u * 16u))
+                : "memory");
+        }
+        // block scales of the stage: nch * 4 bytes per row; lane l takes row l / 2 and every other piece
+        // of it, in the widest copies the row's alignment allows (a row starts cols / 16 bytes after the
+        // one before it)
+        {
+            const uint32_t r = (uint32_t)lane >> 1, half = (uint32_t)lane & 1u;
+            if (r < unit_rows) {
+                const unsigned char *src = d + ((size_t)(u * 16u + r) * nb + (size_t)ch0 * 2u) * 2u;
+                const uint32_t to = smem_u32(dst + kQuantBytes + r * kScaleStride), bytes = nch * 4u;
+                if ((cols & 255u) == 0u) {
+                    for (uint32_t o = half * 16u; o < bytes; o += 32u)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(to + o), "l"(src + o) : "memory");
+                } else if ((cols & 127u) == 0u) {
+                    for (uint32_t o = half * 8u; o < bytes; o += 16u)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(to + o), "l"(src + o) : "memory");
+                } else {
+                    for (uint32_t o = half * 4u; o < bytes; o += 8u)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to + o), "l"(src + o) : "memory");
                 }
-                // block scales of the stage: nch * 4 bytes per row; lane l takes row l / 2 and every other piece
-                // of it, in the widest copies the row's alignment allows (a row starts cols / 16 bytes after the
-                // one before it)
-                {
-                    const uint32_t r = (uint32_t)lane >> 1, half = (uint32_t)lane & 1u;
-                    if (r < unit_rows) {
-                        const unsigned char *src = d + ((size_t)(u * 16u + r) * nb + (size_t)ch0 * 2u) * 2u;
-                        const uint32_t to = smem_u32(dst + kQuantBytes + r * kScaleStride), bytes = nch * 4u;
-                        if ((cols & 255u) == 0u) {
-                            for (uint32_t o = half * 16u; o < bytes; o += 32u)
-                                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(to + o), "l"(src + o) : "memory");
-                        } else if ((cols & 127u) == 0u) {
-                            for (uint32_t o = half * 8u; o < bytes; o += 16u)
-                                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(to + o), "l"(src + o) : "memory");
-                        } else {
-                            for (uint32_t o = half * 4u; o < bytes; o += 8u)
-                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to + o), "l"(src + o) : "memory");
-                        }
-                    }
-                }
-                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
             }
         }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
+        near_ok = near.next(P);
     }
-    return n;
+    return near.count;
 }
 
 // The producer leaves only after everything it requested has landed (a CTA must not retire with
 // copies in flight to its shared memory): it waits, bounded, for the last stages it requested.  When
 // the consumers took them all this returns at once (a completed phase stays completed).
-__device__ void producer_drain(const step_params &P, uint64_t *full, uint32_t issued) {
+__device__ __forceinline__ void producer_drain(const step_params &P, uint64_t *full, uint32_t issued) {
     const uint32_t from = issued > P.n_slots ? issued - P.n_slots : 0u;
     for (uint32_t m = from; m < issued; ++m) {
         const uint32_t addr = smem_u32(&full[m % P.n_slots]), parity = (m / P.n_slots) & 1u;
@@ -611,7 +685,7 @@ struct attn_shared {
 // those of attention_decode_fast_kernel (tm_cuda_ops.cu), so both give the same bits; the splits'
 // partial results travel as flagged words and the group of the newest split merges them.
 template <int G, int HD>
-__device__ void attn_item(const step_params &P, const step_op &op, uint32_t oi, uint32_t pos, uint32_t kvh,
+__device__ __forceinline__ void attn_item(const step_params &P, const step_op &op, uint32_t oi, uint32_t pos, uint32_t kvh,
                           uint32_t split, int tid, unsigned char *sm, int bar_id, volatile uint32_t *flags) {
     using S = attn_shared<G, HD>;
     static_assert(sizeof(S) <= kAttnSub, "attention group shared memory");
@@ -910,7 +984,7 @@ __device__ void attn_item(const step_params &P, const step_op &op, uint32_t oi, 
 }
 
 template <int G, int HD>
-__device__ void attn_consume(const step_params &P, const step_op &op, uint32_t oi, uint32_t pos, unsigned char *xs,
+__device__ __forceinline__ void attn_consume(const step_params &P, const step_op &op, uint32_t oi, uint32_t pos, unsigned char *xs,
                              volatile uint32_t *flags) {
     const int tid = threadIdx.x & 127, sub = threadIdx.x >> 7;
     const uint32_t kv_heads = op.u[1], window = op.u[4];
@@ -942,7 +1016,7 @@ __device__ __forceinline__ bool better(float av, uint32_t ai, float bv, uint32_t
 
 // Greedy rule over the consumer threads' candidates (crates/backend/src/sampling.rs:68-82: NaN
 // skipped, larger wins, ties to the lower index); thread 0 returns the CTA's winner.
-__device__ void argmax_cta(float &v, uint32_t &i, float *red) {
+__device__ __forceinline__ void argmax_cta(float &v, uint32_t &i, float *red) {
     uint32_t *ri = (uint32_t *)red + 16;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -973,7 +1047,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const step
     uint64_t *full = (uint64_t *)(slots + (size_t)P.n_slots * kSlotBytes);
     uint64_t *empty = full + kMaxSlots;
     float *partial = (float *)(empty + kMaxSlots);
-    float *red = partial + 2 * kCWarps * 16;
+    float *red = partial + 2 * kUnitBatch * kCWarps * 16;
     uint32_t *desc = (uint32_t *)(red + 32);                 // two operator descriptors, used in turn
     volatile uint32_t *flags = (volatile uint32_t *)(desc + 2 * kDescWords);
     {   // a program whose earlier launch gave up a wait stays stopped: its flagged words are no longer whole
@@ -1168,7 +1242,7 @@ struct tm_step_program {
     uint64_t launches = 0;
     uint32_t xs_bytes = 0, n_slots = 0, smem = 0;
     uint32_t next_cta = 0;          // the round-robin deal of units continues across operators
-    uint32_t seq_skew = 0, spin_limit = 1u << 18;
+    uint32_t seq_skew = 0, spin_limit = 1u << 18, l2_ahead = 0;
     u64 *trace = nullptr;           // device, [ops][8], allocated on the first trace request
     int grid = 0;
 };
@@ -1351,6 +1425,7 @@ int tm_step_launch(tm_cuda_ctx *ctx, tm_step_program *p, char *err, size_t err_c
     P.n_slots = p->n_slots;
     P.xs_bytes = p->xs_bytes;
     P.spin_limit = p->spin_limit;
+    P.l2_ahead = p->l2_ahead;
     P.trace = p->trace;
     p->launches += 1;
     cudaLaunchConfig_t cfg = {};
@@ -1417,10 +1492,15 @@ int tm_cuda_end_program(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, size_t
         return fail(TM_CUDA_ERR_UNSUPPORTED, "the widest GEMV of the program leaves no room for the weight ring");
     uint32_t slots = (uint32_t)((budget - xs - kTailBytes) / kSlotBytes);
     if (slots > kMaxSlots) slots = kMaxSlots;
+    if (const char *e = getenv("TM_CUDA_STEP_SLOTS")) {
+        const uint32_t want = (uint32_t)strtoul(e, nullptr, 10);
+        if (want >= 3 && want < slots) slots = want;
+    }
     p->xs_bytes = xs;
     p->n_slots = slots;
     p->smem = xs + slots * kSlotBytes + kTailBytes;
     if (const char *e = getenv("TM_CUDA_STEP_SPIN")) p->spin_limit = (uint32_t)strtoul(e, nullptr, 10);
+    if (const char *e = getenv("TM_CUDA_STEP_L2_AHEAD")) p->l2_ahead = (uint32_t)strtoul(e, nullptr, 10);
     // device memory: operator table | arrivals, status | argmax words | tensor maps | flagged vectors | attention partials
     p->ops_bytes = tm_round_up((size_t)p->max_ops * sizeof(step_op), 256);
     p->maps_off = p->ops_bytes + 256 + 2 * 8 * 1024;
@@ -1560,6 +1640,10 @@ int tm_cuda_end_program(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, size_t
         }
         if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
     }
+    // shared memory the kernel does not ask for stays L1 (local memory of a register-hungry thread lives there)
+    cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)((p->smem + 1024) * 100 / (228 * 1024) + 1));
+    cudaGetLastError();
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, kStepThreads, p->smem) != cudaSuccess ||
         per_sm < 1) {

@@ -34,7 +34,7 @@ class _Options(C.Structure):
     _fields_ = [("gguf_path", C.c_char_p), ("kernels", C.c_char_p), ("device", C.c_int), ("context", C.c_uint32),
                 ("prefill_batch", C.c_uint32), ("exact", C.c_int), ("budget_bytes", C.c_uint64),
                 ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32), ("comm_id", C.c_void_p),
-                ("step_graph", C.c_int)]
+                ("persistent_step", C.c_int)]
 
 
 class Info(C.Structure):
@@ -109,7 +109,7 @@ def comm_id() -> bytes:
 class Engine:
     def __init__(self, gguf_path, context: int, kernels: str = "cuda", device: int = 0, prefill_batch: int = 0,
                  exact: bool = False, budget_bytes: int = 0, shard_rank: int = 0, shard_world: int = 1,
-                 comm_id: bytes | None = None, step_graph: bool = False):
+                 comm_id: bytes | None = None, persistent_step: bool = False):
         """With shard_world > 1 every rank constructs its Engine with the same
         128-byte `comm_id` (from `comm_id()` on one rank) and then makes the same
         calls in the same order; each call is a collective."""
@@ -119,7 +119,7 @@ class Engine:
         self._comm_id = C.create_string_buffer(comm_id, 128) if comm_id is not None else None
         o = _Options(self._path, self._kernels, device, context, prefill_batch, int(exact), budget_bytes,
                      shard_rank, shard_world, C.cast(self._comm_id, C.c_void_p) if self._comm_id is not None else None,
-                     int(step_graph))
+                     int(persistent_step))
         h, err = C.c_void_p(), C.create_string_buffer(1024)
         _check(self._l.tm_engine_load(C.byref(o), C.byref(h), err, 1024), err)
         self.handle = h

@@ -120,24 +120,40 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def cpu_leg(name: str, threads: int | None, prompt_n: int, decode_n: int, seed: int):
-    """Bounded sample of the workload on the CPU oracle: batched prefill of
-    `prompt_n` tokens, then `decode_n` one-token steps.  Returns decode tok/s."""
+def cpu_leg(name: str, seed: int, decode_sample: int = 16, one_core_sample: int = 0):
+    """Bounded sample of the workload on the CPU oracle, at the workload's own context length: the
+    whole prompt is prefilled in 128-token chunks on all host threads (untimed), then `decode_sample`
+    one-token greedy steps are timed at the positions right after it (the metric is decode tok/s).
+    With `one_core_sample` > 0 that many further steps are timed on ONE thread -- the reference
+    executor's own design (crates/tuckcore/src/executor.rs:813 is single-threaded).
+    Returns (tok/s on all threads, threads, tok/s on one thread or None, description)."""
     import oracle as O
 
     O.build()
-    shape = WORKLOADS[name][0]
+    shape, prompt_n, _ = WORKLOADS[name]
     path = artifact(name, seed)
-    m = O.Model(path, kv_f16=True, threads=threads)
-    m.reset(prompt_n + decode_n + 1)
+    m = O.Model(path, kv_f16=True, threads=None)
+    threads = m.threads
+    m.reset(prompt_n + decode_sample + one_core_sample + 2)
     prompt = T.token_ids(seed, prompt_n, shape.vocab)
-    logits = m.forward(prompt)
+    logits = None
+    for i in range(0, prompt_n, 128):
+        logits = m.forward(prompt[i:i + 128], want_logits=i + 128 >= prompt_n)
     tok = O.argmax(logits)
     t0 = time.perf_counter()
-    for _ in range(decode_n):
+    for _ in range(decode_sample):
         tok = O.argmax(m.forward([tok]))
-    dt = time.perf_counter() - t0
-    return decode_n / dt, m.threads, f"{prompt_n} prompt + {decode_n} decode tokens of the {name} workload"
+    all_cores = decode_sample / (time.perf_counter() - t0)
+    one_core = None
+    if one_core_sample:
+        m.threads = 1
+        t0 = time.perf_counter()
+        for _ in range(one_core_sample):
+            tok = O.argmax(m.forward([tok]))
+        one_core = one_core_sample / (time.perf_counter() - t0)
+    sample = (f"{decode_sample} greedy decode steps at positions {prompt_n}..{prompt_n + decode_sample - 1} of the {name} "
+              f"workload (its {prompt_n}-token prompt prefilled first, untimed)")
+    return all_cores, threads, one_core, sample
 
 
 def run_reference(args):
@@ -145,27 +161,38 @@ def run_reference(args):
     if rank != 0:
         return
     shape, prompt_n, decode_n = WORKLOADS[args.workload]
-    vals = []
+    vals, one = [], None
     t_all = time.perf_counter()
     for i in range(args.warmup + args.steps):
-        v, threads, sample = cpu_leg(args.workload, None, 8, 12, args.seed)
+        v, threads, one_core, sample = cpu_leg(args.workload, args.seed, decode_sample=12,
+                                               one_core_sample=3 if i == args.warmup + args.steps - 1 else 0)
         if i >= args.warmup:
             vals.append(v)
+        if one_core:
+            one = one_core
     value = float(np.mean(vals))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * (time.perf_counter() - t_all) / max(1, args.steps + args.warmup),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1,
-                   "kv": "f16", "weights": "Q8_0 random-init, seed %d" % args.seed},
+        "config": bench_config(args.workload, args.seed),
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline_1core": {"value": one, "unit": "tok/s", "cores": 1, "kind": "port",
+                               "sample": "3 further decode steps of the same session on one thread"},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def gemv_roofline(eng, shape, hbm_gbs, us_per_token):
+def bench_config(workload: str, seed: int) -> dict:
+    """The workload both arms name: the same keys and values in the CUDA line and the reference line."""
+    shape, prompt_n, decode_n = WORKLOADS[workload]
+    return {"workload": workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1, "kv": "f16",
+            "weights": "Q8_0 random-init, seed %d" % seed}
+
+
+def gemv_roofline(eng, shape, hbm_gbs, us_per_token, prompt_n):
     """Roofline of the dominant kernel of the timed region, the Q8_0 GEMV (every
     projection and the lm_head of a decode step are launches of it).
 
@@ -174,7 +201,7 @@ def gemv_roofline(eng, shape, hbm_gbs, us_per_token):
     timed region) times the GEMV's share of the step, the share taken from a
     pass that dispatches each operator on its own with events around it."""
     eng.reset()
-    eng.prefill(T.token_ids(1, 64, shape.vocab), want_token=True)
+    eng.prefill(T.token_ids(1, prompt_n, shape.vocab), want_token=True)  # the share is taken at the timed positions
     eng.decode_ungrouped(3)
     eng.fence()
     eng.profile(True)
@@ -262,9 +289,64 @@ def lm_head_roofline(device, shape, hbm_gbs, torch):
     us = e0.elapsed_time(e1) * 1e3 / n
     nbytes = rows * cols + rows * (cols // 32) * 2 + 4 * cols + 4 * rows
     out = {"rows": rows, "cols": cols, "us_per_launch": us, "bytes_per_launch": nbytes,
-           "achieved": nbytes / (us * 1e3), "unit": "GB/s", "frac": nbytes / (us * 1e3) / hbm_gbs}
+           "achieved": nbytes / (us * 1e3), "unit": "GB/s", "frac": nbytes / (us * 1e3) / hbm_gbs,
+           "traffic": None, "traffic_analytic": nbytes,
+           "traffic_note": "measured DRAM traffic of this launch is in the committed ncu summary, not repeated here"}
     for b in ws + [x, y]:
         b.free()
+    ctx.close()
+    return out
+
+
+def gemm_rooflines(device, torch):
+    """The prefill half of the metric: the tensor-core Q8_0 GEMM alone (tm_cuda_q8_0_gemm_mma: the f16
+    copy of X plus the tcgen05 kernel) at the single-operator configuration (3072 x 1024, M = 512)
+    and at an 8B-scale projection (12288 x 4096, M = 2048).  CUDA events around one replayed graph of
+    n launches that rotate over enough copies of the weights to exceed L2; FLOPs = 2 M N K against the
+    measured dense bf16 peak (the stand-in for the f16 tensor peak)."""
+    from tuckmill_b200 import cuda
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak, kind = (float(peaks["bf16_tflops"]), "measured") if "bf16_tflops" in peaks else (1590.0, "fallback")
+    ctx = cuda.CudaContext(device)
+    st = torch.cuda.ExternalStream(ctx.stream(), device=device)
+    out = []
+    for rows, cols, m in ((3072, 1024, 512), (12288, 4096, 2048)):
+        base = T.q8_0_matrix(0, 97, min(rows, 1024), cols)
+        raw = np.tile(base, ((rows + base.shape[0] - 1) // base.shape[0], 1, 1))[:rows]
+        copies = max(2, int(140e6 // (rows * cols * 1.0625)) + 1)
+        ws = [ctx.q8_0_matrix(raw, rows, cols) for _ in range(copies)]
+        x = ctx.buffer(m * cols * 4)
+        x.upload(0, T.activations(0, 96, m * cols))
+        y = ctx.buffer(m * rows * 4)
+        ctx.mma_workspace_reserve(m * cols * 2)
+        n = max(copies, 12)
+        ctx.begin_group()
+        for i in range(n):
+            ctx.q8_0_gemm_mma(ws[i % copies], x, y, rows, cols, m)
+        graph = ctx.end_group_retain()
+        for _ in range(3):
+            graph.launch()
+        ctx.fence()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(st):
+            e0.record()
+        graph.launch()
+        with torch.cuda.stream(st):
+            e1.record()
+        ctx.fence()
+        torch.cuda.synchronize()
+        graph.free()
+        assert not ctx.mma_aborted()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        tf = 2.0 * m * rows * cols / us / 1e6
+        out.append({"bound": "tensor", "rows": rows, "cols": cols, "batch": m, "us_per_launch": us, "achieved": tf,
+                    "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                    "kernel": "x_to_f16_kernel + q8_gemm_mma_kernel<%d>" % ctx.mma_last_tile(),
+                    "weights": "%d copies in turn (%.0f MB)" % (copies, copies * rows * cols * 1.0625 / 1e6),
+                    "peak_source": "MEASURED_PEAKS.json bf16_tflops (%s), burst" % kind})
+        for b in ws + [x, y]:
+            b.free()
     ctx.close()
     return out
 
@@ -357,27 +439,25 @@ def run_cuda(args):
                           tokens) if world > 1 else None
 
     if rank == 0:
-        roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens)
+        roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens, prompt_n)
         roof["lm_head"] = lm_head_roofline(local, shape, hbm_gbs, torch)
-        if args.workload == "qwen3-0.6b":
-            # dram__bytes_read.sum + dram__bytes_write.sum of this launch in the committed ncu capture
-            roof["lm_head"]["traffic"] = 164954112 + 7096576
-            roof["lm_head"]["traffic_source"] = "profiles/q8_gemv_lm_head.md (one ncu capture of the same shape)"
         roof["copy_gbs_this_gpu"] = copy_bandwidth(torch, local)
         roof["lm_head"]["frac_of_this_gpu_copy"] = roof["lm_head"]["achieved"] / roof["copy_gbs_this_gpu"]
         roof["peak_source"] = f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})"
         step_bytes = shape.decode_weight_bytes()
-        cpu = None
+        cpu = cpu1 = None
         if not args.no_cpu:
-            v, threads, sample = cpu_leg(args.workload, None, 8, 12 if shape.layers > 8 else 64, args.seed)
+            v, threads, one_core, sample = cpu_leg(args.workload, args.seed, decode_sample=16, one_core_sample=3)
             cpu = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample}
+            cpu1 = {"value": one_core, "unit": "tok/s", "cores": 1, "kind": "port",
+                    "sample": "3 further decode steps of the same session on one thread (the reference executor "
+                              "is single-threaded)"}
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "s8 x s8 -> s32 tensor-core products, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": args.workload, "prompt_tokens": prompt_n, "decode_tokens": decode_n, "batch": 1,
-                       "kv": "f16", "weights": "Q8_0 random-init, seed %d" % args.seed,
+            "config": {**bench_config(args.workload, args.seed),
                        "prefill_chunk": prefill_batch or 512,
                        "parallelism": f"replicas x{world}" if world > 1 else "single",
                        "l2": "per-token weight stream %.0f MB exceeds the 126 MB L2" % (step_bytes / 1e6)},
@@ -385,7 +465,9 @@ def run_cuda(args):
                     "ttft_ms": ttft_ms / args.steps, "prefill_tok_s": world * args.steps * prompt_n / (ttft_ms / 1e3)},
             "gpu_launches": int(launches),
             "roofline": roof,
+            "roofline_gemm": gemm_rooflines(local, torch) if args.workload == "qwen3-0.6b" else None,
             "cpu_baseline": cpu,
+            "cpu_baseline_1core": cpu1,
             "clocks": clocks.summary(),
             "prefill_tok_s": world * args.steps * prompt_n / (prefill_ms / 1e3),
             "decode_us_per_token": 1e3 * decode_ms / dec_tokens,

@@ -457,10 +457,10 @@ def run_cuda(args):
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "s8 x s8 -> s32 tensor-core products, f32 accumulate",
             "data": "synthetic",
-            "config": {**bench_config(args.workload, args.seed),
-                       "prefill_chunk": prefill_batch or 512,
-                       "parallelism": f"replicas x{world}" if world > 1 else "single",
-                       "l2": "per-token weight stream %.0f MB exceeds the 126 MB L2" % (step_bytes / 1e6)},
+            "config": bench_config(args.workload, args.seed),
+            "run": {"prefill_chunk": prefill_batch or 512,
+                    "parallelism": f"replicas x{world}" if world > 1 else "single",
+                    "l2": "per-token weight stream %.0f MB exceeds the 126 MB L2" % (step_bytes / 1e6)},
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ttft_ms": ttft_ms / args.steps, "prefill_tok_s": world * args.steps * prompt_n / (ttft_ms / 1e3)},
             "gpu_launches": int(launches),

@@ -400,14 +400,15 @@ int tm_cuda_attention_chunk_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buf
  * (tm_cuda_attention_decode_scratch_bytes, zero-filled once by the caller;
  * the kernel leaves the counters at zero).  Calls sharing one scratch buffer
  * must be ordered on the stream.
- * Cache contract: the kernel reads cache rows below `pos` while the kernel
+ * Cache contract: the kernel reads cache rows below `pos` while kernels
  * launched before it on the stream may still be running (programmatic
- * dependent launch).  Row pos - 1 is read again once the predecessor has
- * finished, so consecutive decode calls at pos, pos + 1 on one cache are safe
- * however close together they are issued; rows below pos - 1 must have been
- * written by work that completed before the PREDECESSOR kernel was launched
- * (true of any earlier dispatch group or graph launch, and of a decode step
- * two or more positions back). */
+ * dependent launch).  Row pos - 1 is read again once they have finished, and
+ * an attention kernel lets its successor start only after its own predecessor
+ * is complete, so any sequence of decode calls at pos, pos + 1, pos + 2, ... on
+ * one cache is safe however close together the calls are issued (one dispatch
+ * group included).  Rows that something OTHER than this operator wrote (a
+ * prefill chunk, a host upload) must be complete when the call is made, which
+ * every earlier dispatch group, graph launch or upload is. */
 size_t tm_cuda_attention_decode_scratch_bytes(uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                                               uint32_t cap);
 int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k,

@@ -409,8 +409,12 @@ __global__ void __launch_bounds__(32) attention_decode_kernel(
             asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)(vp + (size_t)j * hd) + off));
         }
     }
-    tmdev::pdl_trigger();
     tmdev::pdl_wait();
+    // The successor may start only now, when this kernel's own predecessor has finished: a kernel that
+    // let its successor start at once would let a whole chain of launches run ahead, and a later
+    // attention call could read cache rows early that a call several places back is still storing.
+    // This way only the call directly before can still be running: the row it stores is read again below.
+    tmdev::pdl_trigger();
     // Every small input is fetched in one trip, before the position is needed.
     // Lane l holds quads l and l + 32 of a row.
     constexpr int QW = DPL > 4 ? 2 : 1;
@@ -603,10 +607,10 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     }
     // This thread's half of key row split*64 + tid/2: written by an earlier step's kernel (or is a row past
     // the sequence, masked below; or the current position's row, replaced below by the fresh one), so it
-    // is read before the predecessor finishes.  One row is the exception: every kernel of a chain of
-    // programmatic launches lets its successor start early, so the attention call of the PREVIOUS token
-    // (two or more kernels back) may still be storing row pos - 1; that row is read again after the wait.
-    // Rows below pos - 1 must be complete before the predecessor kernel is launched.
+    // is read before the predecessor finishes.  One row is the exception: the attention call of the
+    // PREVIOUS token (two kernels back in a chain of programmatic launches) may still be storing row
+    // pos - 1; that row is read again after the wait.  Calls further back have finished, because an
+    // attention kernel lets its successor start only after its own predecessor is complete.
     constexpr int NL0 = HD / 16;  // 16-byte loads per thread
     int4 kraw[NL0];
     {
@@ -627,8 +631,12 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
             vpre[c] = *(const __half2 *)(vp + (size_t)j * HD + 2 * dp00);
         }
     }
-    tmdev::pdl_trigger();
     tmdev::pdl_wait();
+    // The successor may start only now, when this kernel's own predecessor has finished: a kernel that
+    // let its successor start at once would let a whole chain of launches run ahead, and a later
+    // attention call could read cache rows early that a call several places back is still storing.
+    // This way only the call directly before can still be running: the row it stores is read again below.
+    tmdev::pdl_trigger();
     // The first vector this warp will normalise (q_warp, or k for warp G) does not depend on the
     // position: its loads are issued together with the position's, one memory trip instead of two.
     constexpr int EPL0 = HD / 32;

@@ -112,6 +112,12 @@ mod ffi {
         pub fn tm_cuda_mma_aborted(ctx: *mut TmCudaCtx) -> c_int;
         pub fn tm_cuda_mma_last_tile(ctx: *mut TmCudaCtx) -> c_int;
         pub fn tm_cuda_q8_0_row_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, out: *mut TmCudaBuffer, row: u32, cols: u32, out_off: u32, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_gemv(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_gemm(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, batch: u32, x_off: u32, y_off: u32, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_row_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, out: *mut TmCudaBuffer, row: u32, cols: u32, out_off: u32, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_gemv_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_row_indirect_f32_dev(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, base: u32, pos_buf: *mut TmCudaBuffer, pos_index: u32, bias: i32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_f16_rows_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, first: u32, n: u32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_row_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, type_id: u32, rows: u32, cols: u32, ids: *mut TmCudaBuffer, slot: u32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_rows_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, first: u32, n: u32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_q8_0_gemv_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
@@ -587,6 +593,17 @@ impl CudaContext {
     }
     pub fn q8_0_row(&self, w: &CudaBuffer, out: &CudaBuffer, row: u32, cols: u32, out_off: u32) -> Result<()> {
         call!(self, "q8_0_row_f32", tm_cuda_q8_0_row_f32(w.raw(), out.raw(), row, cols, out_off))
+    }
+    // F16-weight matrices (rows * cols binary16, uploaded verbatim): crates/metal/src/lib.rs f16_gemv / f16_gemm / f16_row.
+    pub fn f16_gemv(&self, w: &CudaBuffer, x: &CudaBuffer, y: &CudaBuffer, rows: u32, cols: u32) -> Result<()> {
+        call!(self, "f16_gemv", tm_cuda_f16_gemv(w.raw(), x.raw(), y.raw(), rows, cols))
+    }
+    #[allow(clippy::too_many_arguments)]
+    pub fn f16_gemm(&self, w: &CudaBuffer, x: &CudaBuffer, y: &CudaBuffer, rows: u32, cols: u32, batch: u32, x_off: u32, y_off: u32) -> Result<()> {
+        call!(self, "f16_gemm", tm_cuda_f16_gemm(w.raw(), x.raw(), y.raw(), rows, cols, batch, x_off, y_off))
+    }
+    pub fn f16_row(&self, w: &CudaBuffer, out: &CudaBuffer, row: u32, cols: u32, out_off: u32) -> Result<()> {
+        call!(self, "f16_row_f32", tm_cuda_f16_row_f32(w.raw(), out.raw(), row, cols, out_off))
     }
     #[allow(clippy::too_many_arguments)]
     pub fn row_indirect_f32(&self, w: &CudaBuffer, type_id: u32, rows: u32, cols: u32, ids: &CudaBuffer, slot: u32, out: &CudaBuffer) -> Result<()> {

@@ -188,6 +188,32 @@ int tm_cuda_mma_last_tile(tm_cuda_ctx *ctx);
 /* tm_metal.h:138 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
 int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
                          uint32_t cols, uint32_t out_off, char *err, size_t err_cap);
+/* ---------------- F16 weights ----------------
+ * tm_metal.h:142 tm_metal_f16_gemv: y[r] = dot(f32(w_row_r), x); `w` holds rows * cols binary16
+ * values, row-major, uploaded verbatim (no packing).  Serves F16-weight artifacts: the
+ * reference's own model fixtures and F16 twins of quantized models. */
+int tm_cuda_f16_gemv(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                     uint32_t cols, char *err, size_t err_cap);
+/* tm_metal.h:179 tm_metal_f16_gemm: the contract of tm_cuda_q8_0_gemm (batch 1..32, x_off / y_off,
+ * batch 1 bit-identical to the GEMV). */
+int tm_cuda_f16_gemm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                     uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off, char *err, size_t err_cap);
+/* tm_metal.h:156 tm_metal_f16_row_f32: row `row` as f32 to out[out_off..]. */
+int tm_cuda_f16_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row, uint32_t cols,
+                        uint32_t out_off, char *err, size_t err_cap);
+/* No counterpart: the F16 forms of tm_cuda_q8_0_gemv_fused, tm_cuda_row_indirect_f32_dev (pos_buf may
+ * be NULL: slot = base) and tm_cuda_rows_indirect_f32, so the engine's decode and prefill loops run
+ * F16-weight artifacts with the same launches per layer. */
+int tm_cuda_f16_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                           uint32_t cols, int prologue, tm_cuda_buffer *pro, float eps, int epilogue, char *err,
+                           size_t err_cap);
+int tm_cuda_f16_row_indirect_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                                     tm_cuda_buffer *ids, uint32_t base, tm_cuda_buffer *pos_buf, uint32_t pos_index,
+                                     int32_t bias, float scale, tm_cuda_buffer *out, char *err, size_t err_cap);
+int tm_cuda_f16_rows_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols, tm_cuda_buffer *ids,
+                                  uint32_t first, uint32_t n, float scale, tm_cuda_buffer *out, char *err,
+                                  size_t err_cap);
+
 /* tm_metal.h:104 tm_metal_row_indirect_f32: row ids[slot] (type 8 only); an
  * id >= rows writes zeros. */
 int tm_cuda_row_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t type_id, uint32_t rows,

@@ -114,6 +114,23 @@ def matmul_q8_0(raw: np.ndarray, rows: int, cols: int, x: np.ndarray, threads: i
     return y[0] if np.ndim(x) == 1 else y
 
 
+def matmul_f16(w: np.ndarray, rows: int, cols: int, x: np.ndarray, threads: int | None = None) -> np.ndarray:
+    """y[b][r] = dot(f32(w[r]), x[b]) over an F16 matrix (`w`: rows * cols float16), the scalar
+    order of crates/tuckcore/src/kernels.rs:223-232."""
+    w = np.ascontiguousarray(w, dtype=np.float16).reshape(rows, cols)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    batch = 1 if x.ndim == 1 else x.shape[0]
+    assert x.size == batch * cols
+    y = np.empty(batch * rows, dtype=np.float32)
+    fn = lib().tmo_matmul_f16
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
+    rc = fn(_p(w), rows, cols, _p(x), batch, _p(y), threads or default_threads())
+    if rc != 0:
+        raise ValueError("malformed F16 matmul")
+    return y if x.ndim == 1 else y.reshape(batch, rows)
+
+
 def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     w = np.ascontiguousarray(w, dtype=np.float32)
@@ -170,7 +187,7 @@ class _Model(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("layers", "hidden", "ffn", "heads", "kv_heads", "head_dim", "vocab")] + \
                [("eps", C.c_float), ("embedding_scale", C.c_float), ("kv_f16", C.c_uint32),
                 ("embedding", C.c_void_p), ("head", C.c_void_p), ("final_norm", C.c_void_p),
-                ("layer", C.POINTER(_Layer))]
+                ("layer", C.POINTER(_Layer)), ("weight_type", C.c_uint32)]
 
 
 class Model:
@@ -193,9 +210,14 @@ class Model:
         base_addr = data.ctypes.data
         self._keep = []
 
+        # every matrix of an artifact has one type: Q8_0 (8) or F16 (1, the reference's fixtures)
+        self.weight_type = int(tensors["token_embd.weight"][0])
+        if self.weight_type not in (1, 8):
+            raise ValueError(f"unsupported matrix type {self.weight_type}")
+
         def q8(name):
             ty, dims, off, nbytes = tensors[name]
-            assert ty == 8, name
+            assert ty == self.weight_type, name
             return base_addr + off
 
         def f32(name):
@@ -240,6 +262,7 @@ class Model:
         m.head = q8("output.weight") if "output.weight" in tensors else m.embedding
         m.final_norm = f32("output_norm.weight")
         m.layer = C.cast(self._layers, C.POINTER(_Layer))
+        m.weight_type = self.weight_type
         self._m = m
         self.vocab, self.hidden = m.vocab, m.hidden
         self._kv = None

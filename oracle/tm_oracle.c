@@ -233,6 +233,61 @@ TMO_API int tmo_matmul_q8_0(const uint8_t *w, size_t rows, size_t cols, const fl
     return 0;
 }
 
+/* crates/tuckcore/src/kernels.rs:223-232 -- scalar::dot_f16_x_f32: one sequential
+ * sum from 0.0 of f16_to_f32(w_i) * x_i. */
+TMO_API float tmo_dot_f16_x_f32(const uint8_t *row, size_t cols, const float *x) {
+    float acc = 0.0f;
+    for (size_t i = 0; i < cols; ++i) {
+        const float w = tmo_f16_to_f32(read_u16(row + 2 * i));
+        acc += w * x[i];
+    }
+    return acc;
+}
+
+typedef struct {
+    const uint8_t *w;
+    size_t rows, cols, batch;
+    const float *x;
+    float *y;
+    size_t r0, r1;
+} mvh_job;
+
+static void *mvh_worker(void *arg) {
+    mvh_job *j = (mvh_job *)arg;
+    for (size_t t = 0; t < j->batch; ++t)
+        for (size_t r = j->r0; r < j->r1; ++r)
+            j->y[t * j->rows + r] = tmo_dot_f16_x_f32(j->w + r * j->cols * 2, j->cols, j->x + t * j->cols);
+    return NULL;
+}
+
+/* The row loop of crates/tuckcore/src/forward.rs:562-737 over an F16 matrix
+ * (rows * cols binary16 values, row-major). */
+TMO_API int tmo_matmul_f16(const uint8_t *w, size_t rows, size_t cols, const float *x, size_t batch,
+                           float *y, int threads) {
+    if (rows == 0 || cols == 0 || batch == 0) return -1;
+    if (threads < 1) threads = 1;
+    if ((size_t)threads > rows) threads = (int)rows;
+    if (threads > 256) threads = 256;
+    mvh_job jobs[256];
+    pthread_t tids[256];
+    const size_t per = (rows + (size_t)threads - 1) / (size_t)threads;
+    int n = 0;
+    for (int t = 0; t < threads; ++t) {
+        const size_t r0 = (size_t)t * per;
+        if (r0 >= rows) break;
+        const size_t r1 = r0 + per < rows ? r0 + per : rows;
+        jobs[n] = (mvh_job){w, rows, cols, batch, x, y, r0, r1};
+        ++n;
+    }
+    if (n == 1) {
+        mvh_worker(&jobs[0]);
+        return 0;
+    }
+    for (int t = 0; t < n; ++t) pthread_create(&tids[t], NULL, mvh_worker, &jobs[t]);
+    for (int t = 0; t < n; ++t) pthread_join(tids[t], NULL);
+    return 0;
+}
+
 /* ------------------------------------------------------------ small ops -- */
 
 /* crates/tuckcore/src/forward.rs:917-926 -- rmsnorm_in_place. */
@@ -347,7 +402,15 @@ typedef struct {
     const uint8_t *head;      /* [vocab][hidden] Q8_0 (may equal embedding) */
     const float *final_norm;
     const tmo_layer *layer;
+    uint32_t weight_type; /* GGML type of every matrix: 8 = Q8_0 (also when 0), 1 = F16 */
 } tmo_model;
+
+/* y = W x for the model's matrix type. */
+static int model_matmul(const tmo_model *m, const uint8_t *w, size_t rows, size_t cols, const float *x,
+                        size_t batch, float *y, int threads) {
+    if (m->weight_type == 1) return tmo_matmul_f16(w, rows, cols, x, batch, y, threads);
+    return tmo_matmul_q8_0(w, rows, cols, x, batch, y, threads);
+}
 
 typedef struct {
     float *k, *v; /* [layer][kv_head][cap][head_dim] */
@@ -412,8 +475,13 @@ TMO_API int tmo_forward(const tmo_model *m, tmo_kv *kv, const uint32_t *tokens, 
 
     /* forward.rs:552-558 -- embedding row dequant */
     for (size_t t = 0; t < n; ++t) {
-        tmo_dequant_q8_0(m->embedding + (size_t)tokens[t] * (hidden / 32) * 34, hidden / 32,
-                         x + t * hidden);
+        if (m->weight_type == 1) {
+            const uint8_t *row = m->embedding + (size_t)tokens[t] * hidden * 2;
+            for (size_t i = 0; i < hidden; ++i) x[t * hidden + i] = tmo_f16_to_f32(read_u16(row + 2 * i));
+        } else {
+            tmo_dequant_q8_0(m->embedding + (size_t)tokens[t] * (hidden / 32) * 34, hidden / 32,
+                             x + t * hidden);
+        }
         if (m->embedding_scale != 0.0f)
             for (size_t i = 0; i < hidden; ++i) x[t * hidden + i] *= m->embedding_scale;
     }
@@ -423,9 +491,9 @@ TMO_API int tmo_forward(const tmo_model *m, tmo_kv *kv, const uint32_t *tokens, 
         tmo_rope_inv_freq(hd, L->rope_base, inv_freq);
         for (size_t t = 0; t < n; ++t)
             tmo_rmsnorm(x + t * hidden, L->pre_norm, m->eps, hidden, h + t * hidden);
-        tmo_matmul_q8_0(L->q, heads * hd, hidden, h, n, q, threads);
-        tmo_matmul_q8_0(L->k, kvh * hd, hidden, h, n, k, threads);
-        tmo_matmul_q8_0(L->v, kvh * hd, hidden, h, n, v, threads);
+        model_matmul(m, L->q, heads * hd, hidden, h, n, q, threads);
+        model_matmul(m, L->k, kvh * hd, hidden, h, n, k, threads);
+        model_matmul(m, L->v, kvh * hd, hidden, h, n, v, threads);
         float *kplane = kv->k + (size_t)l * kvh * kv->cap * hd;
         float *vplane = kv->v + (size_t)l * kvh * kv->cap * hd;
         for (size_t t = 0; t < n; ++t) {
@@ -458,18 +526,18 @@ TMO_API int tmo_forward(const tmo_model *m, tmo_kv *kv, const uint32_t *tokens, 
                                 att + (t * heads + hh) * hd);
             }
         }
-        tmo_matmul_q8_0(L->o, hidden, heads * hd, att, n, proj, threads);
+        model_matmul(m, L->o, hidden, heads * hd, att, n, proj, threads);
         for (size_t t = 0; t < n; ++t) {
             float *p = proj + t * hidden;
             if (L->mixer_out_norm) tmo_rmsnorm(p, L->mixer_out_norm, m->eps, hidden, p);
             for (size_t i = 0; i < hidden; ++i) x[t * hidden + i] += p[i];
             tmo_rmsnorm(x + t * hidden, L->post_norm, m->eps, hidden, h + t * hidden);
         }
-        tmo_matmul_q8_0(L->gate, ffn, hidden, h, n, g, threads);
-        tmo_matmul_q8_0(L->up, ffn, hidden, h, n, u, threads);
+        model_matmul(m, L->gate, ffn, hidden, h, n, g, threads);
+        model_matmul(m, L->up, ffn, hidden, h, n, u, threads);
         for (size_t i = 0; i < n * ffn; ++i)
             g[i] = (L->act_gelu ? tmo_gelu_tanh(g[i]) : tmo_silu(g[i])) * u[i];
-        tmo_matmul_q8_0(L->down, hidden, ffn, g, n, proj, threads);
+        model_matmul(m, L->down, hidden, ffn, g, n, proj, threads);
         for (size_t t = 0; t < n; ++t) {
             float *p = proj + t * hidden;
             if (L->ffn_out_norm) tmo_rmsnorm(p, L->ffn_out_norm, m->eps, hidden, p);
@@ -478,7 +546,7 @@ TMO_API int tmo_forward(const tmo_model *m, tmo_kv *kv, const uint32_t *tokens, 
     }
     if (logits) {
         tmo_rmsnorm(x + (n - 1) * hidden, m->final_norm, m->eps, hidden, h);
-        tmo_matmul_q8_0(m->head, m->vocab, hidden, h, 1, logits, threads);
+        model_matmul(m, m->head, m->vocab, hidden, h, 1, logits, threads);
     }
     free(x); free(h); free(q); free(k); free(v); free(att);
     free(proj); free(g); free(u); free(scores); free(inv_freq);

@@ -174,3 +174,44 @@ def test_f16_kv_rounding_is_visible(oracle, tmp_path):
         outs.append(m.forward(toks))
     assert not np.array_equal(outs[0], outs[1])
     assert np.max(np.abs(outs[0] - outs[1])) < 0.05 * max(1.0, float(np.max(np.abs(outs[1]))))
+
+
+def test_f16_dot_and_the_reference_fixture_values(oracle, tmp_path):
+    """The F16 dot (crates/tuckcore/src/kernels.rs:223-232: widen each weight, multiply,
+    add in element order) and the tensor contents of the reference's synthetic fixtures
+    (crates/manifest/src/testing.rs:611-614: element e = ((31 e + 7) mod 64 - 32) / 64;
+    :678-690: Q8_0 d = 1/128, q = (11 e + 5) mod 128 - 64)."""
+    v = T.fixture_values(130)
+    assert v[0] == (7 - 32) / 64 and v[1] == (38 - 32) / 64 and v[2] == (5 - 32) / 64 and v[64] == v[0]
+    assert np.array_equal(v.astype(np.float16).astype(np.float32), v) and v.min() >= -0.5 and v.max() < 0.5
+    blocks = T.fixture_q8_0(3)
+    assert blocks.shape == (1, 3, 34) and bytes(blocks[0, 0, :2]) == np.float16(1 / 128).tobytes()
+    q = blocks[0, :, 2:].view(np.int8).reshape(-1)
+    assert q[0] == 5 - 64 and q[1] == 16 - 64 and q[12] == (11 * 12 + 5) % 128 - 64
+    rows, cols = 9, 70
+    w = (T.normals(1, 2, 3, 0, rows * cols).reshape(rows, cols) * 0.5).astype(np.float16)
+    x = T.activations(4, 5, 2 * cols).reshape(2, cols)
+    got = oracle.matmul_f16(w, rows, cols, x)
+    for b in range(2):
+        for r in range(rows):
+            acc = np.float32(0)
+            for c in range(cols):
+                acc = np.float32(acc + np.float32(w[r, c]) * x[b, c])
+            assert got[b, r] == acc
+    # the fixture artifact: an F16 model end to end, one token at a time == batched
+    path = tmp_path / "f16.gguf"
+    T.write_gguf(path, T.TINY_QWEN3, fill="fixture-f16")
+    _, tensors, data = T.read_gguf(path)
+    ty, dims, off, nbytes = tensors["blk.1.ffn_down.weight"]
+    assert ty == T.GGML_F16 and dims == [256, 128] and nbytes == 256 * 128 * 2
+    np.testing.assert_array_equal(np.frombuffer(data[off:off + 64], np.float16).astype(np.float32), T.fixture_values(32))
+    m = oracle.Model(path, threads=1)
+    assert m.weight_type == 1
+    toks = T.token_ids(3, 7, 512)
+    m.reset(16)
+    a = m.forward(toks)
+    m.reset(16)
+    for t in toks[:-1]:
+        m.forward([t], want_logits=False)
+    np.testing.assert_array_equal(m.forward([toks[-1]]), a)
+    assert np.isfinite(a).all()

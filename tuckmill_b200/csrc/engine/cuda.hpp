@@ -178,6 +178,26 @@ public:
         TM_CALL(tm_cuda_q8_0_gemv_fused, w.raw(), x.raw(), y.raw(), rows, cols, prologue,
                 pro ? pro->raw() : nullptr, eps, epilogue);
     }
+    // F16-weight forms (include/tm_cuda.h): matrices are rows * cols binary16 values, uploaded verbatim.
+    void f16_gemv_fused(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows, uint32_t cols,
+                        int prologue, const CudaBuffer *pro, float eps, int epilogue) const {
+        TM_CALL(tm_cuda_f16_gemv_fused, w.raw(), x.raw(), y.raw(), rows, cols, prologue, pro ? pro->raw() : nullptr, eps,
+                epilogue);
+    }
+    void f16_gemm(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows, uint32_t cols,
+                  uint32_t batch, uint32_t x_off, uint32_t y_off) const {
+        TM_CALL(tm_cuda_f16_gemm, w.raw(), x.raw(), y.raw(), rows, cols, batch, x_off, y_off);
+    }
+    void f16_row_indirect_dev(const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &ids, uint32_t base,
+                              const CudaBuffer &pos_buf, uint32_t pos_index, int32_t bias, float scale,
+                              const CudaBuffer &out) const {
+        TM_CALL(tm_cuda_f16_row_indirect_f32_dev, w.raw(), rows, cols, ids.raw(), base, pos_buf.raw(), pos_index, bias,
+                scale, out.raw());
+    }
+    void f16_rows_indirect(const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &ids, uint32_t first,
+                           uint32_t n, float scale, const CudaBuffer &out) const {
+        TM_CALL(tm_cuda_f16_rows_indirect_f32, w.raw(), rows, cols, ids.raw(), first, n, scale, out.raw());
+    }
     void q8_0_gemm(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows, uint32_t cols,
                    uint32_t batch, uint32_t x_off, uint32_t y_off) const {
         TM_CALL(tm_cuda_q8_0_gemm, w.raw(), x.raw(), y.raw(), rows, cols, batch, x_off, y_off);

@@ -86,22 +86,28 @@ struct Matrix {
     std::vector<CudaBuffer> parts;  // row views, one per source tensor (empty when single)
     std::vector<uint32_t> part_rows;
     uint32_t rows = 0, cols = 0;
+    uint32_t type = 8;  // GGML type of the source tensors: 8 = Q8_0 (repacked), 1 = F16 (verbatim)
 
     static void geometry(const WeightSource &src, const std::vector<Tensor> &ts, Shard sh, uint32_t *rows,
-                         uint32_t *cols) {
+                         uint32_t *cols, uint32_t *type = nullptr) {
         *rows = 0;
         *cols = 0;
+        uint32_t seen = 0;
         for (Tensor t : ts) {
             const uint32_t ty = src.tensor_type_id(t.index);
             auto d = src.tensor_dims(t.index);
             if (d.second <= 1)
                 throw TuckmillError(ErrorCode::Internal,
                                     "tensor " + std::to_string(t.index) + " is 1-D; vectors use the f32 path");
-            if (ty != 8)
+            // F16 or Q8_0, like the reference's Matrix::load (engine/metal.rs:129-137)
+            if (ty != 8 && ty != 1)
                 throw TuckmillError(ErrorCode::UnsupportedQuantization,
-                                    "CUDA engine matrices must be Q8_0; tensor " + std::to_string(t.index) +
+                                    "CUDA engine matrices must be Q8_0 or F16; tensor " + std::to_string(t.index) +
                                         " is type " + std::to_string(ty));
-            if (d.first % 32 != 0 || d.first > UINT32_MAX || d.second > UINT32_MAX)
+            if (seen != 0 && seen != ty)
+                throw TuckmillError(ErrorCode::UnsupportedQuantization, "fused projections differ in type");
+            seen = ty;
+            if ((ty == 8 && d.first % 32 != 0) || d.first > UINT32_MAX || d.second > UINT32_MAX)
                 throw TuckmillError(ErrorCode::InvalidArtifact, "Q8_0 tensor rows are not block aligned");
             if (*cols != 0 && *cols != (uint32_t)d.first)
                 throw TuckmillError(ErrorCode::Internal, "fused projections differ in input width");
@@ -112,18 +118,55 @@ struct Matrix {
             *cols = (uint32_t)d.first;
             *rows += (uint32_t)(d.second / sh.world);
         }
+        if (type) *type = seen;
+    }
+
+    static uint64_t bytes_of(uint32_t type, uint32_t rows, uint32_t cols) {
+        return type == 1 ? (uint64_t)rows * cols * 2 : tm_cuda_q8_0_packed_bytes(rows, cols);
     }
 
     static uint64_t plan(const WeightSource &src, const std::vector<Tensor> &ts, Shard sh = Shard()) {
-        uint32_t rows, cols;
-        geometry(src, ts, sh, &rows, &cols);
-        return tm_cuda_q8_0_packed_bytes(rows, cols);
+        uint32_t rows, cols, type;
+        geometry(src, ts, sh, &rows, &cols, &type);
+        return bytes_of(type, rows, cols);
+    }
+
+    // F16: the tensor bytes verbatim, row ranges uploaded straight into place.
+    static Matrix load_f16(const CudaContext &ctx, const WeightSource &src, const std::vector<Tensor> &ts, Shard sh,
+                           Matrix m) {
+        m.buf = ctx.buffer(bytes_of(1, m.rows, m.cols));
+        const size_t row_bytes = (size_t)m.cols * 2;
+        const size_t step = std::max<size_t>(1, kStagingChunkBytes / row_bytes);
+        std::vector<unsigned char> host(step * row_bytes);
+        uint32_t row0 = 0;
+        for (Tensor t : ts) {
+            const uint32_t n = (uint32_t)(src.tensor_dims(t.index).second / sh.world);
+            const uint64_t first = (uint64_t)sh.rank * n;
+            for (uint32_t r = 0; r < n; r += (uint32_t)step) {
+                const uint32_t k = std::min<uint32_t>((uint32_t)step, n - r);
+                src.read_tensor_into(t.index, (first + r) * row_bytes, host.data(), (size_t)k * row_bytes);
+                m.buf.upload((size_t)(row0 + r) * row_bytes, host.data(), (size_t)k * row_bytes);
+            }
+            m.part_rows.push_back(n);
+            row0 += n;
+        }
+        if (ts.size() > 1) {
+            uint32_t r = 0;
+            for (uint32_t n : m.part_rows) {
+                if (((size_t)r * row_bytes) % 16 != 0)
+                    throw TuckmillError(ErrorCode::UnsupportedArchitecture, "a fused F16 projection does not start on a 16-byte boundary");
+                m.parts.push_back(m.buf.view((size_t)r * row_bytes, (size_t)n * row_bytes));
+                r += n;
+            }
+        }
+        return m;
     }
 
     static Matrix load(const CudaContext &ctx, const WeightSource &src, const std::vector<Tensor> &ts,
                        Shard sh = Shard()) {
         Matrix m;
-        geometry(src, ts, sh, &m.rows, &m.cols);
+        geometry(src, ts, sh, &m.rows, &m.cols, &m.type);
+        if (m.type == 1) return load_f16(ctx, src, ts, sh, std::move(m));
         m.buf = ctx.buffer(tm_cuda_q8_0_packed_bytes(m.rows, m.cols));
         const size_t row_bytes = (size_t)m.cols / 32 * 34;
         const size_t step = std::max<size_t>(1, kStagingChunkBytes / row_bytes);
@@ -157,7 +200,14 @@ struct Matrix {
     // slices of at most 32 tokens; other batches use the tensor cores in one
     // launch (the dispatch rule of engine/metal.rs:167-196).
     static void gemm(const CudaContext &ctx, const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &x,
-                     const CudaBuffer &y, uint32_t batch, bool exact) {
+                     const CudaBuffer &y, uint32_t batch, bool exact, uint32_t type = 8) {
+        if (type == 1) {  // F16: the per-row kernel in slices (engine/metal.rs:181-195 keeps F16 off the matrix units too)
+            for (uint32_t t0 = 0; t0 < batch; t0 += TM_CUDA_GEMM_MAX_BATCH) {
+                const uint32_t n = std::min<uint32_t>(batch - t0, TM_CUDA_GEMM_MAX_BATCH);
+                ctx.f16_gemm(w, x, y, rows, cols, n, t0 * cols, t0 * rows);
+            }
+            return;
+        }
         if (!exact && batch >= 2 && batch <= TM_CUDA_GEMM_MMA_MAX_BATCH) {
             ctx.q8_0_gemm_mma(w, x, y, rows, cols, batch, 0, 0);
             return;
@@ -169,10 +219,19 @@ struct Matrix {
     }
     void gemm_part(const CudaContext &ctx, size_t part, const CudaBuffer &x, const CudaBuffer &y, uint32_t batch,
                    bool exact) const {
-        gemm(ctx, parts[part], part_rows[part], cols, x, y, batch, exact);
+        gemm(ctx, parts[part], part_rows[part], cols, x, y, batch, exact, type);
     }
     void gemm_all(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &y, uint32_t batch, bool exact) const {
-        gemm(ctx, buf, rows, cols, x, y, batch, exact);
+        gemm(ctx, buf, rows, cols, x, y, batch, exact, type);
+    }
+    // One token, with the neighbouring elementwise operators folded in (include/tm_cuda.h).
+    void gemv_fused(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &y, int prologue, const CudaBuffer *pro,
+                    float eps, int epilogue) const {
+        if (type == 1) ctx.f16_gemv_fused(buf, x, y, rows, cols, prologue, pro, eps, epilogue);
+        else ctx.q8_0_gemv_fused(buf, x, y, rows, cols, prologue, pro, eps, epilogue);
+    }
+    void gemv(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &y) const {
+        gemv_fused(ctx, x, y, TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_STORE);
     }
 };
 
@@ -300,12 +359,11 @@ struct SwiGluBlock {
     }
     // x += ffn(norm(x, post_norm)) for one token: 2 launches (3 more with an output norm).
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &post_norm, size_t hidden) const {
-        ctx.q8_0_gemv_fused(gate_up.buf, x, gu, gate_up.rows, gate_up.cols, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
-                            TM_CUDA_EPI_STORE);
+        gate_up.gemv_fused(ctx, x, gu, TM_CUDA_PRO_RMSNORM, &post_norm, eps, TM_CUDA_EPI_STORE);
         if (sh.world > 1) {
             act_mul(ctx, g_view, u_view, (uint32_t)wl);
             ctx.push_rows(g_view, h_full, 1, (uint32_t)wl);
-            ctx.q8_0_gemv(down.buf, h_full, out_local, down.rows, down.cols);
+            down.gemv(ctx, h_full, out_local);
             ctx.push_rows(out_local, out, 1, (uint32_t)(hidden / sh.world));
             if (out_norm) ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
             else ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
@@ -313,15 +371,15 @@ struct SwiGluBlock {
         }
         const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
         if (out_norm) {
-            ctx.q8_0_gemv_fused(down.buf, g_view, out, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
+            down.gemv_fused(ctx, g_view, out, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
             ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
         } else {
-            ctx.q8_0_gemv_fused(down.buf, g_view, x, down.rows, down.cols, pro, &u_view, 0.0f, TM_CUDA_EPI_ADD);
+            down.gemv_fused(ctx, g_view, x, pro, &u_view, 0.0f, TM_CUDA_EPI_ADD);
         }
     }
     // The tolerance-qualified batched form: norm and activation folded into the GEMMs' f16 copies,
     // gate|up as one launch, the residual add in the down projection's epilogue (5 launches -> 4).
-    bool fusable() const { return sh.world == 1 && width % 128 == 0; }
+    bool fusable() const { return sh.world == 1 && width % 128 == 0 && gate_up.type == 8 && down.type == 8; }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
                        size_t hidden) const {
         const uint32_t nn = (uint32_t)n;
@@ -346,7 +404,7 @@ struct SwiGluBlock {
             gate_up.gemm_part(ctx, 1, s.h2, s.loc2, nn, exact);
             act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
             ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
-            if (exact) {
+            if (exact || down.type == 1) {
                 down.gemm_all(ctx, s.g, s.loc, nn, exact);
                 ctx.push_rows(s.loc, s.d2, nn, (uint32_t)(hidden / sh.world));
             } else {  // multiply and exchange as one kernel
@@ -447,8 +505,7 @@ struct AttentionBlock {
     // attn = attention(norm(x, pre_norm)) at the device-held position: 2 launches.
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pre_norm, const CudaBuffer &pos_buf,
                 const CudaBuffer &status, bool exact) const {
-        ctx.q8_0_gemv_fused(qkv.buf, x, qkv_out, qkv.rows, qkv.cols, TM_CUDA_PRO_RMSNORM, &pre_norm, eps,
-                            TM_CUDA_EPI_STORE);
+        qkv.gemv_fused(ctx, x, qkv_out, TM_CUDA_PRO_RMSNORM, &pre_norm, eps, TM_CUDA_EPI_STORE);
         ctx.attention_decode_dev(q_view, k_view, v_view, q_norm, k_norm, inv_freq, k_cache, v_cache, attn, kv_scratch,
                                  pos_buf, 0, status, (uint32_t)heads_l, (uint32_t)kv_l, (uint32_t)spec.head_dim,
                                  (uint32_t)spec.rope_dims, (uint32_t)cap, (uint32_t)spec.window, eps, scale(), exact);
@@ -456,13 +513,13 @@ struct AttentionBlock {
     // Row split: proj = all_gather(o_local * all_gather(attn_local)), one token.
     void project_sharded(const CudaContext &ctx, const CudaBuffer &proj, size_t hidden) const {
         ctx.push_rows(attn, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
-        ctx.q8_0_gemv(o.buf, attn_full, proj_local, o.rows, o.cols);
+        o.gemv(ctx, attn_full, proj_local);
         ctx.push_rows(proj_local, proj, 1, (uint32_t)(hidden / sh.world));
     }
     // The tolerance-qualified batched form: input norm folded into the f16 copy, q|k|v as one GEMM
     // launch, the four launches before attention as one, tensor-core attention (9 launches -> 4).
     bool fusable() const {
-        return sh.world == 1 && qkv.part_rows.size() == 3 && qkv.part_rows[0] % 128 == 0 && qkv.part_rows[1] % 128 == 0 &&
+        return sh.world == 1 && qkv.type == 8 && o.type == 8 && qkv.part_rows.size() == 3 && qkv.part_rows[0] % 128 == 0 && qkv.part_rows[1] % 128 == 0 &&
                tm_cuda_attention_chunk_mma_supported((uint32_t)spec.head_dim);
     }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0,
@@ -497,7 +554,7 @@ struct AttentionBlock {
                                 nn, (uint32_t)spec.window);
         if (sh.world > 1) {
             ctx.push_rows(s.e, s.efull, nn, heads * hd);
-            if (exact) {
+            if (exact || o.type == 1) {
                 o.gemm_all(ctx, s.efull, s.loc, nn, exact);
                 ctx.push_rows(s.loc, s.proj, nn, (uint32_t)(hidden / sh.world));
             } else {  // multiply and exchange as one kernel
@@ -539,12 +596,11 @@ struct Layer {
         mixer.decode(ctx, x, pre_norm, pos_buf, status, exact);
         if (mixer.sh.world > 1 || mixer_out_norm) {
             if (mixer.sh.world > 1) mixer.project_sharded(ctx, proj, hidden);
-            else ctx.q8_0_gemv(mixer.o.buf, mixer.attn, proj, mixer.o.rows, mixer.o.cols);
+            else mixer.o.gemv(ctx, mixer.attn, proj);
             if (mixer_out_norm) ctx.rmsnorm_add(proj, mixer_out_norm, x, 1, (uint32_t)hidden, eps);
             else ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
         } else {
-            ctx.q8_0_gemv_fused(mixer.o.buf, mixer.attn, x, mixer.o.rows, mixer.o.cols, TM_CUDA_PRO_NONE, nullptr, 0.0f,
-                                TM_CUDA_EPI_ADD);
+            mixer.o.gemv_fused(ctx, mixer.attn, x, TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_ADD);
         }
         ffn.decode(ctx, x, post_norm, hidden);
     }
@@ -595,6 +651,16 @@ struct EngineModel::Impl {
     bool persistent = false;  // decode_graph is a persistent program
     const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
     uint32_t head_cols() const { return embedding.cols; }
+    uint32_t head_type() const { return tied ? embedding.type : head_own.type; }
+    // Final norm folded into the vocabulary projection of the one row in `x`.
+    void project_head(const CudaContext &c, float eps) const {
+        if (head_type() == 1)
+            c.f16_gemv_fused(head_buf(), x, logits, head_rows, head_cols(), TM_CUDA_PRO_RMSNORM, &final_norm, eps,
+                             TM_CUDA_EPI_STORE);
+        else
+            c.q8_0_gemv_fused(head_buf(), x, logits, head_rows, head_cols(), TM_CUDA_PRO_RMSNORM, &final_norm, eps,
+                              TM_CUDA_EPI_STORE);
+    }
 };
 
 DecodeProgramSize decode_program_size(const ModelGraph &graph, size_t capacity) {
@@ -610,6 +676,17 @@ DecodeProgramSize decode_program_size(const ModelGraph &graph, size_t capacity) 
             s.attention_elems, tm_cuda_program_attention_elems((uint32_t)m.heads, (uint32_t)m.head_dim, (uint32_t)capacity));
     }
     return s;
+}
+
+bool persistent_decode_applies(const ModelGraph &graph, const WeightSource &src, const EngineOptions &opts) {
+    // the program's weight ring streams the repacked Q8_0 planes only
+    auto q8 = [&](Tensor t) { return src.tensor_type_id(t.index) == 8; };
+    if (!q8(graph.embedding) || !q8(graph.head)) return false;
+    for (const LayerSpec &l : graph.layers)
+        if (!q8(l.mixer.q) || !q8(l.mixer.k) || !q8(l.mixer.v) || !q8(l.mixer.o) || !q8(l.ffn.gate) || !q8(l.ffn.up) ||
+            !q8(l.ffn.down))
+            return false;
+    return persistent_decode_applies(graph, opts);
 }
 
 bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opts) {
@@ -667,7 +744,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     const size_t n = std::min<size_t>(opts.prefill_batch, capacity);
     PrefillScratch::plan(graph, capacity, n, sh, p);
     if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, n));
-    if (persistent_decode_applies(graph, opts)) p.scratch_bytes(decode_program_size(graph, capacity).bytes());
+    if (persistent_decode_applies(graph, src, opts)) p.scratch_bytes(decode_program_size(graph, capacity).bytes());
     GpuAllocPlan out;
     out.weights = p.weights;
     out.state = p.state;
@@ -707,7 +784,11 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     I.head_rows = (uint32_t)(graph.vocab / sh.world);
     if (!I.tied) I.head_own = Matrix::load(c, src, {graph.head}, sh);
     else if (sh.world > 1)
-        I.tied_view = c.row_view(I.embedding.buf, I.embedding.rows, I.embedding.cols, sh.rank * I.head_rows, I.head_rows);
+        I.tied_view = I.embedding.type == 1
+                          ? I.embedding.buf.view((size_t)sh.rank * I.head_rows * I.embedding.cols * 2,
+                                                 (size_t)I.head_rows * I.embedding.cols * 2)
+                          : c.row_view(I.embedding.buf, I.embedding.rows, I.embedding.cols, sh.rank * I.head_rows,
+                                       I.head_rows);
     if (I.embedding.cols != graph.hidden || I.embedding.rows != graph.vocab ||
         (!I.tied && (I.head_own.cols != graph.hidden || I.head_own.rows != I.head_rows)))
         throw TuckmillError(ErrorCode::UnsupportedArchitecture, "embedding / head shapes do not match the graph");
@@ -733,7 +814,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // position advanced.  (One command buffer per step in the reference:
     // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)  Where the
     // model allows it the step becomes one persistent kernel, else a graph of kernels.
-    I.persistent = persistent_decode_applies(g, opts);
+    I.persistent = persistent_decode_applies(g, src, opts);
     if (I.persistent) {
         const DecodeProgramSize ps = decode_program_size(g, capacity);
         c.begin_program(ps.max_ops, ps.vector_elems, ps.attention_elems);
@@ -769,11 +850,14 @@ void EngineModel::encode_decode_step() {
     Impl &I = *impl_;
     const CudaContext &c = *ctx_;
     const ModelGraph &g = graph_;
-    c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
-                       g.embedding_scale, I.x);
+    if (I.embedding.type == 1)
+        c.f16_row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
+                               g.embedding_scale, I.x);
+    else
+        c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
+                           g.embedding_scale, I.x);
     for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
-    c.q8_0_gemv_fused(I.head_buf(), I.x, I.logits, I.head_rows, I.head_cols(), TM_CUDA_PRO_RMSNORM, &I.final_norm,
-                      g.eps, TM_CUDA_EPI_STORE);
+    I.project_head(c, g.eps);
     if (I.sh.world > 1)
         c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens, 1, &I.pos_buf, 0,
                          (uint32_t)capacity_ + 1, &I.tokens_mirror);
@@ -852,14 +936,17 @@ void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) {
         const bool last = t0 + k == n;
         const uint32_t pos0 = (uint32_t)(pos_ + t0);
         c.grouped([&] {
-            c.rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
-                            graph_.embedding_scale, I.scratch.x);
+            if (I.embedding.type == 1)
+                c.f16_rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
+                                    graph_.embedding_scale, I.scratch.x);
+            else
+                c.rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
+                                graph_.embedding_scale, I.scratch.x);
             for (const Layer &L : I.layers) L.prefill(c, I.scratch, k, pos0, graph_.hidden, graph_.eps, opts_.exact);
             if (last && want_token) {
                 // Vocabulary projection for the last row only (engine/metal.rs:2610-2617).
                 c.copy_f32(I.scratch.x, (uint32_t)((k - 1) * graph_.hidden), I.x, 0, (uint32_t)graph_.hidden);
-                c.q8_0_gemv_fused(I.head_buf(), I.x, I.logits, I.head_rows, I.head_cols(), TM_CUDA_PRO_RMSNORM,
-                                  &I.final_norm, graph_.eps, TM_CUDA_EPI_STORE);
+                I.project_head(c, graph_.eps);
                 if (I.sh.world > 1)
                     c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens,
                                      pos0 + (uint32_t)k, nullptr, 0, (uint32_t)capacity_ + 1, nullptr);

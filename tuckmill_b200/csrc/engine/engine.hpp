@@ -42,6 +42,8 @@ struct EngineOptions {
 // Whether load_with will record the decode step as a persistent program for this graph and options
 // (the plan prices the program's device memory exactly when this holds).
 bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opts);
+// The same, also requiring every matrix of `src` to be Q8_0 (what load_with and the plan ask).
+bool persistent_decode_applies(const ModelGraph &graph, const WeightSource &src, const EngineOptions &opts);
 // What the decode program of `graph` at `capacity` positions is opened for: operators at most,
 // elements of all the vectors its operators produce, elements of its largest attention's partials
 // (the arguments of tm_cuda_begin_program / tm_cuda_program_bytes).

@@ -63,6 +63,12 @@ _OPS = {
     "row_indirect_f32": [_P, _P, _U32, _U32, _U32, _P, _U32, _P],
     "rows_indirect_f32": [_P, _P, _U32, _U32, _P, _U32, _U32, _F, _P],
     "row_indirect_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
+    "f16_gemv": [_P, _P, _P, _P, _U32, _U32],
+    "f16_gemm": [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32],
+    "f16_row_f32": [_P, _P, _P, _U32, _U32, _U32],
+    "f16_gemv_fused": [_P, _P, _P, _P, _U32, _U32, _I, _P, _F, _I],
+    "f16_row_indirect_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
+    "f16_rows_indirect_f32": [_P, _P, _U32, _U32, _P, _U32, _U32, _F, _P],
     "begin_group": [_P],
     "end_group": [_P],
     "abort_group": [_P],
@@ -381,6 +387,24 @@ class CudaContext:
         self._call("q8_0_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)
 
     def q8_0_row(self, w, out, row, cols, out_off=0): self._call("q8_0_row_f32", w.handle, out.handle, row, cols, out_off)
+
+    # F16-weight matrices: rows * cols binary16 values, uploaded verbatim (tm_metal.h:156-179 forms)
+    def f16_gemv(self, w, x, y, rows, cols): self._call("f16_gemv", w.handle, x.handle, y.handle, rows, cols)
+
+    def f16_gemm(self, w, x, y, rows, cols, batch, x_off=0, y_off=0):
+        self._call("f16_gemm", w.handle, x.handle, y.handle, rows, cols, batch, x_off, y_off)
+
+    def f16_row(self, w, out, row, cols, out_off=0): self._call("f16_row_f32", w.handle, out.handle, row, cols, out_off)
+
+    def f16_gemv_fused(self, w, x, y, rows, cols, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
+        self._call("f16_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)
+
+    def f16_row_indirect_dev(self, w, rows, cols, ids, base, pos_buf, pos_index, bias, scale, out):
+        self._call("f16_row_indirect_f32_dev", w.handle, rows, cols, ids.handle, base, self._h(pos_buf), pos_index,
+                   bias, scale, out.handle)
+
+    def f16_rows_indirect(self, w, rows, cols, ids, first, n, scale, out):
+        self._call("f16_rows_indirect_f32", w.handle, rows, cols, ids.handle, first, n, scale, out.handle)
 
     def row_indirect_f32(self, w, type_id, rows, cols, ids, slot, out):
         self._call("row_indirect_f32", w.handle, type_id, rows, cols, ids.handle, slot, out.handle)

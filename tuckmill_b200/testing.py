@@ -233,13 +233,36 @@ def _gguf_kv(key: str, value) -> bytes:
     raise TypeError(type(value))
 
 
-def write_gguf(path, shape: DecoderShape, seed: int = 0, norm_jitter: float = 0.0,
-               alignment: int = 32) -> dict:
-    """Write a valid GGUF v3 with seeded Q8_0 matrices and f32 norm vectors.
+def fixture_values(count: int) -> np.ndarray:
+    """Element e of every F32 / F16 tensor of the reference's synthetic model fixtures:
+    ((31 e + 7) mod 64 - 32) / 64, multiples of 1/64 in [-0.5, 0.5), exact in binary16
+    (crates/manifest/src/testing.rs:611-614)."""
+    e = np.arange(count, dtype=np.uint64)
+    return (((e * np.uint64(31) + np.uint64(7)) % np.uint64(64)).astype(np.float32) - 32.0) / 64.0
 
-    Norm vectors are 1.0 (+ ``norm_jitter`` * N(0,1) when asked).  Returns
-    ``{name: (type, dims, absolute file offset, bytes)}``.
+
+def fixture_q8_0(blocks: int) -> np.ndarray:
+    """Q8_0 blocks of the same fixtures: d = 1/128, q[e] = (11 e + 5) mod 128 - 64
+    (crates/manifest/src/testing.rs:678-690)."""
+    e = np.arange(blocks * 32, dtype=np.uint64)
+    q = (((e * np.uint64(11) + np.uint64(5)) % np.uint64(128)).astype(np.int32) - 64).astype(np.int8)
+    return q8_0_from_parts(np.full((1, blocks), 0.0078125, dtype=np.float16), q.reshape(1, blocks * 32))
+
+
+def write_gguf(path, shape: DecoderShape, seed: int = 0, norm_jitter: float = 0.0,
+               alignment: int = 32, fill: str = "seeded") -> dict:
+    """Write a valid GGUF v3 with Q8_0 or F16 matrices and f32 norm vectors.
+
+    ``fill="seeded"``: seeded Q8_0 matrices, norm vectors 1.0 (+ ``norm_jitter`` * N(0,1)
+    when asked); ``"seeded-f16"``: the same matrices dequantised and rounded to binary16 (an
+    F16 twin whose rows differ, unlike the reference fixture's).  ``fill="fixture-f16"`` / ``"fixture-q8_0"``: the tensor contents of the
+    reference's synthetic fixtures (crates/manifest/src/testing.rs:236-396, 611-690) -- with
+    TINY_QWEN3 and "fixture-f16" every tensor equals the reference's ``tiny_qwen3`` artifact
+    byte for byte (the tokenizer metadata, which no engine path reads, is left out).
+    Returns ``{name: (type, dims, absolute file offset, bytes)}``.
     """
+    if fill not in ("seeded", "seeded-f16", "fixture-f16", "fixture-q8_0"):
+        raise ValueError(fill)
     a = shape.arch
     kv = {
         "general.architecture": a, "general.alignment": alignment,
@@ -256,7 +279,10 @@ def write_gguf(path, shape: DecoderShape, seed: int = 0, norm_jitter: float = 0.
     tensors: list[tuple[str, list[int], int, int]] = []  # name, dims, type, bytes
 
     def q8(name, out_dim, in_dim):
-        tensors.append((name, [in_dim, out_dim], GGML_Q8_0, out_dim * (in_dim // 32) * 34))
+        if fill in ("fixture-f16", "seeded-f16"):
+            tensors.append((name, [in_dim, out_dim], GGML_F16, out_dim * in_dim * 2))
+        else:
+            tensors.append((name, [in_dim, out_dim], GGML_Q8_0, out_dim * (in_dim // 32) * 34))
 
     def f32(name, n):
         tensors.append((name, [n], GGML_F32, n * 4))
@@ -287,7 +313,18 @@ def write_gguf(path, shape: DecoderShape, seed: int = 0, norm_jitter: float = 0.
         f.write(b"\0" * (start - len(head) - len(infos)))
         for tid, ((name, dims, ty, nbytes), r) in enumerate(zip(tensors, rel)):
             f.seek(start + r)
-            if ty == GGML_Q8_0:
+            if fill == "seeded-f16" and ty == GGML_F16:
+                rows, cols = dims[1], dims[0]
+                step = max(1, (1 << 25) // cols)
+                for r0 in range(0, rows, step):
+                    f.write(q8_0_dequant(q8_0_rows(seed, tid, r0, min(step, rows - r0), cols)).astype(np.float16).tobytes())
+            elif fill.startswith("fixture"):
+                if ty == GGML_Q8_0:
+                    f.write(fixture_q8_0(dims[0] * dims[1] // 32).tobytes())
+                else:
+                    v = fixture_values(int(np.prod(dims)))
+                    f.write((v.astype(np.float16) if ty == GGML_F16 else v).tobytes())
+            elif ty == GGML_Q8_0:
                 rows, cols = dims[1], dims[0]
                 step = max(1, (1 << 25) // cols)
                 for r0 in range(0, rows, step):

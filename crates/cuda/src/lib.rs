@@ -121,6 +121,7 @@ mod ffi {
         pub fn tm_cuda_row_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, type_id: u32, rows: u32, cols: u32, ids: *mut TmCudaBuffer, slot: u32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_rows_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, first: u32, n: u32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_q8_0_gemv_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_q8_0_gemm_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, batch: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_begin_group(ctx: *mut TmCudaCtx, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_end_group(ctx: *mut TmCudaCtx, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_abort_group(ctx: *mut TmCudaCtx, err: *mut c_char, err_cap: usize) -> c_int;
@@ -164,6 +165,10 @@ mod ffi {
         pub fn tm_cuda_attention_decode_dev(ctx: *mut TmCudaCtx, q: *mut TmCudaBuffer, k: *mut TmCudaBuffer, v: *mut TmCudaBuffer, q_norm: *mut TmCudaBuffer, k_norm: *mut TmCudaBuffer, inv_freq: *mut TmCudaBuffer, k_cache: *mut TmCudaBuffer, v_cache: *mut TmCudaBuffer, out: *mut TmCudaBuffer, scratch: *mut TmCudaBuffer, pos_buf: *mut TmCudaBuffer, pos_index: u32, status: *mut TmCudaBuffer, heads: u32, kv_heads: u32, head_dim: u32, n_rot: u32, cap: u32, window: u32, eps: f32, scale: f32, exact: c_int, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_attention_decode_static_max_scratch() -> usize;
         pub fn tm_cuda_attention_decode_dev_static(ctx: *mut TmCudaCtx, q: *mut TmCudaBuffer, k: *mut TmCudaBuffer, v: *mut TmCudaBuffer, q_norm: *mut TmCudaBuffer, k_norm: *mut TmCudaBuffer, inv_freq: *mut TmCudaBuffer, k_cache: *mut TmCudaBuffer, v_cache: *mut TmCudaBuffer, out: *mut TmCudaBuffer, pos_buf: *mut TmCudaBuffer, pos_index: u32, status: *mut TmCudaBuffer, heads: u32, kv_heads: u32, head_dim: u32, n_rot: u32, cap: u32, window: u32, eps: f32, scale: f32, exact: c_int, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_attention_decode_batch_dev(ctx: *mut TmCudaCtx, q: *mut TmCudaBuffer, k: *mut TmCudaBuffer, v: *mut TmCudaBuffer, q_norm: *mut TmCudaBuffer, k_norm: *mut TmCudaBuffer, inv_freq: *mut TmCudaBuffer, k_cache: *mut TmCudaBuffer, v_cache: *mut TmCudaBuffer, out: *mut TmCudaBuffer, scratch: *mut TmCudaBuffer, pos_buf: *mut TmCudaBuffer, status: *mut TmCudaBuffer, n_seq: u32, q_stride: u32, kv_stride: u32, heads: u32, kv_heads: u32, head_dim: u32, n_rot: u32, cap: u32, window: u32, eps: f32, scale: f32, exact: c_int, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_rows_indirect_seq_f32_dev(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, ids_stride: u32, pos_buf: *mut TmCudaBuffer, n_seq: u32, bias: i32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_argmax_rows_f32_dev(ctx: *mut TmCudaCtx, x: *mut TmCudaBuffer, n_rows: u32, n: u32, partial: *mut TmCudaBuffer, out: *mut TmCudaBuffer, out_stride: u32, base: u32, pos_buf: *mut TmCudaBuffer, out_cap: u32, mirror: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_u32_add_sat(ctx: *mut TmCudaCtx, buf: *mut TmCudaBuffer, first: u32, count: u32, delta: u32, limit: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_u32_add(ctx: *mut TmCudaCtx, buf: *mut TmCudaBuffer, index: u32, delta: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_argmax_f32_dev(ctx: *mut TmCudaCtx, x: *mut TmCudaBuffer, n: u32, partial: *mut TmCudaBuffer, out: *mut TmCudaBuffer, base: u32, pos_buf: *mut TmCudaBuffer, pos_index: u32, out_cap: u32, mirror: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_row_indirect_f32_dev(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, base: u32, pos_buf: *mut TmCudaBuffer, pos_index: u32, bias: i32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;

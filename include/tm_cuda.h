@@ -241,6 +241,13 @@ int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer 
                             tm_cuda_buffer *y, uint32_t rows, uint32_t cols, int prologue,
                             tm_cuda_buffer *pro, float eps, int epilogue, char *err,
                             size_t err_cap);
+/* No counterpart: the same fused forms for `batch` tokens (1..TM_CUDA_GEMM_MAX_BATCH), token-major x
+ * [batch][cols] and y [batch][rows]; the activation prologues take `pro` as [batch][cols], the norm
+ * weight as [cols].  Row t of the result is bit-identical to the one-token call on row t (the
+ * contract of tm_cuda_q8_0_gemm).  A decode step of several sequences uses it. */
+int tm_cuda_q8_0_gemm_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                            uint32_t cols, uint32_t batch, int prologue, tm_cuda_buffer *pro, float eps, int epilogue,
+                            char *err, size_t err_cap);
 
 /* ---------------- grouped encoding ---------------- */
 /* tm_metal.h:133-135 begin/end/abort_group: operations between begin and end
@@ -476,6 +483,45 @@ int tm_cuda_attention_decode_dev_static(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_
                                         uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t n_rot,
                                         uint32_t cap, uint32_t window, float eps, float scale, int exact,
                                         char *err, size_t err_cap);
+/* No counterpart: decode steps of SEVERAL sequences in one recorded graph (the reference serves one
+ * request at a time, crates/supervisor/src/queue.rs:1-4).  A step of n_seq sequences is a batch of
+ * n_seq rows through the batched projections (tm_cuda_q8_0_gemm / _gemm_mma), with these operators
+ * around them; sequence s owns position pos_buf[s] (consecutive u32), the s-th row of every
+ * activation matrix, the s-th cache plane pair and the s-th token log.
+ * tm_cuda_attention_decode_batch_dev: tm_cuda_attention_decode_dev for every sequence in ONE launch.
+ * Row s of q starts at element s * q_stride (0 = dense, heads * head_dim), rows of k and v at
+ * s * kv_stride (0 = kv_heads * head_dim) -- so the three may be views into one [n_seq][q|k|v]
+ * projection output; the caches are [n_seq][kv_heads][cap][head_dim] f16, out is dense
+ * [n_seq][heads * head_dim], scratch n_seq regions of
+ * tm_cuda_attention_decode_scratch_bytes (zero-filled once).  Results per sequence are those of the
+ * single call, bit for bit (same kernels, one more grid dimension); a sequence whose position is
+ * >= cap writes nothing and sets bit 0 of status[0]. */
+int tm_cuda_attention_decode_batch_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k, tm_cuda_buffer *v,
+                                       tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm, tm_cuda_buffer *inv_freq,
+                                       tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                       tm_cuda_buffer *scratch, tm_cuda_buffer *pos_buf, tm_cuda_buffer *status,
+                                       uint32_t n_seq, uint32_t q_stride, uint32_t kv_stride, uint32_t heads,
+                                       uint32_t kv_heads, uint32_t head_dim,
+                                       uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale,
+                                       int exact, char *err, size_t err_cap);
+/* out[s] = row ids[s * ids_stride + pos_buf[s] + bias] of the packed Q8_0 matrix (times `scale` when
+ * non-zero), s < n_seq: the embedding rows of a batched step, each sequence reading its own token
+ * log at its own position.  A slot outside the log or an id >= rows writes zeros. */
+int tm_cuda_rows_indirect_seq_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                                      tm_cuda_buffer *ids, uint32_t ids_stride, tm_cuda_buffer *pos_buf,
+                                      uint32_t n_seq, int32_t bias, float scale, tm_cuda_buffer *out, char *err,
+                                      size_t err_cap);
+/* Greedy choice of n_rows rows of n logits in two launches: row r's winner (the rule of
+ * tm_cuda_argmax_f32) goes to out[r * out_stride + base + pos_buf[r]] (and to `mirror`, when given)
+ * if base + pos_buf[r] < out_cap <= out_stride.  `partial` holds n_rows * 512 bytes. */
+int tm_cuda_argmax_rows_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n_rows, uint32_t n,
+                                tm_cuda_buffer *partial, tm_cuda_buffer *out, uint32_t out_stride, uint32_t base,
+                                tm_cuda_buffer *pos_buf, uint32_t out_cap, tm_cuda_buffer *mirror, char *err,
+                                size_t err_cap);
+/* buf[first + i] = min(buf[first + i] + delta, limit), i < count: advances every sequence's position;
+ * a sequence that has filled its cache stays on its last row instead of running past it. */
+int tm_cuda_u32_add_sat(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t first, uint32_t count, uint32_t delta,
+                        uint32_t limit, char *err, size_t err_cap);
 /* No counterpart: buf[index] += delta (u32), to advance a device position
  * inside a recorded graph. */
 int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint32_t delta,

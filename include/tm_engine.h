@@ -59,6 +59,10 @@ typedef struct {
      * as ONE persistent kernel (tm_cuda_begin_program) where the model allows it (single device,
      * not exact, attention shapes the program kernel serves), the graph otherwise. */
     int persistent_step;
+    /* Concurrent sequences the engine holds state for and decodes together, one row each, in one
+     * recorded step (0 or 1 = one sequence: the reference's engine, which serves one request at a
+     * time, crates/supervisor/src/queue.rs:1-4).  KV state and admission scale with it. */
+    uint32_t sequences;
 } tm_engine_options;
 
 /* 128 opaque bytes naming a new communicator (tm_cuda_comm_unique_id). */
@@ -101,6 +105,25 @@ int tm_engine_logits(tm_engine *e, float *logits, char *err, size_t err_cap);
 int tm_engine_generate(tm_engine *e, const uint32_t *prompt, uint32_t n_prompt, uint32_t max_new,
                        int ignore_eos, uint32_t *out_tokens, uint32_t *n_out, tm_engine_stats *stats,
                        char *err, size_t err_cap);
+/* ---- several sequences (tm_engine_options.sequences > 1); no counterpart in the reference ---- */
+/* Prompt tokens of sequence `seq` at its own position; the other sequences are untouched. */
+int tm_engine_prefill_seq(tm_engine *e, uint32_t seq, const uint32_t *tokens, uint32_t n, int want_token, char *err,
+                          size_t err_cap);
+int tm_engine_prefill_token_of(tm_engine *e, uint32_t seq, uint32_t *token, char *err, size_t err_cap);
+/* One decode step of every sequence: tokens[s] goes to sequence s at its position; `logits` (NULL or
+ * sequences * vocab floats) receives every row.  Row s equals the one-sequence step on the same state
+ * bit for bit in `exact` mode, and for up to 8 sequences in any mode. */
+int tm_engine_step_batch(tm_engine *e, const uint32_t *tokens, float *logits, char *err, size_t err_cap);
+/* `steps` device-greedy steps of all sequences with no host read in between (kernel-only timing). */
+int tm_engine_decode_steps_batch(tm_engine *e, uint32_t steps, char *err, size_t err_cap);
+/* Greedy generation for n_requests <= sequences prompts at once (prompts concatenated in `prompts`,
+ * lengths in prompt_lens): request r's tokens go to out_tokens[r * max_new ..], its count to
+ * out_counts[r].  A request stops at max_new tokens, at EOS unless ignore_eos, or at capacity; the
+ * others go on.  `stats` counts all requests. */
+int tm_engine_generate_batch(tm_engine *e, const uint32_t *prompts, const uint32_t *prompt_lens, uint32_t n_requests,
+                             uint32_t max_new, int ignore_eos, uint32_t *out_tokens, uint32_t *out_counts,
+                             tm_engine_stats *stats, char *err, size_t err_cap);
+
 /* `steps` decode-graph replays with no host read in between (device-greedy),
  * for kernel-only timing; the caller brackets it with events on the stream. */
 int tm_engine_decode_steps(tm_engine *e, uint32_t steps, char *err, size_t err_cap);

@@ -49,14 +49,16 @@ uint64_t artifact_weight_bytes(const ModelGraph &g, const WeightSource &src) {
     return alloc_plan_with(g, src, 1, o).weights;
 }
 
-PlanBudget admit(const ModelGraph &g, const WeightSource &src, uint32_t context, uint64_t budget) {
+PlanBudget admit(const ModelGraph &g, const WeightSource &src, uint32_t context, uint64_t budget,
+                 uint32_t sequences = 1) {
     KvGeometry kv;
     kv.layers = g.layers.size();
     kv.kv_head_count = g.layers.empty() ? 0 : g.layers[0].mixer.kv_heads;
     kv.key_length = kv.value_length = g.layers.empty() ? 0 : g.layers[0].mixer.head_dim;
     PlannerPolicy policy;
     uint64_t kv_total = 0, per_token = 0;
-    if (!estimate_kv_bytes(kv, context, policy.kv_bytes_per_element, &kv_total, &per_token))
+    // every sequence holds `context` positions of KV
+    if (!estimate_kv_bytes(kv, (uint64_t)context * sequences, policy.kv_bytes_per_element, &kv_total, &per_token))
         throw TuckmillError(ErrorCode::ContextExceedsBudget, "KV payload overflows at context " + std::to_string(context));
     PlanBudget b = make_resident_plan(budget, artifact_weight_bytes(g, src), kv_total, policy);
     require_admitted(b, context);
@@ -99,8 +101,11 @@ int tm_engine_load(const tm_engine_options *o, tm_engine **out, char *err, size_
                 throw TuckmillError(ErrorCode::Internal, "cannot query device memory");
             budget = total_b;
         }
-        e->budget = admit(graph, *e->weights, o->context, budget);
         EngineOptions eo;
+        eo.sequences = o->sequences ? o->sequences : 1;
+        if (eo.sequences > kMaxSequences)
+            throw TuckmillError(ErrorCode::InvalidRequest, "sequences must be 1.." + std::to_string(kMaxSequences));
+        e->budget = admit(graph, *e->weights, o->context, budget, eo.sequences);
         eo.prefill_batch = o->prefill_batch ? o->prefill_batch : kPrefillBatchDefault;
         eo.exact = o->exact != 0;
         eo.persistent = o->persistent_step != 0;
@@ -193,6 +198,59 @@ int tm_engine_generate(tm_engine *e, const uint32_t *prompt, uint32_t n_prompt, 
         std::vector<uint32_t> toks = e->model->generate(prompt, n_prompt, max_new, ignore_eos != 0, &s);
         for (size_t i = 0; i < toks.size(); ++i) out_tokens[i] = toks[i];
         *n_out = (uint32_t)toks.size();
+        if (stats) {
+            stats->ttft_ns = s.ttft_ns;
+            stats->decode_span_ns = s.decode_span_ns;
+            stats->prompt_tokens = s.prompt_tokens;
+            stats->generated = s.generated;
+            stats->kernel_launches = s.kernel_launches;
+            stats->dispatches = s.dispatches;
+            stats->h2d_bytes = s.h2d_bytes;
+            stats->d2h_bytes = s.d2h_bytes;
+        }
+    })
+}
+
+int tm_engine_prefill_seq(tm_engine *e, uint32_t seq, const uint32_t *tokens, uint32_t n, int want_token, char *err,
+                          size_t err_cap) {
+    GUARD(e->model->prefill_seq(seq, tokens, n, want_token != 0))
+}
+
+int tm_engine_prefill_token_of(tm_engine *e, uint32_t seq, uint32_t *token, char *err, size_t err_cap) {
+    GUARD(*token = e->model->prefill_token_of(seq))
+}
+
+int tm_engine_step_batch(tm_engine *e, const uint32_t *tokens, float *logits, char *err, size_t err_cap) {
+    GUARD({
+        e->model->step_batch(tokens);
+        if (logits) e->model->logits_batch(logits);
+    })
+}
+
+int tm_engine_decode_steps_batch(tm_engine *e, uint32_t steps, char *err, size_t err_cap) {
+    GUARD({
+        for (uint32_t i = 0; i < steps; ++i) e->model->submit_batch_greedy();
+    })
+}
+
+int tm_engine_generate_batch(tm_engine *e, const uint32_t *prompts, const uint32_t *prompt_lens, uint32_t n_requests,
+                             uint32_t max_new, int ignore_eos, uint32_t *out_tokens, uint32_t *out_counts,
+                             tm_engine_stats *stats, char *err, size_t err_cap) {
+    GUARD({
+        if (!prompts || !prompt_lens || !out_tokens || !out_counts)
+            throw TuckmillError(ErrorCode::InvalidRequest, "null batch arguments");
+        std::vector<std::vector<uint32_t>> ps(n_requests);
+        size_t off = 0;
+        for (uint32_t r = 0; r < n_requests; ++r) {
+            ps[r].assign(prompts + off, prompts + off + prompt_lens[r]);
+            off += prompt_lens[r];
+        }
+        GenerateStats s;
+        const auto toks = e->model->generate_batch(ps, max_new, ignore_eos != 0, &s);
+        for (uint32_t r = 0; r < n_requests; ++r) {
+            for (size_t i = 0; i < toks[r].size(); ++i) out_tokens[(size_t)r * max_new + i] = toks[r][i];
+            out_counts[r] = (uint32_t)toks[r].size();
+        }
         if (stats) {
             stats->ttft_ns = s.ttft_ns;
             stats->decode_span_ns = s.decode_span_ns;

@@ -309,6 +309,38 @@ public:
                 n_rot, cap, window, eps, scale, exact ? 1 : 0);
     }
 
+    // ---- decode steps of several sequences (include/tm_cuda.h) ----
+    void attention_decode_batch(const CudaBuffer &q, const CudaBuffer &k, const CudaBuffer &v, const CudaBuffer &qn,
+                                const CudaBuffer &kn, const CudaBuffer &inv_freq, const CudaBuffer &kc,
+                                const CudaBuffer &vc, const CudaBuffer &out, const CudaBuffer &scratch,
+                                const CudaBuffer &pos, const CudaBuffer &status, uint32_t n_seq, uint32_t q_stride,
+                                uint32_t kv_stride, uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot,
+                                uint32_t cap, uint32_t window, float eps, float scale, bool exact) const {
+        TM_CALL(tm_cuda_attention_decode_batch_dev, q.raw(), k.raw(), v.raw(), qn.raw(), kn.raw(), inv_freq.raw(),
+                kc.raw(), vc.raw(), out.raw(), scratch.raw(), pos.raw(), status.raw(), n_seq, q_stride, kv_stride,
+                heads, kvh, hd, n_rot, cap, window, eps, scale, exact ? 1 : 0);
+    }
+    void rows_indirect_seq(const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &ids,
+                           uint32_t ids_stride, const CudaBuffer &pos, uint32_t n_seq, int32_t bias, float scale,
+                           const CudaBuffer &out) const {
+        TM_CALL(tm_cuda_rows_indirect_seq_f32_dev, w.raw(), rows, cols, ids.raw(), ids_stride, pos.raw(), n_seq, bias,
+                scale, out.raw());
+    }
+    void argmax_rows_dev(const CudaBuffer &x, uint32_t n_rows, uint32_t n, const CudaBuffer &partial,
+                         const CudaBuffer &out, uint32_t out_stride, uint32_t base, const CudaBuffer &pos,
+                         uint32_t out_cap, const CudaBuffer *mirror) const {
+        TM_CALL(tm_cuda_argmax_rows_f32_dev, x.raw(), n_rows, n, partial.raw(), out.raw(), out_stride, base, pos.raw(),
+                out_cap, mirror ? mirror->raw() : nullptr);
+    }
+    void u32_add_sat(const CudaBuffer &b, uint32_t first, uint32_t count, uint32_t delta, uint32_t limit) const {
+        TM_CALL(tm_cuda_u32_add_sat, b.raw(), first, count, delta, limit);
+    }
+    void q8_0_gemm_fused(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows, uint32_t cols,
+                         uint32_t batch, int prologue, const CudaBuffer *pro, float eps, int epilogue) const {
+        TM_CALL(tm_cuda_q8_0_gemm_fused, w.raw(), x.raw(), y.raw(), rows, cols, batch, prologue,
+                pro ? pro->raw() : nullptr, eps, epilogue);
+    }
+
     // ---- multi-GPU row split ----
     void comm_init(const void *id128, int rank, int world) const {
         char e[256] = "";

@@ -305,6 +305,13 @@ struct PrefillScratch {
     }
 };
 
+// What the n rows of a batched pass are: n consecutive positions of sequence `seq` (a prefill chunk),
+// or -- with `pos_buf` set -- one decode row per sequence, sequence s at the device position pos_buf[s].
+struct RowsAre {
+    size_t seq = 0;
+    const CudaBuffer *pos_buf = nullptr, *status = nullptr;
+};
+
 // Gated FFN: down(act(gate x) * up x), optional RMS norm on the output before
 // the residual add (engine/metal.rs:431-535).  gate|up are one matrix.  With a
 // row split every rank owns width/world gate and up rows and hidden/world down
@@ -435,29 +442,37 @@ struct AttentionBlock {
     CudaBuffer attn_full, proj_local;  // row split only
     size_t cap = 0, heads_l = 0, kv_l = 0;
     Shard sh;
+    // Several sequences: the caches are [seqs] plane pairs (sequence 0 first, so the one-sequence
+    // operators work on the whole buffers), the views below are the single planes a prefill writes.
+    size_t seqs = 1;
+    std::vector<CudaBuffer> k_seq, v_seq;
+    CudaBuffer q_rows, k_rows, v_rows;  // q | k | v columns of the [seqs][q|k|v] projection output
+    const CudaBuffer &kc(size_t seq) const { return seqs > 1 ? k_seq[seq] : k_cache; }
+    const CudaBuffer &vc(size_t seq) const { return seqs > 1 ? v_seq[seq] : v_cache; }
 
     static uint64_t kv_plane_bytes(const AttentionSpec &s, size_t cap, Shard sh) {
         return (uint64_t)(s.kv_heads / sh.world) * cap * s.head_dim * 2;
     }
-    static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, size_t hidden, Shard sh, Plan &p) {
+    static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, size_t hidden, Shard sh, Plan &p,
+                     size_t seqs) {
         p.weights += Matrix::plan(src, {s.q, s.k, s.v}, sh) + Matrix::plan(src, {s.o}, sh);
         p.weights_f32(vector_len(src, s.q_norm));
         p.weights_f32(vector_len(src, s.k_norm));
         // The RoPE table is derived by the engine, not artifact bytes: scratch.
         p.scratch_f32(s.rope_dims / 2);
-        p.state += 2 * kv_plane_bytes(s, cap, sh);
+        p.state += 2 * kv_plane_bytes(s, cap, sh) * seqs;
         const size_t hl = s.heads / sh.world, kl = s.kv_heads / sh.world;
-        p.scratch_f32((hl + 2 * kl) * s.head_dim);
+        p.scratch_f32((hl + 2 * kl) * s.head_dim * seqs);
         p.scratch_f32(hl * s.head_dim);
-        p.scratch_bytes(tm_cuda_attention_decode_scratch_bytes((uint32_t)hl, (uint32_t)kl, (uint32_t)s.head_dim,
-                                                               (uint32_t)cap));
+        p.scratch_bytes(seqs * tm_cuda_attention_decode_scratch_bytes((uint32_t)hl, (uint32_t)kl, (uint32_t)s.head_dim,
+                                                                      (uint32_t)cap));
         if (sh.world > 1) {
             p.target_f32(s.heads * s.head_dim, sh.world);  // attn_full
             p.scratch_f32(hidden / sh.world);
         }
     }
     static AttentionBlock load(const CudaContext &ctx, const WeightSource &src, const AttentionSpec &s, float eps,
-                               size_t cap, size_t hidden, Shard sh) {
+                               size_t cap, size_t hidden, Shard sh, size_t seqs) {
         if (s.head_dim % 32 != 0 || (s.head_dim / 32 > 4 && s.head_dim != 256) || s.rope_dims % 2 != 0)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture,
                                 "attention head size " + std::to_string(s.head_dim) + " has no CUDA block");
@@ -481,15 +496,31 @@ struct AttentionBlock {
         b.q_norm = vector(ctx, src, s.q_norm);
         b.k_norm = vector(ctx, src, s.k_norm);
         b.inv_freq = ctx.floats(rope_inv_freq(s.rope_dims, s.rope_base));
-        b.k_cache = ctx.buffer(kv_plane_bytes(s, cap, sh));
-        b.v_cache = ctx.buffer(kv_plane_bytes(s, cap, sh));
-        b.qkv_out = zeros_f32(ctx, hd + 2 * kv);
+        b.seqs = seqs;
+        const size_t plane = kv_plane_bytes(s, cap, sh);
+        b.k_cache = ctx.buffer(plane * seqs);
+        b.v_cache = ctx.buffer(plane * seqs);
+        if (seqs > 1) {
+            if (plane % 16 != 0)
+                throw TuckmillError(ErrorCode::InvalidRequest, "KV plane of one sequence is not a 16-byte multiple");
+            for (size_t i = 0; i < seqs; ++i) {
+                b.k_seq.push_back(b.k_cache.view(i * plane, plane));
+                b.v_seq.push_back(b.v_cache.view(i * plane, plane));
+            }
+        }
+        b.qkv_out = zeros_f32(ctx, (hd + 2 * kv) * seqs);
+        {
+            const size_t all = (hd + 2 * kv) * seqs * 4;
+            b.q_rows = b.qkv_out.view(0, all);
+            b.k_rows = b.qkv_out.view(hd * 4, all - hd * 4);
+            b.v_rows = b.qkv_out.view((hd + kv) * 4, all - (hd + kv) * 4);
+        }
         b.q_view = b.qkv_out.view(0, hd * 4);
         b.k_view = b.qkv_out.view(hd * 4, kv * 4);
         b.v_view = b.qkv_out.view((hd + kv) * 4, kv * 4);
         b.attn = zeros_f32(ctx, hd);
-        b.kv_scratch = ctx.zeros(tm_cuda_attention_decode_scratch_bytes((uint32_t)b.heads_l, (uint32_t)b.kv_l,
-                                                                        (uint32_t)s.head_dim, (uint32_t)cap));
+        b.kv_scratch = ctx.zeros(seqs * tm_cuda_attention_decode_scratch_bytes((uint32_t)b.heads_l, (uint32_t)b.kv_l,
+                                                                               (uint32_t)s.head_dim, (uint32_t)cap));
         if (sh.world > 1) {
             b.attn_full = gather_target_f32(ctx, s.heads * s.head_dim, sh);
             b.proj_local = zeros_f32(ctx, hidden / sh.world);
@@ -510,6 +541,16 @@ struct AttentionBlock {
                                  pos_buf, 0, status, (uint32_t)heads_l, (uint32_t)kv_l, (uint32_t)spec.head_dim,
                                  (uint32_t)spec.rope_dims, (uint32_t)cap, (uint32_t)spec.window, eps, scale(), exact);
     }
+    // The per-token core for one row per sequence: row s of q / k / v (strides in elements, 0 = dense) is
+    // sequence s at its own position pos_buf[s], attending to its own cache planes.
+    void attend_batch(const CudaContext &ctx, const CudaBuffer &q, const CudaBuffer &k, const CudaBuffer &v,
+                      uint32_t q_stride, uint32_t kv_stride, const CudaBuffer &out, size_t n_seq,
+                      const CudaBuffer &pos_buf, const CudaBuffer &status, bool exact) const {
+        ctx.attention_decode_batch(q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, out, kv_scratch, pos_buf, status,
+                                   (uint32_t)n_seq, q_stride, kv_stride, (uint32_t)heads_l, (uint32_t)kv_l,
+                                   (uint32_t)spec.head_dim, (uint32_t)spec.rope_dims, (uint32_t)cap,
+                                   (uint32_t)spec.window, eps, scale(), exact);
+    }
     // Row split: proj = all_gather(o_local * all_gather(attn_local)), one token.
     void project_sharded(const CudaContext &ctx, const CudaBuffer &proj, size_t hidden) const {
         ctx.push_rows(attn, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
@@ -523,35 +564,44 @@ struct AttentionBlock {
                tm_cuda_attention_chunk_mma_supported((uint32_t)spec.head_dim);
     }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0,
-                       const CudaBuffer &pre_norm) const {
+                       const CudaBuffer &pre_norm, const RowsAre &rows) const {
         const uint32_t nn = (uint32_t)n, heads = (uint32_t)heads_l, kv = (uint32_t)kv_l, hd = (uint32_t)spec.head_dim;
         ctx.q8_0_gemm_mma_fused(qkv.buf, s.x, qkv.rows, qkv.cols, nn, {&s.a, &s.b, &s.c},
                                 {qkv.part_rows[0], qkv.part_rows[1], qkv.part_rows[2]}, TM_CUDA_PRO_RMSNORM, &pre_norm,
                                 eps, TM_CUDA_EPI_STORE);
-        ctx.qk_prep_chunk(s.a, s.b, s.c, q_norm, k_norm, inv_freq, k_cache, v_cache, heads, kv, hd,
+        if (rows.pos_buf) {  // one row per sequence
+            attend_batch(ctx, s.a, s.b, s.c, 0, 0, s.e, n, *rows.pos_buf, *rows.status, false);
+            return;
+        }
+        ctx.qk_prep_chunk(s.a, s.b, s.c, q_norm, k_norm, inv_freq, kc(rows.seq), vc(rows.seq), heads, kv, hd,
                           (uint32_t)spec.rope_dims, pos0, (uint32_t)cap, nn, eps);
-        ctx.attention_chunk_mma(s.a, k_cache, v_cache, s.e, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
-                                (uint32_t)spec.window);
+        ctx.attention_chunk_mma(s.a, kc(rows.seq), vc(rows.seq), s.e, heads, pos0, (uint32_t)cap, hd, heads / kv,
+                                scale(), nn, (uint32_t)spec.window);
     }
     // Chunk core over n queries at pos0.. (engine/metal.rs:1170-1233): every
     // chunk K/V row is stored before any chunk query attends.
     void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, size_t hidden,
-                 bool exact) const {
+                 bool exact, const RowsAre &rows) const {
         const uint32_t nn = (uint32_t)n, heads = (uint32_t)heads_l, kv = (uint32_t)kv_l, hd = (uint32_t)spec.head_dim;
         qkv.gemm_part(ctx, 0, s.h, s.a, nn, exact);
         qkv.gemm_part(ctx, 1, s.h, s.b, nn, exact);
         qkv.gemm_part(ctx, 2, s.h, s.c, nn, exact);
-        ctx.rmsnorm(s.a, q_norm, s.a, nn * heads, hd, eps);
-        ctx.rmsnorm(s.b, k_norm, s.b, nn * kv, hd, eps);
-        ctx.rope_partial_chunk(s.a, s.b, inv_freq, pos0, heads, kv, hd, (uint32_t)spec.rope_dims, nn);
-        ctx.kv_store_chunk(s.b, s.c, k_cache, v_cache, pos0, (uint32_t)cap, hd, kv, nn);
-        // Tolerance-qualified tensor-core form unless bit identity with the per-token path is asked.
-        if (!exact && tm_cuda_attention_chunk_mma_supported(hd))
-            ctx.attention_chunk_mma(s.a, k_cache, v_cache, s.e, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
-                                    (uint32_t)spec.window);
-        else
-            ctx.attention_chunk(s.a, k_cache, v_cache, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(),
-                                nn, (uint32_t)spec.window);
+        if (rows.pos_buf) {  // one row per sequence
+            attend_batch(ctx, s.a, s.b, s.c, 0, 0, s.e, n, *rows.pos_buf, *rows.status, exact);
+        } else {
+            const CudaBuffer &kcs = kc(rows.seq), &vcs = vc(rows.seq);
+            ctx.rmsnorm(s.a, q_norm, s.a, nn * heads, hd, eps);
+            ctx.rmsnorm(s.b, k_norm, s.b, nn * kv, hd, eps);
+            ctx.rope_partial_chunk(s.a, s.b, inv_freq, pos0, heads, kv, hd, (uint32_t)spec.rope_dims, nn);
+            ctx.kv_store_chunk(s.b, s.c, kcs, vcs, pos0, (uint32_t)cap, hd, kv, nn);
+            // Tolerance-qualified tensor-core form unless bit identity with the per-token path is asked.
+            if (!exact && tm_cuda_attention_chunk_mma_supported(hd))
+                ctx.attention_chunk_mma(s.a, kcs, vcs, s.e, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(), nn,
+                                        (uint32_t)spec.window);
+            else
+                ctx.attention_chunk(s.a, kcs, vcs, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(),
+                                    nn, (uint32_t)spec.window);
+        }
         if (sh.world > 1) {
             ctx.push_rows(s.e, s.efull, nn, heads * hd);
             if (exact || o.type == 1) {
@@ -572,22 +622,23 @@ struct Layer {
     AttentionBlock mixer;
     SwiGluBlock ffn;
 
-    static void plan(const LayerSpec &l, const ModelGraph &g, const WeightSource &src, size_t cap, Shard sh, Plan &p) {
+    static void plan(const LayerSpec &l, const ModelGraph &g, const WeightSource &src, size_t cap, Shard sh, Plan &p,
+                     size_t seqs) {
         p.weights_f32(vector_len(src, l.pre_norm));
         p.weights_f32(vector_len(src, l.post_norm));
         if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
         p.target_f32(g.hidden, sh.world);  // proj
-        AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p);
+        AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p, seqs);
         SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, sh, p);
     }
     static Layer load(const CudaContext &ctx, const WeightSource &src, const LayerSpec &l, const ModelGraph &g,
-                      size_t cap, Shard sh) {
+                      size_t cap, Shard sh, size_t seqs) {
         Layer L;
         L.pre_norm = vector(ctx, src, l.pre_norm);
         if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
         L.post_norm = vector(ctx, src, l.post_norm);
         L.proj = gather_target_f32(ctx, g.hidden, sh);
-        L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh);
+        L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh, seqs);
         L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps, sh);
         return L;
     }
@@ -604,11 +655,50 @@ struct Layer {
         }
         ffn.decode(ctx, x, post_norm, hidden);
     }
+    // Every matrix Q8_0 on one device: the batched fused GEMV forms apply.
+    bool slices_apply() const {
+        return mixer.sh.world == 1 && mixer.qkv.type == 8 && mixer.o.type == 8 && ffn.gate_up.type == 8 &&
+               ffn.down.type == 8;
+    }
+    // One decode row per sequence with the decode step's own launches (q|k|v as one fused-norm multiply,
+    // activation and residual folded into the projections), `n` rows per launch in slices of 8: row s
+    // is bit-identical to the one-sequence step.  Serves `exact` mode and small batches.
+    void decode_rows(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &pos_buf,
+                     const CudaBuffer &status, size_t hidden, float eps, bool exact) const {
+        const uint32_t nn = (uint32_t)n, stride = mixer.qkv.rows;
+        ctx.q8_0_gemm_fused(mixer.qkv.buf, s.x, mixer.qkv_out, mixer.qkv.rows, mixer.qkv.cols, nn, TM_CUDA_PRO_RMSNORM,
+                            &pre_norm, eps, TM_CUDA_EPI_STORE);
+        mixer.attend_batch(ctx, mixer.q_rows, mixer.k_rows, mixer.v_rows, stride, stride, s.e, n, pos_buf, status, exact);
+        if (mixer_out_norm) {
+            ctx.q8_0_gemm_fused(mixer.o.buf, s.e, s.proj, mixer.o.rows, mixer.o.cols, nn, TM_CUDA_PRO_NONE, nullptr, 0.0f,
+                                TM_CUDA_EPI_STORE);
+            ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
+        } else {
+            ctx.q8_0_gemm_fused(mixer.o.buf, s.e, s.x, mixer.o.rows, mixer.o.cols, nn, TM_CUDA_PRO_NONE, nullptr, 0.0f,
+                                TM_CUDA_EPI_ADD);
+        }
+        // gate and up as two launches into dense [n][width] matrices (the activation prologue of the
+        // down projection wants dense operands); each part takes the whole matrix's column split.
+        const Matrix &gu = ffn.gate_up;
+        ctx.q8_0_gemm_fused(gu.parts[0], s.x, s.g, gu.part_rows[0], gu.cols, nn, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
+                            TM_CUDA_EPI_STORE);
+        ctx.q8_0_gemm_fused(gu.parts[1], s.x, s.u, gu.part_rows[1], gu.cols, nn, TM_CUDA_PRO_RMSNORM, &post_norm, eps,
+                            TM_CUDA_EPI_STORE);
+        const int pro = ffn.act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        if (ffn.out_norm) {
+            ctx.q8_0_gemm_fused(ffn.down.buf, s.g, s.d2, ffn.down.rows, ffn.down.cols, nn, pro, &s.u, 0.0f,
+                                TM_CUDA_EPI_STORE);
+            ctx.rmsnorm_add(s.d2, ffn.out_norm, s.x, nn, (uint32_t)hidden, eps);
+        } else {
+            ctx.q8_0_gemm_fused(ffn.down.buf, s.g, s.x, ffn.down.rows, ffn.down.cols, nn, pro, &s.u, 0.0f,
+                                TM_CUDA_EPI_ADD);
+        }
+    }
     void prefill(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0, size_t hidden, float eps,
-                 bool exact) const {
+                 bool exact, const RowsAre &rows = RowsAre()) const {
         const uint32_t nn = (uint32_t)n;
         if (!exact && mixer.fusable() && ffn.fusable()) {
-            mixer.prefill_fused(ctx, s, n, pos0, pre_norm);
+            mixer.prefill_fused(ctx, s, n, pos0, pre_norm, rows);
             if (mixer_out_norm) {
                 mixer.o.gemm_all(ctx, s.e, s.proj, nn, false);
                 ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
@@ -620,7 +710,7 @@ struct Layer {
             return;
         }
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
-        mixer.prefill(ctx, s, n, pos0, hidden, exact);
+        mixer.prefill(ctx, s, n, pos0, hidden, exact, rows);
         if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
         else ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
         ctx.rmsnorm(s.x, post_norm, s.h2, nn, (uint32_t)hidden, eps);
@@ -649,6 +739,12 @@ struct EngineModel::Impl {
     PrefillScratch scratch;
     CudaGraph decode_graph;
     bool persistent = false;  // decode_graph is a persistent program
+    // Several sequences: positions pos_buf[s], token logs tokens[s * log_stride ..], logits [s][head_rows];
+    // one recorded step advances all of them.
+    size_t seqs = 1, log_stride = 0;
+    CudaGraph batch_graph;
+    std::vector<size_t> pos_b;  // host copy of every sequence's position
+    std::vector<CudaBuffer> logits_row, tokens_row, mirror_row;  // row split: per-sequence views for the sharded argmax
     const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
     uint32_t head_cols() const { return embedding.cols; }
     uint32_t head_type() const { return tied ? embedding.type : head_own.type; }
@@ -705,10 +801,22 @@ bool persistent_decode_applies(const ModelGraph &graph, const EngineOptions &opt
     return true;
 }
 
+// Slots of one sequence's token log: capacity + 1, rounded so that every sequence's log starts on a
+// 16-byte boundary when there are several.
+static size_t token_log_stride(size_t capacity, size_t seqs) {
+    return seqs > 1 ? (capacity + 1 + 3) & ~(size_t)3 : capacity + 1;
+}
+// Rows of the chunk-wide scratch: a prefill chunk, or one decode row per sequence.
+static size_t chunk_rows(const EngineOptions &opts, size_t capacity) {
+    return std::max<size_t>(std::min<size_t>(opts.prefill_batch, capacity), opts.sequences);
+}
+
 GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, size_t capacity,
                              const EngineOptions &opts) {
     if (opts.shard_world == 0 || opts.shard_rank >= opts.shard_world)
         throw TuckmillError(ErrorCode::InvalidRequest, "shard rank outside the split");
+    if (opts.sequences == 0 || opts.sequences > kMaxSequences)
+        throw TuckmillError(ErrorCode::InvalidRequest, "sequences must be 1.." + std::to_string(kMaxSequences));
     const Shard sh{opts.shard_rank, opts.shard_world};
     // Whole attention heads stay on one rank, and every row range is N/world.
     auto divides = [&](size_t v, const char *what) {
@@ -726,22 +834,23 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
         divides(l.ffn.width, "FFN width");
     }
     Plan p;
-    for (const LayerSpec &l : graph.layers) Layer::plan(l, graph, src, capacity, sh, p);
+    const size_t seqs = opts.sequences;
+    for (const LayerSpec &l : graph.layers) Layer::plan(l, graph, src, capacity, sh, p, seqs);
     p.weights += Matrix::plan(src, {graph.embedding});  // the embedding table is replicated
     if (graph.head != graph.embedding) p.weights += Matrix::plan(src, {graph.head}, sh);
     p.weights_f32(vector_len(src, graph.final_norm));
     p.scratch_f32(graph.hidden);              // x
-    p.scratch_f32(graph.vocab / sh.world);    // logits (this rank's slice)
-    p.scratch_bytes(kArgmaxPartialBytes);     // argmax partials
-    p.scratch_bytes((capacity + 1) * 4);      // device token log
-    p.scratch_bytes((capacity + 1) * 4);      // its host-visible mirror
-    p.scratch_bytes(16);                      // device position
+    p.scratch_f32(graph.vocab / sh.world * seqs);  // logits (this rank's slice), a row per sequence
+    p.scratch_bytes(kArgmaxPartialBytes * seqs);   // argmax partials
+    p.scratch_bytes(token_log_stride(capacity, seqs) * seqs * 4);  // device token logs
+    p.scratch_bytes(token_log_stride(capacity, seqs) * seqs * 4);  // their host-visible mirror
+    p.scratch_bytes(std::max<size_t>(16, seqs * 4));  // device positions
     p.scratch_bytes(16);                      // status word
     if (sh.world > 1) {
         p.scratch_f32(graph.vocab);           // gathered logits (only when a caller asks for them)
         p.scratch_bytes((sh.world + 1) * 8);  // (value, index) pairs of the sharded argmax
     }
-    const size_t n = std::min<size_t>(opts.prefill_batch, capacity);
+    const size_t n = chunk_rows(opts, capacity);
     PrefillScratch::plan(graph, capacity, n, sh, p);
     if (!opts.exact) p.scratch_bytes(PrefillScratch::mma_workspace(graph, n));
     if (persistent_decode_applies(graph, src, opts)) p.scratch_bytes(decode_program_size(graph, capacity).bytes());
@@ -778,7 +887,10 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     if (opts.shard_world > 1) I.arena.buf = c.symm_zeros(m->plan_.gather);
     const Shard sh{opts.shard_rank, opts.shard_world, opts.shard_world > 1 ? &I.arena : nullptr};
     I.sh = sh;
-    for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity, sh));
+    I.seqs = opts.sequences;
+    I.log_stride = token_log_stride(capacity, I.seqs);
+    I.pos_b.assign(I.seqs, 0);
+    for (const LayerSpec &l : graph.layers) I.layers.push_back(Layer::load(c, src, l, graph, capacity, sh, I.seqs));
     I.embedding = Matrix::load(c, src, {graph.embedding});
     I.tied = graph.head == graph.embedding;
     I.head_rows = (uint32_t)(graph.vocab / sh.world);
@@ -794,18 +906,27 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
         throw TuckmillError(ErrorCode::UnsupportedArchitecture, "embedding / head shapes do not match the graph");
     I.final_norm = vector(c, src, graph.final_norm);
     I.x = zeros_f32(c, graph.hidden);
-    I.logits = zeros_f32(c, I.head_rows);
+    I.logits = zeros_f32(c, (size_t)I.head_rows * I.seqs);
     if (sh.world > 1) {
         I.logits_full = zeros_f32(c, graph.vocab);
         I.pairs = c.zeros((sh.world + 1) * 8);
     }
-    I.partial = c.zeros(kArgmaxPartialBytes);
-    I.tokens = c.zeros((capacity + 1) * 4);
-    I.tokens_mirror = c.zeros((capacity + 1) * 4, true);
-    I.pos_buf = c.zeros(16);
+    I.partial = c.zeros(kArgmaxPartialBytes * I.seqs);
+    I.tokens = c.zeros(I.log_stride * I.seqs * 4);
+    I.tokens_mirror = c.zeros(I.log_stride * I.seqs * 4, true);
+    I.pos_buf = c.zeros(std::max<size_t>(16, I.seqs * 4));
     I.status = c.zeros(16, true);
-    I.scratch = PrefillScratch::alloc(c, graph, capacity, std::min<size_t>(opts.prefill_batch, capacity), sh);
-    if (!opts.exact) c.mma_workspace_reserve(PrefillScratch::mma_workspace(graph, std::min<size_t>(opts.prefill_batch, capacity)));
+    I.scratch = PrefillScratch::alloc(c, graph, capacity, chunk_rows(opts, capacity), sh);
+    if (!opts.exact) c.mma_workspace_reserve(PrefillScratch::mma_workspace(graph, chunk_rows(opts, capacity)));
+    if (I.seqs > 1 && sh.world > 1) {
+        if (((size_t)I.head_rows * 4) % 16 != 0)
+            throw TuckmillError(ErrorCode::InvalidRequest, "head rows per rank are not a 16-byte multiple");
+        for (size_t i = 0; i < I.seqs; ++i) {
+            I.logits_row.push_back(I.logits.view(i * I.head_rows * 4, (size_t)I.head_rows * 4));
+            I.tokens_row.push_back(I.tokens.view(i * I.log_stride * 4, I.log_stride * 4));
+            I.mirror_row.push_back(I.tokens_mirror.view(i * I.log_stride * 4, I.log_stride * 4));
+        }
+    }
     m->graph_ = std::move(graph);
     const ModelGraph &g = m->graph_;
 
@@ -834,6 +955,16 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
             throw;
         }
         I.decode_graph = c.end_group_retain();
+    }
+    if (I.seqs > 1) {  // the step of all sequences, recorded once too
+        c.begin_group();
+        try {
+            m->encode_batch_step();
+        } catch (...) {
+            c.abort_group();
+            throw;
+        }
+        I.batch_graph = c.end_group_retain();
     }
 
     // The ledger must equal the preflight (crates/tuckcore/src/executor.rs:1571-1580).
@@ -865,6 +996,47 @@ void EngineModel::encode_decode_step() {
         c.argmax_dev(I.logits, (uint32_t)g.vocab, I.partial, I.tokens, 1, I.pos_buf, 0, (uint32_t)capacity_ + 1,
                      &I.tokens_mirror);
     c.u32_add(I.pos_buf, 0, 1);
+}
+
+// One decode row per sequence: sequence s reads its logged token at pos_buf[s], attends to its own
+// cache planes, appends its greedy token to its own log; every position advances (and stays on the
+// last cache row once a sequence is full -- the host has stopped reading that sequence by then).
+void EngineModel::encode_batch_step() {
+    Impl &I = *impl_;
+    const CudaContext &c = *ctx_;
+    const ModelGraph &g = graph_;
+    const size_t S = I.seqs;
+    const uint32_t cap1 = (uint32_t)capacity_ + 1, stride = (uint32_t)I.log_stride;
+    if (I.embedding.type != 8)
+        throw TuckmillError(ErrorCode::UnsupportedQuantization, "several sequences need a Q8_0 embedding table");
+    c.rows_indirect_seq(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, stride, I.pos_buf, (uint32_t)S, 0,
+                        g.embedding_scale, I.scratch.x);
+    bool slices = S <= TM_CUDA_GEMM_MAX_BATCH && (opts_.exact || S <= 8) && I.head_type() == 8;
+    for (const Layer &L : I.layers) slices = slices && L.slices_apply();
+    RowsAre rows;
+    rows.pos_buf = &I.pos_buf;
+    rows.status = &I.status;
+    for (const Layer &L : I.layers) {
+        if (slices) L.decode_rows(c, I.scratch, S, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+        else L.prefill(c, I.scratch, S, 0, g.hidden, g.eps, opts_.exact, rows);
+    }
+    if (slices) {
+        c.q8_0_gemm_fused(I.head_buf(), I.scratch.x, I.logits, I.head_rows, I.head_cols(), (uint32_t)S,
+                          TM_CUDA_PRO_RMSNORM, &I.final_norm, g.eps, TM_CUDA_EPI_STORE);
+    } else {
+        c.rmsnorm(I.scratch.x, I.final_norm, I.scratch.h, (uint32_t)S, (uint32_t)g.hidden, g.eps);
+        Matrix::gemm(c, I.head_buf(), I.head_rows, I.head_cols(), I.scratch.h, I.logits, (uint32_t)S, opts_.exact,
+                     I.head_type());
+    }
+    if (I.sh.world > 1) {
+        for (size_t s = 0; s < S; ++s)
+            c.argmax_sharded(I.logits_row[s], I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens_row[s], 1,
+                             &I.pos_buf, (uint32_t)s, cap1, &I.mirror_row[s]);
+    } else {
+        c.argmax_rows_dev(I.logits, (uint32_t)S, (uint32_t)g.vocab, I.partial, I.tokens, stride, 1, I.pos_buf, cap1,
+                          &I.tokens_mirror);
+    }
+    c.u32_add_sat(I.pos_buf, 0, (uint32_t)S, 1, (uint32_t)capacity_ - 1);
 }
 
 void EngineModel::step_ungrouped() {
@@ -915,9 +1087,19 @@ void EngineModel::reset() {
     impl_->status.zero();
     ctx_->fence();
     pos_ = 0;
+    std::fill(impl_->pos_b.begin(), impl_->pos_b.end(), 0);
 }
 
-void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) {
+size_t EngineModel::sequences() const { return impl_->seqs; }
+size_t EngineModel::position_of(size_t seq) const { return seq < impl_->seqs ? impl_->pos_b[seq] : 0; }
+
+void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) { prefill_seq(0, tokens, n, want_token); }
+
+void EngineModel::prefill_seq(size_t seq, const uint32_t *tokens, size_t n, bool want_token) {
+    if (seq >= impl_->seqs)
+        throw TuckmillError(ErrorCode::InvalidRequest, "sequence " + std::to_string(seq) + " outside the " +
+                                                           std::to_string(impl_->seqs) + " the engine holds");
+    const size_t pos_ = impl_->pos_b[seq];  // this sequence's position (shadows the member: sequence 0's)
     if (n == 0) throw TuckmillError(ErrorCode::InvalidRequest, "prefill of zero tokens");
     if (pos_ + n > capacity_)
         throw TuckmillError(ErrorCode::ContextExceedsBudget, "position " + std::to_string(pos_ + n - 1) +
@@ -929,41 +1111,180 @@ void EngineModel::prefill(const uint32_t *tokens, size_t n, bool want_token) {
                                                                std::to_string(graph_.vocab) + ")");
     Impl &I = *impl_;
     const CudaContext &c = *ctx_;
-    I.tokens.upload(pos_ * 4, tokens, n * 4);
+    const size_t log0 = seq * I.log_stride;  // this sequence's token log
+    I.tokens.upload((log0 + pos_) * 4, tokens, n * 4);
     const size_t batch = std::min<size_t>(opts_.prefill_batch, capacity_);
+    RowsAre rows;
+    rows.seq = seq;
     for (size_t t0 = 0; t0 < n; t0 += batch) {
         const size_t k = std::min(batch, n - t0);
         const bool last = t0 + k == n;
-        const uint32_t pos0 = (uint32_t)(pos_ + t0);
+        const uint32_t pos0 = (uint32_t)(pos_ + t0), slot0 = (uint32_t)(log0 + pos_ + t0);
         c.grouped([&] {
             if (I.embedding.type == 1)
-                c.f16_rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
+                c.f16_rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, slot0, (uint32_t)k,
                                     graph_.embedding_scale, I.scratch.x);
             else
-                c.rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, pos0, (uint32_t)k,
+                c.rows_indirect(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, slot0, (uint32_t)k,
                                 graph_.embedding_scale, I.scratch.x);
-            for (const Layer &L : I.layers) L.prefill(c, I.scratch, k, pos0, graph_.hidden, graph_.eps, opts_.exact);
+            for (const Layer &L : I.layers)
+                L.prefill(c, I.scratch, k, pos0, graph_.hidden, graph_.eps, opts_.exact, rows);
             if (last && want_token) {
                 // Vocabulary projection for the last row only (engine/metal.rs:2610-2617).
                 c.copy_f32(I.scratch.x, (uint32_t)((k - 1) * graph_.hidden), I.x, 0, (uint32_t)graph_.hidden);
                 I.project_head(c, graph_.eps);
                 if (I.sh.world > 1)
                     c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens,
-                                     pos0 + (uint32_t)k, nullptr, 0, (uint32_t)capacity_ + 1, nullptr);
+                                     slot0 + (uint32_t)k, nullptr, 0, (uint32_t)(I.log_stride * I.seqs), nullptr);
                 else
-                    c.argmax_f32(I.logits, (uint32_t)graph_.vocab, I.partial, I.tokens, pos0 + (uint32_t)k);
+                    c.argmax_f32(I.logits, (uint32_t)graph_.vocab, I.partial, I.tokens, slot0 + (uint32_t)k);
             }
         });
     }
-    pos_ += n;
-    const uint32_t p32 = (uint32_t)pos_;
-    I.pos_buf.upload(0, &p32, 4);
+    I.pos_b[seq] = pos_ + n;
+    if (seq == 0) this->pos_ = I.pos_b[0];
+    const uint32_t p32 = (uint32_t)I.pos_b[seq];
+    I.pos_buf.upload(seq * 4, &p32, 4);
 }
 
-uint32_t EngineModel::prefill_token() {
+uint32_t EngineModel::prefill_token() { return prefill_token_of(0); }
+
+uint32_t EngineModel::prefill_token_of(size_t seq) {
+    if (seq >= impl_->seqs) throw TuckmillError(ErrorCode::InvalidRequest, "sequence outside the engine's");
     uint32_t t = 0;
-    impl_->tokens.download(pos_ * 4, &t, 4);
+    impl_->tokens.download((seq * impl_->log_stride + impl_->pos_b[seq]) * 4, &t, 4);
     return t;
+}
+
+void EngineModel::step_batch(const uint32_t *tokens) {
+    Impl &I = *impl_;
+    if (I.seqs < 2) throw TuckmillError(ErrorCode::InvalidRequest, "the engine was loaded for one sequence");
+    for (size_t s = 0; s < I.seqs; ++s) {
+        if (tokens[s] >= graph_.vocab)
+            throw TuckmillError(ErrorCode::InvalidRequest, "token id " + std::to_string(tokens[s]) +
+                                                               " is outside the vocabulary (0.." +
+                                                               std::to_string(graph_.vocab) + ")");
+        if (I.pos_b[s] >= capacity_)
+            throw TuckmillError(ErrorCode::ContextExceedsBudget, "sequence " + std::to_string(s) + " at position " +
+                                                                     std::to_string(I.pos_b[s]) + " exceeds KV capacity " +
+                                                                     std::to_string(capacity_));
+    }
+    for (size_t s = 0; s < I.seqs; ++s) I.tokens.upload((s * I.log_stride + I.pos_b[s]) * 4, &tokens[s], 4);
+    I.batch_graph.launch();
+    for (size_t s = 0; s < I.seqs; ++s) I.pos_b[s] += 1;
+    pos_ = I.pos_b[0];
+}
+
+void EngineModel::submit_batch_greedy() {
+    Impl &I = *impl_;
+    if (I.seqs < 2) throw TuckmillError(ErrorCode::InvalidRequest, "the engine was loaded for one sequence");
+    for (size_t s = 0; s < I.seqs; ++s)
+        if (I.pos_b[s] >= capacity_)
+            throw TuckmillError(ErrorCode::ContextExceedsBudget, "sequence " + std::to_string(s) + " is at capacity");
+    I.batch_graph.launch();
+    for (size_t s = 0; s < I.seqs; ++s) I.pos_b[s] += 1;
+    pos_ = I.pos_b[0];
+}
+
+void EngineModel::logits_batch(float *out) {
+    Impl &I = *impl_;
+    check_device_status();
+    if (I.sh.world > 1)
+        throw TuckmillError(ErrorCode::InvalidRequest, "per-sequence logits are not gathered across a row split");
+    I.logits.download(0, out, (size_t)I.seqs * graph_.vocab * 4);
+}
+
+std::vector<std::vector<uint32_t>> EngineModel::generate_batch(const std::vector<std::vector<uint32_t>> &prompts,
+                                                               size_t max_new, bool ignore_eos, GenerateStats *stats) {
+    Impl &I = *impl_;
+    const size_t S = I.seqs, R = prompts.size();
+    if (S < 2) throw TuckmillError(ErrorCode::InvalidRequest, "the engine was loaded for one sequence");
+    if (R == 0 || R > S)
+        throw TuckmillError(ErrorCode::InvalidRequest, std::to_string(R) + " requests for " + std::to_string(S) + " sequences");
+    std::vector<std::vector<uint32_t>> out(R);
+    if (max_new == 0) return out;
+    const uint64_t l0 = ctx_->kernel_launches(), d0 = ctx_->committed();
+    const uint64_t t_start = now_ns();
+    reset();
+    uint64_t n_prompt = 0;
+    for (size_t s = 0; s < R; ++s) {
+        prefill_seq(s, prompts[s].data(), prompts[s].size(), true);
+        n_prompt += prompts[s].size();
+    }
+    auto is_stop = [&](uint32_t t) {
+        return t == 0xFFFFFFFFu || (!ignore_eos && graph_.has_eos && t == graph_.eos_token_id);
+    };
+    std::vector<char> done(R, 0);
+    for (size_t s = 0; s < R; ++s) {
+        const uint32_t tok = prefill_token_of(s);
+        if (tok == 0xFFFFFFFFu)
+            throw TuckmillError(ErrorCode::Internal, "every logit was NaN; refusing to guess a token");
+        out[s].push_back(tok);
+        done[s] = is_stop(tok);
+    }
+    const uint64_t t_first = now_ns();
+    uint64_t t_last = t_first;
+    // A step advances every sequence on the device; the host follows the ones still wanted.  Step
+    // i + 1 is submitted before step i is read (executor.rs:1080-1087), so a sequence that stops runs
+    // one step too many, whose token is dropped.
+    constexpr size_t kNone = (size_t)-1;
+    struct Flight { uint64_t dispatch; std::vector<size_t> slot; };
+    std::vector<size_t> submitted(R, 0), host_pos(I.pos_b.begin(), I.pos_b.begin() + R);
+    auto wants = [&](size_t s) { return !done[s] && submitted[s] + 1 < max_new && host_pos[s] < capacity_; };
+    auto any_wants = [&] {
+        for (size_t s = 0; s < R; ++s)
+            if (wants(s)) return true;
+        return false;
+    };
+    auto submit = [&] {
+        Flight f;
+        f.slot.assign(R, kNone);
+        for (size_t s = 0; s < R; ++s)
+            if (wants(s)) {
+                f.slot[s] = s * I.log_stride + host_pos[s] + 1;
+                host_pos[s] += 1;
+                submitted[s] += 1;
+            }
+        I.batch_graph.launch();
+        f.dispatch = ctx_->committed();
+        return f;
+    };
+    std::vector<Flight> inflight;
+    if (any_wants()) inflight.push_back(submit());
+    while (!inflight.empty()) {
+        if (any_wants()) inflight.push_back(submit());
+        const Flight f = inflight.front();
+        inflight.erase(inflight.begin());
+        for (size_t s = 0; s < R; ++s) {
+            if (f.slot[s] == kNone || done[s]) continue;
+            uint32_t tok = 0;
+            I.tokens_mirror.download_after(f.slot[s] * 4, &tok, 4, f.dispatch);
+            if (tok == 0xFFFFFFFFu)
+                throw TuckmillError(ErrorCode::Internal, "every logit was NaN; refusing to guess a token");
+            out[s].push_back(tok);
+            if (is_stop(tok)) done[s] = 1;
+        }
+        t_last = now_ns();
+    }
+    ctx_->fence();
+    check_device_status();
+    // The device went on stepping the sequences the host had stopped following: the engine's state is
+    // spent until the next reset().
+    for (size_t s = 0; s < S; ++s) I.pos_b[s] = capacity_;
+    pos_ = capacity_;
+    if (stats) {
+        uint64_t gen = 0;
+        for (const auto &o : out) gen += o.size();
+        stats->ttft_ns = t_first - t_start;
+        stats->decode_span_ns = t_last - t_first;
+        stats->prompt_tokens = n_prompt;
+        stats->generated = gen;
+        stats->kernel_launches = ctx_->kernel_launches() - l0;
+        stats->dispatches = ctx_->committed() - d0;
+        stats->h2d_bytes = n_prompt * 4 + 4 * R;
+        stats->d2h_bytes = gen * 4 + 4 * R;
+    }
+    return out;
 }
 
 void EngineModel::step(uint32_t token) {
@@ -977,6 +1298,7 @@ void EngineModel::step(uint32_t token) {
     impl_->tokens.upload(pos_ * 4, &token, 4);
     impl_->decode_graph.launch();
     pos_ += 1;
+    impl_->pos_b[0] = pos_;
 }
 
 // With a row split this is a collective: every rank must call it.
@@ -1000,6 +1322,7 @@ EngineModel::Ticket EngineModel::submit_greedy() {
     t.dispatch = ctx_->committed();
     t.slot = pos_ + 1;
     pos_ += 1;
+    impl_->pos_b[0] = pos_;
     return t;
 }
 

@@ -25,6 +25,7 @@ namespace tuckmill {
 constexpr uint32_t kPrefillBatchDefault = 512;  // reference PREFILL_BATCH is 128 (engine/metal.rs:25)
 constexpr uint32_t kArgmaxPartialBytes = 512;
 constexpr size_t kStagingChunkBytes = 4u << 20;  // crates/tuckcore/src/qwen35_gpu.rs:1176
+constexpr uint32_t kMaxSequences = 256;
 
 struct EngineOptions {
     uint32_t prefill_batch = kPrefillBatchDefault;
@@ -37,6 +38,10 @@ struct EngineOptions {
     // kernel serves.  Off by default: on the decoders measured so far the recorded graph of
     // per-operator kernels is the faster of the two.
     bool persistent = false;
+    // Concurrent sequences the engine holds state for (KV planes, position and token log per
+    // sequence) and decodes together, one row each, in ONE recorded step.  The reference serves one
+    // request at a time (crates/supervisor/src/queue.rs:1-4); 1 keeps exactly that engine.
+    uint32_t sequences = 1;
 };
 
 // Whether load_with will record the decode step as a persistent program for this graph and options
@@ -106,6 +111,26 @@ public:
     struct Ticket { uint64_t dispatch = 0; size_t slot = 0; };
     Ticket submit_greedy();
     uint32_t collect_greedy(const Ticket &t);
+    // ---- several sequences (EngineOptions::sequences > 1) ----
+    size_t sequences() const;
+    size_t position_of(size_t seq) const;
+    // `n` prompt tokens of sequence `seq` at its current position (chunked like prefill; the other
+    // sequences are untouched); with `want_token` its greedy token goes to that sequence's log.
+    void prefill_seq(size_t seq, const uint32_t *tokens, size_t n, bool want_token);
+    uint32_t prefill_token_of(size_t seq);
+    // One decode step of EVERY sequence: tokens[s] is fed to sequence s at its position.  Every
+    // sequence must have room.  Row s of the result equals the one-sequence step on the same state
+    // bit for bit in `exact` mode (and for up to 8 sequences in any mode).
+    void step_batch(const uint32_t *tokens);
+    void logits_batch(float *out);  // [sequences][vocab]; single device only
+    // Device-greedy steps of all sequences with no host read in between (kernel-only timing).
+    void submit_batch_greedy();
+    // Greedy generation for prompts.size() <= sequences() requests at once: each prompt is
+    // prefilled into its own sequence, then all decode together, step i + 1 submitted before step i
+    // is read.  Sequence s stops at max_new tokens, at EOS unless ignore_eos, or at capacity, the
+    // others go on.  `stats` counts all sequences (ttft = until every first token is on the host).
+    std::vector<std::vector<uint32_t>> generate_batch(const std::vector<std::vector<uint32_t>> &prompts, size_t max_new,
+                                                      bool ignore_eos, GenerateStats *stats);
     // The same decode step encoded operator by operator (one dispatch each, no
     // graph): the attribution mode of engine/metal.rs:1964-1968, used with the
     // context's per-operator profile table.
@@ -131,6 +156,7 @@ private:
     struct Impl;
     EngineModel() = default;
     void encode_decode_step();
+    void encode_batch_step();
     std::shared_ptr<CudaContext> ctx_;
     ModelGraph graph_;
     EngineOptions opts_;

@@ -148,6 +148,57 @@ __global__ void __launch_bounds__(kThreads) argmax_final_kernel(const float *pv,
     }
 }
 
+// The same two passes for several rows in one launch each (blockIdx.y = row): row r of `x` is n
+// values; its winner goes to out[r * out_stride + base + pos[r]].
+__global__ void __launch_bounds__(kThreads) argmax_rows_partial_kernel(const float *x, float *pv, uint32_t *pi,
+                                                                       uint32_t n) {
+    __shared__ float tv[kWarps];
+    __shared__ uint32_t ti[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const float *xr = x + (size_t)blockIdx.y * n;
+    float v = -INFINITY;
+    uint32_t i = kArgmaxNone;
+    for (uint32_t k = blockIdx.x * kThreads + threadIdx.x; k < n; k += kArgmaxGroups * kThreads) {
+        const float xv = xr[k];
+        if (!isnan(xv) && better(xv, k, v, i)) { v = xv; i = k; }
+    }
+    argmax_block(v, i, tv, ti);
+    if (threadIdx.x == 0) {
+        pv[blockIdx.y * kArgmaxGroups + blockIdx.x] = v;
+        pi[blockIdx.y * kArgmaxGroups + blockIdx.x] = i;
+    }
+}
+__global__ void __launch_bounds__(kThreads) argmax_rows_final_kernel(const float *pv, const uint32_t *pi, uint32_t *out,
+                                                                     uint32_t out_stride, uint32_t base,
+                                                                     const uint32_t *pos, uint32_t out_cap,
+                                                                     uint32_t *mirror) {
+    __shared__ float tv[kWarps];
+    __shared__ uint32_t ti[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t r = blockIdx.x;
+    float v = threadIdx.x < kArgmaxGroups ? pv[r * kArgmaxGroups + threadIdx.x] : -INFINITY;
+    uint32_t i = threadIdx.x < kArgmaxGroups ? pi[r * kArgmaxGroups + threadIdx.x] : kArgmaxNone;
+    argmax_block(v, i, tv, ti);
+    if (threadIdx.x == 0) {
+        const uint32_t slot = base + pos[r];
+        if (slot < out_cap) {
+            out[(size_t)r * out_stride + slot] = i;
+            if (mirror) mirror[(size_t)r * out_stride + slot] = i;
+        }
+    }
+}
+__global__ void u32_add_sat_kernel(uint32_t *p, uint32_t count, uint32_t delta, uint32_t limit) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        const uint32_t v = p[i];
+        p[i] = v >= limit || limit - v < delta ? limit : v + delta;
+    }
+}
+
 // ---- RoPE / KV store ---------------------------------------------------------
 // (x, y) = (a c - b s, a s + b c), with the fused multiply-adds spelled out so
 // every kernel that rotates rounds the same way.
@@ -383,12 +434,32 @@ __global__ void __launch_bounds__(32) attention_chunk_kernel(const float *q, con
 // partial to `scratch`, and the last warp to arrive for a head merges that
 // head's blocks in order.
 //   scratch: float part[heads][nblk][hd + 2], then u32 count[heads]
+// Several sequences in one launch (blockIdx.z = sequence): element strides between the sequences'
+// q / k / v / out rows, cache planes and scratch regions; positions are consecutive u32.  All zero
+// (and a grid of depth 1) is the single-sequence call.
+struct decode_seq_strides {
+    size_t q = 0, k = 0, v = 0, out = 0, cache = 0, scratch = 0;
+};
+#define TM_DECODE_SEQ_OFFSETS(st)                    \
+    {                                                \
+        const size_t sq_ = blockIdx.z;               \
+        q += sq_ * (st).q;                           \
+        k += sq_ * (st).k;                           \
+        v += sq_ * (st).v;                           \
+        out += sq_ * (st).out;                       \
+        kc += sq_ * (st).cache;                      \
+        vc += sq_ * (st).cache;                      \
+        scratch += sq_ * (st).scratch;               \
+        pos_p += sq_;                                \
+    }
+
 template <int DPL>
 __global__ void __launch_bounds__(32) attention_decode_kernel(
     const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
     const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos_p,
     uint32_t *status, uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot, uint32_t cap,
-    uint32_t window, float eps, float scale) {
+    uint32_t window, float eps, float scale, const decode_seq_strides seqs) {
+    TM_DECODE_SEQ_OFFSETS(seqs)
     __shared__ __align__(16) float qs[32 * DPL];
     __shared__ __align__(16) float ks[32 * DPL];
     __shared__ __align__(16) __half kh[32 * DPL];
@@ -583,7 +654,9 @@ template <int G, int HD>
 __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     const float *q, const float *k, const float *v, const float *q_norm, const float *k_norm,
     const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos_p,
-    uint32_t *status, uint32_t kv_heads, uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale) {
+    uint32_t *status, uint32_t kv_heads, uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale,
+    const decode_seq_strides seqs) {
+    TM_DECODE_SEQ_OFFSETS(seqs)
     constexpr int EPL = HD / 32;          // elements of a head vector per lane (strided by 32)
     constexpr int PAIRS = HD / 2;         // value dim pairs
     constexpr int KP = kFastThreads / PAIRS > 0 ? kFastThreads / PAIRS : 1;  // key parts in the value sum
@@ -917,10 +990,11 @@ template <int G, int HD>
 void launch_decode_fast(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v, const float *qn,
                         const float *kn, const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch,
                         const uint32_t *pos, uint32_t *status, uint32_t kvh, uint32_t n_rot, uint32_t cap,
-                        uint32_t window, float eps, float scale) {
-    tm_launch_pdl(ctx, attention_decode_fast_kernel<G, HD>, dim3(kvh, (cap + kFastSplit - 1) / kFastSplit),
+                        uint32_t window, float eps, float scale, uint32_t n_seq = 1,
+                        const decode_seq_strides seqs = decode_seq_strides()) {
+    tm_launch_pdl(ctx, attention_decode_fast_kernel<G, HD>, dim3(kvh, (cap + kFastSplit - 1) / kFastSplit, n_seq),
                   dim3(kFastThreads), 0, q, k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, kvh, n_rot, cap,
-                  window, eps, scale);
+                  window, eps, scale, seqs);
 }
 
 inline bool attn_fast_ok(uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot) {
@@ -942,10 +1016,11 @@ template <int DPL>
 void launch_decode(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v, const float *qn, const float *kn,
                    const float *inv_freq, __half *kc, __half *vc, float *out, float *scratch, const uint32_t *pos,
                    uint32_t *status, uint32_t heads, uint32_t kvh, uint32_t hd, uint32_t n_rot, uint32_t cap,
-                   uint32_t window, float eps, float scale) {
-    tm_launch_pdl(ctx, attention_decode_kernel<DPL>, dim3(heads, (cap + kAttnBlock - 1) / kAttnBlock), dim3(32), 0, q,
-                  k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, heads, kvh, hd, n_rot, cap, window, eps,
-                  scale);
+                   uint32_t window, float eps, float scale, uint32_t n_seq = 1,
+                   const decode_seq_strides seqs = decode_seq_strides()) {
+    tm_launch_pdl(ctx, attention_decode_kernel<DPL>, dim3(heads, (cap + kAttnBlock - 1) / kAttnBlock, n_seq), dim3(32),
+                  0, q, k, v, qn, kn, inv_freq, kc, vc, out, scratch, pos, status, heads, kvh, hd, n_rot, cap, window,
+                  eps, scale, seqs);
 }
 
 #define TM_ATTN_DISPATCH(FN, G, DPL, ...)                                         \
@@ -1071,6 +1146,46 @@ int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint3
     TM_OP_BEGIN("u32_add");
     TM_CUDA_TRY(tm_launch_pdl(ctx, u32_add_kernel, dim3(1), dim3(1), 0, (uint32_t *)buf->dev + index, delta));
     TM_OP_END(1);
+}
+
+int tm_cuda_u32_add_sat(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t first, uint32_t count, uint32_t delta,
+                        uint32_t limit, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (count == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "no counters");
+    TM_CHECK_BUF(buf, ((size_t)first + count) * 4, "counters");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator u32_add_sat cannot be recorded into a persistent program");
+    TM_OP_BEGIN("u32_add_sat");
+    TM_CUDA_TRY(tm_launch_pdl(ctx, u32_add_sat_kernel, dim3((count + 127) / 128), dim3(128), 0,
+                              (uint32_t *)buf->dev + first, count, delta, limit));
+    TM_OP_END(1);
+}
+
+int tm_cuda_argmax_rows_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n_rows, uint32_t n,
+                                tm_cuda_buffer *partial, tm_cuda_buffer *out, uint32_t out_stride, uint32_t base,
+                                tm_cuda_buffer *pos_buf, uint32_t out_cap, tm_cuda_buffer *mirror, char *err,
+                                size_t err_cap) {
+    TM_ENTER();
+    if (n == 0 || n_rows == 0 || n_rows > 65535u)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "argmax over %u rows of %u elements", n_rows, n);
+    if (out_cap == 0 || out_cap > out_stride)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "token log of %u slots in rows of %u", out_cap, out_stride);
+    TM_CHECK_BUF(x, (size_t)n_rows * n * 4, "logits");
+    TM_CHECK_BUF(partial, (size_t)n_rows * 512, "argmax partials");
+    TM_CHECK_BUF(out, ((size_t)(n_rows - 1) * out_stride + out_cap) * 4, "token logs");
+    if (mirror) TM_CHECK_BUF(mirror, ((size_t)(n_rows - 1) * out_stride + out_cap) * 4, "token log mirrors");
+    TM_CHECK_BUF(pos_buf, (size_t)n_rows * 4, "positions");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator argmax_rows cannot be recorded into a persistent program");
+    TM_OP_BEGIN("argmax_rows");
+    float *pv = (float *)partial->dev;
+    uint32_t *pi = (uint32_t *)(partial->dev + (size_t)n_rows * 256);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_rows_partial_kernel, dim3(kArgmaxGroups, n_rows), dim3(kThreads), 0,
+                              (const float *)x->dev, pv, pi, n));
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_rows_final_kernel, dim3(n_rows), dim3(kThreads), 0, (const float *)pv,
+                              (const uint32_t *)pi, (uint32_t *)out->dev, out_stride, base,
+                              (const uint32_t *)pos_buf->dev, out_cap, mirror ? (uint32_t *)mirror->dev : nullptr));
+    TM_OP_END(2);
 }
 
 int tm_cuda_rmsnorm_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *x, tm_cuda_buffer *weight,
@@ -1331,6 +1446,86 @@ int tm_cuda_attention_decode_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_bu
 #define TM_DECODE(DPL)                                                                                        \
     launch_decode<DPL>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads, head_dim, n_rot, \
                        cap, window, eps, scale)
+    switch (head_dim / 32) {
+        case 1: TM_DECODE(1); break;
+        case 2: TM_DECODE(2); break;
+        case 3: TM_DECODE(3); break;
+        case 4: TM_DECODE(4); break;
+        default: TM_DECODE(8); break;
+    }
+#undef TM_DECODE
+    const uint64_t launches = 1;
+    TM_OP_END(launches);
+}
+
+int tm_cuda_attention_decode_batch_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_cuda_buffer *k, tm_cuda_buffer *v,
+                                       tm_cuda_buffer *q_norm, tm_cuda_buffer *k_norm, tm_cuda_buffer *inv_freq,
+                                       tm_cuda_buffer *k_cache, tm_cuda_buffer *v_cache, tm_cuda_buffer *out,
+                                       tm_cuda_buffer *scratch, tm_cuda_buffer *pos_buf, tm_cuda_buffer *status,
+                                       uint32_t n_seq, uint32_t q_stride, uint32_t kv_stride, uint32_t heads,
+                                       uint32_t kv_heads, uint32_t head_dim,
+                                       uint32_t n_rot, uint32_t cap, uint32_t window, float eps, float scale,
+                                       int exact, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 32 || !attn_shape_ok(head_dim) ||
+        n_rot == 0 || n_rot > head_dim || n_rot % 2 != 0 || cap == 0 || cap > 65535u * kAttnBlock)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS,
+                       "decode attention geometry: heads %u/%u, head_dim %u (32, 64, 96, 128 or 256), n_rot %u, "
+                       "capacity %u", heads, kv_heads, head_dim, n_rot, cap);
+    if (n_seq == 0 || n_seq > 65535u)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "sequence count %u outside 1..65535", n_seq);
+    const size_t plane = (size_t)kv_heads * cap * head_dim * 2;
+    const size_t per_seq = tm_cuda_attention_decode_scratch_bytes(heads, kv_heads, head_dim, cap);
+    if (q_stride == 0) q_stride = heads * head_dim;
+    if (kv_stride == 0) kv_stride = kv_heads * head_dim;
+    if (q_stride < heads * head_dim || kv_stride < kv_heads * head_dim || q_stride % 4 != 0 || kv_stride % 4 != 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "row strides %u / %u below the row widths or not 16-byte multiples",
+                       q_stride, kv_stride);
+    TM_CHECK_BUF(q, ((size_t)(n_seq - 1) * q_stride + (size_t)heads * head_dim) * 4, "q");
+    TM_CHECK_BUF(k, ((size_t)(n_seq - 1) * kv_stride + (size_t)kv_heads * head_dim) * 4, "k");
+    TM_CHECK_BUF(v, ((size_t)(n_seq - 1) * kv_stride + (size_t)kv_heads * head_dim) * 4, "v");
+    TM_CHECK_BUF(q_norm, (size_t)head_dim * 4, "q norm");
+    TM_CHECK_BUF(k_norm, (size_t)head_dim * 4, "k norm");
+    TM_CHECK_BUF(inv_freq, (size_t)(n_rot / 2) * 4, "inv_freq");
+    TM_CHECK_BUF(k_cache, (size_t)n_seq * plane, "k caches");
+    TM_CHECK_BUF(v_cache, (size_t)n_seq * plane, "v caches");
+    TM_CHECK_BUF(out, (size_t)n_seq * heads * head_dim * 4, "attention output");
+    TM_CHECK_BUF(scratch, (size_t)n_seq * per_seq, "decode attention scratch");
+    TM_CHECK_BUF(pos_buf, (size_t)n_seq * 4, "positions");
+    TM_CHECK_BUF(status, 4, "status");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator attention_decode_batch cannot be recorded into a persistent program");
+    const float *qp = (const float *)q->dev, *kp = (const float *)k->dev, *vp = (const float *)v->dev;
+    const float *qn = (const float *)q_norm->dev, *kn = (const float *)k_norm->dev, *fq = (const float *)inv_freq->dev;
+    __half *kcp = (__half *)k_cache->dev, *vcp = (__half *)v_cache->dev;
+    float *op = (float *)out->dev, *sp = (float *)scratch->dev;
+    const uint32_t *pp = (const uint32_t *)pos_buf->dev;
+    uint32_t *stp = (uint32_t *)status->dev;
+    decode_seq_strides st;
+    st.q = q_stride;
+    st.out = (size_t)heads * head_dim;
+    st.k = st.v = kv_stride;
+    st.cache = plane / 2;
+    st.scratch = per_seq / 4;
+    TM_OP_BEGIN("attention_decode_batch");
+    if (!exact && attn_fast_ok(heads, kv_heads, head_dim, n_rot)) {
+#define TM_FAST(G, HD)                                                                                       \
+    launch_decode_fast<G, HD>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, kv_heads, n_rot, cap, window, \
+                              eps, scale, n_seq, st)
+        switch ((heads / kv_heads) * 1000 + head_dim) {
+            case 1128: TM_FAST(1, 128); break;
+            case 2128: TM_FAST(2, 128); break;
+            case 4128: TM_FAST(4, 128); break;
+            case 1256: TM_FAST(1, 256); break;
+            case 2256: TM_FAST(2, 256); break;
+            default: TM_FAST(4, 256); break;
+        }
+#undef TM_FAST
+        TM_OP_END(1);
+    }
+#define TM_DECODE(DPL)                                                                                        \
+    launch_decode<DPL>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads, head_dim, n_rot, \
+                       cap, window, eps, scale, n_seq, st)
     switch (head_dim / 32) {
         case 1: TM_DECODE(1); break;
         case 2: TM_DECODE(2); break;

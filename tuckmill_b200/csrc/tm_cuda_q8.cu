@@ -50,6 +50,7 @@ struct gemv_args {
     int prologue, epilogue;
     uint32_t plane;         // bytes between digit planes (== 64 mod 128)
     uint32_t ks;            // column splits per row tile (1, 2, 4 or 8)
+    uint32_t shape_rows;    // host only: rows of the matrix the column split is chosen for (a row view: its parent's)
 };
 
 // Bytes of shared memory one token's staged activations take.
@@ -477,8 +478,11 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
     // warps of one resident wave: the column split grows only while the grid stays within it
     // (taken from the one-token form whatever m is: the split must depend on the shape alone)
     const uint32_t want = (uint32_t)ctx->sm_count * resident_ctas_per_sm(ctx, a.cols, 1) * kWarps;
+    // A row view takes the split of the matrix it is a view of, so that a row's partial sums are added
+    // in the same order whether the whole matrix or a part of it is multiplied.
+    const uint32_t shape_tiles = ((a.shape_rows ? a.shape_rows : a.rows) + 15u) / 16u;
     uint32_t ks = 1;
-    while (ks < (uint32_t)kWarps && n_tiles * ks * 2u <= want && ks * 2u <= n_chunks) ks <<= 1;
+    while (ks < (uint32_t)kWarps && shape_tiles * ks * 2u <= want && ks * 2u <= n_chunks) ks <<= 1;
     a.ks = ks;
     const uint32_t tiles_per_cta = kWarps / ks;
     uint32_t ctas = (n_tiles + tiles_per_cta - 1u) / tiles_per_cta;
@@ -528,13 +532,13 @@ cudaError_t gemv_slice(tm_cuda_ctx *ctx, gemv_args a, int m) {
     if (ctas > 2u * slots && rem != 0u && rem * 2u < slots) {
         const uint32_t bulk_rows = (ctas - rem) * rows_per_cta;
         gemv_args bulk = a, rest = a;
-        bulk.rows = bulk_rows;
+        bulk.rows = bulk.shape_rows = bulk_rows;
         cudaError_t e = gemv_part(ctx, bulk, m);
         if (e != cudaSuccess) return e;
         rest.q = a.q + (size_t)bulk_rows * a.cols;
         rest.d = a.d + (size_t)bulk_rows * (a.cols / 32u);
         rest.y = a.y + bulk_rows;
-        rest.rows = a.rows - bulk_rows;
+        rest.rows = rest.shape_rows = a.rows - bulk_rows;
         return gemv_part(ctx, rest, m);
     }
     return gemv_part(ctx, a, m);
@@ -643,6 +647,25 @@ __global__ void q8_rows_gather_kernel(const signed char *q, const __half *d, uin
                                       const uint32_t *ids, uint32_t first, float scale, float *out) {
     const uint32_t t = blockIdx.y, nb = cols / 32u;
     const uint32_t id = ids[first + t];
+    for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
+        float v = 0.0f;
+        if (id < rows) {
+            v = __half2float(d[(size_t)id * nb + c / 32u]) * (float)q[(size_t)id * cols + c];
+            if (scale != 0.0f) v *= scale;
+        }
+        out[(size_t)t * cols + c] = v;
+    }
+}
+
+// One row per sequence: out[s] = row ids[s * stride + pos[s] + bias] (zeros when the slot or the id is outside).
+__global__ void q8_rows_gather_seq_kernel(const signed char *q, const __half *d, uint32_t rows, uint32_t cols,
+                                          const uint32_t *ids, uint32_t stride, const uint32_t *pos, int bias,
+                                          float scale, float *out) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t t = blockIdx.y, nb = cols / 32u;
+    const uint32_t slot = pos[t] + (uint32_t)bias;
+    const uint32_t id = slot < stride ? ids[(size_t)t * stride + slot] : 0xFFFFFFFFu;
     for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
         float v = 0.0f;
         if (id < rows) {
@@ -763,6 +786,8 @@ static int gemv_common(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, t
     a.pro = pro ? (const float *)pro->dev : nullptr;
     a.rows = rows;
     a.cols = cols;
+    a.shape_rows = rows;
+    for (const tm_cuda_buffer *p = w->parent; p && p->layout == TM_LAYOUT_Q8_0_PACKED; p = p->parent) a.shape_rows = p->rows;
     a.eps = eps;
     a.prologue = prologue;
     a.epilogue = epilogue;
@@ -797,6 +822,16 @@ int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer 
     TM_ENTER();
     return gemv_common(ctx, w, x, y, rows, cols, 1, 0, 0, prologue, pro, eps, epilogue,
                        "q8_0_gemv_fused", err, err_cap);
+}
+
+int tm_cuda_q8_0_gemm_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
+                            uint32_t cols, uint32_t batch, int prologue, tm_cuda_buffer *pro, float eps, int epilogue,
+                            char *err, size_t err_cap) {
+    TM_ENTER();
+    if (ctx->program && batch != 1)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator q8_0_gemm_fused cannot be recorded into a persistent program");
+    return gemv_common(ctx, w, x, y, rows, cols, batch, 0, 0, prologue, pro, eps, epilogue, "q8_0_gemm_fused", err,
+                       err_cap);
 }
 
 int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
@@ -862,6 +897,27 @@ int tm_cuda_rows_indirect_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows
     q8_rows_gather_kernel<<<dim3((cols + 255) / 256, n), 256, 0, ctx->stream>>>(
         (const signed char *)w->qp, (const __half *)w->dp, rows, cols, (const uint32_t *)ids->dev, first,
         scale, (float *)out->dev);
+    TM_OP_END(1);
+}
+
+int tm_cuda_rows_indirect_seq_f32_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *w, uint32_t rows, uint32_t cols,
+                                      tm_cuda_buffer *ids, uint32_t ids_stride, tm_cuda_buffer *pos_buf,
+                                      uint32_t n_seq, int32_t bias, float scale, tm_cuda_buffer *out, char *err,
+                                      size_t err_cap) {
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (n_seq == 0 || n_seq > 65535u || ids_stride == 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "%u sequences with logs of %u slots", n_seq, ids_stride);
+    TM_CHECK_BUF(ids, (size_t)n_seq * ids_stride * 4, "token logs");
+    TM_CHECK_BUF(pos_buf, (size_t)n_seq * 4, "positions");
+    TM_CHECK_BUF(out, (size_t)n_seq * cols * 4, "rows output");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator rows_indirect_seq cannot be recorded into a persistent program");
+    TM_OP_BEGIN("rows_indirect_seq");
+    TM_CUDA_TRY(tm_launch_pdl(ctx, q8_rows_gather_seq_kernel, dim3((cols + 255) / 256, n_seq), dim3(256), 0,
+                              (const signed char *)w->qp, (const __half *)w->dp, rows, cols, (const uint32_t *)ids->dev,
+                              ids_stride, (const uint32_t *)pos_buf->dev, (int)bias, scale, (float *)out->dev));
     TM_OP_END(1);
 }
 

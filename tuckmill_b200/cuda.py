@@ -69,6 +69,11 @@ _OPS = {
     "f16_gemv_fused": [_P, _P, _P, _P, _U32, _U32, _I, _P, _F, _I],
     "f16_row_indirect_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
     "f16_rows_indirect_f32": [_P, _P, _U32, _U32, _P, _U32, _U32, _F, _P],
+    "q8_0_gemm_fused": [_P, _P, _P, _P, _U32, _U32, _U32, _I, _P, _F, _I],
+    "attention_decode_batch_dev": [_P] * 13 + [_U32] * 9 + [_F, _F, _I],
+    "rows_indirect_seq_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
+    "argmax_rows_f32_dev": [_P, _P, _U32, _U32, _P, _P, _U32, _U32, _P, _U32, _P],
+    "u32_add_sat": [_P, _P, _U32, _U32, _U32, _U32],
     "begin_group": [_P],
     "end_group": [_P],
     "abort_group": [_P],
@@ -405,6 +410,29 @@ class CudaContext:
 
     def f16_rows_indirect(self, w, rows, cols, ids, first, n, scale, out):
         self._call("f16_rows_indirect_f32", w.handle, rows, cols, ids.handle, first, n, scale, out.handle)
+
+    # decode steps of several sequences (include/tm_cuda.h)
+    def q8_0_gemm_fused(self, w, x, y, rows, cols, batch, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
+        self._call("q8_0_gemm_fused", w.handle, x.handle, y.handle, rows, cols, batch, prologue, self._h(pro), eps, epilogue)
+
+    def attention_decode_batch(self, q, k, v, q_norm, k_norm, inv_freq, k_cache, v_cache, out, scratch, pos_buf, status,
+                               n_seq, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale, exact,
+                               q_stride=0, kv_stride=0):
+        self._call("attention_decode_batch_dev", q.handle, k.handle, v.handle, q_norm.handle, k_norm.handle,
+                   inv_freq.handle, k_cache.handle, v_cache.handle, out.handle, scratch.handle, pos_buf.handle,
+                   status.handle, n_seq, q_stride, kv_stride, heads, kv_heads, head_dim, n_rot, cap, window, eps, scale,
+                   int(exact))
+
+    def rows_indirect_seq(self, w, rows, cols, ids, ids_stride, pos_buf, n_seq, bias, scale, out):
+        self._call("rows_indirect_seq_f32_dev", w.handle, rows, cols, ids.handle, ids_stride, pos_buf.handle, n_seq,
+                   bias, scale, out.handle)
+
+    def argmax_rows_dev(self, x, n_rows, n, partial, out, out_stride, base, pos_buf, out_cap, mirror=None):
+        self._call("argmax_rows_f32_dev", x.handle, n_rows, n, partial.handle, out.handle, out_stride, base,
+                   pos_buf.handle, out_cap, self._h(mirror))
+
+    def u32_add_sat(self, buf, first, count, delta, limit):
+        self._call("u32_add_sat", buf.handle, first, count, delta, limit)
 
     def row_indirect_f32(self, w, type_id, rows, cols, ids, slot, out):
         self._call("row_indirect_f32", w.handle, type_id, rows, cols, ids.handle, slot, out.handle)

@@ -34,7 +34,7 @@ class _Options(C.Structure):
     _fields_ = [("gguf_path", C.c_char_p), ("kernels", C.c_char_p), ("device", C.c_int), ("context", C.c_uint32),
                 ("prefill_batch", C.c_uint32), ("exact", C.c_int), ("budget_bytes", C.c_uint64),
                 ("shard_rank", C.c_uint32), ("shard_world", C.c_uint32), ("comm_id", C.c_void_p),
-                ("persistent_step", C.c_int)]
+                ("persistent_step", C.c_int), ("sequences", C.c_uint32)]
 
 
 class Info(C.Structure):
@@ -75,6 +75,11 @@ def load_library() -> C.CDLL:
     L.tm_engine_generate.argtypes = [P, P, C.c_uint32, C.c_uint32, C.c_int, P, C.POINTER(C.c_uint32),
                                      C.POINTER(Stats)] + E
     L.tm_engine_decode_steps.argtypes = [P, C.c_uint32] + E
+    L.tm_engine_prefill_seq.argtypes = [P, C.c_uint32, P, C.c_uint32, C.c_int] + E
+    L.tm_engine_prefill_token_of.argtypes = [P, C.c_uint32, C.POINTER(C.c_uint32)] + E
+    L.tm_engine_step_batch.argtypes = [P, P, P] + E
+    L.tm_engine_decode_steps_batch.argtypes = [P, C.c_uint32] + E
+    L.tm_engine_generate_batch.argtypes = [P, P, P, C.c_uint32, C.c_uint32, C.c_int, P, P, C.POINTER(Stats)] + E
     L.tm_engine_decode_ungrouped.argtypes = [P, C.c_uint32] + E
     L.tm_engine_plan.argtypes = [C.c_char_p, C.c_uint32, C.c_uint64, C.POINTER(Info)] + E
     L.tm_engine_plan_shard.argtypes = [C.c_char_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.POINTER(Info)] + E
@@ -109,7 +114,7 @@ def comm_id() -> bytes:
 class Engine:
     def __init__(self, gguf_path, context: int, kernels: str = "cuda", device: int = 0, prefill_batch: int = 0,
                  exact: bool = False, budget_bytes: int = 0, shard_rank: int = 0, shard_world: int = 1,
-                 comm_id: bytes | None = None, persistent_step: bool = False):
+                 comm_id: bytes | None = None, persistent_step: bool = False, sequences: int = 1):
         """With shard_world > 1 every rank constructs its Engine with the same
         128-byte `comm_id` (from `comm_id()` on one rank) and then makes the same
         calls in the same order; each call is a collective."""
@@ -119,7 +124,8 @@ class Engine:
         self._comm_id = C.create_string_buffer(comm_id, 128) if comm_id is not None else None
         o = _Options(self._path, self._kernels, device, context, prefill_batch, int(exact), budget_bytes,
                      shard_rank, shard_world, C.cast(self._comm_id, C.c_void_p) if self._comm_id is not None else None,
-                     int(persistent_step))
+                     int(persistent_step), sequences)
+        self.sequences = max(1, sequences)
         h, err = C.c_void_p(), C.create_string_buffer(1024)
         _check(self._l.tm_engine_load(C.byref(o), C.byref(h), err, 1024), err)
         self.handle = h
@@ -212,6 +218,39 @@ class Engine:
         self._call(self._l.tm_engine_generate, p.ctypes.data, p.size, max_new, int(ignore_eos), out.ctypes.data,
                    C.byref(n), C.byref(st))
         return out[:n.value].copy(), st
+
+    # ---- several sequences (Engine(..., sequences=S)) ----
+    def prefill_seq(self, seq: int, tokens, want_token: bool = True):
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        self._call(self._l.tm_engine_prefill_seq, seq, t.ctypes.data, t.size, int(want_token))
+
+    def prefill_token_of(self, seq: int) -> int:
+        tok = C.c_uint32()
+        self._call(self._l.tm_engine_prefill_token_of, seq, C.byref(tok))
+        return tok.value
+
+    def step_batch(self, tokens, want_logits: bool = True):
+        """One decode step of every sequence; returns logits [sequences, vocab] when asked."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        if t.size != self.sequences:
+            raise ValueError(f"{t.size} tokens for {self.sequences} sequences")
+        out = np.empty((self.sequences, self.vocab), dtype=np.float32) if want_logits else None
+        self._call(self._l.tm_engine_step_batch, t.ctypes.data, out.ctypes.data if want_logits else None)
+        return out
+
+    def decode_steps_batch(self, steps: int):
+        self._call(self._l.tm_engine_decode_steps_batch, steps)
+
+    def generate_batch(self, prompts, max_new: int, ignore_eos: bool = True):
+        """Greedy generation for len(prompts) <= sequences requests at once: (list of token arrays, Stats)."""
+        ps = [np.ascontiguousarray(p, dtype=np.uint32) for p in prompts]
+        flat = np.concatenate(ps) if ps else np.zeros(0, np.uint32)
+        lens = np.array([p.size for p in ps], dtype=np.uint32)
+        out = np.zeros((len(ps), max_new), dtype=np.uint32)
+        counts, st = np.zeros(len(ps), dtype=np.uint32), Stats()
+        self._call(self._l.tm_engine_generate_batch, flat.ctypes.data, lens.ctypes.data, len(ps), max_new,
+                   int(ignore_eos), out.ctypes.data, counts.ctypes.data, C.byref(st))
+        return [out[r, :counts[r]].copy() for r in range(len(ps))], st
 
     def score(self, tokens) -> np.ndarray:
         """Teacher-forced logits at every position (crates/tuckcore/src/executor.rs:716-762)."""

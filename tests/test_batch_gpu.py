@@ -115,6 +115,7 @@ def test_row_gather_argmax_and_positions_per_sequence(ctx):
 
     n = 1000
     x = T.activations(5, 1, S * n).reshape(S, n)
+    x[0, 123] = 60.0
     x[1, 17] = x[1, 900] = 50.0  # tie: the lower index
     x[2, :] = np.nan             # every logit NaN: the "none" id
     xb, partial = ctx.floats(x), ctx.buffer(S * 512)
@@ -123,7 +124,7 @@ def test_row_gather_argmax_and_positions_per_sequence(ctx):
     pb = ctx.from_array(np.array([0, 3, 8, 9], np.uint32))  # 1 + 9 = slot 10 is outside a log of 10 slots
     ctx.argmax_rows_dev(xb, S, n, partial, tok, stride, 1, pb, cap1, mirror)
     got = tok.download(0, S * stride * 4, np.uint32).reshape(S, stride)
-    assert got[0, 1] == int(np.argmax(x[0])) and got[1, 4] == 17 and got[2, 9] == 0xFFFFFFFF
+    assert got[0, 1] == 123 and got[1, 4] == 17 and got[2, 9] == 0xFFFFFFFF
     assert not got[3].any() and np.count_nonzero(got) == 3
     np.testing.assert_array_equal(mirror.download(0, S * stride * 4, np.uint32).reshape(S, stride), got)
     with pytest.raises(cuda.CudaError):

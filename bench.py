@@ -435,8 +435,13 @@ def run_cuda(args):
     value = world * dec_tokens / (decode_ms / 1e3)
     e2e = world * gen / (span_ms / 1e3)
 
+    eng.close()
+    # several sequences at once, on this GPU alone (every rank its own under torchrun; rank 0's is printed)
+    batched = batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decode_n,
+                          args.sequences) if args.sequences > 1 else None
     split = row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n,
                           tokens) if world > 1 else None
+    eng = E.Engine(path, context=context, device=local, prefill_batch=prefill_batch) if rank == 0 else None
 
     if rank == 0:
         roof = gemv_roofline(eng, shape, hbm_gbs, 1e3 * decode_ms / dec_tokens, prompt_n)
@@ -475,12 +480,90 @@ def run_cuda(args):
             "wall_s": wall,
             "tokens_head": [int(t) for t in tokens[:8]],
         }
+        if batched is not None:
+            line["batched"] = batched
         if split is not None:
             line["row_split"] = split
         print(json.dumps(line), flush=True)
-    eng.close()
+    if eng is not None:
+        eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decode_n, sequences, shard=None):
+    """Decode of `sequences` concurrent requests of the workload in ONE recorded step (one row per
+    sequence through the batched projections, every sequence attending to its own KV planes): the
+    serving shape of the 8-GPU configuration.  Device-timed like `value` (events on the engine's
+    stream, max over ranks when the model is split); `e2e_decode_tok_s` goes through
+    generate_batch() with host buffers.  With `shard` = (rank, world, comm_id) the ONE model is split
+    by output rows and every exchange carries `sequences` rows."""
+    context = prompt_n + decode_n + 16
+    kw = dict(shard_rank=shard[0], shard_world=shard[1], comm_id=shard[2]) if shard else {}
+    eng = E.Engine(path, context=context, device=local, sequences=sequences,
+                   prefill_batch=2048 if shape.hidden >= 4096 else 0, **kw)
+    stream = torch.cuda.ExternalStream(eng.stream(), device=local)
+    prompts = [T.token_ids(args.seed + 7919 * (s + 1), prompt_n, shape.vocab) for s in range(sequences)]
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e.record()
+        return e
+
+    def session():
+        eng.reset()
+        e0 = ev()
+        for s in range(sequences):
+            eng.prefill_seq(s, prompts[s], want_token=True)
+        e1 = ev()
+        eng.decode_steps_batch(decode_n - 1)
+        e2 = ev()
+        return e0, e1, e2
+
+    steps = max(1, min(args.steps, 2))
+    session()
+    if world > 1 and shard:
+        dist.barrier()
+    eng.fence()
+    l0 = _launches(eng)
+    evs = [session() for _ in range(steps)]
+    eng.fence()
+    torch.cuda.synchronize()
+    launches = _launches(eng) - l0
+    toks, st = eng.generate_batch(prompts, decode_n)
+    vals = torch.tensor([sum(a.elapsed_time(b) for a, b, c in evs), sum(b.elapsed_time(c) for a, b, c in evs),
+                         st.decode_span_ns / 1e6], dtype=torch.float64, device="cuda")
+    if world > 1 and shard:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms, span_ms = vals.tolist()
+    n_steps = steps * (decode_n - 1)
+    info = eng.refresh_info()
+    # bytes one step must read: the weights once, and every sequence's K and V rows up to its position
+    kv_row = 2 * shape.layers * shape.kv_heads * shape.head_dim * 2
+    window = shape.window if shape.arch == "gemma3" and shape.window else 0
+    mean_pos = prompt_n + decode_n / 2
+    kv_read = sequences * kv_row * (mean_pos if not window else min(mean_pos, window))  # upper bound for Gemma's global layers
+    share = (shard[1] if shard else 1)
+    step_bytes = (shape.decode_weight_bytes() + kv_read) / share
+    hbm_gbs, _ = measured_peaks()
+    us_step = 1e3 * decode_ms / n_steps
+    out = {
+        "sequences": sequences, "prompt_tokens": prompt_n, "decode_tokens": decode_n,
+        "parallelism": f"output-row split x{shard[1]}" if shard else "single",
+        "decode_tok_s": sequences * n_steps / (decode_ms / 1e3),
+        "us_per_step": us_step,
+        "prefill_tok_s": steps * sequences * prompt_n / (prefill_ms / 1e3),
+        "e2e_decode_tok_s": (st.generated - sequences) / (span_ms / 1e3),
+        "h2d_bytes_per_step": int(st.h2d_bytes), "d2h_bytes_per_step": int(st.d2h_bytes),
+        "gpu_launches": int(launches),
+        "step_bytes_per_gpu": int(step_bytes),
+        "step_hbm_frac": step_bytes / (us_step * 1e3) / hbm_gbs,
+        "kv_bytes_per_gpu": int(info.plan_state),
+        "tokens_head": [int(t[1]) if len(t) > 1 else -1 for t in toks[:8]],
+    }
+    eng.close()
+    return out
 
 
 def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n, replica_tokens):
@@ -496,12 +579,15 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
         S.shard_geometry(shape, world)
     except ValueError as e:
         return {"unavailable": str(e)}
-    ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
-    if rank == 0:
-        ident.copy_(torch.frombuffer(bytearray(E.comm_id()), dtype=torch.uint8))
-    dist.broadcast(ident, 0)
+    def fresh_comm_id() -> bytes:  # one communicator per engine: an id is not reused
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            ident.copy_(torch.frombuffer(bytearray(E.comm_id()), dtype=torch.uint8))
+        dist.broadcast(ident, 0)
+        return bytes(ident.cpu().numpy().tobytes())
+
     eng = E.Engine(path, context=context, device=local, shard_rank=rank, shard_world=world,
-                   comm_id=bytes(ident.cpu().numpy().tobytes()), prefill_batch=2048 if shape.hidden >= 4096 else 0)
+                   comm_id=fresh_comm_id(), prefill_batch=2048 if shape.hidden >= 4096 else 0)
     stream = torch.cuda.ExternalStream(eng.stream(), device=local)
     prompt = T.token_ids(args.seed, prompt_n, shape.vocab)  # rank 0's prompt of the replica arm, on every rank
 
@@ -543,6 +629,9 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
         "tokens_equal_single_device": bool(replica_tokens is not None and list(tokens) == list(replica_tokens)),
     }
     eng.close()
+    if args.sequences > 1:
+        out["batched"] = batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decode_n, args.sequences,
+                                     shard=(rank, world, fresh_comm_id()))
     return out
 
 
@@ -703,6 +792,36 @@ def run_op(args):
         eng.close()
         return
     ctx = cuda.CudaContext(0)
+    if args.op == "attn":
+        # decode attention of `--sequences` sequences at position `--batch`, geometry of the workload
+        shape = WORKLOADS[args.workload][0]
+        S, pos, heads, kvh, hd = args.sequences, args.batch, shape.heads, shape.kv_heads, shape.head_dim
+        cap = pos + 64
+        plane = kvh * cap * hd
+        rng = np.random.default_rng(0)
+        fill = (rng.standard_normal(min(S * plane, 1 << 24)) * 0.5).astype(np.float16)
+        caches = []
+        for _ in range(2):
+            kc = ctx.buffer(S * plane * 2)
+            for off in range(0, S * plane, fill.size):
+                kc.upload(off * 2, fill[:min(fill.size, S * plane - off)])
+            caches.append(kc)
+        one = ctx.floats(np.ones(hd, np.float32))
+        inv = ctx.floats((shape.rope_base ** (-np.arange(hd // 2, dtype=np.float64) * 2 / hd)).astype(np.float32))
+        q = ctx.floats(T.activations(0, 1, S * heads * hd))
+        k, v = ctx.floats(T.activations(0, 2, S * kvh * hd)), ctx.floats(T.activations(0, 3, S * kvh * hd))
+        out = ctx.buffer(S * heads * hd * 4)
+        sb = ctx.buffer(S * cuda.decode_attention_scratch_bytes(heads, kvh, hd, cap))
+        sb.zero()
+        pb, st = ctx.from_array(np.full(S, pos, np.uint32)), ctx.buffer(4, shared=True)
+        st.zero()
+        for _ in range(3):
+            ctx.attention_decode_batch(q, k, v, one, one, inv, caches[0], caches[1], out, sb, pb, st, S, heads, kvh, hd, hd,
+                                       cap, 0, shape.eps, float(1 / np.sqrt(hd)), False)
+        ctx.fence()
+        print("attn %s: %d sequences at position %d, 3 launches, %.1f MB of K and V per launch" %
+              (args.workload, S, pos, S * 2 * kvh * (pos + 1) * hd * 2 / 1e6))
+        return
     rows, cols, m = args.rows, args.cols, args.batch
     base = T.q8_0_matrix(0, 1, min(rows, 1024), cols)
     w = ctx.q8_0_matrix(np.tile(base, ((rows + base.shape[0] - 1) // base.shape[0], 1, 1))[:rows], rows, cols)
@@ -733,7 +852,10 @@ def main():
     ap.add_argument("--workload", default="qwen3-0.6b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--op", choices=["gemv", "gemm", "slice", "sweep"],
+    ap.add_argument("--sequences", type=int, default=32,
+                    help="concurrent sequences of the batched-decode leg reported beside the one-sequence metric "
+                         "(1 switches the leg off)")
+    ap.add_argument("--op", choices=["gemv", "gemm", "slice", "sweep", "attn"],
                     help="profiler case / projection sweep instead of the benchmark")
     ap.add_argument("--rows", type=int, default=12288)
     ap.add_argument("--cols", type=int, default=4096)

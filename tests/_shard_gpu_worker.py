@@ -11,6 +11,21 @@ def main() -> None:
     from tuckmill_b200 import engine as E, testing as T
 
     shape = T.TINY_QWEN3
+    if mode.startswith("batch-"):
+        # several sequences on a split model: every exchange carries one row per sequence
+        eng = E.Engine(path, context=64, device=rank, exact=(mode == "batch-exact"), prefill_batch=16, shard_rank=rank,
+                       shard_world=world, comm_id=bytes.fromhex(comm_hex), sequences=5)
+        info = eng.refresh_info()
+        assert info.allocated_bytes == info.plan_weights + info.plan_state + info.plan_scratch
+        prompts = [T.token_ids(30 + i, 4 + 5 * i, shape.vocab) for i in range(4)]
+        first, _ = eng.generate_batch(prompts, 14)
+        again, stats = eng.generate_batch(prompts, 14)
+        assert all(list(a) == list(b) for a, b in zip(first, again))
+        if rank == 0:
+            np.savez(out, **{f"tokens{i}": np.asarray(t, dtype=np.int64) for i, t in enumerate(first)},
+                     generated=stats.generated)
+        eng.close()
+        return
     eng = E.Engine(path, context=96, device=rank, exact=(mode == "exact"), prefill_batch=16, shard_rank=rank,
                    shard_world=world, comm_id=bytes.fromhex(comm_hex))
     info = eng.refresh_info()

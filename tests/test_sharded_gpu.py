@@ -72,6 +72,27 @@ def test_two_device_split_matches_single_device_and_oracle(oracle, tmp_path, mod
     assert list(got["generated"]) == list(ref_tokens)
 
 
+@pytest.mark.parametrize("mode", ["batch-exact", "batch-mma"])
+def test_two_device_split_decodes_several_sequences(tmp_path, mode):
+    """generate_batch on a model split over two devices: every request's tokens are the ones the
+    single-device engine produces for that request alone."""
+    if cuda.available() < 2:
+        pytest.skip("needs two devices")
+    shape = T.TINY_QWEN3
+    path = tmp_path / "tiny.gguf"
+    T.write_gguf(path, shape, seed=3, norm_jitter=0.1)
+    got = run_ranks(2, path, mode, tmp_path / "rank0.npz")
+    prompts = [T.token_ids(30 + i, 4 + 5 * i, shape.vocab) for i in range(4)]
+    one = E.Engine(path, context=64, exact=(mode == "batch-exact"), prefill_batch=16)
+    total = 0
+    for i, p in enumerate(prompts):
+        want, _ = one.generate(p, 14)
+        assert list(got[f"tokens{i}"]) == list(want), f"request {i}"
+        total += len(want)
+    assert int(got["generated"]) == total
+    one.close()
+
+
 def test_peer_memory_push_all_gather(tmp_path):
     """tm_cuda_push_rows_f32 over a symmetric arena: every rank receives every rank's
     rows at the interleaved position, round after round, eagerly and from a replayed

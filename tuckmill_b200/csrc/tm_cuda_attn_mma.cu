@@ -332,6 +332,296 @@ __global__ void __launch_bounds__(256) qk_prep_chunk_kernel(float *q, const floa
     }
 }
 
+// ---- decode attention for many sequences on the tensor cores ---------------------------------
+// The per-token core (per-head q/k RMS norm, RoPE, f16 KV store, windowed causal attention) for one
+// row per sequence, throughput form: when tens of sequences decode together the step reads every
+// sequence's K and V rows and is bandwidth-bound, which the latency-optimised kernel (scalar dot
+// products, two threads per key) cannot feed.  Here one CTA of 4 warps serves ONE (sequence, KV head,
+// split of `tiles` 64-key tiles): the G query heads of the group are the rows of a 16-row MMA tile,
+// K/V tiles arrive by cp.async (double-buffered), warp w owns keys 16w..16w+15 of every tile with its
+// own running (max, sum, output), the four are merged through shared memory, and the splits of a
+// (sequence, KV head) by last arrival through `scratch` (no waiting).  Same mathematics as the other
+// decode kernels, f16 Q and softmax weights, base-2 exponentials: tolerance-qualified.
+//   scratch (per sequence): float part[kv_heads][nsplit][G][HD + 2] = (m, l, o[HD]); then, at the offset
+//   the other decode kernels use, u32 count[kv_heads] (left at zero).
+struct decode_mma_args {
+    const float *q, *k, *v, *q_norm, *k_norm, *inv_freq;
+    __half *kc, *vc;
+    float *out, *scratch;
+    const uint32_t *pos;
+    uint32_t *status;
+    uint32_t kv_heads, cap, window, tiles, count_off;  // count_off: floats from a sequence's scratch to its counters
+    float eps, scale_log2e;
+    size_t sq, sk, sv, so, scache, sscratch;  // element strides between sequences
+};
+
+template <int G, int HD>
+__global__ void __launch_bounds__(kThreads) attention_decode_mma_kernel(const decode_mma_args a) {
+    constexpr int PITCH = HD * 2, EPL = HD / 32;
+    constexpr uint32_t kQBytes = 16 * PITCH, kTile = kBKV * PITCH, kStage = 2 * kTile;
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char *sQ = smem, *sKV = smem + kQBytes;
+    __shared__ __align__(16) __half kh[HD];
+    __shared__ __align__(16) __half vh[HD];
+    __shared__ float wm[4][G], wl[4][G];
+    __shared__ uint32_t s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y;
+    const size_t sidx = blockIdx.z;
+    const float *q = a.q + sidx * a.sq, *k = a.k + sidx * a.sk, *v = a.v + sidx * a.sv;
+    __half *kc = a.kc + sidx * a.scache + (size_t)kvh * a.cap * HD, *vc = a.vc + sidx * a.scache + (size_t)kvh * a.cap * HD;
+    float *out = a.out + sidx * a.so, *scratch = a.scratch + sidx * a.sscratch;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t pos = a.pos[sidx];
+    if (pos >= a.cap) {
+        if (tid == 0 && split == 0 && kvh == 0) atomicOr(a.status, 1u);
+        return;
+    }
+    const uint32_t seq = pos + 1u, start = (a.window != 0u && seq > a.window) ? seq - a.window : 0u;
+    const uint32_t first_tile = start / kBKV, last_tile = pos / kBKV;
+    const uint32_t tile_lo = first_tile + split * a.tiles;
+    if (tile_lo > last_tile) return;
+    const uint32_t tile_hi = min(tile_lo + a.tiles - 1u, last_tile);
+    const uint32_t nact = (last_tile - first_tile) / a.tiles + 1u;  // splits of this (sequence, KV head)
+    const bool owns_new = tile_hi == last_tile;
+
+    auto load_tile = [&](uint32_t tile, int stage) {
+        unsigned char *sK = sKV + stage * kStage, *sV = sK + kTile;
+        const uint32_t j0 = tile * kBKV;
+        constexpr int CH = HD / 8;  // 16-byte chunks per row
+        for (int i = tid; i < kBKV * CH; i += kThreads) {
+            const uint32_t r = i / CH, c = i % CH;
+            const uint32_t j = min(j0 + r, pos);  // rows past the position repeat its row (masked below)
+            cp_async16(smem_u32(sK) + sw<PITCH>(r, c), kc + (size_t)j * HD + c * 8);
+            cp_async16(smem_u32(sV) + sw<PITCH>(r, c), vc + (size_t)j * HD + c * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(tile_lo, 0);
+
+    // ---- q_0..q_{G-1} (and k, v for the split that holds the position): RMS norm + RoPE, a warp each ----
+    for (int i = tid; i < 16 * (HD / 8); i += kThreads) *(uint4 *)(sQ + i * 16) = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    for (int vec = warp; vec < G + (owns_new ? 1 : 0); vec += kThreads / 32) {
+        const bool is_k = vec == G;
+        const float *src = is_k ? k + (size_t)kvh * HD : q + ((size_t)kvh * G + vec) * HD;
+        const float *nw = is_k ? a.k_norm : a.q_norm;
+        float x[EPL];
+        float ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < EPL; ++r) {
+            x[r] = src[lane + 32 * r];
+            ss = fmaf(x[r], x[r], ss);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+        for (int r = 0; r < EPL; ++r) x[r] = x[r] * inv * nw[lane + 32 * r];
+        // full rotation: pair (i, i + HD/2), i = lane + 32 r, has both members in this lane
+#pragma unroll
+        for (int r = 0; r < EPL / 2; ++r) {
+            float sn, cs;
+            sincosf((float)pos * a.inv_freq[lane + 32 * r], &sn, &cs);
+            const float a0 = x[r], b0 = x[r + EPL / 2];
+            x[r] = a0 * cs - b0 * sn;
+            x[r + EPL / 2] = a0 * sn + b0 * cs;
+        }
+        if (is_k) {
+            const float *vsrc = v + (size_t)kvh * HD;
+#pragma unroll
+            for (int r = 0; r < EPL; ++r) {
+                const uint32_t e = lane + 32 * r;
+                const __half hk = __float2half_rn(x[r]), hv = __float2half_rn(vsrc[e]);
+                kh[e] = hk;
+                vh[e] = hv;
+                kc[(size_t)pos * HD + e] = hk;
+                vc[(size_t)pos * HD + e] = hv;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < EPL; ++r) {
+                const uint32_t e = lane + 32 * r;
+                *(__half *)(sQ + sw<PITCH>((uint32_t)vec, e >> 3) + (e & 7u) * 2u) = __float2half_rn(x[r]);
+            }
+        }
+    }
+
+    // This warp's running state over its 16 keys of every tile; rows g < G are the group's heads.
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    const bool row_live = g < G;
+
+    for (uint32_t tile = tile_lo; tile <= tile_hi; ++tile) {
+        const int stage = (int)((tile - tile_lo) & 1u);
+        if (tile < tile_hi) {
+            load_tile(tile + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // the tile has landed (and, first time round, Q and the new row are written)
+        const uint32_t j0 = tile * kBKV;
+        if (tile == last_tile) {  // the position's own row comes from this step, not from the cache
+            const uint32_t r = pos - j0;
+            unsigned char *sK = sKV + stage * kStage, *sV = sK + kTile;
+            if (tid < HD / 8) *(uint4 *)(sK + sw<PITCH>(r, tid)) = *(const uint4 *)(kh + tid * 8);
+            else if (tid < HD / 4) *(uint4 *)(sV + sw<PITCH>(r, tid - HD / 8)) = *(const uint4 *)(vh + (tid - HD / 8) * 8);
+            __syncthreads();
+        }
+        const uint32_t sK = smem_u32(sKV + stage * kStage), sV = sK + kTile;
+        // ---- S = Q K^T: 16 rows x this warp's 16 keys ----
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+        for (int kt = 0; kt < HD / 16; ++kt) {
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            const uint32_t m = lane >> 3;
+            ldsm_x4(smem_u32(sQ) + sw<PITCH>((m & 1u) * 8 + (lane & 7), kt * 2 + (m >> 1)), a0, a1, a2, a3);
+            ldsm_x4(sK + sw<PITCH>(warp * 16 + (m >> 1) * 8 + (lane & 7), kt * 2 + (m & 1u)), b0, b1, b2, b3);
+            mma_f16(s[0], a0, a1, a2, a3, b0, b1);
+            mma_f16(s[1], a0, a1, a2, a3, b2, b3);
+        }
+        // ---- mask, running maximum, weights (rows g only: rows g + 8 are padding) ----
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t j = j0 + warp * 16 + i * 8 + 2 * t + e;
+                const bool vis = row_live && j >= start && j <= pos;
+                s[i][e] = vis ? s[i][e] * a.scale_log2e : -INFINITY;
+                mx = fmaxf(mx, s[i][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+        const float alpha = exp2f(m_run - m_use);
+        m_run = m_new;
+        const float p00 = exp2f(s[0][0] - m_use), p01 = exp2f(s[0][1] - m_use);
+        const float p10 = exp2f(s[1][0] - m_use), p11 = exp2f(s[1][1] - m_use);
+        float rs = p00 + p01 + p10 + p11;
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        l_run = l_run * alpha + rs;
+        const uint32_t pa0 = pack_h2(p00, p01), pa2 = pack_h2(p10, p11);  // rows g: keys 0-7 / 8-15; rows g + 8: zero
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= alpha;
+            o[i][1] *= alpha;
+        }
+        // ---- O += P V over this warp's 16 keys ----
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            uint32_t b0, b1, b2, b3;
+            const uint32_t m = lane >> 3;
+            ldsm_x4_t(sV + sw<PITCH>(warp * 16 + (m & 1u) * 8 + (lane & 7), dp * 2 + (m >> 1)), b0, b1, b2, b3);
+            mma_f16(o[2 * dp], pa0, 0u, pa2, 0u, b0, b1);
+            mma_f16(o[2 * dp + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+        __syncthreads();  // the stage is refilled by the next iteration's prefetch
+    }
+
+    // ---- the four warps' (m, l, o) -> this split's; the K/V stages are free now ----
+    float *wo = (float *)sKV;  // [4][G][HD]
+    if (row_live) {
+        if (t == 0) {
+            wm[warp][g] = m_run;
+            wl[warp][g] = l_run;
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i)
+            *(float2 *)(wo + ((size_t)warp * G + g) * HD + i * 8 + 2 * t) = make_float2(o[i][0], o[i][1]);
+    }
+    __syncthreads();
+    constexpr uint32_t stride = HD + 2;
+    const uint32_t nsplit = gridDim.y;
+    float *part = scratch + ((size_t)kvh * nsplit + split) * G * stride;
+    const bool single = nact == 1u;
+    for (uint32_t i = tid; i < G * HD; i += kThreads) {
+        const uint32_t gg = i / HD, d = i % HD;
+        float M = fmaxf(fmaxf(wm[0][gg], wm[1][gg]), fmaxf(wm[2][gg], wm[3][gg]));
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(wm[w][gg] - M);  // a warp that saw no key: exp2(-inf) = 0
+            L = fmaf(f, wl[w][gg], L);
+            O = fmaf(f, wo[((size_t)w * G + gg) * HD + d], O);
+        }
+        if (single) {
+            out[((size_t)kvh * G + gg) * HD + d] = O / L;
+        } else {
+            part[gg * stride + 2 + d] = O;
+            if (d == 0) {
+                part[gg * stride] = M;
+                part[gg * stride + 1] = L;
+            }
+        }
+    }
+    if (single) return;
+    __threadfence();
+    __syncthreads();
+    uint32_t *count = (uint32_t *)(scratch + a.count_off) + kvh;
+    if (tid == 0) s_last = atomicAdd(count, 1u) == nact - 1u ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (uint32_t i = tid; i < G * HD; i += kThreads) {
+        const uint32_t gg = i / HD, d = i % HD;
+        const float *base = scratch + (size_t)kvh * nsplit * G * stride + gg * stride;
+        float M = -INFINITY, L = 0.0f, O = 0.0f;
+        for (uint32_t s0 = 0; s0 < nact; s0 += 8) {
+            float mb[8], lb[8], ob[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float *pb = base + (size_t)(s0 + c < nact ? s0 + c : nact - 1) * G * stride;
+                mb[c] = __ldcg(pb);
+                lb[c] = __ldcg(pb + 1);
+                ob[c] = __ldcg(pb + 2 + d);
+            }
+            float mx = M;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (s0 + c < nact) mx = fmaxf(mx, mb[c]);
+            const float al = exp2f(M - mx);
+            L *= al;
+            O *= al;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (s0 + c < nact) {
+                    const float wgt = exp2f(mb[c] - mx);
+                    L = fmaf(wgt, lb[c], L);
+                    O = fmaf(wgt, ob[c], O);
+                }
+            M = mx;
+        }
+        out[((size_t)kvh * G + gg) * HD + d] = O / L;
+    }
+    if (tid == 0) *count = 0u;  // ready for the next launch on this stream
+}
+
+template <int G, int HD>
+cudaError_t launch_decode_mma(tm_cuda_ctx *ctx, const decode_mma_args &a, uint32_t n_seq) {
+    constexpr uint32_t kBytes = 16 * HD * 2 + 2 * 2 * kBKV * HD * 2;
+    static std::atomic<bool> attr_done[64] = {};
+    const int device = ctx->device;
+    if (device < 0 || device >= 64 || !attr_done[device].load(std::memory_order_acquire)) {
+        const cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<G, HD>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBytes);
+        if (e != cudaSuccess) return e;
+        if (device >= 0 && device < 64) attr_done[device].store(true, std::memory_order_release);
+    }
+    const uint32_t n_tiles = (a.cap + kBKV - 1) / kBKV;
+    const dim3 grid(a.kv_heads, (n_tiles + a.tiles - 1) / a.tiles, n_seq);
+    return tm_launch_pdl(ctx, attention_decode_mma_kernel<G, HD>, grid, dim3(kThreads), kBytes, a);
+}
+
 template <int HD>
 cudaError_t launch_attn(const attn_args &a, int device, cudaStream_t stream) {
     using C = attn_cfg<HD>;
@@ -348,6 +638,41 @@ cudaError_t launch_attn(const attn_args &a, int device, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// Whether the tensor-core decode form serves this geometry.
+bool tm_attention_decode_mma_ok(uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot) {
+    const uint32_t g = kv_heads ? heads / kv_heads : 0;
+    return hd == 128 && n_rot == hd && (g == 1 || g == 2 || g == 4);
+}
+
+// One launch for n_seq sequences (pointers are sequence 0's; strides in elements between sequences).
+cudaError_t tm_attention_decode_mma_launch(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v,
+                                           const float *qn, const float *kn, const float *inv_freq, void *kc, void *vc,
+                                           float *out, float *scratch, const uint32_t *pos, uint32_t *status,
+                                           uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t cap, uint32_t window,
+                                           float eps, float scale, uint32_t n_seq, size_t sq, size_t skv, size_t so,
+                                           size_t scache, size_t sscratch, uint32_t count_off) {
+    decode_mma_args a;
+    a.q = q; a.k = k; a.v = v; a.q_norm = qn; a.k_norm = kn; a.inv_freq = inv_freq;
+    a.kc = (__half *)kc; a.vc = (__half *)vc;
+    a.out = out; a.scratch = scratch; a.pos = pos; a.status = status;
+    a.kv_heads = kv_heads; a.cap = cap; a.window = window;
+    a.count_off = count_off;
+    a.eps = eps;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    a.sq = sq; a.sk = a.sv = skv; a.so = so; a.scache = scache; a.sscratch = sscratch;
+    // Keys per CTA: enough CTAs to fill the machine a few times over, as few splits as that allows.
+    const uint32_t n_tiles = (cap + kBKV - 1) / kBKV;
+    uint32_t tiles = 8;
+    while (tiles > 1 && (uint64_t)n_seq * kv_heads * ((n_tiles + tiles - 1) / tiles) < 4ull * (uint64_t)ctx->sm_count) tiles >>= 1;
+    a.tiles = tiles;
+    (void)hd;
+    switch (heads / kv_heads) {
+        case 1: return launch_decode_mma<1, 128>(ctx, a, n_seq);
+        case 2: return launch_decode_mma<2, 128>(ctx, a, n_seq);
+        default: return launch_decode_mma<4, 128>(ctx, a, n_seq);
+    }
+}
 
 extern "C" {
 

@@ -180,6 +180,15 @@ inline cudaError_t tm_launch_pdl(tm_cuda_ctx *ctx, void (*kernel)(KArgs...), dim
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Tensor-core decode attention for several sequences in one launch (tm_cuda_attn_mma.cu).
+bool tm_attention_decode_mma_ok(uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t n_rot);
+cudaError_t tm_attention_decode_mma_launch(tm_cuda_ctx *ctx, const float *q, const float *k, const float *v,
+                                           const float *qn, const float *kn, const float *inv_freq, void *kc, void *vc,
+                                           float *out, float *scratch, const uint32_t *pos, uint32_t *status,
+                                           uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t cap, uint32_t window,
+                                           float eps, float scale, uint32_t n_seq, size_t sq, size_t skv, size_t so,
+                                           size_t scache, size_t sscratch, uint32_t count_off);
+
 cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi);
 
 // ---- persistent decode program (tm_cuda_step.cu) ----

@@ -1508,6 +1508,17 @@ int tm_cuda_attention_decode_batch_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *q, tm_c
     st.cache = plane / 2;
     st.scratch = per_seq / 4;
     TM_OP_BEGIN("attention_decode_batch");
+    // Several sequences, tolerance mode: the throughput form on the tensor cores (a step of many
+    // sequences is bound by the K/V bytes it reads).  TM_CUDA_DECODE_MMA=0 keeps the latency form.
+    static const bool mma_off = [] { const char *e = getenv("TM_CUDA_DECODE_MMA"); return e && e[0] == '0'; }();
+    if (!exact && n_seq > 1 && !mma_off && tm_attention_decode_mma_ok(heads, kv_heads, head_dim, n_rot)) {
+        const size_t nsplit64 = (cap + kFastSplit - 1) / kFastSplit;
+        const uint32_t count_off = (uint32_t)((size_t)kv_heads * nsplit64 * (heads / kv_heads) * (head_dim + 2));
+        TM_CUDA_TRY(tm_attention_decode_mma_launch(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, heads, kv_heads,
+                                                   head_dim, cap, window, eps, scale, n_seq, st.q, st.k, st.out, st.cache,
+                                                   st.scratch, count_off));
+        TM_OP_END(1);
+    }
     if (!exact && attn_fast_ok(heads, kv_heads, head_dim, n_rot)) {
 #define TM_FAST(G, HD)                                                                                       \
     launch_decode_fast<G, HD>(ctx, qp, kp, vp, qn, kn, fq, kcp, vcp, op, sp, pp, stp, kv_heads, n_rot, cap, window, \

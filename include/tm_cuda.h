@@ -596,6 +596,14 @@ int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, 
                                tm_cuda_buffer *partial, tm_cuda_buffer *pairs, tm_cuda_buffer *out, uint32_t base,
                                tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
                                tm_cuda_buffer *mirror, char *err, size_t err_cap);
+/* The same for n_rows rows in one exchange (a decode step of several sequences on a split model):
+ * row r of the local [n_rows][n] logits slice; its winner over all ranks goes to
+ * out[r * out_stride + base + pos_buf[r]] when that slot is below out_cap <= out_stride.
+ * `partial` holds n_rows * 512 bytes, `pairs` (world + 1) * n_rows * 8. */
+int tm_cuda_argmax_rows_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n_rows, uint32_t n,
+                                    uint32_t index_offset, tm_cuda_buffer *partial, tm_cuda_buffer *pairs,
+                                    tm_cuda_buffer *out, uint32_t out_stride, uint32_t base, tm_cuda_buffer *pos_buf,
+                                    uint32_t out_cap, tm_cuda_buffer *mirror, char *err, size_t err_cap);
 
 #ifdef __cplusplus
 }

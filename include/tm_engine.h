@@ -112,7 +112,7 @@ int tm_engine_prefill_seq(tm_engine *e, uint32_t seq, const uint32_t *tokens, ui
 int tm_engine_prefill_token_of(tm_engine *e, uint32_t seq, uint32_t *token, char *err, size_t err_cap);
 /* One decode step of every sequence: tokens[s] goes to sequence s at its position; `logits` (NULL or
  * sequences * vocab floats) receives every row.  Row s equals the one-sequence step on the same state
- * bit for bit in `exact` mode, and for up to 8 sequences in any mode. */
+ * bit for bit in `exact` mode; otherwise within the bars of the tolerance-qualified kernels. */
 int tm_engine_step_batch(tm_engine *e, const uint32_t *tokens, float *logits, char *err, size_t err_cap);
 /* `steps` device-greedy steps of all sequences with no host read in between (kernel-only timing). */
 int tm_engine_decode_steps_batch(tm_engine *e, uint32_t steps, char *err, size_t err_cap);

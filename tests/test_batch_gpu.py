@@ -1,8 +1,8 @@
 """Decode steps of several sequences at once (no counterpart in the reference, which serves one
 request at a time: crates/supervisor/src/queue.rs:1-4).  The bar: a sequence decoded in a batch is
-the sequence decoded alone -- bit for bit wherever the same kernels run (`exact` mode, and up to 8
-sequences in any mode), within the tolerance-qualified kernels' bars otherwise -- so every parity
-statement about the one-sequence engine carries over."""
+the sequence decoded alone -- bit for bit wherever the same kernels run (`exact` mode; small batches
+of models whose attention has no tensor-core form), within the tolerance-qualified kernels' bars
+otherwise -- so every parity statement about the one-sequence engine carries over."""
 import numpy as np
 import pytest
 

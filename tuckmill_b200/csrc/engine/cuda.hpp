@@ -366,6 +366,14 @@ public:
                 pos ? pos->raw() : nullptr, pos_index, out_cap, mirror ? mirror->raw() : nullptr);
     }
 
+    void argmax_rows_sharded(const CudaBuffer &x, uint32_t n_rows, uint32_t n, uint32_t index_offset,
+                             const CudaBuffer &partial, const CudaBuffer &pairs, const CudaBuffer &out,
+                             uint32_t out_stride, uint32_t base, const CudaBuffer &pos, uint32_t out_cap,
+                             const CudaBuffer *mirror) const {
+        TM_CALL(tm_cuda_argmax_rows_sharded_dev, x.raw(), n_rows, n, index_offset, partial.raw(), pairs.raw(), out.raw(),
+                out_stride, base, pos.raw(), out_cap, mirror ? mirror->raw() : nullptr);
+    }
+
     // ---- grouping / measurement (crates/tuckcore/src/qwen35_gpu.rs:62-86) ----
     void begin_group() const {
         char e[256] = "";

@@ -744,7 +744,6 @@ struct EngineModel::Impl {
     size_t seqs = 1, log_stride = 0;
     CudaGraph batch_graph;
     std::vector<size_t> pos_b;  // host copy of every sequence's position
-    std::vector<CudaBuffer> logits_row, tokens_row, mirror_row;  // row split: per-sequence views for the sharded argmax
     const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
     uint32_t head_cols() const { return embedding.cols; }
     uint32_t head_type() const { return tied ? embedding.type : head_own.type; }
@@ -848,7 +847,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     p.scratch_bytes(16);                      // status word
     if (sh.world > 1) {
         p.scratch_f32(graph.vocab);           // gathered logits (only when a caller asks for them)
-        p.scratch_bytes((sh.world + 1) * 8);  // (value, index) pairs of the sharded argmax
+        p.scratch_bytes((sh.world + 1) * 8 * seqs);  // (value, index) pairs of the sharded argmax, per sequence
     }
     const size_t n = chunk_rows(opts, capacity);
     PrefillScratch::plan(graph, capacity, n, sh, p);
@@ -909,7 +908,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     I.logits = zeros_f32(c, (size_t)I.head_rows * I.seqs);
     if (sh.world > 1) {
         I.logits_full = zeros_f32(c, graph.vocab);
-        I.pairs = c.zeros((sh.world + 1) * 8);
+        I.pairs = c.zeros((sh.world + 1) * 8 * I.seqs);
     }
     I.partial = c.zeros(kArgmaxPartialBytes * I.seqs);
     I.tokens = c.zeros(I.log_stride * I.seqs * 4);
@@ -918,15 +917,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     I.status = c.zeros(16, true);
     I.scratch = PrefillScratch::alloc(c, graph, capacity, chunk_rows(opts, capacity), sh);
     if (!opts.exact) c.mma_workspace_reserve(PrefillScratch::mma_workspace(graph, chunk_rows(opts, capacity)));
-    if (I.seqs > 1 && sh.world > 1) {
-        if (((size_t)I.head_rows * 4) % 16 != 0)
-            throw TuckmillError(ErrorCode::InvalidRequest, "head rows per rank are not a 16-byte multiple");
-        for (size_t i = 0; i < I.seqs; ++i) {
-            I.logits_row.push_back(I.logits.view(i * I.head_rows * 4, (size_t)I.head_rows * 4));
-            I.tokens_row.push_back(I.tokens.view(i * I.log_stride * 4, I.log_stride * 4));
-            I.mirror_row.push_back(I.tokens_mirror.view(i * I.log_stride * 4, I.log_stride * 4));
-        }
-    }
+
     m->graph_ = std::move(graph);
     const ModelGraph &g = m->graph_;
 
@@ -1011,7 +1002,11 @@ void EngineModel::encode_batch_step() {
         throw TuckmillError(ErrorCode::UnsupportedQuantization, "several sequences need a Q8_0 embedding table");
     c.rows_indirect_seq(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, stride, I.pos_buf, (uint32_t)S, 0,
                         g.embedding_scale, I.scratch.x);
-    bool slices = S <= TM_CUDA_GEMM_MAX_BATCH && (opts_.exact || S <= 8) && I.head_type() == 8;
+    // The batched fused GEMV (rows bit-identical to the one-sequence step) serves `exact` mode and the
+    // small cases; from three sequences on a wide model, and from nine on any, the tensor-core GEMM
+    // streams the weights once for all rows and wins (measured on the 0.6B and 8B shapes).
+    const size_t slice_limit = g.hidden >= 2048 ? 2 : 8;
+    bool slices = S <= TM_CUDA_GEMM_MAX_BATCH && (opts_.exact || S <= slice_limit) && I.head_type() == 8;
     for (const Layer &L : I.layers) slices = slices && L.slices_apply();
     RowsAre rows;
     rows.pos_buf = &I.pos_buf;
@@ -1029,9 +1024,8 @@ void EngineModel::encode_batch_step() {
                      I.head_type());
     }
     if (I.sh.world > 1) {
-        for (size_t s = 0; s < S; ++s)
-            c.argmax_sharded(I.logits_row[s], I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens_row[s], 1,
-                             &I.pos_buf, (uint32_t)s, cap1, &I.mirror_row[s]);
+        c.argmax_rows_sharded(I.logits, (uint32_t)S, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens,
+                              stride, 1, I.pos_buf, cap1, &I.tokens_mirror);
     } else {
         c.argmax_rows_dev(I.logits, (uint32_t)S, (uint32_t)g.vocab, I.partial, I.tokens, stride, 1, I.pos_buf, cap1,
                           &I.tokens_mirror);

@@ -120,7 +120,7 @@ public:
     uint32_t prefill_token_of(size_t seq);
     // One decode step of EVERY sequence: tokens[s] is fed to sequence s at its position.  Every
     // sequence must have room.  Row s of the result equals the one-sequence step on the same state
-    // bit for bit in `exact` mode (and for up to 8 sequences in any mode).
+    // bit for bit in `exact` mode; otherwise within the bars of the tolerance-qualified kernels.
     void step_batch(const uint32_t *tokens);
     void logits_batch(float *out);  // [sequences][vocab]; single device only
     // Device-greedy steps of all sequences with no host read in between (kernel-only timing).

@@ -124,6 +124,53 @@ __global__ void argmax_pair_kernel(const float *pv, const uint32_t *pi, float *p
 }
 
 
+// The two kernels above for n_rows rows: thread r handles row r.
+__global__ void argmax_pair_rows_kernel(const float *pv, const uint32_t *pi, float *pair, uint32_t index_offset,
+                                        uint32_t n_rows) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    float bv = 0.0f;
+    uint32_t bi = kNone;
+    for (int g = 0; g < 64; ++g) {
+        const uint32_t i = pi[r * 64u + g];
+        const float v = pv[r * 64u + g];
+        if (i == kNone) continue;
+        if (bi == kNone || v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    pair[2 * r] = bv;
+    pair[2 * r + 1] = __uint_as_float(bi == kNone ? kNone : bi + index_offset);
+}
+// pairs: [world][n_rows] (value, index); row r's winner goes to out[r * out_stride + base + pos[r]].
+__global__ void argmax_pairs_final_rows_kernel(const float *pairs, uint32_t world, uint32_t n_rows, uint32_t *out,
+                                               uint32_t out_stride, uint32_t base, const uint32_t *pos,
+                                               uint32_t out_cap, uint32_t *mirror) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    float bv = 0.0f;
+    uint32_t bi = kNone;
+    for (uint32_t w = 0; w < world; ++w) {
+        const float v = pairs[2 * ((size_t)w * n_rows + r)];
+        const uint32_t i = __float_as_uint(pairs[2 * ((size_t)w * n_rows + r) + 1]);
+        if (i == kNone) continue;
+        if (bi == kNone || v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    const uint32_t slot = base + pos[r];
+    if (slot < out_cap) {
+        out[(size_t)r * out_stride + slot] = bi;
+        if (mirror) mirror[(size_t)r * out_stride + slot] = bi;
+    }
+}
+
 // ---- exchange through peer memory --------------------------------------------
 // A symmetric buffer is the same allocation on every rank, each mapped into every
 // other rank's address space (CUDA IPC).  An all-gather is then a PUSH: the producer
@@ -306,6 +353,38 @@ int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, 
     TM_OP_END(4);
 }
 
+int tm_cuda_argmax_rows_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n_rows, uint32_t n,
+                                    uint32_t index_offset, tm_cuda_buffer *partial, tm_cuda_buffer *pairs,
+                                    tm_cuda_buffer *out, uint32_t out_stride, uint32_t base, tm_cuda_buffer *pos_buf,
+                                    uint32_t out_cap, tm_cuda_buffer *mirror, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (n == 0 || n_rows == 0 || n_rows > 65535u)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "argmax over %u rows of %u elements", n_rows, n);
+    if (out_cap == 0 || out_cap > out_stride)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "token log of %u slots in rows of %u", out_cap, out_stride);
+    comm_state *c = (comm_state *)ctx->comm;
+    nccl_api *nc = nccl();
+    if (!c || !nc) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the context has no communicator");
+    TM_CHECK_BUF(x, (size_t)n_rows * n * 4, "logits");
+    TM_CHECK_BUF(partial, (size_t)n_rows * 512, "argmax partials");
+    TM_CHECK_BUF(pairs, (size_t)(c->world + 1) * n_rows * 8, "argmax pairs");
+    TM_CHECK_BUF(out, ((size_t)(n_rows - 1) * out_stride + out_cap) * 4, "token logs");
+    if (mirror) TM_CHECK_BUF(mirror, ((size_t)(n_rows - 1) * out_stride + out_cap) * 4, "token log mirrors");
+    TM_CHECK_BUF(pos_buf, (size_t)n_rows * 4, "positions");
+    TM_OP_BEGIN("argmax_rows_sharded");
+    float *pv = (float *)partial->dev;
+    uint32_t *pi = (uint32_t *)(partial->dev + (size_t)n_rows * 256);
+    float *mine = (float *)pairs->dev + 2 * (size_t)c->world * n_rows;  // own pairs after the gathered block
+    TM_CUDA_TRY(tm_argmax_rows_partial_launch(ctx, (const float *)x->dev, n_rows, n, pv, pi));
+    TM_CUDA_TRY(tm_launch_pdl(ctx, argmax_pair_rows_kernel, dim3((n_rows + 63) / 64), dim3(64), 0, (const float *)pv,
+                              (const uint32_t *)pi, mine, index_offset, n_rows));
+    const ncclResult_t r = nc->AllGather(mine, pairs->dev, 2 * (size_t)n_rows, ncclFloat32, c->comm, ctx->stream);
+    if (r != 0) return tm_fail(err, err_cap, TM_CUDA_ERR_INTERNAL, "ncclAllGather failed");
+    argmax_pairs_final_rows_kernel<<<(n_rows + 63) / 64, 64, 0, ctx->stream>>>(
+        (const float *)pairs->dev, (uint32_t)c->world, n_rows, (uint32_t *)out->dev, out_stride, base,
+        (const uint32_t *)pos_buf->dev, out_cap, mirror ? (uint32_t *)mirror->dev : nullptr);
+    TM_OP_END(4);
+}
 
 void tm_cuda_symm_release(tm_cuda_buffer *b) {
     if (!b || !b->symm) return;

@@ -190,6 +190,8 @@ cudaError_t tm_attention_decode_mma_launch(tm_cuda_ctx *ctx, const float *q, con
                                            size_t scache, size_t sscratch, uint32_t count_off);
 
 cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi);
+cudaError_t tm_argmax_rows_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n_rows, uint32_t n, float *pv,
+                                          uint32_t *pi);
 
 // ---- persistent decode program (tm_cuda_step.cu) ----
 // While ctx->program is set, the operators a program can hold record themselves through these

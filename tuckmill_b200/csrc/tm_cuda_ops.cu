@@ -1046,6 +1046,11 @@ inline bool attn_shape_ok(uint32_t hd) { return hd % 32 == 0 && (hd / 32 <= 4 ||
 
 // Pass 1 of the greedy argmax alone (64 partial (value, index) pairs), for callers
 // that finish the reduction themselves (the row-sharded head).
+// The same for n_rows rows of n values: row r's 64 pairs at pv / pi + 64 r.
+cudaError_t tm_argmax_rows_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n_rows, uint32_t n, float *pv,
+                                          uint32_t *pi) {
+    return tm_launch_pdl(ctx, argmax_rows_partial_kernel, dim3(kArgmaxGroups, n_rows), dim3(kThreads), 0, x, pv, pi, n);
+}
 cudaError_t tm_argmax_partial_launch(tm_cuda_ctx *ctx, const float *x, uint32_t n, float *pv, uint32_t *pi) {
     return tm_launch_pdl(ctx, argmax_partial_kernel, dim3(kArgmaxGroups), dim3(kThreads), 0, x, pv, pi, n);
 }

@@ -487,6 +487,14 @@ cudaError_t gemv_part(tm_cuda_ctx *ctx, gemv_args a, int m) {
     const uint32_t tiles_per_cta = kWarps / ks;
     uint32_t ctas = (n_tiles + tiles_per_cta - 1u) / tiles_per_cta;
     if (ctas > 1u << 20) ctas = 1u << 20;  // the kernel strides over any remainder
+    if (m > 1) {
+        // Several tokens: staging them (norm, digit split) costs a CTA far more than streaming one row
+        // tile's weights, so the grid is one resident wave and every warp walks its share of the tiles
+        // with the activations staged once.  (Which CTA multiplies a tile does not change its sums.)
+        const size_t fit = (size_t)ctx->smem_optin / (smem + 1024u);
+        const uint32_t wave = (uint32_t)ctx->sm_count * (uint32_t)(fit >= 2u ? 2u : 1u);
+        if (ctas > wave) ctas = wave;
+    }
     switch (m) {
         case 8: return launch_gemv<8, 2, 2>(ctx, a, (int)ctas, smem);
         case 4: return launch_gemv<4, 2, 2>(ctx, a, (int)ctas, smem);

@@ -436,9 +436,9 @@ def run_cuda(args):
     e2e = world * gen / (span_ms / 1e3)
 
     eng.close()
-    # several sequences at once, on this GPU alone (every rank its own under torchrun; rank 0's is printed)
+    # several sequences at once on one GPU (single-process runs; under torchrun the row-split leg carries its own)
     batched = batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decode_n,
-                          args.sequences) if args.sequences > 1 else None
+                          args.sequences) if args.sequences > 1 and world == 1 else None
     split = row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n,
                           tokens) if world > 1 else None
     eng = E.Engine(path, context=context, device=local, prefill_batch=prefill_batch) if rank == 0 else None

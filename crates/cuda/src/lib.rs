@@ -111,6 +111,7 @@ mod ffi {
         pub fn tm_cuda_mma_workspace_reserve(ctx: *mut TmCudaCtx, bytes: usize, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_mma_aborted(ctx: *mut TmCudaCtx) -> c_int;
         pub fn tm_cuda_mma_last_tile(ctx: *mut TmCudaCtx) -> c_int;
+        pub fn tm_cuda_mma_last_split(ctx: *mut TmCudaCtx) -> c_int;
         pub fn tm_cuda_q8_0_row_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, out: *mut TmCudaBuffer, row: u32, cols: u32, out_off: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_f16_gemv(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_f16_gemm(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, batch: u32, x_off: u32, y_off: u32, err: *mut c_char, err_cap: usize) -> c_int;

@@ -185,6 +185,12 @@ int tm_cuda_mma_aborted(tm_cuda_ctx *ctx);
  * launch used, as its token sub-tile width (64, 128 or 192; 0 before the first launch).
  * The launcher picks it from the shape; tests use this to prove each one is covered. */
 int tm_cuda_mma_last_tile(tm_cuda_ctx *ctx);
+/* No counterpart: how many parts the last GEMM launch cut the K range of every output tile into
+ * (1: none; 0 before the first launch).  A call with fewer output tiles than half the SMs (a batch of
+ * decode rows, a narrow projection) is split so that the whole machine streams its weights; the
+ * parts' sums are added in part order by whichever part finishes last, so the result does not depend
+ * on timing. */
+int tm_cuda_mma_last_split(tm_cuda_ctx *ctx);
 /* tm_metal.h:138 tm_metal_q8_0_row_f32: dequantise one row to out[out_off..]. */
 int tm_cuda_q8_0_row_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *out, uint32_t row,
                          uint32_t cols, uint32_t out_off, char *err, size_t err_cap);

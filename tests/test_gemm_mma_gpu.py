@@ -74,6 +74,43 @@ def test_mma_gemm_large_shapes_every_instantiation(ctx, oracle, rows, cols, batc
         b.free()
 
 
+# Few output tiles (decode batches, narrow projections): the K range is cut into parts whose sums meet
+# in a workspace and are added in part order.  (rows, cols, batch, expected parts)
+SPLIT_CASES = [(4096, 12288, 32, 4), (6144, 4096, 32, 2), (1024, 3072, 64, 8), (1024, 2048, 17, 8),
+               (4096, 1024, 32, 4), (2048, 4096, 300, 2), (12288, 4096, 32, 1)]
+
+
+@pytest.mark.parametrize("rows,cols,batch,parts", SPLIT_CASES)
+def test_mma_gemm_split_k_is_deterministic_and_within_the_profile(ctx, oracle, rows, cols, batch, parts):
+    raw = T.q8_0_matrix(5, rows + cols, rows, cols)
+    X = T.activations(5, 7, batch * cols).reshape(batch, cols)
+    w = ctx.q8_0_matrix(raw, rows, cols)
+    xb, yb = ctx.floats(X), ctx.buffer(batch * rows * 4)
+    runs = []
+    for _ in range(3):
+        yb.zero()
+        ctx.q8_0_gemm_mma(w, xb, yb, rows, cols, batch)
+        runs.append(yb.download(0, batch * rows * 4, np.float32).reshape(batch, rows).copy())
+    assert not ctx.mma_aborted()
+    assert ctx.mma_last_split() == parts
+    np.testing.assert_array_equal(runs[1], runs[0])
+    np.testing.assert_array_equal(runs[2], runs[0])
+    for r0 in sorted({0, rows // 2 - 64, rows - 256}):
+        sub = np.ascontiguousarray(raw[r0:r0 + 256])
+        got = runs[0][:, r0:r0 + 256]
+        assert rel_err(got, f16_profile_reference(sub, X)) <= 2e-5, f"rows {r0}..{r0 + 256}"
+        assert float(np.max(np.abs(got - oracle.matmul_q8_0(sub, 256, cols, X)))) <= 2e-2
+    # the residual-adding epilogue runs after the parts are summed
+    base = T.activations(5, 9, batch * rows).reshape(batch, rows)
+    acc = ctx.floats(base)
+    ctx.q8_0_gemm_mma_fused(w, xb, rows, cols, batch, [acc], [rows], cuda.PRO_NONE, None, 0.0, cuda.EPI_ADD)
+    got = acc.download(0, batch * rows * 4, np.float32).reshape(batch, rows)
+    assert ctx.mma_last_split() == parts
+    np.testing.assert_array_equal(got, base + runs[0])
+    for b in (w, xb, yb, acc):
+        b.free()
+
+
 def test_mma_gemm_row_view_and_larger_scales(ctx, oracle):
     """A projection stored inside a fused matrix (row view), scales up to ~1."""
     rows, cols, batch = 384, 512, 200

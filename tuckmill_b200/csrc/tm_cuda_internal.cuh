@@ -83,6 +83,7 @@ struct tm_cuda_ctx {
     unsigned char *mma_scratch = nullptr;
     size_t mma_scratch_bytes = 0;
     int mma_last_bn = 0;                 // token sub-tile width of the last tensor-core GEMM launch
+    int mma_last_ksplit = 0;             // K parts per output tile of that launch
     void *comm = nullptr;  // multi-GPU communicator state (tm_cuda_comm.cu)
     void *program = nullptr;  // the persistent program being recorded (tm_step_program), if any
 };

@@ -48,6 +48,15 @@ constexpr int kWarpRaw = kConvWarps + kEpiWarps, kWarpTok = kWarpRaw + 1, kWarpM
 constexpr int kMmaThreads = (kWarpMma + kIssuers) * 32;
 constexpr int kScaleAhead = 4;  // a converter's own steps (every other K step) between a scale's load and its use
 constexpr uint32_t kSpinLimit = 1u << 20;  // a healthy wait is microseconds; this is ~seconds
+// Split-K: when a call has fewer output tiles than half the SMs (a decode batch, a narrow projection)
+// the K range of every tile is cut into `ksplit` equal parts, each its own tile of the persistent grid;
+// the parts' accumulators meet in a workspace slot per (tile, part) and the warp that arrives last for a
+// (tile, row quarter) adds them IN PART ORDER and runs the epilogue -- no waiting, and a sum that does not
+// depend on which part finished last.
+constexpr uint32_t kSplitSlots = 148;                       // (output tile, part) slots of the workspace
+constexpr uint32_t kSplitSlotFloats = 128u * 256u;          // 128 rows x the 256 tokens of the widest split tile
+constexpr size_t kSplitCountBytes = 4096;                   // kSplitSlots x 4 row quarters of u32, rounded
+constexpr size_t kSplitBytes = (size_t)kSplitSlots * kSplitSlotFloats * 4 + kSplitCountBytes;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -147,6 +156,9 @@ struct mma_args {
     float *y[3];
     uint32_t part_end[3];  // exclusive row bound of each part (the last one is `rows`)
     uint32_t accumulate;   // 1: Y += W X (the residual add folded into the epilogue)
+    uint32_t ksplit;       // K parts per output tile (1: none)
+    float *kpart;          // [slot][token][128 rows] partial accumulators, slot = output tile * ksplit + part
+    uint32_t *kcount;      // [output tile][4 row quarters] arrivals (left at zero)
     // Row split: the epilogue stores this rank's rows straight into EVERY rank's gathered
     // Y[t][rank * rows + r] (peer memory, plain stores over NVLink), so the all-gather overlaps the
     // MMAs of later tiles; the last CTA ends the exchange (tm_symm_finish).  push_world = 0: off.
@@ -206,9 +218,11 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     volatile uint32_t *abort_s = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t nkb = (a.cols + kBK - 1) / kBK, nb = a.cols / 32u;
+    // A tile of the grid is (output tile, K part): tile / ksplit and tile % ksplit; nkb K steps each.
+    const uint32_t ksplit = a.ksplit;
+    const uint32_t nkb = (a.cols + kBK - 1) / kBK / ksplit, nb = a.cols / 32u;
     const uint32_t row_tiles = (a.rows + kBM - 1) / kBM, tok_tiles = (a.batch + kTB - 1) / kTB;
-    const uint32_t n_tiles = row_tiles * tok_tiles;
+    const uint32_t n_tiles = row_tiles * tok_tiles * ksplit;
     // Consecutive tiles share a token tile, so CTAs running side by side read the same X.
 
     if (tid == 0) {
@@ -255,8 +269,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         };
         auto scale_load = [&]() -> uint32_t {
             if (la_tile >= n_tiles) return 0u;
-            const uint32_t r = min((la_tile % row_tiles) * kBM + trow, a.rows - 1u);
-            const uint32_t blk = la_kb * 2u;
+            const uint32_t r = min(((la_tile / ksplit) % row_tiles) * kBM + trow, a.rows - 1u);
+            const uint32_t blk = ((la_tile % ksplit) * nkb + la_kb) * 2u;
             const unsigned short *p = (const unsigned short *)a.d + (size_t)r * nb + blk;
             if (pair_load) return __ldg((const uint32_t *)p);
             const uint32_t lo = __ldg(p), hi = blk + 1u < nb ? (uint32_t)__ldg(p + 1) : 0u;
@@ -329,25 +343,55 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+          const uint32_t ot = tile / ksplit, part = tile % ksplit;
+          // Split K, pass 0: the accumulators go to this part's workspace slot; pass 1 (only the warp that
+          // arrived last for this tile's row quarter): the parts are added in order and stored.
+          for (uint32_t pass = 0; pass < (ksplit > 1u ? 2u : 1u) && ok; ++pass) {
+          if (pass == 1u) {
+              __threadfence();
+              __syncwarp();
+              uint32_t last = 0u;
+              if (lane == 0) last = atomicAdd(a.kcount + ot * 4u + quarter, 1u) == ksplit - 1u ? 1u : 0u;
+              last = __shfl_sync(0xffffffffu, last, 0);
+              if (!last) break;
+              __threadfence();
+              if (lane == 0) a.kcount[ot * 4u + quarter] = 0u;  // ready for the next launch
+          }
           for (uint32_t sub = 0; sub < (uint32_t)kIssuers && ok; ++sub) {
-            const uint32_t tile_row0 = (tile % row_tiles) * kBM;
+            const uint32_t tile_row0 = (ot % row_tiles) * kBM;
             const uint32_t rr = tile_row0 + quarter * 32u + (uint32_t)lane;
-            const uint32_t tok0 = (tile / row_tiles) * kTB + sub * BN;
+            const uint32_t tok0 = (ot / row_tiles) * kTB + sub * BN;
             // (selects, not indexing: the arrays are kernel parameters)
             const bool p0 = tile_row0 < a.part_end[0], p1 = tile_row0 < a.part_end[1];
             const uint32_t part_row0 = p0 ? 0u : p1 ? a.part_end[0] : a.part_end[1];
             const uint32_t part_row1 = p0 ? a.part_end[0] : p1 ? a.part_end[1] : a.part_end[2];
             const size_t stride = part_row1 - part_row0;  // rows of this part = token stride of its output
             float *ybase = (p0 ? a.y[0] : p1 ? a.y[1] : a.y[2]) + (rr - part_row0);
-            if (ok) ok = mbar_wait(&acc_full[sub], it & 1u, abort_s);
-            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (pass == 0u) {
+                if (ok) ok = mbar_wait(&acc_full[sub], it & 1u, abort_s);
+                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 const uint32_t t0 = tok0 + (uint32_t)c0;
                 if (t0 >= a.batch) break;  // uniform: the rest of the sub-tile is past the batch
                 uint32_t v[32];
+                if (pass == 1u) {
+                    // this row's 32 tokens of every part, part 0 first
+                    const size_t at = ((size_t)(sub * BN + (uint32_t)c0)) * 128u + quarter * 32u + (uint32_t)lane;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                    for (uint32_t pp = 0; pp < ksplit; ++pp) {
+                        const float *src = a.kpart + (size_t)(ot * ksplit + pp) * kSplitSlotFloats + at;
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = __ldcg(src + (size_t)j * 128u);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(pp == 0u ? f[j] : __uint_as_float(v[j]) + f[j]);
+                    }
+                } else {
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + sub * BN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -361,7 +405,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (rr < a.rows) {
+                }
+                if (ksplit > 1u && pass == 0u) {
+                    float *dst = a.kpart + (size_t)(ot * ksplit + part) * kSplitSlotFloats +
+                                 ((size_t)(sub * BN + (uint32_t)c0)) * 128u + quarter * 32u + (uint32_t)lane;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) dst[(size_t)j * 128u] = __uint_as_float(v[j]);
+                } else if (rr < a.rows) {
                     // Lane = row: for a fixed token the warp writes 128 contiguous bytes; the addresses
                     // are independent (no add chain between the stores).
                     float *p = ybase + (size_t)t0 * stride;
@@ -396,10 +446,14 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
             }
           }
             if (!ok) break;
-            // The accumulator may be overwritten once every warp has its values in registers.
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty);
+            if (pass == 0u) {
+                // The accumulator may be overwritten once every warp has its values in registers.
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty);
+            }
+          }
+            if (!ok) break;
         }
         if (a.push_world) __threadfence_system();  // this thread's peer stores, before the CTA counts itself in
     } else if (warp == kWarpRaw) {
@@ -408,14 +462,15 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
             uint32_t g = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int row0 = (int)((tile % row_tiles) * kBM);
+                const int row0 = (int)(((tile / ksplit) % row_tiles) * kBM);
+                const uint32_t kb0 = (tile % ksplit) * nkb;
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
                     const uint32_t s = ring<kRawStages>::stage(g);
                     if (ring<kRawStages>::must_wait_empty(g))
                         ok = mbar_wait(&raw_empty[s], ring<kRawStages>::empty_parity(g), abort_s);
                     if (!ok) break;
                     mbar_expect_tx(&raw_full[s], L::kRawBytes);
-                    tma_load_2d(sRaw + s * L::kRawBytes, &wmap, (int)(kb * kBK), row0, &raw_full[s]);
+                    tma_load_2d(sRaw + s * L::kRawBytes, &wmap, (int)((kb0 + kb) * kBK), row0, &raw_full[s]);
                 }
             }
             // Giving up with copies still in flight: let them land before the CTA's memory goes away.
@@ -430,7 +485,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
             uint32_t g = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const uint32_t tok0 = (tile / row_tiles) * kTB;
+                const uint32_t tok0 = (tile / ksplit / row_tiles) * kTB;
+                const uint32_t kb0 = (tile % ksplit) * nkb;
                 // A sub-tile wholly past the batch is neither loaded nor multiplied.
                 const uint32_t subs = tok0 + BN < a.batch ? (uint32_t)kIssuers : 1u;
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
@@ -440,7 +496,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                     if (!ok) break;
                     mbar_expect_tx(&full[s], subs * L::kSubBytes);
                     for (uint32_t sub = 0; sub < subs; ++sub)
-                        tma_load_2d(sB + s * L::kBBytes + sub * L::kSubBytes, &xmap, (int)(kb * kBK),
+                        tma_load_2d(sB + s * L::kBBytes + sub * L::kSubBytes, &xmap, (int)((kb0 + kb) * kBK),
                                     (int)(tok0 + sub * BN), &full[s]);
                 }
             }
@@ -461,7 +517,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
             uint32_t it = 0, st = 0, par = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-                const bool live = (tile / row_tiles) * kTB + sub * BN < a.batch;  // else: the barrier protocol only
+                const bool live = (tile / ksplit / row_tiles) * kTB + sub * BN < a.batch;  // else: the barrier protocol only
                 if (it >= 1u) ok = mbar_wait(acc_empty, (it - 1u) & 1u, abort_s);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -615,7 +671,10 @@ int tm_cuda_mma_workspace_reserve(tm_cuda_ctx *ctx, size_t bytes, char *err, siz
     return TM_CUDA_OK;
 }
 
-size_t tm_cuda_mma_workspace_bytes(uint32_t cols, uint32_t batch) { return (size_t)cols * batch * 2; }
+// The f16 copy of X, then the split-K slots and counters.
+size_t tm_cuda_mma_workspace_bytes(uint32_t cols, uint32_t batch) {
+    return tm_round_up((size_t)cols * batch * 2, 256) + kSplitBytes;
+}
 
 // Grows the f16 workspace when the call needs more (outside a dispatch group only).
 static int mma_ensure_workspace(tm_cuda_ctx *ctx, uint32_t cols, uint32_t batch, char *err, size_t err_cap) {
@@ -692,6 +751,23 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
         a.part_end[p] = part_end[p];
     }
     a.accumulate = accumulate ? 1u : 0u;
+    // Split K when the output tiles leave more than half of the SMs idle (never for the pushing form).
+    a.ksplit = 1;
+    {
+        const uint32_t out_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn)), nkb = (cols + kBK - 1) / kBK;
+        const uint32_t room = sms < kSplitSlots ? sms : kSplitSlots;
+        static const bool off = [] { const char *e = getenv("TM_CUDA_MMA_SPLITK"); return e && e[0] == '0'; }();
+        if (!off && push.world == 0 && bn <= 128 && cols % kBK == 0 && out_tiles * 2 <= sms &&
+            ctx->mma_scratch_bytes >= kSplitBytes)
+            for (uint32_t cand : {8u, 6u, 4u, 3u, 2u})
+                if (nkb % cand == 0 && nkb / cand >= 4 && out_tiles * cand <= room) {
+                    a.ksplit = cand;
+                    break;
+                }
+    }
+    unsigned char *split_base = ctx->mma_scratch + ((ctx->mma_scratch_bytes >= kSplitBytes ? ctx->mma_scratch_bytes - kSplitBytes : 0) & ~(size_t)255);
+    a.kpart = (float *)split_base;
+    a.kcount = (uint32_t *)(split_base + (size_t)kSplitSlots * kSplitSlotFloats * 4);
     a.peer = push.peer;
     a.push_world = push.world;
     a.push_rank = push.rank;
@@ -702,7 +778,8 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
     a.batch = batch;
     a.abort_flag = abort_flag;
     ctx->mma_last_bn = bn;
-    const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn));
+    ctx->mma_last_ksplit = (int)a.ksplit;
+    const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn)) * a.ksplit;
     const int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
     TM_CUDA_TRY(bn == 192   ? launch_mma<192>(wmap, xmap, a, grid, ctx->device, ctx->stream)
                 : bn == 128 ? launch_mma<128>(wmap, xmap, a, grid, ctx->device, ctx->stream)
@@ -834,6 +911,13 @@ int tm_cuda_mma_last_tile(tm_cuda_ctx *ctx) {
     if (!ctx) return 0;
     std::lock_guard<std::mutex> lock(ctx->mu);
     return ctx->mma_last_bn;
+}
+
+// K parts per output tile of the last GEMM launch (1: no split).
+int tm_cuda_mma_last_split(tm_cuda_ctx *ctx) {
+    if (!ctx) return 0;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return ctx->mma_last_ksplit;
 }
 
 // 1 when a tensor-core GEMM on this context ever gave up a bounded wait.

@@ -147,6 +147,8 @@ def load_library() -> C.CDLL:
     L.tm_cuda_mma_aborted.argtypes = [_P]
     L.tm_cuda_mma_last_tile.restype = C.c_int
     L.tm_cuda_mma_last_tile.argtypes = [_P]
+    L.tm_cuda_mma_last_split.restype = C.c_int
+    L.tm_cuda_mma_last_split.argtypes = [_P]
     L.tm_cuda_program_bytes.restype = _SZ
     L.tm_cuda_program_bytes.argtypes = [_U32, C.c_uint64, C.c_uint64]
     L.tm_cuda_program_attention_elems.restype = C.c_uint64
@@ -387,6 +389,7 @@ class CudaContext:
     def mma_workspace_reserve(self, nbytes: int): self._call("mma_workspace_reserve", nbytes)
     def mma_aborted(self) -> bool: return bool(self._l.tm_cuda_mma_aborted(self.handle))
     def mma_last_tile(self) -> int: return int(self._l.tm_cuda_mma_last_tile(self.handle))
+    def mma_last_split(self) -> int: return int(self._l.tm_cuda_mma_last_split(self.handle))
 
     def q8_0_gemv_fused(self, w, x, y, rows, cols, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
         self._call("q8_0_gemv_fused", w.handle, x.handle, y.handle, rows, cols, prologue, self._h(pro), eps, epilogue)

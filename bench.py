@@ -319,7 +319,7 @@ def gemm_rooflines(device, torch):
         x = ctx.buffer(m * cols * 4)
         x.upload(0, T.activations(0, 96, m * cols))
         y = ctx.buffer(m * rows * 4)
-        ctx.mma_workspace_reserve(m * cols * 2)
+        ctx.mma_workspace_reserve(cuda.mma_workspace_bytes(cols, m))
         n = max(copies, 12)
         ctx.begin_group()
         for i in range(n):
@@ -708,7 +708,7 @@ def run_sweep(args):
             y = ctx.buffer(m * rows * 4) if world > 1 else y_loc
             stage = ctx.buffer(m * rows * 4) if world > 1 and m > 1 else y
             if m > 8:
-                ctx.mma_workspace_reserve(m * cols * 2)
+                ctx.mma_workspace_reserve(cuda.mma_workspace_bytes(cols, m))
             turn = [0]
 
             def multiply():

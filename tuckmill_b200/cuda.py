@@ -204,6 +204,12 @@ def decode_attention_static_max_scratch() -> int:
     return int(L.tm_cuda_attention_decode_static_max_scratch())
 
 
+def mma_workspace_bytes(cols: int, batch: int) -> int:
+    """Context workspace a tensor-core GEMM of `batch` tokens by `cols` columns needs (reserve it with
+    CudaContext.mma_workspace_reserve before opening a dispatch group that contains such a call)."""
+    return int(load_library().tm_cuda_mma_workspace_bytes(cols, batch))
+
+
 def packed_bytes(rows: int, cols: int) -> int:
     return int(load_library().tm_cuda_q8_0_packed_bytes(rows, cols))
 

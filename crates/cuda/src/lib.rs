@@ -129,6 +129,7 @@ mod ffi {
         pub fn tm_cuda_end_group_retain(ctx: *mut TmCudaCtx, out: *mut *mut TmCudaGraph, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_graph_launch(ctx: *mut TmCudaCtx, graph: *mut TmCudaGraph, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_graph_free(ctx: *mut TmCudaCtx, graph: *mut TmCudaGraph);
+        pub fn tm_cuda_prefetch_l2(ctx: *mut TmCudaCtx, bufs: *const *mut TmCudaBuffer, n: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_program_bytes(max_ops: u32, vector_elems: u64, attention_elems: u64) -> usize;
         pub fn tm_cuda_program_attention_elems(heads: u32, head_dim: u32, cap: u32) -> u64;
         pub fn tm_cuda_program_supports_gemv(cols: u32) -> c_int;

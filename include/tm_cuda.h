@@ -270,6 +270,14 @@ int tm_cuda_end_group_retain(tm_cuda_ctx *ctx, tm_cuda_graph **out, char *err, s
 int tm_cuda_graph_launch(tm_cuda_ctx *ctx, tm_cuda_graph *graph, char *err, size_t err_cap);
 void tm_cuda_graph_free(tm_cuda_ctx *ctx, tm_cuda_graph *graph);
 
+/* No counterpart: ask for the bytes of up to 64 buffers to be brought into the L2 cache, on a side
+ * stream that forks from the context's stream at this call and runs beside whatever is dispatched
+ * next; it joins the stream again when the open dispatch group ends (at once outside a group).  A
+ * decode step whose per-layer weights fit the cache calls it a layer or two ahead, so that a
+ * projection finds its weights in L2 instead of paying a DRAM round trip per launch.  A hint only:
+ * results never depend on it.  The first call of a context must be made outside a dispatch group. */
+int tm_cuda_prefetch_l2(tm_cuda_ctx *ctx, tm_cuda_buffer *const *bufs, uint32_t n, char *err, size_t err_cap);
+
 /* No counterpart: a decode step as ONE persistent kernel.  Between begin_program and
  * end_program the operators a step is made of do not launch; they are recorded, in
  * order, into a program: tm_cuda_q8_0_gemv / _gemv_fused (one token),

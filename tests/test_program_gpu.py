@@ -8,8 +8,10 @@ added in another order), the attention core to rounding of the split merge
 (same arithmetic, same split), the greedy choice exactly.  The engine's decode loop on the program must
 give the oracle's tokens, like the graph of kernels it replaces
 (crates/tuckcore/src/executor.rs:2204-2230).  The bounded waits are made to run
-out from the host (a barrier told to wait for one CTA more than exist) and must
-end in a status word, not a hang."""
+out from the host (consumers told to expect sequence numbers that no producer writes,
+with a short polling limit) and must end in a status word, not a hang."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -231,3 +233,30 @@ def test_engine_decodes_on_the_program_like_the_graph_and_the_oracle(ctx, oracle
             assert np.max(np.abs(out - want)) <= 2e-2 * max(1.0, float(np.max(np.abs(want))))
         eng.close()
     assert runs["program"][1] < runs["graph"][1]
+
+
+def test_engine_refuses_to_return_tokens_after_a_wait_ran_out(ctx, small_artifact):
+    """The engine reads the device status words before it hands tokens or logits to the caller: a decode
+    program whose consumers are made to wait for sequence numbers nobody writes (short polling limit,
+    set on the host) stops itself, and generate() / logits() answer with a typed Internal error
+    naming the wait instead of tokens."""
+    path, shape = small_artifact
+    eng = E.Engine(path, context=128, prefill_batch=32, persistent_step=True)
+    prog = eng.decode_program()
+    assert prog
+    good, _ = eng.generate(T.token_ids(3, 9, shape.vocab), 6)
+    assert len(good) == 6
+    L, err = cuda.load_library(), C.create_string_buffer(256)
+    assert L.tm_cuda_program_debug(C.c_void_p(eng.cuda_ctx()), C.c_void_p(prog), 5, 20000, err, 256) == 0
+    with pytest.raises(E.EngineError) as e:
+        eng.generate(T.token_ids(3, 9, shape.vocab), 6)
+    assert e.value.code == "INTERNAL" and "wait" in e.value.message
+    with pytest.raises(E.EngineError) as e:
+        eng.logits()
+    assert e.value.code == "INTERNAL"
+    eng.close()
+    # the context of another engine is unaffected
+    other = E.Engine(path, context=128, prefill_batch=32)
+    again, _ = other.generate(T.token_ids(3, 9, shape.vocab), 6)
+    np.testing.assert_array_equal(again, good)
+    other.close()

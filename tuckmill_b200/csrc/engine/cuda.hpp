@@ -374,6 +374,12 @@ public:
                 out_stride, base, pos.raw(), out_cap, mirror ? mirror->raw() : nullptr);
     }
 
+    void prefetch_l2(std::initializer_list<const CudaBuffer *> bufs) const {
+        std::vector<tm_cuda_buffer *> raw;
+        for (const CudaBuffer *b : bufs) raw.push_back(b->raw());
+        TM_CALL(tm_cuda_prefetch_l2, raw.data(), (uint32_t)raw.size());
+    }
+
     // ---- grouping / measurement (crates/tuckcore/src/qwen35_gpu.rs:62-86) ----
     void begin_group() const {
         char e[256] = "";

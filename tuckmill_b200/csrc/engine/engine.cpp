@@ -742,6 +742,7 @@ struct EngineModel::Impl {
     // Several sequences: positions pos_buf[s], token logs tokens[s * log_stride ..], logits [s][head_rows];
     // one recorded step advances all of them.
     size_t seqs = 1, log_stride = 0;
+    size_t l2_ahead = 0;  // layers whose weights the decode step asks into L2 ahead of use (0: off)
     CudaGraph batch_graph;
     std::vector<size_t> pos_b;  // host copy of every sequence's position
     const CudaBuffer &head_buf() const { return tied ? (sh.world > 1 ? tied_view : embedding.buf) : head_own.buf; }
@@ -927,6 +928,21 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // crates/tuckcore/src/qwen35_gpu.rs:66-86, engine/metal.rs:2381-2449.)  Where the
     // model allows it the step becomes one persistent kernel, else a graph of kernels.
     I.persistent = persistent_decode_applies(g, src, opts);
+    {
+        // Bytes of one layer's four matrices: two layers ahead when three of them are well inside the
+        // 126 MB L2, one ahead when two are, not at all for wider models (their projections stream
+        // long enough to be bandwidth-bound) or a split one.
+        uint64_t per_layer = 0;
+        if (!I.layers.empty())
+            for (const Matrix *mx : {&I.layers[0].mixer.qkv, &I.layers[0].mixer.o, &I.layers[0].ffn.gate_up,
+                                     &I.layers[0].ffn.down})
+                per_layer += Matrix::bytes_of(mx->type, mx->rows, mx->cols);
+        size_t ahead = per_layer == 0 ? 0 : per_layer <= (20u << 20) ? 2 : per_layer <= (40u << 20) ? 1 : 0;
+        if (const char *e = std::getenv("TM_ENGINE_L2_AHEAD")) ahead = (size_t)std::max(0, std::min(8, std::atoi(e)));
+        if (opts.shard_world > 1 || I.persistent) ahead = 0;
+        I.l2_ahead = ahead;
+        if (ahead) c.prefetch_l2({&I.final_norm});  // the context's side stream comes into being outside a group
+    }
     if (I.persistent) {
         const DecodeProgramSize ps = decode_program_size(g, capacity);
         c.begin_program(ps.max_ops, ps.vector_elems, ps.attention_elems);
@@ -978,7 +994,20 @@ void EngineModel::encode_decode_step() {
     else
         c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
                            g.embedding_scale, I.x);
-    for (const Layer &L : I.layers) L.decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+    // Layers whose weights fit the L2 cache several times over are asked for two layers ahead, on a
+    // side branch of the recorded graph: a projection of a small decoder streams 2-6 MB and is bound
+    // by the DRAM round trip, not by bandwidth, so its weights are made to wait in L2 instead.
+    const size_t ahead = I.l2_ahead;
+    auto prefetch = [&](size_t l) {
+        if (ahead == 0 || l >= I.layers.size()) return;
+        const Layer &P = I.layers[l];
+        c.prefetch_l2({&P.mixer.qkv.buf, &P.mixer.o.buf, &P.ffn.gate_up.buf, &P.ffn.down.buf});
+    };
+    for (size_t l = 0; l < ahead; ++l) prefetch(l);
+    for (size_t l = 0; l < I.layers.size(); ++l) {
+        prefetch(l + ahead);
+        I.layers[l].decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+    }
     I.project_head(c, g.eps);
     if (I.sh.world > 1)
         c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens, 1, &I.pos_buf, 0,

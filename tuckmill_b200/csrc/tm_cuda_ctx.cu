@@ -200,6 +200,12 @@ void tm_cuda_destroy(tm_cuda_ctx *ctx) {
         for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
         if (ctx->mma_scratch) cudaFree(ctx->mma_scratch);
     }
+    if (ctx->side) {
+        cudaStreamSynchronize(ctx->side);
+        cudaEventDestroy(ctx->side_fork);
+        cudaEventDestroy(ctx->side_join);
+        cudaStreamDestroy(ctx->side);
+    }
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -366,6 +372,43 @@ int tm_cuda_download_after(tm_cuda_ctx *ctx, tm_cuda_buffer *src, size_t off, vo
     return TM_CUDA_OK;
 }
 
+static void join_side(tm_cuda_ctx *ctx);
+
+__global__ void l2_prefetch_kernel(const char *p, size_t bytes) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x * 128u;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 128u; i < bytes; i += stride)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
+}
+
+int tm_cuda_prefetch_l2(tm_cuda_ctx *ctx, tm_cuda_buffer *const *bufs, uint32_t n, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (!bufs || n == 0 || n > 64) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "1 to 64 buffers, got %u", n);
+    for (uint32_t i = 0; i < n; ++i)
+        if (!bufs[i] || ctx->live.find(bufs[i]) == ctx->live.end())
+            return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "buffer %u does not belong to this context", i);
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator prefetch_l2 cannot be recorded into a persistent program");
+    if (!ctx->side) {
+        if (ctx->group_open)
+            return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the first prefetch of a context must come outside a dispatch group");
+        TM_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking));
+        TM_CUDA_TRY(cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
+        TM_CUDA_TRY(cudaEventCreateWithFlags(&ctx->side_join, cudaEventDisableTiming));
+    }
+    TM_CUDA_TRY(cudaEventRecord(ctx->side_fork, ctx->stream));
+    TM_CUDA_TRY(cudaStreamWaitEvent(ctx->side, ctx->side_fork, 0));
+    for (uint32_t i = 0; i < n; ++i)
+        l2_prefetch_kernel<<<8, 256, 0, ctx->side>>>((const char *)bufs[i]->dev, bufs[i]->len);
+    TM_CUDA_TRY(cudaGetLastError());
+    ctx->side_pending = true;
+    if (ctx->group_open) ctx->group_kernels += n;
+    else {
+        ctx->launches.fetch_add(n);
+        join_side(ctx);
+    }
+    return TM_CUDA_OK;
+}
+
 int tm_cuda_begin_group(tm_cuda_ctx *ctx, char *err, size_t err_cap) {
     TM_ENTER();
     if (ctx->group_open || ctx->program)
@@ -376,8 +419,16 @@ int tm_cuda_begin_group(tm_cuda_ctx *ctx, char *err, size_t err_cap) {
     return TM_CUDA_OK;
 }
 
+// The side stream's work rejoins the main stream (inside a capture: before the capture can end).
+static void join_side(tm_cuda_ctx *ctx) {
+    if (!ctx->side_pending) return;
+    ctx->side_pending = false;
+    if (cudaEventRecord(ctx->side_join, ctx->side) == cudaSuccess) cudaStreamWaitEvent(ctx->stream, ctx->side_join, 0);
+}
+
 static int end_capture(tm_cuda_ctx *ctx, cudaGraphExec_t *exec, char *err, size_t err_cap) {
     cudaGraph_t graph = nullptr;
+    join_side(ctx);
     ctx->group_open = false;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
     if (e != cudaSuccess || !graph) {

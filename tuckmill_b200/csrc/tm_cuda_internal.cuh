@@ -62,6 +62,11 @@ struct tm_cuda_ctx {
     int sm_count = 0;
     size_t smem_optin = 0;
     cudaStream_t stream = nullptr;
+    // Side stream of tm_cuda_prefetch_l2: forks from `stream` at the call and joins it again before a
+    // capture ends (or at once outside a group).
+    cudaStream_t side = nullptr;
+    cudaEvent_t side_fork = nullptr, side_join = nullptr;
+    bool side_pending = false;
     std::mutex mu;
     std::unordered_set<const tm_cuda_buffer *> live;
     std::unordered_set<const tm_cuda_graph *> graphs;

@@ -387,6 +387,20 @@ struct SwiGluBlock {
     // The tolerance-qualified batched form: norm and activation folded into the GEMMs' f16 copies,
     // gate|up as one launch, the residual add in the down projection's epilogue (5 launches -> 4).
     bool fusable() const { return sh.world == 1 && width % 128 == 0 && gate_up.type == 8 && down.type == 8; }
+    bool fusable_rows() const { return wl % 128 == 0 && gate_up.type == 8 && down.type == 8; }
+    // A rank's share of the tolerance-qualified batched form: norm folded into ONE gate|up launch over
+    // the rank's rows, activation, then the two exchanges (the down projection pushes as it multiplies).
+    void prefill_split_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
+                             size_t hidden) const {
+        const uint32_t nn = (uint32_t)n;
+        ctx.q8_0_gemm_mma_fused(gate_up.buf, s.x, gate_up.rows, gate_up.cols, nn, {&s.loc, &s.loc2},
+                                {(uint32_t)wl, (uint32_t)wl}, TM_CUDA_PRO_RMSNORM, &post_norm, eps, TM_CUDA_EPI_STORE);
+        act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
+        ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
+        ctx.q8_0_gemm_mma_push(down.buf, s.g, s.d2, down.rows, down.cols, nn);
+        if (out_norm) ctx.rmsnorm_add(s.d2, out_norm, s.x, nn, (uint32_t)hidden, eps);
+        else ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+    }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
                        size_t hidden) const {
         const uint32_t nn = (uint32_t)n;
@@ -559,10 +573,12 @@ struct AttentionBlock {
     }
     // The tolerance-qualified batched form: input norm folded into the f16 copy, q|k|v as one GEMM
     // launch, the four launches before attention as one, tensor-core attention (9 launches -> 4).
-    bool fusable() const {
-        return sh.world == 1 && qkv.type == 8 && o.type == 8 && qkv.part_rows.size() == 3 && qkv.part_rows[0] % 128 == 0 && qkv.part_rows[1] % 128 == 0 &&
-               tm_cuda_attention_chunk_mma_supported((uint32_t)spec.head_dim);
+    // (the q|k|v part of it applies to a rank's rows of a split model as well: fusable_rows)
+    bool fusable_rows() const {
+        return qkv.type == 8 && o.type == 8 && qkv.part_rows.size() == 3 && qkv.part_rows[0] % 128 == 0 &&
+               qkv.part_rows[1] % 128 == 0 && tm_cuda_attention_chunk_mma_supported((uint32_t)spec.head_dim);
     }
+    bool fusable() const { return sh.world == 1 && fusable_rows(); }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, uint32_t pos0,
                        const CudaBuffer &pre_norm, const RowsAre &rows) const {
         const uint32_t nn = (uint32_t)n, heads = (uint32_t)heads_l, kv = (uint32_t)kv_l, hd = (uint32_t)spec.head_dim;
@@ -707,6 +723,18 @@ struct Layer {
                                         TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_ADD);
             }
             ffn.prefill_fused(ctx, s, n, post_norm, hidden);
+            return;
+        }
+        if (!exact && mixer.sh.world > 1 && mixer.fusable_rows() && ffn.fusable_rows()) {
+            // Split model, tolerance mode: q|k|v and gate|up as one fused launch each over this rank's
+            // rows (4 GEMM calls per layer instead of 7), attention on the rank's heads, then the exchanges.
+            const uint32_t hl = (uint32_t)(mixer.heads_l * mixer.spec.head_dim);
+            mixer.prefill_fused(ctx, s, n, pos0, pre_norm, rows);
+            ctx.push_rows(s.e, s.efull, nn, hl);
+            ctx.q8_0_gemm_mma_push(mixer.o.buf, s.efull, s.proj, mixer.o.rows, mixer.o.cols, nn);
+            if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
+            else ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+            ffn.prefill_split_fused(ctx, s, n, post_norm, hidden);
             return;
         }
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
@@ -929,15 +957,17 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // model allows it the step becomes one persistent kernel, else a graph of kernels.
     I.persistent = persistent_decode_applies(g, src, opts);
     {
-        // Bytes of one layer's four matrices: two layers ahead when three of them are well inside the
-        // 126 MB L2, one ahead when two are, not at all for wider models (their projections stream
-        // long enough to be bandwidth-bound) or a split one.
+        // Bytes of one layer's four matrices.  Measured on this part: a decoder whose projections are
+        // 2-6 MB (17 MB per layer) gains nothing -- its launches are bound by the dependency chain, not by
+        // the DRAM round trip, and the side branch costs a microsecond per layer (827 -> 857 us per token) --
+        // while 20-40 MB layers (the 1B-class shape, 7-15 MB projections) gain 2 % with one layer ahead;
+        // wider models stream long enough per launch to be bandwidth-bound and do not fit anyway.
         uint64_t per_layer = 0;
         if (!I.layers.empty())
             for (const Matrix *mx : {&I.layers[0].mixer.qkv, &I.layers[0].mixer.o, &I.layers[0].ffn.gate_up,
                                      &I.layers[0].ffn.down})
                 per_layer += Matrix::bytes_of(mx->type, mx->rows, mx->cols);
-        size_t ahead = per_layer == 0 ? 0 : per_layer <= (20u << 20) ? 2 : per_layer <= (40u << 20) ? 1 : 0;
+        size_t ahead = per_layer > (20u << 20) && per_layer <= (40u << 20) ? 1 : 0;
         if (const char *e = std::getenv("TM_ENGINE_L2_AHEAD")) ahead = (size_t)std::max(0, std::min(8, std::atoi(e)));
         if (opts.shard_world > 1 || I.persistent) ahead = 0;
         I.l2_ahead = ahead;
@@ -994,9 +1024,8 @@ void EngineModel::encode_decode_step() {
     else
         c.row_indirect_dev(I.embedding.buf, I.embedding.rows, I.embedding.cols, I.tokens, 0, I.pos_buf, 0, 0,
                            g.embedding_scale, I.x);
-    // Layers whose weights fit the L2 cache several times over are asked for two layers ahead, on a
-    // side branch of the recorded graph: a projection of a small decoder streams 2-6 MB and is bound
-    // by the DRAM round trip, not by bandwidth, so its weights are made to wait in L2 instead.
+    // Where it pays (see load_with), the weights of the layer(s) ahead are asked into L2 on a side
+    // branch of the recorded graph.
     const size_t ahead = I.l2_ahead;
     auto prefetch = [&](size_t l) {
         if (ahead == 0 || l >= I.layers.size()) return;

@@ -250,6 +250,11 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // Programmatic dependent launch: the weight pipeline (TMA of the raw tiles, converters) reads
+    // nothing a predecessor writes and starts at once, overlapping the predecessor's tail -- the f16
+    // copy of X that precedes every call; the two roles that touch a predecessor's data, the token
+    // TMA thread (X) and the epilogue warps (Y), wait for it first.  The successor is let go only
+    // by those roles after their wait, so at most this kernel's direct predecessor can still be running.
     if (warp < kConvWarps) {
         // ---------------- converters ----------------
         // Warps q and q + 4 reach tensor-memory lanes 32q..32q+31; set 0 (warps 0-3) converts the even K
@@ -302,39 +307,48 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                 const uint32_t dd = ring_d[u];
                 const __half2 d_lo = __half2half2(__ushort_as_half((unsigned short)(dd & 0xffffu)));
                 const __half2 d_hi = __half2half2(__ushort_as_half((unsigned short)(dd >> 16)));
-                uint32_t v[32];
+                // The four 16-byte pieces of this row (k 16c..16c+15) come out of shared memory at once; the
+                // raw stage then goes back to the TMA thread, not after the stores below have completed.
+                int4 w4[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {  // piece c = k 16c..16c+15 of this K step
-                    const int4 w = *(const int4 *)(raw + ((c ^ rsw) << 4));
-                    const __half2 d2 = c < 2 ? d_lo : d_hi;
-                    dequant8((uint32_t)w.x, (uint32_t)w.y, d2, v + 8 * c);
-                    dequant8((uint32_t)w.z, (uint32_t)w.w, d2, v + 8 * c + 4);
-                }
+                for (uint32_t c = 0; c < 4; ++c) w4[c] = *(const int4 *)(raw + ((c ^ rsw) << 4));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[sr]);
+                uint32_t v[32];
+                dequant8((uint32_t)w4[0].x, (uint32_t)w4[0].y, d_lo, v);
+                dequant8((uint32_t)w4[0].z, (uint32_t)w4[0].w, d_lo, v + 4);
+                dequant8((uint32_t)w4[1].x, (uint32_t)w4[1].y, d_lo, v + 8);
+                dequant8((uint32_t)w4[1].z, (uint32_t)w4[1].w, d_lo, v + 12);
                 ring_d[u] = scale_load();
                 la_advance(2);
                 if (ok && ring<kStages>::must_wait_empty(g))
                     ok = mbar_wait(&empty[sa], ring<kStages>::empty_parity(g), abort_s);
-                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory store below is warp-collective
+                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory stores below are warp-collective
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // Register i -> column i of this thread's lane: k = 2i (low half), 2i + 1 (high half).
+                // Register i -> column i of this thread's lane: k = 2i (low half), 2i + 1 (high half).  Two
+                // stores of 16 columns: the second half is converted while the first store is in flight.
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + L::kACol0 + sa * 32u;
                 asm volatile(
-                    "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                    "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
-                    "%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                    "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
                     "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-                    "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
-                    "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
-                    "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                    "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                    : "memory");
+                dequant8((uint32_t)w4[2].x, (uint32_t)w4[2].y, d_hi, v + 16);
+                dequant8((uint32_t)w4[2].z, (uint32_t)w4[2].w, d_hi, v + 20);
+                dequant8((uint32_t)w4[3].x, (uint32_t)w4[3].y, d_hi, v + 24);
+                dequant8((uint32_t)w4[3].z, (uint32_t)w4[3].w, d_hi, v + 28);
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                    "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr + 16u),
+                    "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                    "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
                     : "memory");
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full[sa]);
-                    mbar_arrive(&raw_empty[sr]);  // every lane's reads of the raw tile are done
-                }
+                if (lane == 0) mbar_arrive(&full[sa]);
             }
         }
     } else if (warp < kWarpRaw) {
@@ -342,6 +356,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         const uint32_t quarter = (uint32_t)warp & 3u;  // a warp reaches tensor-memory lanes 32*(warp%4)..+31
         uint32_t it = 0;
         bool ok = true;
+        tmdev::pdl_wait();  // Y (and the split-K slots) belong to the predecessors until they have finished
+        tmdev::pdl_trigger();
         for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
           const uint32_t ot = tile / ksplit, part = tile % ksplit;
           // Split K, pass 0: the accumulators go to this part's workspace slot; pass 1 (only the warp that
@@ -484,6 +500,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         if (lane == 0) {
             uint32_t g = 0;
             bool ok = true;
+            tmdev::pdl_wait();  // the f16 copy of X is the predecessor's output
             for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const uint32_t tok0 = (tile / ksplit / row_tiles) * kTB;
                 const uint32_t kb0 = (tile % ksplit) * nkb;
@@ -555,6 +572,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
 
 // f32 -> f16 copy of the activations (round to nearest even), the TMA source.
 __global__ void x_to_f16_kernel(const float *x, __half *out, size_t n) {
+    tmdev::pdl_wait();  // x is the predecessor's output; the workspace may still be read by the GEMM before
+    tmdev::pdl_trigger();
     for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
         if (i + 3 < n && (((size_t)(x + i)) & 15u) == 0) {
             const float4 v = *(const float4 *)(x + i);
@@ -572,6 +591,8 @@ template <int PRO>
 __global__ void __launch_bounds__(256) x_prep_f16_kernel(const float *x, const float *pro, __half *out, uint32_t cols,
                                                           float eps) {
     __shared__ float red[8];
+    tmdev::pdl_wait();  // x is the predecessor's output; the workspace may still be read by the GEMM before
+    tmdev::pdl_trigger();
     const float *xr = x + (size_t)blockIdx.x * cols;
     __half *orow = out + (size_t)blockIdx.x * cols;
     float inv = 1.0f;
@@ -627,8 +648,8 @@ encode_tiled_fn get_encode_tiled() {
 }
 
 template <int BN>
-cudaError_t launch_mma(const CUtensorMap &wmap, const CUtensorMap &xmap, const mma_args &a, int grid, int device,
-                       cudaStream_t stream) {
+cudaError_t launch_mma(tm_cuda_ctx *ctx, const CUtensorMap &wmap, const CUtensorMap &xmap, const mma_args &a, int grid) {
+    const int device = ctx->device;
     static std::atomic<bool> attr_done[64] = {};  // per device; contexts of a process share it
     if (device < 0 || device >= 64 || !attr_done[device].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(q8_gemm_mma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -636,8 +657,7 @@ cudaError_t launch_mma(const CUtensorMap &wmap, const CUtensorMap &xmap, const m
         if (e != cudaSuccess) return e;
         if (device >= 0 && device < 64) attr_done[device].store(true, std::memory_order_release);
     }
-    q8_gemm_mma_kernel<BN><<<grid, kMmaThreads, mma_smem<BN>::kBytes, stream>>>(wmap, xmap, a);
-    return cudaGetLastError();
+    return tm_launch_pdl(ctx, q8_gemm_mma_kernel<BN>, dim3(grid), dim3(kMmaThreads), mma_smem<BN>::kBytes, wmap, xmap, a);
 }
 
 }  // namespace
@@ -781,9 +801,9 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
     ctx->mma_last_ksplit = (int)a.ksplit;
     const uint32_t n_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn)) * a.ksplit;
     const int grid = (int)(n_tiles < (uint32_t)ctx->sm_count ? n_tiles : (uint32_t)ctx->sm_count);
-    TM_CUDA_TRY(bn == 192   ? launch_mma<192>(wmap, xmap, a, grid, ctx->device, ctx->stream)
-                : bn == 128 ? launch_mma<128>(wmap, xmap, a, grid, ctx->device, ctx->stream)
-                            : launch_mma<64>(wmap, xmap, a, grid, ctx->device, ctx->stream));
+    TM_CUDA_TRY(bn == 192   ? launch_mma<192>(ctx, wmap, xmap, a, grid)
+                : bn == 128 ? launch_mma<128>(ctx, wmap, xmap, a, grid)
+                            : launch_mma<64>(ctx, wmap, xmap, a, grid));
     return TM_CUDA_OK;
 }
 
@@ -807,8 +827,8 @@ int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x
     TM_OP_BEGIN("q8_0_gemm_mma");
     const size_t n = (size_t)batch * cols;
     const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
-    x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev + x_off,
-                                                                      (__half *)ctx->mma_scratch, n);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, x_to_f16_kernel, dim3(cgrid < 1 ? 1 : cgrid), dim3(256), 0,
+                              (const float *)x->dev + x_off, (__half *)ctx->mma_scratch, n));
     float *const ys[3] = {(float *)y->dev + y_off, nullptr, nullptr};
     const uint32_t ends[3] = {rows, rows, rows};
     rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, 0, err, err_cap);
@@ -854,16 +874,16 @@ int tm_cuda_q8_0_gemm_mma_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buf
     const float *xp = (const float *)x->dev, *pp = pro ? (const float *)pro->dev : nullptr;
     switch (prologue) {
         case TM_CUDA_PRO_RMSNORM:
-            x_prep_f16_kernel<TM_CUDA_PRO_RMSNORM><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            TM_CUDA_TRY(tm_launch_pdl(ctx, x_prep_f16_kernel<TM_CUDA_PRO_RMSNORM>, dim3(batch), dim3(256), 0, xp, pp, xh, cols, eps));
             break;
         case TM_CUDA_PRO_SILU_MUL:
-            x_prep_f16_kernel<TM_CUDA_PRO_SILU_MUL><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            TM_CUDA_TRY(tm_launch_pdl(ctx, x_prep_f16_kernel<TM_CUDA_PRO_SILU_MUL>, dim3(batch), dim3(256), 0, xp, pp, xh, cols, eps));
             break;
         case TM_CUDA_PRO_GELU_MUL:
-            x_prep_f16_kernel<TM_CUDA_PRO_GELU_MUL><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            TM_CUDA_TRY(tm_launch_pdl(ctx, x_prep_f16_kernel<TM_CUDA_PRO_GELU_MUL>, dim3(batch), dim3(256), 0, xp, pp, xh, cols, eps));
             break;
         default:
-            x_prep_f16_kernel<TM_CUDA_PRO_NONE><<<batch, 256, 0, ctx->stream>>>(xp, pp, xh, cols, eps);
+            TM_CUDA_TRY(tm_launch_pdl(ctx, x_prep_f16_kernel<TM_CUDA_PRO_NONE>, dim3(batch), dim3(256), 0, xp, pp, xh, cols, eps));
     }
     rc = mma_launch(ctx, w, rows, cols, batch, ys, ends, epilogue == TM_CUDA_EPI_ADD, err, err_cap);
     if (rc != TM_CUDA_OK) return rc;
@@ -892,7 +912,8 @@ int tm_cuda_q8_0_gemm_mma_push(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buff
     TM_OP_BEGIN("q8_0_gemm_mma_push");
     const size_t n = (size_t)batch * cols;
     const int cgrid = (int)((n / 4 + 255) / 256 > 148 * 8 ? 148 * 8 : (n / 4 + 255) / 256);
-    x_to_f16_kernel<<<cgrid < 1 ? 1 : cgrid, 256, 0, ctx->stream>>>((const float *)x->dev, (__half *)ctx->mma_scratch, n);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, x_to_f16_kernel, dim3(cgrid < 1 ? 1 : cgrid), dim3(256), 0, (const float *)x->dev,
+                              (__half *)ctx->mma_scratch, n));
     float *const ys[3] = {(float *)dst->dev, nullptr, nullptr};  // unused by the pushing epilogue
     const uint32_t ends[3] = {rows, rows, rows};
     mma_push push;

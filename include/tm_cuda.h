@@ -610,6 +610,14 @@ int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, 
                                tm_cuda_buffer *partial, tm_cuda_buffer *pairs, tm_cuda_buffer *out, uint32_t base,
                                tm_cuda_buffer *pos_buf, uint32_t pos_index, uint32_t out_cap,
                                tm_cuda_buffer *mirror, char *err, size_t err_cap);
+/* The reduction of a projection split by COLUMNS over the ranks (each rank multiplies its column
+ * range by its own slice of the input and holds a full-width partial product): `slots` is
+ * [world][n_rows][cols] f32 with rank r's partial in slot r (tm_cuda_push_rows_f32 with one row of
+ * n_rows * cols values puts it there on every rank); x[t][c] += slots[0][t][c] + slots[1][t][c] + ...
+ * added in rank order, so every rank computes the same bits.  With `weight` (may be NULL) the sum is
+ * RMS-normed with that weight before it is added (a layer's output norm; slot 0 is overwritten). */
+int tm_cuda_reduce_ranks_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *slots, tm_cuda_buffer *x, tm_cuda_buffer *weight,
+                                 uint32_t world, uint32_t n_rows, uint32_t cols, float eps, char *err, size_t err_cap);
 /* The same for n_rows rows in one exchange (a decode step of several sequences on a split model):
  * row r of the local [n_rows][n] logits slice; its winner over all ranks goes to
  * out[r * out_stride + base + pos_buf[r]] when that slot is below out_cap <= out_stride.

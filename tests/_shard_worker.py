@@ -34,6 +34,20 @@ def run(rank: int, world: int, port: int, out_path: str) -> None:
         whole = oracle.matmul_q8_0(T.q8_0_matrix(0, 7, rows, cols), rows, cols, x, threads=1).reshape(n, rows)
         assert np.array_equal(y, whole), "row split + all-gather differs from the whole product"
 
+        # Column split (o, down): each rank multiplies its column range by its slice of the input; the
+        # full-width partial products are exchanged and added in rank order, identically on every rank.
+        c0, c1 = S.col_range(rank, world, cols)
+        raw = T.q8_0_matrix(0, 7, rows, cols)  # [rows][cols / 32][34]
+        w_cols = np.ascontiguousarray(raw[:, c0 // 32:c1 // 32])
+        part = oracle.matmul_q8_0(w_cols, rows, c1 - c0, np.ascontiguousarray(x[:, c0:c1]), threads=1).reshape(n, rows)
+        slots = [torch.empty(n, rows) for _ in range(world)]
+        dist.all_gather(slots, torch.from_numpy(np.ascontiguousarray(part)))
+        summed = S.reduce_ranks([p.numpy() for p in slots])
+        assert np.max(np.abs(summed - whole)) <= 1e-4 * max(1.0, float(np.max(np.abs(whole)))), "column split + reduce"
+        check = [torch.empty(n, rows) for _ in range(world)]
+        dist.all_gather(check, torch.from_numpy(summed))
+        assert all(np.array_equal(c.numpy(), summed) for c in check), "ranks disagree on the reduced product"
+
         # Sharded greedy choice: 8 bytes per rank instead of the logits.
         picks = []
         for t in range(n):

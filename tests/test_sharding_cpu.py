@@ -28,6 +28,18 @@ def test_row_ranges_tile_the_matrix():
         S.shard_geometry(T.GEMMA3_1B, 2)  # one KV head cannot be divided
 
 
+def test_column_ranges_are_whole_blocks():
+    assert S.col_range(1, 4, 4096) == (1024, 2048)
+    assert [S.col_range(r, 2, 64) for r in range(2)] == [(0, 32), (32, 64)]
+    with pytest.raises(ValueError):
+        S.col_range(0, 4, 96)  # 24 columns per rank: not whole Q8_0 blocks
+    with pytest.raises(ValueError):
+        S.col_range(2, 2, 64)
+    parts = [np.full(3, 0.1, np.float32), np.full(3, 0.2, np.float32), np.full(3, 0.3, np.float32)]
+    want = np.float32(np.float32(np.float32(0.1) + np.float32(0.2)) + np.float32(0.3))
+    assert np.all(S.reduce_ranks(parts) == want)
+
+
 def test_per_rank_plan_divides_projections_and_kv(tmp_path):
     """The preflight of rank r prices 1/W of every projection and of the KV
     cache, the whole embedding table and the norm vectors (per-rank plans of the

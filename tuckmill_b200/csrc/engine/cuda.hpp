@@ -366,6 +366,12 @@ public:
                 pos ? pos->raw() : nullptr, pos_index, out_cap, mirror ? mirror->raw() : nullptr);
     }
 
+    // x += sum of the ranks' partial products (then an optional output norm), include/tm_cuda.h.
+    void reduce_ranks_add(const CudaBuffer &slots, const CudaBuffer &x, const CudaBuffer *weight, uint32_t world,
+                          uint32_t n_rows, uint32_t cols, float eps) const {
+        TM_CALL(tm_cuda_reduce_ranks_add_f32, slots.raw(), x.raw(), weight ? weight->raw() : nullptr, world, n_rows, cols,
+                eps);
+    }
     void argmax_rows_sharded(const CudaBuffer &x, uint32_t n_rows, uint32_t n, uint32_t index_offset,
                              const CudaBuffer &partial, const CudaBuffer &pairs, const CudaBuffer &out,
                              uint32_t out_stride, uint32_t base, const CudaBuffer &pos, uint32_t out_cap,

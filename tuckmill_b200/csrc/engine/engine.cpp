@@ -75,8 +75,12 @@ std::vector<float> rope_inv_freq(size_t rope_dims, float base) {
     return out;
 }
 
-// Output-row split: this rank owns rows [rank*n/world, (rank+1)*n/world) of every
-// projection (each output element needs one weight row and the whole input).
+// The split over `world` devices: q|k|v, gate|up and the head are cut by OUTPUT ROWS (rank r owns rows
+// [r*N/world, (r+1)*N/world): whole attention heads, a slice of the FFN width, a slice of the
+// vocabulary), so attention and the gated activation stay on the rank; o and down are cut by INPUT
+// COLUMNS (Matrix::load_cols: the columns that multiply this rank's heads / FFN slice), each rank
+// produces a full-width partial product and one exchange per projection adds the partials in rank
+// order -- two exchanges per layer, none between a rank's q|k|v and its o, or its gate|up and its down.
 // A device matrix: one or more Q8_0 tensors of equal width, rows concatenated,
 // repacked into the two-plane form at upload (crates/tuckcore/src/engine/
 // metal.rs:107-226 uploads the GGUF bytes verbatim; the row concatenation and
@@ -129,6 +133,51 @@ struct Matrix {
         uint32_t rows, cols, type;
         geometry(src, ts, sh, &rows, &cols, &type);
         return bytes_of(type, rows, cols);
+    }
+
+    // Column shard of ONE tensor: every row, this rank's cols/world columns of it (whole Q8_0 blocks).
+    static void geometry_cols(const WeightSource &src, Tensor t, Shard sh, uint32_t *rows, uint32_t *cols,
+                              uint32_t *type) {
+        Shard whole;
+        geometry(src, {t}, whole, rows, cols, type);
+        if (*cols % sh.world != 0 || (*type == 8 && (*cols / sh.world) % 32 != 0) || (*type == 1 && (*cols / sh.world) % 8 != 0))
+            throw TuckmillError(ErrorCode::InvalidRequest, "tensor " + std::to_string(t.index) + " has " +
+                                                               std::to_string(*cols) + " columns, which do not divide into " +
+                                                               std::to_string(sh.world) + " block-aligned ranges");
+        *cols /= sh.world;
+    }
+    static uint64_t plan_cols(const WeightSource &src, Tensor t, Shard sh) {
+        uint32_t rows, cols, type;
+        geometry_cols(src, t, sh, &rows, &cols, &type);
+        return bytes_of(type, rows, cols);
+    }
+    static Matrix load_cols(const CudaContext &ctx, const WeightSource &src, Tensor t, Shard sh) {
+        Matrix m;
+        geometry_cols(src, t, sh, &m.rows, &m.cols, &m.type);
+        const bool q8 = m.type == 8;
+        const size_t full_row = q8 ? (size_t)m.cols * sh.world / 32 * 34 : (size_t)m.cols * sh.world * 2;
+        const size_t row_bytes = q8 ? (size_t)m.cols / 32 * 34 : (size_t)m.cols * 2;
+        const size_t col0 = (size_t)sh.rank * row_bytes;  // this rank's bytes inside a source row
+        m.buf = ctx.buffer(bytes_of(m.type, m.rows, m.cols));
+        const size_t step = std::max<size_t>(1, kStagingChunkBytes / row_bytes);
+        std::vector<unsigned char> host(step * row_bytes);
+        CudaBuffer stage;
+        if (q8) stage = ctx.buffer(step * row_bytes);  // transient: freed before the ledger is checked
+        for (uint32_t r = 0; r < m.rows; r += (uint32_t)step) {
+            const uint32_t k = std::min<uint32_t>((uint32_t)step, m.rows - r);
+            for (uint32_t i = 0; i < k; ++i)
+                src.read_tensor_into(t.index, (size_t)(r + i) * full_row + col0, host.data() + (size_t)i * row_bytes,
+                                     row_bytes);
+            if (q8) {
+                stage.upload(0, host.data(), (size_t)k * row_bytes);
+                ctx.q8_0_pack(m.buf, m.rows, m.cols, stage, 0, r, k);
+            } else {
+                m.buf.upload((size_t)r * row_bytes, host.data(), (size_t)k * row_bytes);
+            }
+        }
+        ctx.fence();
+        m.part_rows.push_back(m.rows);
+        return m;
     }
 
     // F16: the tensor bytes verbatim, row ranges uploaded straight into place.
@@ -239,7 +288,7 @@ struct Matrix {
 // token-major, `n` = prefill batch.
 struct PrefillScratch {
     CudaBuffer x, h, a, b, c, e, proj, h2, g, u, d2, ascr;
-    CudaBuffer loc, loc2, efull;  // row-split only: local GEMM outputs, gathered attention
+    CudaBuffer loc, loc2;  // split only: a rank's local GEMM outputs
     static size_t widest(const ModelGraph &g) {
         size_t w = g.hidden;
         for (const LayerSpec &l : g.layers) w = std::max(w, std::max(l.mixer.heads * l.mixer.head_dim, l.ffn.width));
@@ -253,12 +302,8 @@ struct PrefillScratch {
         return tm_cuda_mma_workspace_bytes((uint32_t)widest, (uint32_t)n);
     }
     static void plan(const ModelGraph &g, size_t cap, size_t n, Shard sh, Plan &p) {
-        if (sh.world > 1) {
-            size_t awf = 0;
-            for (const LayerSpec &l : g.layers) awf = std::max(awf, l.mixer.heads * l.mixer.head_dim);
-            for (int i = 0; i < 2; ++i) p.scratch_f32(n * widest(g));
-            p.target_f32(n * awf, sh.world);  // efull
-        }
+        if (sh.world > 1)
+            for (int i = 0; i < 2; ++i) p.scratch_f32(n * widest(g));  // loc, loc2
         size_t aw = 0, kvw = 0, ffn = 0, heads = 0;
         for (const LayerSpec &l : g.layers) {
             aw = std::max(aw, l.mixer.heads * l.mixer.head_dim);
@@ -268,7 +313,9 @@ struct PrefillScratch {
         }
         for (size_t e : {g.hidden, g.hidden, aw, kvw, kvw, aw, g.hidden, ffn})  // x h a b c e h2 u
             p.scratch_f32(n * e);
-        for (size_t e : {g.hidden, ffn, g.hidden}) p.target_f32(n * e, sh.world);  // proj g d2: gathered when split
+        // proj, d2: every rank's full-width partial product lands here when the model is split
+        for (int i = 0; i < 2; ++i) p.target_f32(n * g.hidden * sh.world, sh.world);
+        p.scratch_f32(sh.world > 1 ? 1 : n * ffn);  // g (a split rank keeps its gate slice in loc)
         (void)heads;
         (void)cap;
         p.scratch_f32(1);  // the chunk attention streams key blocks; its scratch argument is a placeholder
@@ -288,18 +335,17 @@ struct PrefillScratch {
         s.b = zeros_f32(ctx, n * kvw);
         s.c = zeros_f32(ctx, n * kvw);
         s.e = zeros_f32(ctx, n * aw);
-        s.proj = gather_target_f32(ctx, n * g.hidden, sh);
+        s.proj = gather_target_f32(ctx, n * g.hidden * sh.world, sh);
         s.h2 = zeros_f32(ctx, n * g.hidden);
-        s.g = gather_target_f32(ctx, n * ffn, sh);
+        s.g = zeros_f32(ctx, sh.world > 1 ? 1 : n * ffn);
         s.u = zeros_f32(ctx, n * ffn);
-        s.d2 = gather_target_f32(ctx, n * g.hidden, sh);
+        s.d2 = gather_target_f32(ctx, n * g.hidden * sh.world, sh);
         (void)heads;
         (void)cap;
         s.ascr = zeros_f32(ctx, 1);
         if (sh.world > 1) {
             s.loc = zeros_f32(ctx, n * widest(g));
             s.loc2 = zeros_f32(ctx, n * widest(g));
-            s.efull = gather_target_f32(ctx, n * aw, sh);
         }
         return s;
     }
@@ -313,36 +359,35 @@ struct RowsAre {
 };
 
 // Gated FFN: down(act(gate x) * up x), optional RMS norm on the output before
-// the residual add (engine/metal.rs:431-535).  gate|up are one matrix.  With a
-// row split every rank owns width/world gate and up rows and hidden/world down
-// rows; the activated slice and the down output are all-gathered.
+// the residual add (engine/metal.rs:431-535).  gate|up are one matrix.  On a split
+// model every rank owns width/world gate and up rows and the matching width/world
+// COLUMNS of down: its activated slice feeds its own down columns, and the ranks'
+// full-width partial products are added in one exchange (with the residual).
 struct SwiGluBlock {
     Matrix gate_up, down;
     GluActivation act = GluActivation::Silu;
     CudaBuffer out_norm;  // empty unless the artifact has it
     float eps = 0;
     CudaBuffer gu, g_view, u_view, out;
-    CudaBuffer h_full, out_local;  // row split only
+    CudaBuffer out_local;  // split only: this rank's partial product
     size_t width = 0, wl = 0;      // full and per-rank FFN width
     Shard sh;
 
     static void plan(const FfnSpec &f, bool has_norm, Tensor norm, size_t hidden, const WeightSource &src, Shard sh,
                      Plan &p) {
-        p.weights += Matrix::plan(src, {f.gate, f.up}, sh) + Matrix::plan(src, {f.down}, sh);
+        p.weights += Matrix::plan(src, {f.gate, f.up}, sh) +
+                     (sh.world > 1 ? Matrix::plan_cols(src, f.down, sh) : Matrix::plan(src, {f.down}));
         if (has_norm) p.weights_f32(vector_len(src, norm));
         p.scratch_f32(2 * f.width / sh.world);
-        p.target_f32(hidden, sh.world);  // out
-        if (sh.world > 1) {
-            p.target_f32(f.width, sh.world);  // h_full
-            p.scratch_f32(hidden / sh.world);
-        }
+        p.target_f32(hidden * sh.world, sh.world);  // out: one slot per rank when split
+        if (sh.world > 1) p.scratch_f32(hidden);    // out_local
     }
     static SwiGluBlock load(const CudaContext &ctx, const WeightSource &src, const FfnSpec &f, bool has_norm,
                             Tensor norm, size_t hidden, float eps, Shard sh) {
         SwiGluBlock b;
         b.sh = sh;
         b.gate_up = Matrix::load(ctx, src, {f.gate, f.up}, sh);
-        b.down = Matrix::load(ctx, src, {f.down}, sh);
+        b.down = sh.world > 1 ? Matrix::load_cols(ctx, src, f.down, sh) : Matrix::load(ctx, src, {f.down});
         b.act = f.act;
         if (has_norm) b.out_norm = vector(ctx, src, norm);
         b.eps = eps;
@@ -353,11 +398,10 @@ struct SwiGluBlock {
         b.gu = zeros_f32(ctx, 2 * b.wl);
         b.g_view = b.gu.view(0, b.wl * 4);
         b.u_view = b.gu.view(b.wl * 4, b.wl * 4);
-        b.out = gather_target_f32(ctx, hidden, sh);
-        if (sh.world > 1) {
-            b.h_full = gather_target_f32(ctx, f.width, sh);
-            b.out_local = zeros_f32(ctx, hidden / sh.world);
-        }
+        b.out = gather_target_f32(ctx, hidden * sh.world, sh);
+        if (sh.world > 1) b.out_local = zeros_f32(ctx, hidden);
+        if (b.down.rows != hidden || b.down.cols != b.wl)
+            throw TuckmillError(ErrorCode::UnsupportedArchitecture, "down projection shape does not match the FFN width");
         return b;
     }
     void act_mul(const CudaContext &ctx, const CudaBuffer &g, const CudaBuffer &u, uint32_t n) const {
@@ -367,16 +411,13 @@ struct SwiGluBlock {
     // x += ffn(norm(x, post_norm)) for one token: 2 launches (3 more with an output norm).
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &post_norm, size_t hidden) const {
         gate_up.gemv_fused(ctx, x, gu, TM_CUDA_PRO_RMSNORM, &post_norm, eps, TM_CUDA_EPI_STORE);
-        if (sh.world > 1) {
-            act_mul(ctx, g_view, u_view, (uint32_t)wl);
-            ctx.push_rows(g_view, h_full, 1, (uint32_t)wl);
-            down.gemv(ctx, h_full, out_local);
-            ctx.push_rows(out_local, out, 1, (uint32_t)(hidden / sh.world));
-            if (out_norm) ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
-            else ctx.f32_axpy(out, x, 1.0f, (uint32_t)hidden);
+        const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        if (sh.world > 1) {  // this rank's columns of down, then the ranks' partial products added (4 launches)
+            down.gemv_fused(ctx, g_view, out_local, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
+            ctx.push_rows(out_local, out, 1, (uint32_t)hidden);
+            ctx.reduce_ranks_add(out, x, out_norm ? &out_norm : nullptr, sh.world, 1, (uint32_t)hidden, eps);
             return;
         }
-        const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
         if (out_norm) {
             down.gemv_fused(ctx, g_view, out, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
             ctx.rmsnorm_add(out, out_norm, x, 1, (uint32_t)hidden, eps);
@@ -389,17 +430,17 @@ struct SwiGluBlock {
     bool fusable() const { return sh.world == 1 && width % 128 == 0 && gate_up.type == 8 && down.type == 8; }
     bool fusable_rows() const { return wl % 128 == 0 && gate_up.type == 8 && down.type == 8; }
     // A rank's share of the tolerance-qualified batched form: norm folded into ONE gate|up launch over
-    // the rank's rows, activation, then the two exchanges (the down projection pushes as it multiplies).
+    // the rank's rows, the activation into the rank's columns of down, then the one exchange.
     void prefill_split_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
                              size_t hidden) const {
         const uint32_t nn = (uint32_t)n;
         ctx.q8_0_gemm_mma_fused(gate_up.buf, s.x, gate_up.rows, gate_up.cols, nn, {&s.loc, &s.loc2},
                                 {(uint32_t)wl, (uint32_t)wl}, TM_CUDA_PRO_RMSNORM, &post_norm, eps, TM_CUDA_EPI_STORE);
-        act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
-        ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
-        ctx.q8_0_gemm_mma_push(down.buf, s.g, s.d2, down.rows, down.cols, nn);
-        if (out_norm) ctx.rmsnorm_add(s.d2, out_norm, s.x, nn, (uint32_t)hidden, eps);
-        else ctx.f32_axpy(s.d2, s.x, 1.0f, (uint32_t)(n * hidden));
+        const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        ctx.q8_0_gemm_mma_fused(down.buf, s.loc, down.rows, down.cols, nn, {&s.h}, {down.rows}, pro, &s.loc2, 0.0f,
+                                TM_CUDA_EPI_STORE);
+        ctx.push_rows(s.h, s.d2, 1, (uint32_t)(n * hidden));
+        ctx.reduce_ranks_add(s.d2, s.x, out_norm ? &out_norm : nullptr, sh.world, nn, (uint32_t)hidden, eps);
     }
     void prefill_fused(const CudaContext &ctx, const PrefillScratch &s, size_t n, const CudaBuffer &post_norm,
                        size_t hidden) const {
@@ -424,13 +465,10 @@ struct SwiGluBlock {
             gate_up.gemm_part(ctx, 0, s.h2, s.loc, nn, exact);
             gate_up.gemm_part(ctx, 1, s.h2, s.loc2, nn, exact);
             act_mul(ctx, s.loc, s.loc2, (uint32_t)(n * wl));
-            ctx.push_rows(s.loc, s.g, nn, (uint32_t)wl);
-            if (exact || down.type == 1) {
-                down.gemm_all(ctx, s.g, s.loc, nn, exact);
-                ctx.push_rows(s.loc, s.d2, nn, (uint32_t)(hidden / sh.world));
-            } else {  // multiply and exchange as one kernel
-                ctx.q8_0_gemm_mma_push(down.buf, s.g, s.d2, down.rows, down.cols, nn);
-            }
+            down.gemm_all(ctx, s.loc, s.loc2, nn, exact);  // this rank's partial product [n][hidden]
+            ctx.push_rows(s.loc2, s.d2, 1, (uint32_t)(n * hidden));
+            ctx.reduce_ranks_add(s.d2, s.x, out_norm ? &out_norm : nullptr, sh.world, nn, (uint32_t)hidden, eps);
+            return;
         } else {
             gate_up.gemm_part(ctx, 0, s.h2, s.g, nn, exact);
             gate_up.gemm_part(ctx, 1, s.h2, s.u, nn, exact);
@@ -444,16 +482,17 @@ struct SwiGluBlock {
 
 // Grouped-query attention with per-head Q/K RMS norms, RoPE, packed f16 KV and
 // an optional sliding window (engine/metal.rs:989-1364).  q|k|v are one matrix.
-// With a row split every rank owns heads/world query heads and kv_heads/world
-// KV heads (and only their cache planes); attention is local to the rank, its
-// output and the o projection's output are all-gathered.
+// On a split model every rank owns heads/world query heads and kv_heads/world
+// KV heads (and only their cache planes) and the COLUMNS of o that multiply them:
+// attention is local to the rank and feeds its own o columns; the ranks' partial
+// products are added in one exchange.
 struct AttentionBlock {
     AttentionSpec spec;
     float eps = 0;
     Matrix qkv, o;
     CudaBuffer q_norm, k_norm, inv_freq, k_cache, v_cache;
     CudaBuffer qkv_out, q_view, k_view, v_view, attn, kv_scratch;
-    CudaBuffer attn_full, proj_local;  // row split only
+    CudaBuffer proj_local;  // split only: this rank's partial product of the o projection
     size_t cap = 0, heads_l = 0, kv_l = 0;
     Shard sh;
     // Several sequences: the caches are [seqs] plane pairs (sequence 0 first, so the one-sequence
@@ -469,7 +508,8 @@ struct AttentionBlock {
     }
     static void plan(const AttentionSpec &s, const WeightSource &src, size_t cap, size_t hidden, Shard sh, Plan &p,
                      size_t seqs) {
-        p.weights += Matrix::plan(src, {s.q, s.k, s.v}, sh) + Matrix::plan(src, {s.o}, sh);
+        p.weights += Matrix::plan(src, {s.q, s.k, s.v}, sh) +
+                     (sh.world > 1 ? Matrix::plan_cols(src, s.o, sh) : Matrix::plan(src, {s.o}));
         p.weights_f32(vector_len(src, s.q_norm));
         p.weights_f32(vector_len(src, s.k_norm));
         // The RoPE table is derived by the engine, not artifact bytes: scratch.
@@ -480,10 +520,7 @@ struct AttentionBlock {
         p.scratch_f32(hl * s.head_dim);
         p.scratch_bytes(seqs * tm_cuda_attention_decode_scratch_bytes((uint32_t)hl, (uint32_t)kl, (uint32_t)s.head_dim,
                                                                       (uint32_t)cap));
-        if (sh.world > 1) {
-            p.target_f32(s.heads * s.head_dim, sh.world);  // attn_full
-            p.scratch_f32(hidden / sh.world);
-        }
+        if (sh.world > 1) p.scratch_f32(hidden);  // proj_local
     }
     static AttentionBlock load(const CudaContext &ctx, const WeightSource &src, const AttentionSpec &s, float eps,
                                size_t cap, size_t hidden, Shard sh, size_t seqs) {
@@ -502,10 +539,10 @@ struct AttentionBlock {
         b.heads_l = s.heads / sh.world;
         b.kv_l = s.kv_heads / sh.world;
         b.qkv = Matrix::load(ctx, src, {s.q, s.k, s.v}, sh);
-        b.o = Matrix::load(ctx, src, {s.o}, sh);
+        b.o = sh.world > 1 ? Matrix::load_cols(ctx, src, s.o, sh) : Matrix::load(ctx, src, {s.o});
         const size_t hd = b.heads_l * s.head_dim, kv = b.kv_l * s.head_dim;
-        if (b.qkv.part_rows[0] != hd || b.qkv.part_rows[1] != kv || b.qkv.part_rows[2] != kv ||
-            b.o.cols != s.heads * s.head_dim)
+        if (b.qkv.part_rows[0] != hd || b.qkv.part_rows[1] != kv || b.qkv.part_rows[2] != kv || b.o.cols != hd ||
+            b.o.rows != hidden)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture, "attention projection shapes do not match the head geometry");
         b.q_norm = vector(ctx, src, s.q_norm);
         b.k_norm = vector(ctx, src, s.k_norm);
@@ -535,10 +572,7 @@ struct AttentionBlock {
         b.attn = zeros_f32(ctx, hd);
         b.kv_scratch = ctx.zeros(seqs * tm_cuda_attention_decode_scratch_bytes((uint32_t)b.heads_l, (uint32_t)b.kv_l,
                                                                                (uint32_t)s.head_dim, (uint32_t)cap));
-        if (sh.world > 1) {
-            b.attn_full = gather_target_f32(ctx, s.heads * s.head_dim, sh);
-            b.proj_local = zeros_f32(ctx, hidden / sh.world);
-        }
+        if (sh.world > 1) b.proj_local = zeros_f32(ctx, hidden);
         return b;
     }
     void reset() const {
@@ -565,11 +599,11 @@ struct AttentionBlock {
                                    (uint32_t)spec.head_dim, (uint32_t)spec.rope_dims, (uint32_t)cap,
                                    (uint32_t)spec.window, eps, scale(), exact);
     }
-    // Row split: proj = all_gather(o_local * all_gather(attn_local)), one token.
+    // Split model, one token: this rank's columns of o times its own heads' output, pushed into this
+    // rank's slot of `proj` on every rank (the caller adds the slots).
     void project_sharded(const CudaContext &ctx, const CudaBuffer &proj, size_t hidden) const {
-        ctx.push_rows(attn, attn_full, 1, (uint32_t)(heads_l * spec.head_dim));
-        o.gemv(ctx, attn_full, proj_local);
-        ctx.push_rows(proj_local, proj, 1, (uint32_t)(hidden / sh.world));
+        o.gemv(ctx, attn, proj_local);
+        ctx.push_rows(proj_local, proj, 1, (uint32_t)hidden);
     }
     // The tolerance-qualified batched form: input norm folded into the f16 copy, q|k|v as one GEMM
     // launch, the four launches before attention as one, tensor-core attention (9 launches -> 4).
@@ -618,14 +652,9 @@ struct AttentionBlock {
                 ctx.attention_chunk(s.a, kcs, vcs, s.e, s.ascr, heads, pos0, (uint32_t)cap, hd, heads / kv, scale(),
                                     nn, (uint32_t)spec.window);
         }
-        if (sh.world > 1) {
-            ctx.push_rows(s.e, s.efull, nn, heads * hd);
-            if (exact || o.type == 1) {
-                o.gemm_all(ctx, s.efull, s.loc, nn, exact);
-                ctx.push_rows(s.loc, s.proj, nn, (uint32_t)(hidden / sh.world));
-            } else {  // multiply and exchange as one kernel
-                ctx.q8_0_gemm_mma_push(o.buf, s.efull, s.proj, o.rows, o.cols, nn);
-            }
+        if (sh.world > 1) {  // this rank's partial product into its slot of s.proj on every rank
+            o.gemm_all(ctx, s.e, s.loc, nn, exact);
+            ctx.push_rows(s.loc, s.proj, 1, (uint32_t)(n * hidden));
         } else {
             o.gemm_all(ctx, s.e, s.proj, nn, exact);
         }
@@ -643,7 +672,7 @@ struct Layer {
         p.weights_f32(vector_len(src, l.pre_norm));
         p.weights_f32(vector_len(src, l.post_norm));
         if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
-        p.target_f32(g.hidden, sh.world);  // proj
+        p.target_f32(g.hidden * sh.world, sh.world);  // proj: one slot per rank when split
         AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p, seqs);
         SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, sh, p);
     }
@@ -653,7 +682,7 @@ struct Layer {
         L.pre_norm = vector(ctx, src, l.pre_norm);
         if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
         L.post_norm = vector(ctx, src, l.post_norm);
-        L.proj = gather_target_f32(ctx, g.hidden, sh);
+        L.proj = gather_target_f32(ctx, g.hidden * sh.world, sh);
         L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh, seqs);
         L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps, sh);
         return L;
@@ -661,11 +690,13 @@ struct Layer {
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pos_buf, const CudaBuffer &status,
                 size_t hidden, float eps, bool exact) const {
         mixer.decode(ctx, x, pre_norm, pos_buf, status, exact);
-        if (mixer.sh.world > 1 || mixer_out_norm) {
-            if (mixer.sh.world > 1) mixer.project_sharded(ctx, proj, hidden);
-            else mixer.o.gemv(ctx, mixer.attn, proj);
-            if (mixer_out_norm) ctx.rmsnorm_add(proj, mixer_out_norm, x, 1, (uint32_t)hidden, eps);
-            else ctx.f32_axpy(proj, x, 1.0f, (uint32_t)hidden);
+        if (mixer.sh.world > 1) {
+            mixer.project_sharded(ctx, proj, hidden);
+            ctx.reduce_ranks_add(proj, x, mixer_out_norm ? &mixer_out_norm : nullptr, mixer.sh.world, 1, (uint32_t)hidden,
+                                 eps);
+        } else if (mixer_out_norm) {
+            mixer.o.gemv(ctx, mixer.attn, proj);
+            ctx.rmsnorm_add(proj, mixer_out_norm, x, 1, (uint32_t)hidden, eps);
         } else {
             mixer.o.gemv_fused(ctx, mixer.attn, x, TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_ADD);
         }
@@ -727,19 +758,23 @@ struct Layer {
         }
         if (!exact && mixer.sh.world > 1 && mixer.fusable_rows() && ffn.fusable_rows()) {
             // Split model, tolerance mode: q|k|v and gate|up as one fused launch each over this rank's
-            // rows (4 GEMM calls per layer instead of 7), attention on the rank's heads, then the exchanges.
-            const uint32_t hl = (uint32_t)(mixer.heads_l * mixer.spec.head_dim);
+            // rows, attention on the rank's heads, o and down over this rank's columns (4 GEMM calls and
+            // 2 exchanges per layer).
             mixer.prefill_fused(ctx, s, n, pos0, pre_norm, rows);
-            ctx.push_rows(s.e, s.efull, nn, hl);
-            ctx.q8_0_gemm_mma_push(mixer.o.buf, s.efull, s.proj, mixer.o.rows, mixer.o.cols, nn);
-            if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
-            else ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
+            ctx.q8_0_gemm_mma_fused(mixer.o.buf, s.e, mixer.o.rows, mixer.o.cols, nn, {&s.h}, {mixer.o.rows},
+                                    TM_CUDA_PRO_NONE, nullptr, 0.0f, TM_CUDA_EPI_STORE);
+            ctx.push_rows(s.h, s.proj, 1, (uint32_t)(n * hidden));
+            ctx.reduce_ranks_add(s.proj, s.x, mixer_out_norm ? &mixer_out_norm : nullptr, mixer.sh.world, nn,
+                                 (uint32_t)hidden, eps);
             ffn.prefill_split_fused(ctx, s, n, post_norm, hidden);
             return;
         }
         ctx.rmsnorm(s.x, pre_norm, s.h, nn, (uint32_t)hidden, eps);
         mixer.prefill(ctx, s, n, pos0, hidden, exact, rows);
-        if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
+        if (mixer.sh.world > 1)
+            ctx.reduce_ranks_add(s.proj, s.x, mixer_out_norm ? &mixer_out_norm : nullptr, mixer.sh.world, nn,
+                                 (uint32_t)hidden, eps);
+        else if (mixer_out_norm) ctx.rmsnorm_add(s.proj, mixer_out_norm, s.x, nn, (uint32_t)hidden, eps);
         else ctx.f32_axpy(s.proj, s.x, 1.0f, (uint32_t)(n * hidden));
         ctx.rmsnorm(s.x, post_norm, s.h2, nn, (uint32_t)hidden, eps);
         ffn.prefill(ctx, s, n, hidden, exact);

@@ -86,6 +86,31 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_add_kernel(const float *p, c
         xr[i] = __fadd_rn(xr[i], __fmul_rn(__fmul_rn(pr[i], inv), w[i]));
 }
 
+// x[row] += sum over ranks r (in rank order) of slots[r][row] -- or, with a norm weight, += rmsnorm of
+// that sum: the reduction of a column-split projection's partial products and the residual add (and a
+// layer's output norm) as one launch.  With a norm the sum is written over slot 0 first.
+__global__ void __launch_bounds__(kThreads) reduce_ranks_add_kernel(float *slots, float *x, const float *w,
+                                                                    uint32_t world, uint32_t n_rows, uint32_t cols,
+                                                                    float eps) {
+    __shared__ float red[kWarps];
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    const size_t stride = (size_t)n_rows * cols, base = (size_t)blockIdx.x * cols;
+    float *xr = x + base, *p0 = slots + base;
+    for (uint32_t i = threadIdx.x; i < cols; i += kThreads) {
+        float p = p0[i];
+        for (uint32_t r = 1; r < world; ++r) p = __fadd_rn(p, p0[(size_t)r * stride + i]);
+        if (w) p0[i] = p;
+        else xr[i] = __fadd_rn(xr[i], p);
+    }
+    if (!w) return;
+    __syncthreads();
+    const float ss = tmdev::block_sumsq(p0, cols, red);
+    const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
+    for (uint32_t i = threadIdx.x; i < cols; i += kThreads)
+        xr[i] = __fadd_rn(xr[i], __fmul_rn(__fmul_rn(p0[i], inv), w[i]));
+}
+
 // ---- greedy argmax (crates/backend/src/sampling.rs:68-82) -------------------
 __device__ __forceinline__ bool better(float av, uint32_t ai, float bv, uint32_t bi) {
     if (ai == kArgmaxNone) return false;
@@ -1150,6 +1175,22 @@ int tm_cuda_u32_add(tm_cuda_ctx *ctx, tm_cuda_buffer *buf, uint32_t index, uint3
     if (ctx->program) return tm_step_record_pos_add(ctx, (uint32_t *)buf->dev + index, delta, err, err_cap);
     TM_OP_BEGIN("u32_add");
     TM_CUDA_TRY(tm_launch_pdl(ctx, u32_add_kernel, dim3(1), dim3(1), 0, (uint32_t *)buf->dev + index, delta));
+    TM_OP_END(1);
+}
+
+int tm_cuda_reduce_ranks_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *slots, tm_cuda_buffer *x, tm_cuda_buffer *weight,
+                                 uint32_t world, uint32_t n_rows, uint32_t cols, float eps, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (world == 0 || n_rows == 0 || cols == 0)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "reduction geometry %u x %u x %u", world, n_rows, cols);
+    TM_CHECK_BUF(slots, (size_t)world * n_rows * cols * 4, "rank slots");
+    TM_CHECK_BUF(x, (size_t)n_rows * cols * 4, "x");
+    if (weight) TM_CHECK_BUF(weight, (size_t)cols * 4, "norm weight");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator reduce_ranks_add cannot be recorded into a persistent program");
+    TM_OP_BEGIN("reduce_ranks_add");
+    TM_CUDA_TRY(tm_launch_pdl(ctx, reduce_ranks_add_kernel, dim3(n_rows), dim3(kThreads), 0, (float *)slots->dev,
+                              (float *)x->dev, weight ? (const float *)weight->dev : nullptr, world, n_rows, cols, eps));
     TM_OP_END(1);
 }
 

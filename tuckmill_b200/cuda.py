@@ -74,6 +74,7 @@ _OPS = {
     "rows_indirect_seq_f32_dev": [_P, _P, _U32, _U32, _P, _U32, _P, _U32, C.c_int32, _F, _P],
     "argmax_rows_f32_dev": [_P, _P, _U32, _U32, _P, _P, _U32, _U32, _P, _U32, _P],
     "u32_add_sat": [_P, _P, _U32, _U32, _U32, _U32],
+    "reduce_ranks_add_f32": [_P, _P, _P, _P, _U32, _U32, _U32, _F],
     "begin_group": [_P],
     "end_group": [_P],
     "abort_group": [_P],
@@ -442,6 +443,9 @@ class CudaContext:
 
     def u32_add_sat(self, buf, first, count, delta, limit):
         self._call("u32_add_sat", buf.handle, first, count, delta, limit)
+
+    def reduce_ranks_add(self, slots, x, weight, world, n_rows, cols, eps=0.0):
+        self._call("reduce_ranks_add_f32", slots.handle, x.handle, self._h(weight), world, n_rows, cols, eps)
 
     def row_indirect_f32(self, w, type_id, rows, cols, ids, slot, out):
         self._call("row_indirect_f32", w.handle, type_id, rows, cols, ids.handle, slot, out.handle)

@@ -1,12 +1,16 @@
-"""Host arithmetic of the output-row split (one process per device).
+"""Host arithmetic of the split of one model over W devices (one process per device).
 
 Every Q8_0 row is an independent byte range and every output element depends on
-one weight row and the whole input vector, so rank r of W owns rows
-[r*N/W, (r+1)*N/W) of each projection and of the head, and an all-gather
-reassembles the output.  Attention stays local by keeping whole heads on one
-rank.  The reference runs on one device; this module states the rules the C++
-engine (csrc/engine/engine.cpp) and the collectives (csrc/tm_cuda_comm.cu)
-follow, so launchers and tests can share them.
+one weight row and the whole input vector, so rank r owns rows [r*N/W, (r+1)*N/W)
+of q|k|v, gate|up and the head (`row_range`; an all-gather reassembles such an
+output).  Whole attention heads and a slice of the FFN width therefore stay on one
+rank, and the two projections that consume them, o and down, are cut the other
+way: rank r holds the COLUMNS that multiply its own heads / FFN slice
+(`col_range`, whole 32-column blocks), produces a full-width partial product, and
+the partials are added in rank order (`reduce_ranks`) -- one exchange per
+projection, every rank computing the same bits.  The reference runs on one device;
+this module states the rules the C++ engine (csrc/engine/engine.cpp) and the
+exchanges (csrc/tm_cuda_comm.cu) follow, so launchers and tests can share them.
 """
 from __future__ import annotations
 
@@ -25,6 +29,25 @@ def row_range(rank: int, world: int, rows: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+def col_range(rank: int, world: int, cols: int, block: int = 32) -> tuple[int, int]:
+    """Half-open column range of `rank` for a projection cut by input columns; ranges are whole
+    quantisation blocks."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a split of {world}")
+    if cols % world or (cols // world) % block:
+        raise ValueError(f"{cols} columns do not divide into {world} ranges of whole {block}-column blocks")
+    per = cols // world
+    return rank * per, (rank + 1) * per
+
+
+def reduce_ranks(partials) -> np.ndarray:
+    """Sum of the ranks' partial products, added in rank order in f32 (what every rank computes)."""
+    acc = np.array(partials[0], dtype=np.float32, copy=True)
+    for p in partials[1:]:
+        acc = (acc + np.asarray(p, dtype=np.float32)).astype(np.float32)
+    return acc
+
+
 @dataclass(frozen=True)
 class ShardGeometry:
     """Per-rank sizes of a dense decoder under the split."""
@@ -32,8 +55,8 @@ class ShardGeometry:
     world: int
     heads: int      # query heads on this rank
     kv_heads: int   # KV heads on this rank (the KV cache is divided with them)
-    ffn: int        # gate / up rows on this rank
-    hidden: int     # o / down rows on this rank
+    ffn: int        # gate / up rows (and down columns) on this rank
+    hidden: int     # hidden size / world (head rows are counted in `vocab`)
     vocab: int      # head rows on this rank
 
 

@@ -550,7 +550,7 @@ def batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decod
     us_step = 1e3 * decode_ms / n_steps
     out = {
         "sequences": sequences, "prompt_tokens": prompt_n, "decode_tokens": decode_n,
-        "parallelism": f"output-row split x{shard[1]}" if shard else "single",
+        "parallelism": f"one model split x{shard[1]}" if shard else "single",
         "decode_tok_s": sequences * n_steps / (decode_ms / 1e3),
         "us_per_step": us_step,
         "prefill_tok_s": steps * sequences * prompt_n / (prefill_ms / 1e3),
@@ -567,11 +567,11 @@ def batched_leg(args, E, torch, dist, local, world, path, shape, prompt_n, decod
 
 
 def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape, prompt_n, decode_n, replica_tokens):
-    """The same session with ONE model split by output rows over all ranks (each
-    rank holds 1/world of every projection, of the head and of the KV cache; four
-    exchanges per layer inside the replayed decode graph, pushed through peer
-    memory).  Strong scaling of a single sequence: reported beside the replica
-    figure, not as `value`."""
+    """The same session with ONE model split over all ranks (each rank holds 1/world of
+    every projection, of the head and of the KV cache: q|k|v, gate|up and the head by
+    output rows, o and down by input columns; two exchanges per layer inside the
+    replayed decode graph, pushed through peer memory).  Strong scaling of a single
+    sequence: reported beside the replica figure, not as `value`."""
     if os.environ.get("TM_BENCH_ROW_SPLIT", "1") == "0":
         return {"unavailable": "switched off by TM_BENCH_ROW_SPLIT=0"}
     try:
@@ -619,8 +619,21 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
     dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     prefill_ms, decode_ms, span_ms = vals.tolist()
     info = eng.refresh_info()
+    # where a split step's time goes: every operator dispatched on its own with events around it (all ranks
+    # make the same calls; rank 0's table is printed)
+    eng.reset()
+    eng.prefill(prompt, want_token=True)
+    eng.decode_ungrouped(2)
+    eng.fence()
+    eng.profile(True)
+    eng.decode_ungrouped(4)
+    eng.fence()
+    by_op = {n: round(ns / 4 / 1e3, 2) for n, ns, c in sorted(eng.profile_rows())}
+    eng.profile(False)
     out = {
-        "parallelism": f"output-row split x{world}, exchanges pushed through peer memory on the compute stream", "scaling": "strong",
+        "by_operator_us_per_step_ungrouped": by_op,
+        "parallelism": f"one model split x{world} (q|k|v, gate|up, head by output rows; o, down by input columns; "
+                       "two exchanges per layer pushed through peer memory on the compute stream)", "scaling": "strong",
         "decode_tok_s": args.steps * (decode_n - 1) / (decode_ms / 1e3),
         "decode_us_per_token": 1e3 * decode_ms / (args.steps * (decode_n - 1)),
         "prefill_tok_s": args.steps * prompt_n / (prefill_ms / 1e3),

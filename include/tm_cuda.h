@@ -167,15 +167,17 @@ int tm_cuda_q8_0_gemm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm
 /* tm_metal.h:176 tm_metal_q8_0_gemm_mma: the same contract on the tensor
  * cores (tcgen05, f16 operands: x and d*q are rounded to binary16, f32
  * accumulation in tensor memory); tolerance-qualified, not bit-identical.
- * The batch limit is the reference's 512 raised to what one launch tiles. */
+ * The batch limit is the reference's 512 raised to what one launch tiles.  One or two tokens (up to
+ * eight when cols < 2048) are handed to tm_cuda_q8_0_gemm, which is exact and as fast there. */
 #define TM_CUDA_GEMM_MMA_MAX_BATCH 8192u
 int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x,
                           tm_cuda_buffer *y, uint32_t rows, uint32_t cols, uint32_t batch,
                           uint32_t x_off, uint32_t y_off, char *err, size_t err_cap);
 /* No counterpart: the tensor-core GEMM reads an f16 copy of X through TMA; the
- * copy lives in a workspace owned by the context (cols * batch * 2 bytes,
- * counted in tm_cuda_allocated_bytes).  It grows on demand, except inside an
- * open dispatch group, where it must have been reserved beforehand. */
+ * copy lives in a workspace owned by the context (cols * batch * 2 bytes plus a
+ * fixed 20 MB of split-K slots, counted in tm_cuda_allocated_bytes).  It grows on
+ * demand, except inside an open dispatch group, where it must have been reserved
+ * beforehand with the size tm_cuda_mma_workspace_bytes gives. */
 size_t tm_cuda_mma_workspace_bytes(uint32_t cols, uint32_t batch);
 int tm_cuda_mma_workspace_reserve(tm_cuda_ctx *ctx, size_t bytes, char *err, size_t err_cap);
 /* No counterpart: 1 when a tensor-core GEMM of this context gave up one of its

@@ -11,7 +11,8 @@ from tuckmill_b200 import cuda, testing as T
 
 pytestmark = pytest.mark.gpu
 CASES = [(16, 1024, 16), (3584, 1024, 16), (3584, 1024, 32), (40, 64, 27), (1024, 3584, 64), (100, 96, 77),
-         (40, 64, 512), (130, 1152, 129), (6144, 1024, 300), (1024, 3072, 512), (257, 2048, 640)]
+         (40, 64, 512), (130, 1152, 129), (6144, 1024, 300), (1024, 3072, 512), (257, 2048, 640),
+         (1024, 3584, 7), (384, 4096, 3), (40, 64, 3)]  # a handful of tokens: tensor cores on wide matrices only
 
 
 def f16_profile_reference(raw, X):

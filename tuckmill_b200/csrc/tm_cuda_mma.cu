@@ -809,8 +809,10 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
 
 int tm_cuda_q8_0_gemm_mma(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,
                           uint32_t cols, uint32_t batch, uint32_t x_off, uint32_t y_off, char *err, size_t err_cap) {
-    if (batch >= 1 && batch < 9) {
-        // A handful of tokens is HBM-bound: the exact integer-tensor-core path serves it (and is tighter).
+    if (batch >= 1 && (batch < 3 || (batch < 9 && cols < 2048))) {
+        // One or two tokens (up to eight on a narrow matrix) are served by the exact integer-tensor-core
+        // GEMV, which is tighter and as fast there; its per-token work on every weight chunk makes it
+        // issue-bound beyond that (4096 x 12288 at 8 tokens: 196 us against 28 us here).
         return tm_cuda_q8_0_gemm(ctx, w, x, y, rows, cols, batch, x_off, y_off, err, err_cap);
     }
     {

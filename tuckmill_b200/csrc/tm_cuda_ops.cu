@@ -97,9 +97,18 @@ __global__ void __launch_bounds__(kThreads) reduce_ranks_add_kernel(float *slots
     tmdev::pdl_wait();
     const size_t stride = (size_t)n_rows * cols, base = (size_t)blockIdx.x * cols;
     float *xr = x + base, *p0 = slots + base;
-    for (uint32_t i = threadIdx.x; i < cols; i += kThreads) {
+    // A thread's loads of one column from every rank's slot are issued together (up to 8 ranks at a
+    // time), then added in rank order: one memory round trip per column instead of one per rank.
+    for (uint32_t i = blockIdx.y * kThreads + threadIdx.x; i < cols; i += gridDim.y * kThreads) {
         float p = p0[i];
-        for (uint32_t r = 1; r < world; ++r) p = __fadd_rn(p, p0[(size_t)r * stride + i]);
+        for (uint32_t r0 = 1; r0 < world; r0 += 8) {
+            float v[8];
+#pragma unroll
+            for (uint32_t k = 0; k < 8; ++k) v[k] = r0 + k < world ? p0[(size_t)(r0 + k) * stride + i] : 0.0f;
+#pragma unroll
+            for (uint32_t k = 0; k < 8; ++k)
+                if (r0 + k < world) p = __fadd_rn(p, v[k]);
+        }
         if (w) p0[i] = p;
         else xr[i] = __fadd_rn(xr[i], p);
     }
@@ -1189,8 +1198,12 @@ int tm_cuda_reduce_ranks_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *slots, tm_cud
     if (ctx->program)
         return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator reduce_ranks_add cannot be recorded into a persistent program");
     TM_OP_BEGIN("reduce_ranks_add");
-    TM_CUDA_TRY(tm_launch_pdl(ctx, reduce_ranks_add_kernel, dim3(n_rows), dim3(kThreads), 0, (float *)slots->dev,
-                              (float *)x->dev, weight ? (const float *)weight->dev : nullptr, world, n_rows, cols, eps));
+    // Without a norm the sum is elementwise: the columns of a row spread over several CTAs (a decode
+    // step's single row would otherwise be one CTA walking 16 columns per thread).
+    const uint32_t col_ctas = weight ? 1u : (cols + kThreads - 1) / kThreads;
+    TM_CUDA_TRY(tm_launch_pdl(ctx, reduce_ranks_add_kernel, dim3(n_rows, col_ctas > 64u ? 64u : col_ctas), dim3(kThreads),
+                              0, (float *)slots->dev, (float *)x->dev, weight ? (const float *)weight->dev : nullptr,
+                              world, n_rows, cols, eps));
     TM_OP_END(1);
 }
 

@@ -36,8 +36,12 @@ def test_mma_gemm_matches_oracle_and_f16_profile(ctx, oracle, rows, cols, batch)
     Y = out[y_off:].reshape(batch, rows)
     cpu = oracle.matmul_q8_0(raw, rows, cols, X)
     assert float(np.max(np.abs(Y - cpu))) <= 2e-2
-    ref16 = f16_profile_reference(raw, X)
-    assert rel_err(Y, ref16) <= 2e-5, "differs from the f16-operand profile by more than accumulation error"
+    if batch < 3 or (batch < 9 and cols < 2048):
+        # handed to the exact batched GEMV (one or two tokens; up to eight on a narrow matrix)
+        assert rel_err(Y, cpu) <= 1e-4
+    else:
+        ref16 = f16_profile_reference(raw, X)
+        assert rel_err(Y, ref16) <= 2e-5, "differs from the f16-operand profile by more than accumulation error"
 
 
 # Shapes the launcher serves with its wider instantiations (token sub-tile 128 and 192: a different

@@ -983,39 +983,80 @@ __global__ void __launch_bounds__(kFastThreads) attention_decode_fast_kernel(
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // ---- merge with a running maximum, one thread per (head, dim); the partials
-    // of 8 splits are fetched together so the loop costs one trip per 8 splits ----
-    for (uint32_t i = tid; i < G * HD; i += kFastThreads) {
-        const uint32_t g = i / HD, d = i % HD;
-        const float *base = scratch + ((size_t)kvh * nsplit + first) * G * stride + g * stride;
+    // ---- merge: warp w takes splits w, w + 4, ... with its own running (max, sum, output) per head, a
+    // lane two value dims per 64; the loads of several splits and all heads are issued together, so the
+    // loop costs one memory trip per 8 (16) splits of the CTA -- the merge is the serial tail of a
+    // decode step at long contexts -- and the four warps' states meet in shared memory. ----
+    {
+        constexpr int DJ = HD / 64;            // float2 pieces of a head vector per lane
+        constexpr int B = G > 2 ? 2 : 4;       // own splits fetched together
+        __shared__ __align__(8) float mrg[kFastThreads / 32][G][HD + 2];
         const uint32_t nact = last - first + 1;
-        float M = -INFINITY, L = 0.0f, O = 0.0f;
-        for (uint32_t s0 = 0; s0 < nact; s0 += 8) {
-            float mb[8], lb[8], ob[8];
+        const float *base0 = scratch + ((size_t)kvh * nsplit + first) * G * stride;
+        float Mg[G], Lg[G], Og[G][2 * DJ];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float *pb = base + (size_t)(s0 + c < nact ? s0 + c : nact - 1) * G * stride;
-                mb[c] = __ldcg(pb);
-                lb[c] = __ldcg(pb + 1);
-                ob[c] = __ldcg(pb + 2 + d);
-            }
-            float mx = M;
+        for (int g = 0; g < G; ++g) {
+            Mg[g] = -INFINITY;
+            Lg[g] = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                if (s0 + c < nact) mx = fmaxf(mx, mb[c]);
-            const float a = expf(M - mx);
-            L *= a;
-            O *= a;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                if (s0 + c < nact) {
-                    const float wgt = expf(mb[c] - mx);
-                    L = fmaf(wgt, lb[c], L);
-                    O = fmaf(wgt, ob[c], O);
-                }
-            M = mx;
+            for (int e = 0; e < 2 * DJ; ++e) Og[g][e] = 0.0f;
         }
-        out[((size_t)kvh * G + g) * HD + d] = O / L;
+        for (uint32_t s0 = (uint32_t)warp; s0 < nact; s0 += 4u * B) {
+            float2 ml[B][G], ov[B][G][DJ];
+#pragma unroll
+            for (int c = 0; c < B; ++c) {
+                const uint32_t s = s0 + 4u * c;
+                const float *pb = base0 + (size_t)(s < nact ? s : nact - 1) * G * stride;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    ml[c][g] = __ldcg((const float2 *)(pb + g * stride));
+#pragma unroll
+                    for (int jj = 0; jj < DJ; ++jj)
+                        ov[c][g][jj] = __ldcg((const float2 *)(pb + g * stride + 2 + 2 * lane + 64 * jj));
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < B; ++c) {
+                if (s0 + 4u * c >= nact) break;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float mx = fmaxf(Mg[g], ml[c][g].x);
+                    const float a = expf(Mg[g] - mx), wgt = expf(ml[c][g].x - mx);
+                    Lg[g] = fmaf(wgt, ml[c][g].y, Lg[g] * a);
+#pragma unroll
+                    for (int jj = 0; jj < DJ; ++jj) {
+                        Og[g][2 * jj] = fmaf(wgt, ov[c][g][jj].x, Og[g][2 * jj] * a);
+                        Og[g][2 * jj + 1] = fmaf(wgt, ov[c][g][jj].y, Og[g][2 * jj + 1] * a);
+                    }
+                    Mg[g] = mx;
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (lane == 0) {
+                mrg[warp][g][0] = Mg[g];
+                mrg[warp][g][1] = Lg[g];
+            }
+#pragma unroll
+            for (int jj = 0; jj < DJ; ++jj)
+                *(float2 *)&mrg[warp][g][2 + 2 * lane + 64 * jj] = make_float2(Og[g][2 * jj], Og[g][2 * jj + 1]);
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < G * HD; i += kFastThreads) {
+            const uint32_t g = i / HD, d = i % HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kFastThreads / 32; ++w) M = fmaxf(M, mrg[w][g][0]);
+            float L = 0.0f, O = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kFastThreads / 32; ++w) {
+                const float f = expf(mrg[w][g][0] - M);  // a warp that took no split: exp(-inf) = 0
+                L = fmaf(f, mrg[w][g][1], L);
+                O = fmaf(f, mrg[w][g][2 + d], O);
+            }
+            out[((size_t)kvh * G + g) * HD + d] = O / L;
+        }
     }
     if (tid == 0) *count = 0u;  // ready for the next launch on this stream
 }

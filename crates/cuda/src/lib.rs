@@ -122,6 +122,7 @@ mod ffi {
         pub fn tm_cuda_row_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, type_id: u32, rows: u32, cols: u32, ids: *mut TmCudaBuffer, slot: u32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_rows_indirect_f32(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, rows: u32, cols: u32, ids: *mut TmCudaBuffer, first: u32, n: u32, scale: f32, out: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_q8_0_gemv_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_q8_0_gemv_addnorm(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, add_p: *mut TmCudaBuffer, add_w: *mut TmCudaBuffer, x_out: *mut TmCudaBuffer, norm_w: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, eps: f32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_q8_0_gemm_fused(ctx: *mut TmCudaCtx, w: *mut TmCudaBuffer, x: *mut TmCudaBuffer, y: *mut TmCudaBuffer, rows: u32, cols: u32, batch: u32, prologue: c_int, pro: *mut TmCudaBuffer, eps: f32, epilogue: c_int, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_begin_group(ctx: *mut TmCudaCtx, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_end_group(ctx: *mut TmCudaCtx, err: *mut c_char, err_cap: usize) -> c_int;

@@ -249,6 +249,15 @@ int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer 
                             tm_cuda_buffer *y, uint32_t rows, uint32_t cols, int prologue,
                             tm_cuda_buffer *pro, float eps, int epilogue, char *err,
                             size_t err_cap);
+/* No counterpart: a layer's output norm and residual add folded into the projection that consumes
+ * the result (layers with output norms, e.g. Gemma's): x' = x + rmsnorm(add_p, add_w, eps) rounded
+ * exactly as tm_cuda_rmsnorm_add_f32 rounds it, y = W rmsnorm(x', norm_w, eps) as
+ * tm_cuda_q8_0_gemv_fused(prologue 1) computes it, and x' written to x_out -- a buffer OTHER than x,
+ * because every CTA of the launch reads x.  One launch instead of two; cols <= 4096.  When the row
+ * cut of a tall matrix makes it two launches, both write the same x'. */
+int tm_cuda_q8_0_gemv_addnorm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *add_p,
+                              tm_cuda_buffer *add_w, tm_cuda_buffer *x_out, tm_cuda_buffer *norm_w, tm_cuda_buffer *y,
+                              uint32_t rows, uint32_t cols, float eps, char *err, size_t err_cap);
 /* No counterpart: the same fused forms for `batch` tokens (1..TM_CUDA_GEMM_MAX_BATCH), token-major x
  * [batch][cols] and y [batch][rows]; the activation prologues take `pro` as [batch][cols], the norm
  * weight as [cols].  Row t of the result is bit-identical to the one-token call on row t (the

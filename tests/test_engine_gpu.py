@@ -111,3 +111,23 @@ def test_requests_are_validated(ctx, artifact):
     with pytest.raises(E.EngineError) as e:
         E.Engine(path, context=8, budget_bytes=1 << 20)
     assert e.value.code == "MODEL_EXCEEDS_BUDGET"
+
+
+def test_folded_output_norms_are_bit_identical(ctx, artifact, monkeypatch):
+    """TM_ENGINE_FOLD_NORMS=1 folds each output norm + residual add of a Gemma-style layer into the
+    projection that follows it (tm_cuda_q8_0_gemv_addnorm): fewer launches, the same bits."""
+    path, shape = artifact
+    toks = T.token_ids(21, 12, shape.vocab)
+    runs = []
+    for fold in ("0", "1"):
+        monkeypatch.setenv("TM_ENGINE_FOLD_NORMS", fold)
+        eng = E.Engine(path, context=64, exact=True)
+        got, stats = eng.generate(toks, 10)
+        runs.append((eng.score(toks), got, stats.kernel_launches))
+        eng.close()
+    np.testing.assert_array_equal(runs[1][0], runs[0][0])
+    np.testing.assert_array_equal(runs[1][1], runs[0][1])
+    if shape.arch == "gemma3":
+        assert runs[1][2] < runs[0][2]  # two launches fewer per layer and decode step
+    else:
+        assert runs[1][2] == runs[0][2]  # no output norms: nothing to fold

@@ -395,3 +395,53 @@ def test_rmsnorm_add_equals_rmsnorm_then_axpy(ctx, rows, cols):
     ctx.rmsnorm_add(pb, wb, xb, rows, cols, 1e-6)
     np.testing.assert_array_equal(f32(xb, rows * cols), f32(xa, rows * cols))
     np.testing.assert_array_equal(f32(pb, rows * cols), p)  # the input is left alone
+
+
+@pytest.mark.parametrize("world,n_rows,cols", [(2, 1, 1024), (4, 1, 4096), (8, 3, 1152), (3, 40, 96), (1, 2, 64)])
+def test_rank_reduction_adds_in_rank_order(ctx, world, n_rows, cols):
+    """tm_cuda_reduce_ranks_add_f32 (the reduction of a column-split projection): x += slot 0 + slot 1 + ...
+    in that order, bit for bit; with a norm weight the sum goes through the RMS norm exactly as
+    tm_cuda_rmsnorm_add_f32 would take it."""
+    slots = (T.activations(3, 1, world * n_rows * cols) * np.float32(3.0)).reshape(world, n_rows, cols)
+    x0 = T.activations(3, 2, n_rows * cols).reshape(n_rows, cols)
+    acc = slots[0].copy()
+    for r in range(1, world):
+        acc = (acc + slots[r]).astype(np.float32)
+    xb, sb = ctx.floats(x0), ctx.floats(slots)
+    ctx.reduce_ranks_add(sb, xb, None, world, n_rows, cols)
+    np.testing.assert_array_equal(f32(xb, n_rows * cols).reshape(n_rows, cols), (x0 + acc).astype(np.float32))
+    np.testing.assert_array_equal(f32(sb, world * n_rows * cols).reshape(world, n_rows, cols), slots)  # untouched
+    w = (1 + 0.1 * T.activations(3, 3, cols)).astype(np.float32)
+    wb, want = ctx.floats(w), ctx.floats(x0)
+    ctx.rmsnorm_add(ctx.floats(acc), wb, want, n_rows, cols, 1e-6)
+    xb2, sb2 = ctx.floats(x0), ctx.floats(slots)
+    ctx.reduce_ranks_add(sb2, xb2, wb, world, n_rows, cols, 1e-6)
+    np.testing.assert_array_equal(f32(xb2, n_rows * cols), f32(want, n_rows * cols))
+    with pytest.raises(cuda.CudaError):
+        ctx.reduce_ranks_add(sb, xb, None, world + 1, n_rows, cols)
+
+
+def test_l2_prefetch_is_only_a_hint(ctx):
+    """tm_cuda_prefetch_l2 forks a side stream and rejoins it: alone, and inside a recorded group
+    between dependent operators, nothing about the results changes."""
+    n = 1 << 16
+    x = T.activations(9, 1, n)
+    big = ctx.floats(T.activations(9, 2, 1 << 20))
+    xb, y1, y2 = ctx.floats(x), ctx.floats(np.zeros(n)), ctx.floats(np.zeros(n))
+    ctx.prefetch_l2([big, xb])
+    ctx.f32_scale(xb, y1, 2.0, n)
+    ctx.f32_axpy(xb, y1, 0.5, n)
+    ctx.begin_group()
+    ctx.prefetch_l2([big])
+    ctx.f32_scale(xb, y2, 2.0, n)
+    ctx.prefetch_l2([big, xb])
+    ctx.f32_axpy(xb, y2, 0.5, n)
+    g = ctx.end_group_retain()
+    for _ in range(3):
+        y2.zero()
+        g.launch()
+    ctx.fence()
+    g.free()
+    np.testing.assert_array_equal(f32(y2, n), f32(y1, n))
+    with pytest.raises(cuda.CudaError):
+        ctx.prefetch_l2([])

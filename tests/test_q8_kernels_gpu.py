@@ -173,3 +173,37 @@ def test_row_dequant_exact(ctx):
     for slot in (1, 2):  # out-of-table ids (incl. the all-NaN marker) write zeros
         ctx.row_indirect_f32(w, 8, rows, cols, ids, slot, o2)
         assert np.all(o2.download(0, cols * 4, np.float32) == 0.0)
+
+
+@pytest.mark.parametrize("rows,cols", [(1536, 1152), (13824, 1152), (40, 64), (4096, 1024), (6144, 4096), (262144, 1152)])
+def test_output_norm_and_residual_folded_into_the_next_projection(ctx, rows, cols):
+    """tm_cuda_q8_0_gemv_addnorm is tm_cuda_rmsnorm_add_f32 followed by the norm-prologue GEMV, bit for
+    bit, in one launch (every launch form the shapes select, incl. the row cut of a tall matrix)."""
+    base = T.q8_0_matrix(11, rows + cols, min(rows, 4096), cols)
+    raw = np.tile(base, ((rows + base.shape[0] - 1) // base.shape[0], 1, 1))[:rows]
+    w = ctx.q8_0_matrix(raw, rows, cols)
+    x = T.activations(11, 1, cols)
+    p = (T.activations(11, 2, cols) * np.float32(5.0)).astype(np.float32)
+    aw = (1 + 0.1 * T.activations(11, 3, cols)).astype(np.float32)
+    nw = (1 + 0.1 * T.activations(11, 4, cols)).astype(np.float32)
+    xb, pb, awb, nwb = ctx.floats(x), ctx.floats(p), ctx.floats(aw), ctx.floats(nw)
+    want_x, want_y = ctx.floats(x), ctx.buffer(rows * 4)
+    ctx.rmsnorm_add(pb, awb, want_x, 1, cols, 1e-6)
+    ctx.q8_0_gemv_fused(w, want_x, want_y, rows, cols, cuda.PRO_RMSNORM, nwb, 1e-6)
+    x_out, y = ctx.floats(np.zeros(cols, np.float32)), ctx.buffer(rows * 4)
+    ctx.q8_0_gemv_addnorm(w, xb, pb, awb, x_out, nwb, y, rows, cols, 1e-6)
+    np.testing.assert_array_equal(x_out.download(0, cols * 4, np.float32), want_x.download(0, cols * 4, np.float32))
+    np.testing.assert_array_equal(y.download(0, rows * 4, np.float32), want_y.download(0, rows * 4, np.float32))
+    np.testing.assert_array_equal(xb.download(0, cols * 4, np.float32), x)  # the input stream is left alone
+    with pytest.raises(cuda.CudaError):
+        ctx.q8_0_gemv_addnorm(w, xb, pb, awb, xb, nwb, y, rows, cols, 1e-6)
+    for b in (w, want_y, y):
+        b.free()
+
+
+def test_output_norm_fold_refuses_wide_rows(ctx):
+    rows, cols = 32, 8192
+    w = ctx.q8_0_matrix(T.q8_0_matrix(1, 2, rows, cols), rows, cols)
+    v = ctx.floats(np.zeros(cols, np.float32))
+    with pytest.raises(cuda.CudaError):
+        ctx.q8_0_gemv_addnorm(w, v, v, v, ctx.floats(np.zeros(cols, np.float32)), v, ctx.buffer(rows * 4), rows, cols, 1e-6)

@@ -335,6 +335,13 @@ public:
     void u32_add_sat(const CudaBuffer &b, uint32_t first, uint32_t count, uint32_t delta, uint32_t limit) const {
         TM_CALL(tm_cuda_u32_add_sat, b.raw(), first, count, delta, limit);
     }
+    // y = W rmsnorm(x + rmsnorm(add_p, add_w), norm_w); x + ... goes to x_out (include/tm_cuda.h).
+    void q8_0_gemv_addnorm(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &add_p, const CudaBuffer &add_w,
+                           const CudaBuffer &x_out, const CudaBuffer &norm_w, const CudaBuffer &y, uint32_t rows,
+                           uint32_t cols, float eps) const {
+        TM_CALL(tm_cuda_q8_0_gemv_addnorm, w.raw(), x.raw(), add_p.raw(), add_w.raw(), x_out.raw(), norm_w.raw(), y.raw(),
+                rows, cols, eps);
+    }
     void q8_0_gemm_fused(const CudaBuffer &w, const CudaBuffer &x, const CudaBuffer &y, uint32_t rows, uint32_t cols,
                          uint32_t batch, int prologue, const CudaBuffer *pro, float eps, int epilogue) const {
         TM_CALL(tm_cuda_q8_0_gemm_fused, w.raw(), x.raw(), y.raw(), rows, cols, batch, prologue,

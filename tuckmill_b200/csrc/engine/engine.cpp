@@ -351,6 +351,25 @@ struct PrefillScratch {
     }
 };
 
+// The residual stream of a one-token step on a model whose layers end in output norms: the vector that
+// is still to be normed and added (`pend_p` with weight `pend_w`) rides along until the next projection
+// consumes it (tm_cuda_q8_0_gemv_addnorm), which writes the updated stream to the other of two buffers.
+struct Residual {
+    const CudaBuffer *cur = nullptr, *alt = nullptr;
+    const CudaBuffer *pend_p = nullptr, *pend_w = nullptr;
+    // y = W rmsnorm(stream, norm_w) with whatever is pending folded in first.
+    void project(const CudaContext &ctx, const CudaBuffer &w, uint32_t rows, uint32_t cols, const CudaBuffer &norm_w,
+                 const CudaBuffer &y, float eps) {
+        if (pend_p) {
+            ctx.q8_0_gemv_addnorm(w, *cur, *pend_p, *pend_w, *alt, norm_w, y, rows, cols, eps);
+            std::swap(cur, alt);
+            pend_p = pend_w = nullptr;
+        } else {
+            ctx.q8_0_gemv_fused(w, *cur, y, rows, cols, TM_CUDA_PRO_RMSNORM, &norm_w, eps, TM_CUDA_EPI_STORE);
+        }
+    }
+};
+
 // What the n rows of a batched pass are: n consecutive positions of sequence `seq` (a prefill chunk),
 // or -- with `pos_buf` set -- one decode row per sequence, sequence s at the device position pos_buf[s].
 struct RowsAre {
@@ -702,6 +721,30 @@ struct Layer {
         }
         ffn.decode(ctx, x, post_norm, hidden);
     }
+    // A one-token step of a layer that ends both halves in an output norm (Gemma): the norm-and-add of
+    // each half is folded into the projection that follows it -- 5 launches instead of 7, the same
+    // arithmetic (tm_cuda_q8_0_gemv_addnorm).
+    bool norms_fold(size_t hidden) const {
+        return slices_apply() && mixer_out_norm && ffn.out_norm && hidden <= 4096;
+    }
+    void decode_folded(const CudaContext &ctx, Residual &R, const CudaBuffer &pos_buf, const CudaBuffer &status,
+                       size_t hidden, float eps, bool exact) const {
+        (void)hidden;
+        R.project(ctx, mixer.qkv.buf, mixer.qkv.rows, mixer.qkv.cols, pre_norm, mixer.qkv_out, eps);
+        ctx.attention_decode_dev(mixer.q_view, mixer.k_view, mixer.v_view, mixer.q_norm, mixer.k_norm, mixer.inv_freq,
+                                 mixer.k_cache, mixer.v_cache, mixer.attn, mixer.kv_scratch, pos_buf, 0, status,
+                                 (uint32_t)mixer.heads_l, (uint32_t)mixer.kv_l, (uint32_t)mixer.spec.head_dim,
+                                 (uint32_t)mixer.spec.rope_dims, (uint32_t)mixer.cap, (uint32_t)mixer.spec.window, eps,
+                                 mixer.scale(), exact);
+        mixer.o.gemv(ctx, mixer.attn, proj);
+        R.pend_p = &proj;
+        R.pend_w = &mixer_out_norm;
+        R.project(ctx, ffn.gate_up.buf, ffn.gate_up.rows, ffn.gate_up.cols, post_norm, ffn.gu, eps);
+        const int pro = ffn.act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
+        ffn.down.gemv_fused(ctx, ffn.g_view, ffn.out, pro, &ffn.u_view, 0.0f, TM_CUDA_EPI_STORE);
+        R.pend_p = &ffn.out;
+        R.pend_w = &ffn.out_norm;
+    }
     // Every matrix Q8_0 on one device: the batched fused GEMV forms apply.
     bool slices_apply() const {
         return mixer.sh.world == 1 && mixer.qkv.type == 8 && mixer.o.type == 8 && ffn.gate_up.type == 8 &&
@@ -796,7 +839,8 @@ struct EngineModel::Impl {
     GatherArena arena;  // declared before the blocks that hold views of it (views are released first)
     CudaBuffer tied_view;  // row split of a tied head: this rank's rows of the (replicated) embedding
     uint32_t head_rows = 0;  // rows of the head this rank multiplies (vocab / world)
-    CudaBuffer final_norm, x, logits, partial, tokens, tokens_mirror, pos_buf, status;
+    CudaBuffer final_norm, x, x2, logits, partial, tokens, tokens_mirror, pos_buf, status;
+    bool fold_norms = false;  // every layer's output norms ride into the next projection (Residual)
     CudaBuffer logits_full, pairs;  // row split only
     std::vector<Layer> layers;
     PrefillScratch scratch;
@@ -903,6 +947,7 @@ GpuAllocPlan alloc_plan_with(const ModelGraph &graph, const WeightSource &src, s
     if (graph.head != graph.embedding) p.weights += Matrix::plan(src, {graph.head}, sh);
     p.weights_f32(vector_len(src, graph.final_norm));
     p.scratch_f32(graph.hidden);              // x
+    p.scratch_f32(graph.hidden);              // x2: the other buffer of a residual stream that alternates
     p.scratch_f32(graph.vocab / sh.world * seqs);  // logits (this rank's slice), a row per sequence
     p.scratch_bytes(kArgmaxPartialBytes * seqs);   // argmax partials
     p.scratch_bytes(token_log_stride(capacity, seqs) * seqs * 4);  // device token logs
@@ -969,6 +1014,7 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
         throw TuckmillError(ErrorCode::UnsupportedArchitecture, "embedding / head shapes do not match the graph");
     I.final_norm = vector(c, src, graph.final_norm);
     I.x = zeros_f32(c, graph.hidden);
+    I.x2 = zeros_f32(c, graph.hidden);
     I.logits = zeros_f32(c, (size_t)I.head_rows * I.seqs);
     if (sh.world > 1) {
         I.logits_full = zeros_f32(c, graph.vocab);
@@ -1006,6 +1052,14 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
         if (const char *e = std::getenv("TM_ENGINE_L2_AHEAD")) ahead = (size_t)std::max(0, std::min(8, std::atoi(e)));
         if (opts.shard_world > 1 || I.persistent) ahead = 0;
         I.l2_ahead = ahead;
+        // Folding the output norms into the next projection (Layer::decode_folded) saves two launches per
+        // layer and is bit-identical, but measured slower on the Gemma-3-1B shape (1344 against 1299 us per
+        // token: every CTA of the wide gate|up projection repeats a second reduction and two more vector
+        // loads, which costs more than the small kernel it replaces): off unless TM_ENGINE_FOLD_NORMS=1.
+        const char *fold = std::getenv("TM_ENGINE_FOLD_NORMS");
+        I.fold_norms = fold && fold[0] == '1' && !I.persistent && opts.shard_world == 1 && I.head_type() == 8 &&
+                       !I.layers.empty();
+        for (const Layer &L : I.layers) I.fold_norms = I.fold_norms && L.norms_fold(g.hidden);
         if (ahead) c.prefetch_l2({&I.final_norm});  // the context's side stream comes into being outside a group
     }
     if (I.persistent) {
@@ -1068,11 +1122,22 @@ void EngineModel::encode_decode_step() {
         c.prefetch_l2({&P.mixer.qkv.buf, &P.mixer.o.buf, &P.ffn.gate_up.buf, &P.ffn.down.buf});
     };
     for (size_t l = 0; l < ahead; ++l) prefetch(l);
-    for (size_t l = 0; l < I.layers.size(); ++l) {
-        prefetch(l + ahead);
-        I.layers[l].decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+    if (I.fold_norms) {
+        Residual R;
+        R.cur = &I.x;
+        R.alt = &I.x2;
+        for (size_t l = 0; l < I.layers.size(); ++l) {
+            prefetch(l + ahead);
+            I.layers[l].decode_folded(c, R, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+        }
+        R.project(c, I.head_buf(), I.head_rows, I.head_cols(), I.final_norm, I.logits, g.eps);
+    } else {
+        for (size_t l = 0; l < I.layers.size(); ++l) {
+            prefetch(l + ahead);
+            I.layers[l].decode(c, I.x, I.pos_buf, I.status, g.hidden, g.eps, opts_.exact);
+        }
+        I.project_head(c, g.eps);
     }
-    I.project_head(c, g.eps);
     if (I.sh.world > 1)
         c.argmax_sharded(I.logits, I.head_rows, I.sh.rank * I.head_rows, I.partial, I.pairs, I.tokens, 1, &I.pos_buf, 0,
                          (uint32_t)capacity_ + 1, &I.tokens_mirror);

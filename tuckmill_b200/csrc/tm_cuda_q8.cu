@@ -51,6 +51,11 @@ struct gemv_args {
     uint32_t plane;         // bytes between digit planes (== 64 mod 128)
     uint32_t ks;            // column splits per row tile (1, 2, 4 or 8)
     uint32_t shape_rows;    // host only: rows of the matrix the column split is chosen for (a row view: its parent's)
+    // kAdd forms only: x' = x + rmsnorm(add_p, add_w, eps) is formed first (a layer's output norm and
+    // residual add, folded into the projection that consumes the result), multiplied after the prologue's
+    // own norm, and written to x_out by CTA 0 (a buffer other than x: every CTA reads x).
+    const float *add_p = nullptr, *add_w = nullptr;
+    float *x_out = nullptr;
 };
 
 // Bytes of shared memory one token's staged activations take.
@@ -76,7 +81,7 @@ __host__ __device__ inline size_t token_smem(uint32_t cols, uint32_t plane) {
  * matrix shape, never on the batch, which keeps a (row, token) result
  * bit-identical between the GEMV and any batched call.
  */
-template <int M, int kSlots, int H>
+template <int M, int kSlots, int H, bool kAdd = false>
 __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float red[kWarps];
@@ -228,6 +233,42 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
                     } else {
                         vs[i] = make_float4(xm[c], xm[c + 1], xm[c + 2], xm[c + 3]);
                         if (pp) ps[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+                    }
+                }
+            }
+            if constexpr (kAdd) {
+                // x' = x + rmsnorm(p) * w, rounded like the stand-alone operator (two multiplies, one add);
+                // the host selects this form only for one-pass widths with the norm prologue
+                float4 pv[kBatch], aw[kBatch];
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const uint32_t c = cb + (i * kThreads + threadIdx.x) * 4u;
+                    pv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    aw[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (c < cols) {
+                        if (vec_ok && (((size_t)a.add_p | (size_t)a.add_w) & 15u) == 0) {
+                            pv[i] = *(const float4 *)(a.add_p + c);
+                            aw[i] = *(const float4 *)(a.add_w + c);
+                        } else {
+                            pv[i] = make_float4(a.add_p[c], a.add_p[c + 1], a.add_p[c + 2], a.add_p[c + 3]);
+                            aw[i] = make_float4(a.add_w[c], a.add_w[c + 1], a.add_w[c + 2], a.add_w[c + 3]);
+                        }
+                    }
+                }
+                float sqp = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) sqp = tmdev::sumsq_quad(sqp, pv[i]);
+                const float inv_add = 1.0f / sqrtf(tmdev::block_reduce_sumsq(sqp, red) / (float)cols + a.eps);
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    vs[i].x = __fadd_rn(vs[i].x, __fmul_rn(__fmul_rn(pv[i].x, inv_add), aw[i].x));
+                    vs[i].y = __fadd_rn(vs[i].y, __fmul_rn(__fmul_rn(pv[i].y, inv_add), aw[i].y));
+                    vs[i].z = __fadd_rn(vs[i].z, __fmul_rn(__fmul_rn(pv[i].z, inv_add), aw[i].z));
+                    vs[i].w = __fadd_rn(vs[i].w, __fmul_rn(__fmul_rn(pv[i].w, inv_add), aw[i].w));
+                    const uint32_t c = cb + (i * kThreads + threadIdx.x) * 4u;
+                    if (blockIdx.x == 0 && c < cols) {
+                        if ((((size_t)a.x_out) & 15u) == 0 && (cols & 3u) == 0) *(float4 *)(a.x_out + c) = vs[i];
+                        else { a.x_out[c] = vs[i].x; a.x_out[c + 1] = vs[i].y; a.x_out[c + 2] = vs[i].z; a.x_out[c + 3] = vs[i].w; }
                     }
                 }
             }
@@ -437,18 +478,24 @@ __global__ void __launch_bounds__(kThreads) q8_gemv_kernel(const gemv_args a) {
     }
 }
 
-template <int M, int kSlots, int H>
-cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
+template <int M, int kSlots, int H, bool kAdd>
+cudaError_t launch_gemv_form(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
     static std::atomic<bool> attr_set[64] = {};  // per device; contexts of a process share it
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M, kSlots, H>,
+        cudaError_t e = cudaFuncSetAttribute(q8_gemv_kernel<M, kSlots, H, kAdd>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)ctx->smem_optin - 8192);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    return tm_launch_pdl(ctx, q8_gemv_kernel<M, kSlots, H>, dim3(grid), dim3(kThreads), smem, a);
+    return tm_launch_pdl(ctx, q8_gemv_kernel<M, kSlots, H, kAdd>, dim3(grid), dim3(kThreads), smem, a);
+}
+template <int M, int kSlots, int H>
+cudaError_t launch_gemv(tm_cuda_ctx *ctx, const gemv_args &a, int grid, size_t smem) {
+    if constexpr (M == 1)
+        if (a.add_p) return launch_gemv_form<M, kSlots, H, true>(ctx, a, grid, smem);
+    return launch_gemv_form<M, kSlots, H, false>(ctx, a, grid, smem);
 }
 
 uint32_t digit_plane_bytes(uint32_t cols) {
@@ -830,6 +877,48 @@ int tm_cuda_q8_0_gemv_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer 
     TM_ENTER();
     return gemv_common(ctx, w, x, y, rows, cols, 1, 0, 0, prologue, pro, eps, epilogue,
                        "q8_0_gemv_fused", err, err_cap);
+}
+
+int tm_cuda_q8_0_gemv_addnorm(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *add_p,
+                              tm_cuda_buffer *add_w, tm_cuda_buffer *x_out, tm_cuda_buffer *norm_w, tm_cuda_buffer *y,
+                              uint32_t rows, uint32_t cols, float eps, char *err, size_t err_cap) {
+    TM_ENTER();
+    int rc = tm_check_packed(ctx, w, rows, cols, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    if (cols > (uint32_t)(kThreads * 16))
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "cols %u above the %d this form stages in one pass", cols,
+                       kThreads * 16);
+    TM_CHECK_BUF(x, (size_t)cols * 4, "x");
+    TM_CHECK_BUF(add_p, (size_t)cols * 4, "vector to add");
+    TM_CHECK_BUF(add_w, (size_t)cols * 4, "its norm weight");
+    TM_CHECK_BUF(x_out, (size_t)cols * 4, "x output");
+    TM_CHECK_BUF(norm_w, (size_t)cols * 4, "norm weight");
+    TM_CHECK_BUF(y, (size_t)rows * 4, "output");
+    if (x_out == x || x_out->dev == x->dev)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "x_out must be a buffer other than x (every CTA reads x)");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator q8_0_gemv_addnorm cannot be recorded into a persistent program");
+    gemv_args a;
+    a.q = (const signed char *)w->qp;
+    a.d = (const __half *)w->dp;
+    a.x = (const float *)x->dev;
+    a.y = (float *)y->dev;
+    a.pro = (const float *)norm_w->dev;
+    a.rows = rows;
+    a.cols = cols;
+    a.shape_rows = rows;
+    for (const tm_cuda_buffer *p = w->parent; p && p->layout == TM_LAYOUT_Q8_0_PACKED; p = p->parent) a.shape_rows = p->rows;
+    a.eps = eps;
+    a.prologue = TM_CUDA_PRO_RMSNORM;
+    a.epilogue = TM_CUDA_EPI_STORE;
+    a.add_p = (const float *)add_p->dev;
+    a.add_w = (const float *)add_w->dev;
+    a.x_out = (float *)x_out->dev;
+    TM_OP_BEGIN("q8_0_gemv_addnorm");
+    uint64_t kernels = 0;
+    rc = gemv_batch(ctx, a, 1, &kernels, err, err_cap);
+    if (rc != TM_CUDA_OK) return rc;
+    TM_OP_END(kernels);
 }
 
 int tm_cuda_q8_0_gemm_fused(tm_cuda_ctx *ctx, tm_cuda_buffer *w, tm_cuda_buffer *x, tm_cuda_buffer *y, uint32_t rows,

@@ -75,6 +75,8 @@ _OPS = {
     "argmax_rows_f32_dev": [_P, _P, _U32, _U32, _P, _P, _U32, _U32, _P, _U32, _P],
     "u32_add_sat": [_P, _P, _U32, _U32, _U32, _U32],
     "reduce_ranks_add_f32": [_P, _P, _P, _P, _U32, _U32, _U32, _F],
+    "prefetch_l2": [_P, _P, _U32],
+    "q8_0_gemv_addnorm": [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _F],
     "begin_group": [_P],
     "end_group": [_P],
     "abort_group": [_P],
@@ -422,6 +424,11 @@ class CudaContext:
         self._call("f16_rows_indirect_f32", w.handle, rows, cols, ids.handle, first, n, scale, out.handle)
 
     # decode steps of several sequences (include/tm_cuda.h)
+    def q8_0_gemv_addnorm(self, w, x, add_p, add_w, x_out, norm_w, y, rows, cols, eps):
+        """y = W rmsnorm(x + rmsnorm(add_p, add_w), norm_w); the updated x goes to x_out (not x itself)."""
+        self._call("q8_0_gemv_addnorm", w.handle, x.handle, add_p.handle, add_w.handle, x_out.handle, norm_w.handle,
+                   y.handle, rows, cols, eps)
+
     def q8_0_gemm_fused(self, w, x, y, rows, cols, batch, prologue=PRO_NONE, pro=None, eps=0.0, epilogue=EPI_STORE):
         self._call("q8_0_gemm_fused", w.handle, x.handle, y.handle, rows, cols, batch, prologue, self._h(pro), eps, epilogue)
 
@@ -443,6 +450,11 @@ class CudaContext:
 
     def u32_add_sat(self, buf, first, count, delta, limit):
         self._call("u32_add_sat", buf.handle, first, count, delta, limit)
+
+    def prefetch_l2(self, bufs):
+        """A hint: bring the buffers' bytes into L2 on a side stream (joins at the end of the open group)."""
+        arr = (C.c_void_p * len(bufs))(*[b.handle for b in bufs])
+        self._call("prefetch_l2", arr, len(bufs))
 
     def reduce_ranks_add(self, slots, x, weight, world, n_rows, cols, eps=0.0):
         self._call("reduce_ranks_add_f32", slots.handle, x.handle, self._h(weight), world, n_rows, cols, eps)

@@ -82,7 +82,7 @@ def test_mma_gemm_large_shapes_every_instantiation(ctx, oracle, rows, cols, batc
 # Few output tiles (decode batches, narrow projections): the K range is cut into parts whose sums meet
 # in a workspace and are added in part order.  (rows, cols, batch, expected parts)
 SPLIT_CASES = [(4096, 12288, 32, 4), (6144, 4096, 32, 2), (1024, 3072, 64, 8), (1024, 2048, 17, 8),
-               (4096, 1024, 32, 4), (2048, 4096, 300, 2), (12288, 4096, 32, 1)]
+               (4096, 1024, 32, 4), (2048, 4096, 300, 2), (12288, 4096, 32, 1), (24576, 4096, 32, 2)]
 
 
 @pytest.mark.parametrize("rows,cols,batch,parts", SPLIT_CASES)

@@ -48,14 +48,17 @@ constexpr int kWarpRaw = kConvWarps + kEpiWarps, kWarpTok = kWarpRaw + 1, kWarpM
 constexpr int kMmaThreads = (kWarpMma + kIssuers) * 32;
 constexpr int kScaleAhead = 4;  // a converter's own steps (every other K step) between a scale's load and its use
 constexpr uint32_t kSpinLimit = 1u << 20;  // a healthy wait is microseconds; this is ~seconds
-// Split-K: when a call has fewer output tiles than half the SMs (a decode batch, a narrow projection)
-// the K range of every tile is cut into `ksplit` equal parts, each its own tile of the persistent grid;
+// Split-K: when it shortens the longest CTA's run (few output tiles on many SMs: a decode batch, a narrow
+// projection, a last round that leaves most SMs idle) the K range of every tile is cut into `ksplit`
+// equal parts, each its own tile of the persistent grid;
 // the parts' accumulators meet in a workspace slot per (tile, part) and the warp that arrives last for a
 // (tile, row quarter) adds them IN PART ORDER and runs the epilogue -- no waiting, and a sum that does not
 // depend on which part finished last.
-constexpr uint32_t kSplitSlots = 148;                       // (output tile, part) slots of the workspace
-constexpr uint32_t kSplitSlotFloats = 128u * 256u;          // 128 rows x the 256 tokens of the widest split tile
-constexpr size_t kSplitCountBytes = 4096;                   // kSplitSlots x 4 row quarters of u32, rounded
+// The workspace holds 148 slots of the widest split tile (128 rows x 256 tokens); narrower tiles pack
+// more (output tile, part) slots into the same bytes.  Arrival counters: 4 row quarters per output tile.
+constexpr uint32_t kSplitSlots = 148;
+constexpr uint32_t kSplitSlotFloats = 128u * 256u;
+constexpr size_t kSplitCountBytes = 4096;                   // up to 256 output tiles x 4 x u32
 constexpr size_t kSplitBytes = (size_t)kSplitSlots * kSplitSlotFloats * 4 + kSplitCountBytes;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -158,6 +161,7 @@ struct mma_args {
     uint32_t accumulate;   // 1: Y += W X (the residual add folded into the epilogue)
     uint32_t ksplit;       // K parts per output tile (1: none)
     float *kpart;          // [slot][token][128 rows] partial accumulators, slot = output tile * ksplit + part
+    uint32_t kslot;        // floats per slot: 128 rows x the tokens of a tile (rounded up to 32)
     uint32_t *kcount;      // [output tile][4 row quarters] arrivals (left at zero)
     // Row split: the epilogue stores this rank's rows straight into EVERY rank's gathered
     // Y[t][rank * rows + r] (peer memory, plain stores over NVLink), so the all-gather overlaps the
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0u;
                     for (uint32_t pp = 0; pp < ksplit; ++pp) {
-                        const float *src = a.kpart + (size_t)(ot * ksplit + pp) * kSplitSlotFloats + at;
+                        const float *src = a.kpart + (size_t)(ot * ksplit + pp) * a.kslot + at;
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = __ldcg(src + (size_t)j * 128u);
@@ -423,7 +427,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 }
                 if (ksplit > 1u && pass == 0u) {
-                    float *dst = a.kpart + (size_t)(ot * ksplit + part) * kSplitSlotFloats +
+                    float *dst = a.kpart + (size_t)(ot * ksplit + part) * a.kslot +
                                  ((size_t)(sub * BN + (uint32_t)c0)) * 128u + quarter * 32u + (uint32_t)lane;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) dst[(size_t)j * 128u] = __uint_as_float(v[j]);
@@ -771,19 +775,30 @@ static int mma_launch(tm_cuda_ctx *ctx, const tm_cuda_buffer *w, uint32_t rows, 
         a.part_end[p] = part_end[p];
     }
     a.accumulate = accumulate ? 1u : 0u;
-    // Split K when the output tiles leave more than half of the SMs idle (never for the pushing form).
+    // Split K: the K range of every output tile is cut into `ksplit` equal parts when that shortens the
+    // longest CTA's run -- rounds of the persistent grid x (K steps of a part + the fixed cost of a tile,
+    // about 4 steps, + 2 for the ordered reduction) -- and the parts' accumulators fit the workspace
+    // (never for the pushing form).
     a.ksplit = 1;
+    const uint32_t tile_tokens = batch < 2u * (uint32_t)bn ? (batch + 31u) / 32u * 32u : 2u * (uint32_t)bn;
+    a.kslot = 128u * tile_tokens;
     {
         const uint32_t out_tiles = row_tiles * ((batch + 2 * bn - 1) / (2 * bn)), nkb = (cols + kBK - 1) / kBK;
-        const uint32_t room = sms < kSplitSlots ? sms : kSplitSlots;
         static const bool off = [] { const char *e = getenv("TM_CUDA_MMA_SPLITK"); return e && e[0] == '0'; }();
-        if (!off && push.world == 0 && bn <= 128 && cols % kBK == 0 && out_tiles * 2 <= sms &&
-            ctx->mma_scratch_bytes >= kSplitBytes)
-            for (uint32_t cand : {8u, 6u, 4u, 3u, 2u})
-                if (nkb % cand == 0 && nkb / cand >= 4 && out_tiles * cand <= room) {
+        if (!off && push.world == 0 && bn <= 128 && cols % kBK == 0 && out_tiles * 16 <= kSplitCountBytes &&
+            ctx->mma_scratch_bytes >= kSplitBytes) {
+            const uint64_t whole = (uint64_t)((out_tiles + sms - 1) / sms) * (nkb + 4);
+            uint64_t best = whole;
+            for (uint32_t cand : {2u, 3u, 4u, 6u, 8u}) {
+                if (nkb % cand != 0 || nkb / cand < 4) continue;
+                if ((uint64_t)out_tiles * cand * a.kslot > (uint64_t)kSplitSlots * kSplitSlotFloats) continue;
+                const uint64_t cost = (uint64_t)((out_tiles * cand + sms - 1) / sms) * (nkb / cand + 6);
+                if (cost < best && cost * 10 < whole * 9) {  // a split has to pay for its reduction
+                    best = cost;
                     a.ksplit = cand;
-                    break;
                 }
+            }
+        }
     }
     unsigned char *split_base = ctx->mma_scratch + ((ctx->mma_scratch_bytes >= kSplitBytes ? ctx->mma_scratch_bytes - kSplitBytes : 0) & ~(size_t)255);
     a.kpart = (float *)split_base;

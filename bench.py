@@ -640,6 +640,11 @@ def row_split_leg(args, E, dist, torch, rank, local, world, path, context, shape
         "e2e_decode_tok_s": (st.generated - 1) / (span_ms / 1e3),
         "per_rank_weight_bytes": int(info.plan_weights), "per_rank_kv_bytes": int(info.plan_state),
         "tokens_equal_single_device": bool(replica_tokens is not None and list(tokens) == list(replica_tokens)),
+        # The column-split projections add their partial sums in rank order, not in the single-device order:
+        # the streams may part at a near-tie (tolerance mode); how long they agree is reported beside the flag.
+        "tokens_common_prefix": (None if replica_tokens is None else
+                                 next((i for i, (a, b) in enumerate(zip(tokens, replica_tokens)) if a != b),
+                                      min(len(tokens), len(replica_tokens)))),
     }
     eng.close()
     if args.sequences > 1:

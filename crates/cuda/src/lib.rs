@@ -186,6 +186,7 @@ mod ffi {
         pub fn tm_cuda_symm_status(ctx: *mut TmCudaCtx, buf: *mut TmCudaBuffer, status: *mut u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_argmax_sharded_dev(ctx: *mut TmCudaCtx, x: *mut TmCudaBuffer, n: u32, index_offset: u32, partial: *mut TmCudaBuffer, pairs: *mut TmCudaBuffer, out: *mut TmCudaBuffer, base: u32, pos_buf: *mut TmCudaBuffer, pos_index: u32, out_cap: u32, mirror: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_reduce_ranks_add_f32(ctx: *mut TmCudaCtx, slots: *mut TmCudaBuffer, x: *mut TmCudaBuffer, weight: *mut TmCudaBuffer, world: u32, n_rows: u32, cols: u32, eps: f32, err: *mut c_char, err_cap: usize) -> c_int;
+        pub fn tm_cuda_exchange_add_ll_f32(ctx: *mut TmCudaCtx, src: *mut TmCudaBuffer, slots: *mut TmCudaBuffer, y: *mut TmCudaBuffer, width: u32, err: *mut c_char, err_cap: usize) -> c_int;
         pub fn tm_cuda_argmax_rows_sharded_dev(ctx: *mut TmCudaCtx, x: *mut TmCudaBuffer, n_rows: u32, n: u32, index_offset: u32, partial: *mut TmCudaBuffer, pairs: *mut TmCudaBuffer, out: *mut TmCudaBuffer, out_stride: u32, base: u32, pos_buf: *mut TmCudaBuffer, out_cap: u32, mirror: *mut TmCudaBuffer, err: *mut c_char, err_cap: usize) -> c_int;
     }
 }

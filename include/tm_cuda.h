@@ -629,6 +629,18 @@ int tm_cuda_argmax_sharded_dev(tm_cuda_ctx *ctx, tm_cuda_buffer *x, uint32_t n, 
  * RMS-normed with that weight before it is added (a layer's output norm; slot 0 is overwritten). */
 int tm_cuda_reduce_ranks_add_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *slots, tm_cuda_buffer *x, tm_cuda_buffer *weight,
                                  uint32_t world, uint32_t n_rows, uint32_t cols, float eps, char *err, size_t err_cap);
+/* No counterpart.  The push and the reduction above as ONE launch for one row (a decode step of one
+ * sequence): y[c] += src_0[c] + src_1[c] + ... over the ranks' `src` rows, added in rank order (the
+ * bits of tm_cuda_push_rows_f32 + tm_cuda_reduce_ranks_add_f32 without a weight).  `slots` is a
+ * view of a symmetric buffer of world * width 8-byte words: every value travels as a (value,
+ * exchange number) pair written with one store, and a reader polls the pair it needs until it carries
+ * this exchange's number -- no fence, no flag, no second kernel.  The polls are bounded; one that runs
+ * out sets bit 0 of tm_cuda_symm_status and the sum takes what the slot holds.  Every rank must issue
+ * the same sequence of these calls on the buffer, and two CONSECUTIVE calls must not use the same
+ * view (a fast rank would overwrite a pair a slow rank has not read yet); a view may be reused
+ * once another exchange lies between. */
+int tm_cuda_exchange_add_ll_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *slots, tm_cuda_buffer *y,
+                                uint32_t width, char *err, size_t err_cap);
 /* The same for n_rows rows in one exchange (a decode step of several sequences on a split model):
  * row r of the local [n_rows][n] logits slice; its winner over all ranks goes to
  * out[r * out_stride + base + pos_buf[r]] when that slot is below out_cap <= out_stride.

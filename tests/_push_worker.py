@@ -44,6 +44,42 @@ def main() -> None:
     assert ctx.symm_status(arena) == 0
     g.free()
 
+    # The one-row exchange with the sum folded in (8-byte value/number pairs, one launch): two views
+    # in turn, eagerly and from a replayed dispatch group, against the rank-ordered f32 sum.
+    for width in (300, 4096):
+        pairs = ctx.symm_buffer(2 * width * world * 8)
+        views = [pairs.view(i * width * world * 8, width * world * 8) for i in range(2)]
+        y_host = np.linspace(-1, 1, width, dtype=np.float32)
+        y = ctx.floats(y_host)
+
+        def part(r, rnd):
+            return (np.sin(np.arange(width, dtype=np.float32) * (r + 1) + rnd) * (1 + r)).astype(np.float32)
+
+        def expect(yh, rnd):
+            p = part(0, rnd)
+            for r in range(1, world):
+                p = (p + part(r, rnd)).astype(np.float32)
+            return (yh + p).astype(np.float32)
+
+        for rnd in range(8):
+            src = ctx.floats(part(rank, rnd))
+            ctx.exchange_add_ll(src, views[rnd % 2], y, width)
+            y_host = expect(y_host, rnd)
+            assert np.array_equal(y.download(0, width * 4, np.float32), y_host), (width, rnd)
+        src = ctx.floats(part(rank, 99))
+        ctx.begin_group()
+        for i in range(4):
+            ctx.exchange_add_ll(src, views[i % 2], y, width)
+        g = ctx.end_group_retain()
+        for _ in range(3):
+            g.launch()
+        ctx.fence()
+        for _ in range(12):
+            y_host = expect(y_host, 99)
+        assert np.array_equal(y.download(0, width * 4, np.float32), y_host), width
+        assert ctx.symm_status(pairs) == 0
+        g.free()
+
     # GEMM and exchange as one kernel: this rank multiplies its rows and its epilogue writes them
     # into every rank's gathered Y; the result must be the whole product on every rank.
     import oracle

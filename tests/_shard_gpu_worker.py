@@ -26,7 +26,10 @@ def main() -> None:
                      generated=stats.generated)
         eng.close()
         return
-    eng = E.Engine(path, context=96, device=rank, exact=(mode == "exact"), prefill_batch=16, shard_rank=rank,
+    if mode.endswith("-pair"):  # a decode step's exchanges as single launches of (value, number) pairs
+        import os
+        os.environ["TM_ENGINE_PAIR_EXCHANGE"] = "1"
+    eng = E.Engine(path, context=96, device=rank, exact=mode.startswith("exact"), prefill_batch=16, shard_rank=rank,
                    shard_world=world, comm_id=bytes.fromhex(comm_hex))
     info = eng.refresh_info()
     assert info.allocated_bytes == info.plan_weights + info.plan_state + info.plan_scratch

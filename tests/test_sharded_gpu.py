@@ -33,7 +33,7 @@ def run_ranks(world, path, mode, out):
     return np.load(out)
 
 
-@pytest.mark.parametrize("mode", ["exact", "mma"])
+@pytest.mark.parametrize("mode", ["exact", "mma", "exact-pair", "mma-pair"])
 def test_two_device_split_matches_single_device_and_oracle(oracle, tmp_path, mode):
     if cuda.available() < 2:
         pytest.skip("needs two devices")
@@ -43,7 +43,7 @@ def test_two_device_split_matches_single_device_and_oracle(oracle, tmp_path, mod
     got = run_ranks(2, path, mode, tmp_path / "rank0.npz")
 
     toks = T.token_ids(5, 24, shape.vocab)
-    one = E.Engine(path, context=96, exact=(mode == "exact"), prefill_batch=16)
+    one = E.Engine(path, context=96, exact=mode.startswith("exact"), prefill_batch=16)
     scored = one.score(toks)
     one.reset()
     one.prefill(toks, want_token=True)
@@ -56,7 +56,7 @@ def test_two_device_split_matches_single_device_and_oracle(oracle, tmp_path, mod
     scale = max(1.0, float(np.max(np.abs(scored))))
     # The GEMV's column split depends on the matrix shape, so a rank's rows may be
     # summed in another order than the whole matrix's: tolerance, not identity.
-    tol = 1e-4 if mode == "exact" else 2e-2
+    tol = 1e-4 if mode.startswith("exact") else 2e-2
     assert np.max(np.abs(got["scored"] - scored)) <= 1e-4 * scale
     assert np.max(np.abs(got["prefill_logits"] - prefill_logits)) <= tol * scale
     assert int(got["prefill_token"]) == prefill_token == int(np.argmax(got["prefill_logits"]))

@@ -379,6 +379,10 @@ public:
         TM_CALL(tm_cuda_reduce_ranks_add_f32, slots.raw(), x.raw(), weight ? weight->raw() : nullptr, world, n_rows, cols,
                 eps);
     }
+    // y += sum over ranks of their `src` rows: push, reduction and add as one launch (one row).
+    void exchange_add_ll(const CudaBuffer &src, const CudaBuffer &slots, const CudaBuffer &y, uint32_t width) const {
+        TM_CALL(tm_cuda_exchange_add_ll_f32, src.raw(), slots.raw(), y.raw(), width);
+    }
     void argmax_rows_sharded(const CudaBuffer &x, uint32_t n_rows, uint32_t n, uint32_t index_offset,
                              const CudaBuffer &partial, const CudaBuffer &pairs, const CudaBuffer &out,
                              uint32_t out_stride, uint32_t base, const CudaBuffer &pos, uint32_t out_cap,

@@ -46,6 +46,9 @@ struct GatherArena {
 struct Shard {
     uint32_t rank = 0, world = 1;
     GatherArena *arena = nullptr;  // set while loading a split model
+    // One-row exchanges as a single launch of (value, number) pairs (tm_cuda_exchange_add_ll_f32)
+    // instead of push + reduction; the one-row targets are sized for the pairs either way.
+    bool pair_exchange = false;
 };
 
 // Gather targets of a row split are exchange buffers every rank can store into.
@@ -398,7 +401,7 @@ struct SwiGluBlock {
                      (sh.world > 1 ? Matrix::plan_cols(src, f.down, sh) : Matrix::plan(src, {f.down}));
         if (has_norm) p.weights_f32(vector_len(src, norm));
         p.scratch_f32(2 * f.width / sh.world);
-        p.target_f32(hidden * sh.world, sh.world);  // out: one slot per rank when split
+        p.target_f32(hidden * sh.world * (sh.world > 1 ? 2 : 1), sh.world);  // out: one slot per rank when split (8-byte pairs)
         if (sh.world > 1) p.scratch_f32(hidden);    // out_local
     }
     static SwiGluBlock load(const CudaContext &ctx, const WeightSource &src, const FfnSpec &f, bool has_norm,
@@ -417,7 +420,7 @@ struct SwiGluBlock {
         b.gu = zeros_f32(ctx, 2 * b.wl);
         b.g_view = b.gu.view(0, b.wl * 4);
         b.u_view = b.gu.view(b.wl * 4, b.wl * 4);
-        b.out = gather_target_f32(ctx, hidden * sh.world, sh);
+        b.out = gather_target_f32(ctx, hidden * sh.world * (sh.world > 1 ? 2 : 1), sh);
         if (sh.world > 1) b.out_local = zeros_f32(ctx, hidden);
         if (b.down.rows != hidden || b.down.cols != b.wl)
             throw TuckmillError(ErrorCode::UnsupportedArchitecture, "down projection shape does not match the FFN width");
@@ -433,6 +436,10 @@ struct SwiGluBlock {
         const int pro = act == GluActivation::Silu ? TM_CUDA_PRO_SILU_MUL : TM_CUDA_PRO_GELU_MUL;
         if (sh.world > 1) {  // this rank's columns of down, then the ranks' partial products added (4 launches)
             down.gemv_fused(ctx, g_view, out_local, pro, &u_view, 0.0f, TM_CUDA_EPI_STORE);
+            if (sh.pair_exchange && !out_norm) {
+                ctx.exchange_add_ll(out_local, out, x, (uint32_t)hidden);
+                return;
+            }
             ctx.push_rows(out_local, out, 1, (uint32_t)hidden);
             ctx.reduce_ranks_add(out, x, out_norm ? &out_norm : nullptr, sh.world, 1, (uint32_t)hidden, eps);
             return;
@@ -691,7 +698,7 @@ struct Layer {
         p.weights_f32(vector_len(src, l.pre_norm));
         p.weights_f32(vector_len(src, l.post_norm));
         if (l.has_mixer_out_norm) p.weights_f32(vector_len(src, l.mixer_out_norm));
-        p.target_f32(g.hidden * sh.world, sh.world);  // proj: one slot per rank when split
+        p.target_f32(g.hidden * sh.world * (sh.world > 1 ? 2 : 1), sh.world);  // proj: one slot per rank when split (8-byte pairs)
         AttentionBlock::plan(l.mixer, src, cap, g.hidden, sh, p, seqs);
         SwiGluBlock::plan(l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, src, sh, p);
     }
@@ -701,7 +708,7 @@ struct Layer {
         L.pre_norm = vector(ctx, src, l.pre_norm);
         if (l.has_mixer_out_norm) L.mixer_out_norm = vector(ctx, src, l.mixer_out_norm);
         L.post_norm = vector(ctx, src, l.post_norm);
-        L.proj = gather_target_f32(ctx, g.hidden * sh.world, sh);
+        L.proj = gather_target_f32(ctx, g.hidden * sh.world * (sh.world > 1 ? 2 : 1), sh);
         L.mixer = AttentionBlock::load(ctx, src, l.mixer, g.eps, cap, g.hidden, sh, seqs);
         L.ffn = SwiGluBlock::load(ctx, src, l.ffn, l.has_ffn_out_norm, l.ffn_out_norm, g.hidden, g.eps, sh);
         return L;
@@ -709,7 +716,10 @@ struct Layer {
     void decode(const CudaContext &ctx, const CudaBuffer &x, const CudaBuffer &pos_buf, const CudaBuffer &status,
                 size_t hidden, float eps, bool exact) const {
         mixer.decode(ctx, x, pre_norm, pos_buf, status, exact);
-        if (mixer.sh.world > 1) {
+        if (mixer.sh.world > 1 && mixer.sh.pair_exchange && !mixer_out_norm) {
+            mixer.o.gemv(ctx, mixer.attn, mixer.proj_local);
+            ctx.exchange_add_ll(mixer.proj_local, proj, x, (uint32_t)hidden);
+        } else if (mixer.sh.world > 1) {
             mixer.project_sharded(ctx, proj, hidden);
             ctx.reduce_ranks_add(proj, x, mixer_out_norm ? &mixer_out_norm : nullptr, mixer.sh.world, 1, (uint32_t)hidden,
                                  eps);
@@ -993,7 +1003,10 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // Split model: the exchange arena first (one collective allocation every rank maps), then the
     // blocks take their gather targets from it in plan order.
     if (opts.shard_world > 1) I.arena.buf = c.symm_zeros(m->plan_.gather);
-    const Shard sh{opts.shard_rank, opts.shard_world, opts.shard_world > 1 ? &I.arena : nullptr};
+    Shard sh{opts.shard_rank, opts.shard_world, opts.shard_world > 1 ? &I.arena : nullptr};
+    // The single-launch pair exchange of a one-sequence decode step: off unless every rank's
+    // environment sets TM_ENGINE_PAIR_EXCHANGE=1.
+    if (const char *e = std::getenv("TM_ENGINE_PAIR_EXCHANGE")) sh.pair_exchange = opts.shard_world > 1 && e[0] == '1';
     I.sh = sh;
     I.seqs = opts.sequences;
     I.log_stride = token_log_stride(capacity, I.seqs);

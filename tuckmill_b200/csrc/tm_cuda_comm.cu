@@ -217,6 +217,82 @@ __global__ void __launch_bounds__(256) push_rows_kernel(const push_args a) {
     tm_symm_finish(a.peer, a.tail_off, a.world, a.rank, s_flag);
 }
 
+// One-row exchange with the sum folded in, for a decode step's partial products: every word on the
+// wire is an 8-byte (value, sequence number) pair, written with ONE store into this rank's slot on
+// every peer, so a reader needs no fence and no flag -- it polls the word it wants until the pair
+// carries this exchange's number.  Each thread sends its column of the rank's partial row, collects
+// the same column from every other rank's slot (all loads issued together, re-polled only where the
+// number is old), adds the ranks' values in rank order and adds the sum to y: the exchange, the
+// reduction and the residual add are one launch.  Every poll loop is bounded; one that runs out sets
+// the buffer's status bit 0 and goes on with whatever the slot holds.
+struct ll_args {
+    const float *src;        // [width] this rank's partial row
+    float *y;                // [width] += sum over ranks
+    float *const *peer;      // device table: the arena on every rank
+    uint32_t world, rank, width;
+    uint32_t tail_off;       // float offset of the flag tail inside the arena
+    uint32_t dst_off;        // float offset of the slot view [world][width] of 8-byte pairs
+};
+constexpr uint32_t kLlSpinLimit = 1u << 21;  // polls of ~0.5 us: about a second
+
+__device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) exchange_add_ll_kernel(const ll_args a) {
+    tmdev::pdl_trigger();
+    tmdev::pdl_wait();
+    uint32_t *tail = (uint32_t *)(a.peer[a.rank] + a.tail_off);
+    const uint32_t seq = *(volatile uint32_t *)(tail + 80) + 1u;  // the same number on every rank
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+    if (i < a.width) {
+        const float own = a.src[i];
+        const unsigned long long word = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(own);
+        for (uint32_t r = 0; r < a.world; ++r) {
+            if (r == a.rank) continue;
+            unsigned long long *q = (unsigned long long *)(a.peer[r] + a.dst_off) + (size_t)a.rank * a.width + i;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(q), "l"(word) : "memory");
+        }
+        const unsigned long long *mine = (const unsigned long long *)(a.peer[a.rank] + a.dst_off) + i;
+        float p = 0.0f;
+        for (uint32_t r0 = 0; r0 < a.world; r0 += 8) {
+            unsigned long long w[8];
+#pragma unroll
+            for (uint32_t k = 0; k < 8; ++k)
+                w[k] = r0 + k < a.world && r0 + k != a.rank ? ll_load(mine + (size_t)(r0 + k) * a.width) : 0ull;
+#pragma unroll
+            for (uint32_t k = 0; k < 8; ++k) {
+                const uint32_t r = r0 + k;
+                if (r >= a.world) break;
+                float v = own;
+                if (r != a.rank) {
+                    uint32_t spin = 0;
+                    while ((uint32_t)(w[k] >> 32) != seq) {
+                        if (++spin > kLlSpinLimit) {
+                            atomicOr(tail + 72, 1u);
+                            break;
+                        }
+                        w[k] = ll_load(mine + (size_t)r * a.width);
+                    }
+                    v = __uint_as_float((uint32_t)w[k]);
+                }
+                p = r == 0 ? v : __fadd_rn(p, v);
+            }
+        }
+        a.y[i] = __fadd_rn(a.y[i], p);
+    }
+    // The block that finishes last publishes the number: the next exchange on this rank reads it.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(tail + 84, 1u) == gridDim.x - 1u) {
+            tail[84] = 0u;
+            *(volatile uint32_t *)(tail + 80) = seq;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -488,6 +564,36 @@ int tm_cuda_push_rows_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer 
     int grid = (int)((work + 255) / 256);
     grid = grid < 1 ? 1 : grid > ctx->sm_count * 2 ? ctx->sm_count * 2 : grid;
     TM_CUDA_TRY(tm_launch_pdl(ctx, push_rows_kernel, dim3(grid), dim3(256), 0, a));
+    TM_OP_END(1);
+}
+
+int tm_cuda_exchange_add_ll_f32(tm_cuda_ctx *ctx, tm_cuda_buffer *src, tm_cuda_buffer *slots, tm_cuda_buffer *y,
+                                uint32_t width, char *err, size_t err_cap) {
+    TM_ENTER();
+    if (width == 0) return tm_fail(err, err_cap, TM_CUDA_ERR_BOUNDS, "empty exchange");
+    tm_cuda_buffer *root = slots && slots->parent ? slots->parent : slots;
+    if (!slots || ctx->live.find(slots) == ctx->live.end() || !root || !root->symm)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "the slots are not (a view of) a symmetric buffer of this context");
+    symm_state *st = (symm_state *)root->symm;
+    const size_t dst_off = (size_t)(slots->dev - root->dev);
+    if (dst_off % 16 != 0) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "slot view is not 16-byte aligned");
+    TM_CHECK_BUF(src, (size_t)width * 4, "partial row");
+    TM_CHECK_BUF(y, (size_t)width * 4, "accumulated row");
+    TM_CHECK_BUF(slots, (size_t)width * (size_t)st->world * 8, "exchange slots");
+    if (src == slots || y == slots) return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "exchange in place");
+    if (ctx->program)
+        return tm_fail(err, err_cap, TM_CUDA_ERR_UNSUPPORTED, "operator exchange_add_ll cannot be recorded into a persistent program");
+    TM_OP_BEGIN("exchange_add_ll");
+    ll_args a;
+    a.src = (const float *)src->dev;
+    a.y = (float *)y->dev;
+    a.peer = (float *const *)st->d_peer;
+    a.world = (uint32_t)st->world;
+    a.rank = (uint32_t)st->rank;
+    a.width = width;
+    a.tail_off = (uint32_t)(st->payload / 4);
+    a.dst_off = (uint32_t)(dst_off / 4);
+    TM_CUDA_TRY(tm_launch_pdl(ctx, exchange_add_ll_kernel, dim3((width + 255) / 256), dim3(256), 0, a));
     TM_OP_END(1);
 }
 

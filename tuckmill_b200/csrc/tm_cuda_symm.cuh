@@ -5,7 +5,7 @@
 #include "tm_cuda_internal.cuh"
 
 constexpr int kSymmMaxWorld = 16;
-constexpr uint32_t kSymmTail = 512;        // u32 flags[16] | u32 seq @64 | u32 block counter @68 | u32 status @72
+constexpr uint32_t kSymmTail = 512;        // u32 flags[16] | u32 seq @64 | u32 block counter @68 | u32 status @72 | pair-exchange number @80, its block counter @84
 constexpr uint32_t kSymmSpinLimit = 1u << 24;
 
 struct tm_symm_state {

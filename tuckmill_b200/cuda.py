@@ -75,6 +75,7 @@ _OPS = {
     "argmax_rows_f32_dev": [_P, _P, _U32, _U32, _P, _P, _U32, _U32, _P, _U32, _P],
     "u32_add_sat": [_P, _P, _U32, _U32, _U32, _U32],
     "reduce_ranks_add_f32": [_P, _P, _P, _P, _U32, _U32, _U32, _F],
+    "exchange_add_ll_f32": [_P, _P, _P, _P, _U32],
     "prefetch_l2": [_P, _P, _U32],
     "q8_0_gemv_addnorm": [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _F],
     "begin_group": [_P],
@@ -455,6 +456,9 @@ class CudaContext:
         """A hint: bring the buffers' bytes into L2 on a side stream (joins at the end of the open group)."""
         arr = (C.c_void_p * len(bufs))(*[b.handle for b in bufs])
         self._call("prefetch_l2", arr, len(bufs))
+
+    def exchange_add_ll(self, src, slots, y, width):
+        self._call("exchange_add_ll_f32", src.handle, slots.handle, y.handle, width)
 
     def reduce_ranks_add(self, slots, x, weight, world, n_rows, cols, eps=0.0):
         self._call("reduce_ranks_add_f32", slots.handle, x.handle, self._h(weight), world, n_rows, cols, eps)

@@ -26,9 +26,9 @@ def main() -> None:
                      generated=stats.generated)
         eng.close()
         return
-    if mode.endswith("-pair"):  # a decode step's exchanges as single launches of (value, number) pairs
-        import os
-        os.environ["TM_ENGINE_PAIR_EXCHANGE"] = "1"
+    import os
+    # a decode step's exchanges: single launches of (value, number) pairs, or push + reduction
+    os.environ["TM_ENGINE_PAIR_EXCHANGE"] = "1" if mode.endswith("-pair") else "0"
     eng = E.Engine(path, context=96, device=rank, exact=mode.startswith("exact"), prefill_batch=16, shard_rank=rank,
                    shard_world=world, comm_id=bytes.fromhex(comm_hex))
     info = eng.refresh_info()

@@ -1004,9 +1004,10 @@ std::unique_ptr<EngineModel> EngineModel::load_with(std::shared_ptr<CudaContext>
     // blocks take their gather targets from it in plan order.
     if (opts.shard_world > 1) I.arena.buf = c.symm_zeros(m->plan_.gather);
     Shard sh{opts.shard_rank, opts.shard_world, opts.shard_world > 1 ? &I.arena : nullptr};
-    // The single-launch pair exchange of a one-sequence decode step: off unless every rank's
-    // environment sets TM_ENGINE_PAIR_EXCHANGE=1.
-    if (const char *e = std::getenv("TM_ENGINE_PAIR_EXCHANGE")) sh.pair_exchange = opts.shard_world > 1 && e[0] == '1';
+    // The single-launch pair exchange of a one-sequence decode step (TM_ENGINE_PAIR_EXCHANGE=0 in
+    // every rank's environment goes back to push + reduction).
+    sh.pair_exchange = opts.shard_world > 1;
+    if (const char *e = std::getenv("TM_ENGINE_PAIR_EXCHANGE")) sh.pair_exchange = opts.shard_world > 1 && e[0] != '0';
     I.sh = sh;
     I.seqs = opts.sequences;
     I.log_stride = token_log_stride(capacity, I.seqs);

@@ -233,7 +233,7 @@ struct ll_args {
     uint32_t tail_off;       // float offset of the flag tail inside the arena
     uint32_t dst_off;        // float offset of the slot view [world][width] of 8-byte pairs
 };
-constexpr uint32_t kLlSpinLimit = 1u << 21;  // polls of ~0.5 us: about a second
+constexpr uint32_t kLlSpinLimit = 1u << 23;  // re-polls of ~0.5 us: a few seconds (ranks start a step from their own hosts)
 
 __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
     unsigned long long v;

@@ -61,6 +61,10 @@ def test_per_rank_plan_divides_projections_and_kv(tmp_path):
     norms = 4 * (s.layers * (2 * s.hidden + 2 * hd) + s.hidden)
     assert ranks[0].plan_weights == mats + norms
     assert ranks[0].plan_weights < whole.plan_weights
+    # the one-row exchange slots of every layer (o and down): one 8-byte (value, number) pair per
+    # column and rank, priced on every rank alike
+    assert ranks[0].plan_scratch == ranks[1].plan_scratch
+    assert ranks[0].plan_scratch >= s.layers * 2 * s.hidden * W * 8
 
 
 def test_split_refusals_are_typed(tmp_path):

@@ -48,6 +48,26 @@ def run(rank: int, world: int, port: int, out_path: str) -> None:
         dist.all_gather(check, torch.from_numpy(summed))
         assert all(np.array_equal(c.numpy(), summed) for c in check), "ranks disagree on the reduced product"
 
+        # The decode row's exchange as (value, number) words: two exchanges in turn on two slot views; a
+        # stale view (the number of an earlier exchange) is recognised, the sum is the rank-ordered one.
+        views = [None, None]
+        for number in (1, 2, 3):
+            row = part[number % n]
+            mine = torch.from_numpy(S.pair_words(row, number).view(np.int64))
+            got = [torch.empty(rows, dtype=torch.int64) for _ in range(world)]
+            dist.all_gather(got, mine)
+            views[number % 2] = np.stack([g.numpy().view(np.uint64) for g in got])
+            vals = [S.read_pairs(views[number % 2][r], number) for r in range(world)]
+            assert np.array_equal(vals[rank], row)
+            row_slots = [torch.empty(rows) for _ in range(world)]
+            dist.all_gather(row_slots, torch.from_numpy(np.ascontiguousarray(row)))
+            assert np.array_equal(S.reduce_ranks(vals), S.reduce_ranks([p.numpy() for p in row_slots]))
+        try:
+            S.read_pairs(views[0][0], 3)  # view 0 still holds exchange 2
+            raise AssertionError("a stale word passed for a fresh one")
+        except ValueError:
+            pass
+
         # Sharded greedy choice: 8 bytes per rank instead of the logits.
         picks = []
         for t in range(n):

@@ -8,7 +8,8 @@ rank, and the two projections that consume them, o and down, are cut the other
 way: rank r holds the COLUMNS that multiply its own heads / FFN slice
 (`col_range`, whole 32-column blocks), produces a full-width partial product, and
 the partials are added in rank order (`reduce_ranks`) -- one exchange per
-projection, every rank computing the same bits.  The reference runs on one device;
+projection, every rank computing the same bits (for one decode row the exchange and
+the sum are one launch of 8-byte words, `pair_words` / `read_pairs`).  The reference runs on one device;
 this module states the rules the C++ engine (csrc/engine/engine.cpp) and the
 exchanges (csrc/tm_cuda_comm.cu) follow, so launchers and tests can share them.
 """
@@ -46,6 +47,23 @@ def reduce_ranks(partials) -> np.ndarray:
     for p in partials[1:]:
         acc = (acc + np.asarray(p, dtype=np.float32)).astype(np.float32)
     return acc
+
+
+def pair_words(values, number: int) -> np.ndarray:
+    """The wire format of the one-launch decode exchange (tm_cuda_exchange_add_ll_f32): every f32 value
+    travels as one 8-byte word, value bits in the low half and the exchange number in the high half, so
+    a word is complete or absent -- never half written."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return bits | (np.uint64(number & 0xFFFFFFFF) << np.uint64(32))
+
+
+def read_pairs(words, number: int) -> np.ndarray:
+    """Values of the words that carry `number`; a word with another number has not arrived yet (the
+    kernel polls it again) and makes this host model raise."""
+    w = np.ascontiguousarray(words, dtype=np.uint64)
+    if np.any((w >> np.uint64(32)) != np.uint64(number & 0xFFFFFFFF)):
+        raise ValueError("a word of another exchange")
+    return (w & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.float32)
 
 
 @dataclass(frozen=True)
